@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (`gptq_llama8b_mlp_m1`): the W4A16 M=1 GEMV on GPTQ act-order weights with the
+Llama-3.1-8B MLP shapes (gate/up K=4096 N=14336, down K=14336 N=4096, group 128) -- one step is one pass
+over a 32-layer stack of gate, up and down projections (96 GEMVs, 2.9 GB of packed weights, far larger
+than L2, so every step streams its weights from HBM).  Metric: algorithmic HBM bytes per second.
+
+Prints ONE JSON line on rank 0.  Launched by torchrun for N > 1 (one rank per GPU); every rank then owns its
+own 32-layer stack (weak scaling: independent layers, no data-path collective).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LAYERS = 32
+SHAPES = {"gate": (4096, 14336), "up": (4096, 14336), "down": (14336, 4096)}
+GROUP = 128
+
+
+def algorithmic_bytes(k: int, n: int, m: int = 1) -> int:
+    """Bytes one GEMV must move, exactly as the checkpoint stores them: packed weight, packed zeros,
+    fp16 scales, g_idx, x and y."""
+    return k * n // 2 + (k // GROUP) * n // 2 + (k // GROUP) * n * 2 + k * 4 + m * k * 2 + m * n * 2
+
+
+STEP_BYTES = LAYERS * sum(algorithmic_bytes(k, n) for k, n in SHAPES.values())
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------- our arm
+
+
+def build_stack(device, seed: int):
+    """32 layers of GPTQ act-order weights, generated on the device and repacked at load time."""
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(seed)
+    stack = []
+    for _ in range(LAYERS):
+        layer = {}
+        for name, (k, n) in SHAPES.items():
+            qweight = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, device=device, generator=gen)
+            qzeros = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32, device=device)  # stored 7 = zero 8
+            scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+            perm = torch.randperm(k // GROUP, device=device, generator=gen)
+            g_idx = perm[torch.arange(k, device=device) // GROUP].int()
+            layer[name] = ops.w4_repack(qweight, qzeros, scales, GROUP, "gptq", g_idx=g_idx)
+        stack.append(layer)
+    torch.cuda.synchronize()
+    return stack
+
+
+def run_ours(args, rank, world, local_rank):
+    from emmy_b200 import ops
+    from emmy_b200.build import build
+
+    if not (ROOT / "emmy_b200" / "libemmyq.so").exists():
+        build()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    stack = build_stack(device, seed=1234 + rank)
+    gen = torch.Generator().manual_seed(7 + rank)
+    x_host = torch.randn(1, 4096, generator=gen).half().pin_memory()
+    h_host = torch.randn(1, 14336, generator=gen).half().pin_memory()
+    x, h = x_host.to(device), h_host.to(device)
+    ys = {name: torch.empty(1, n, dtype=torch.float16, device=device) for name, (_, n) in SHAPES.items()}
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
+    out_host = {name: torch.empty(1, n, dtype=torch.float16).pin_memory() for name, (_, n) in SHAPES.items()}
+
+    def step():
+        for layer in stack:
+            ops.w4a16_linear(x, layer["gate"], workspace=ws, out=ys["gate"])
+            ops.w4a16_linear(x, layer["up"], workspace=ws, out=ys["up"])
+            ops.w4a16_linear(h, layer["down"], workspace=ws, out=ys["down"])
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(2):
+            graph.replay()
+        stream.synchronize()
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+        # ---- device-timed region: weights resident, K steps
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            end.record(stream)
+            end.synchronize()
+            dev_ms = start.elapsed_time(end)
+            # keep the sampler fed for short runs
+            if dev_ms < 400:
+                t_end = time.time() + 0.4
+                while time.time() < t_end:
+                    graph.replay()
+                stream.synchronize()
+        barrier()
+
+        # ---- end to end through the operator API with host buffers
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            x.copy_(x_host, non_blocking=True)
+            h.copy_(h_host, non_blocking=True)
+            graph.replay()
+            for name in ys:
+                out_host[name].copy_(ys[name], non_blocking=True)
+            stream.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+        # the same with one operator call per projection instead of the captured graph (reported, not the headline)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            x.copy_(x_host, non_blocking=True)
+            h.copy_(h_host, non_blocking=True)
+            step()
+            for name in ys:
+                out_host[name].copy_(ys[name], non_blocking=True)
+            stream.synchronize()
+        eager_ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+    if rank != 0:
+        return
+    peak, peak_kind = peaks()
+    total_bytes = STEP_BYTES * world
+    value = total_bytes * args.steps / (dev_ms * 1e-3) / 1e9
+    e2e_value = total_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
+    launches = 3 * LAYERS
+    per_launch_us = dev_ms * 1e3 / (args.steps * launches)
+    achieved = (STEP_BYTES / launches) / (per_launch_us * 1e-6) / 1e9
+    line = {
+        "metric": "w4a16_m1_gemv_hbm_gbs",
+        "value": round(value, 1),
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": round(dev_ms / args.steps, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "int4 weights, f16 activations, f32 accumulate",
+        "data": "synthetic",
+        "config": {
+            "workload": "gptq_llama8b_mlp_m1: GPTQ-Int4 act-order W4A16 GEMV, Llama-3.1-8B MLP shapes (gate/up 4096x14336, down 14336x4096, group 128), M=1, 32-layer stack per GPU",
+            "algorithmic_bytes_per_step": STEP_BYTES,
+            "l2": "inputs larger than L2: 2.9 GB of weights streamed per step",
+            "launch": "one CUDA graph of 96 GEMV launches per step",
+        },
+        "e2e": {
+            "value": round(e2e_value, 1),
+            "unit": "GB/s",
+            "h2d_bytes_per_step": int(x_host.numel() * 2 + h_host.numel() * 2),
+            "d2h_bytes_per_step": int(sum(t.numel() * 2 for t in out_host.values())),
+            "eager_calls_value": round(STEP_BYTES * args.steps / (eager_ms * 1e-3) / 1e9, 1),
+        },
+        "gpu_launches": launches * args.steps,
+        "roofline": {
+            "bound": "hbm",
+            "achieved": round(achieved, 1),
+            "peak": peak,
+            "unit": "GB/s",
+            "frac": round(achieved / peak, 4),
+            "peak_kind": peak_kind,
+            "traffic": TRAFFIC_PER_LAUNCH,
+            "kernel": "w4a16_streamk_kernel<__half,1>",
+            "avg_launch_us": round(per_launch_us, 3),
+        },
+        "clocks": clocks.summary(),
+        "cpu_baseline": cpu_baseline(sample_layers=1),
+    }
+    print(json.dumps(line), flush=True)
+
+
+# dram bytes per launch of the GEMV kernel from the ncu capture summarised under profiles/ (None until captured)
+TRAFFIC_PER_LAUNCH = None
+
+
+# --------------------------------------------------------------------------------------------- CPU arm
+
+
+def cpu_layer_seconds(seed: int = 0):
+    """The reference's CPU path for one layer's three projections at M=1: numpy dequantize (with the g_idx
+    gather), one rounding to fp16, torch CPU linear.  Returns (seconds, algorithmic bytes)."""
+    from oracle import formats as fm
+    from oracle import synth
+
+    total_s, total_b = 0.0, 0
+    for k, n in SHAPES.values():
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=seed)
+        x = torch.from_numpy(synth.activations(1, k, "f16", seed=seed + 1)).half()
+        t0 = time.perf_counter()
+        w = fm.dequant_w4(qw, qz, sc, GROUP, "gptq", gi)
+        wt = torch.from_numpy(np.ascontiguousarray(w.T)).half()
+        torch.nn.functional.linear(x, wt)
+        total_s += time.perf_counter() - t0
+        total_b += algorithmic_bytes(k, n)
+    return total_s, total_b
+
+
+def cpu_baseline(sample_layers: int = 1):
+    secs, nbytes = 0.0, 0
+    for i in range(sample_layers):
+        s, b = cpu_layer_seconds(seed=i)
+        secs += s
+        nbytes += b
+    return {
+        "value": round(nbytes / secs / 1e9, 4),
+        "unit": "GB/s",
+        "cores": torch.get_num_threads(),
+        "kind": "port",
+        "sample": f"{sample_layers} of 32 layers (gate, up, down at M=1): numpy dequantize + fp16 torch CPU linear, {secs:.1f} s",
+    }
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    for _ in range(min(args.warmup, 1)):
+        cpu_layer_seconds(seed=99)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for i in range(args.steps):
+        _, b = cpu_layer_seconds(seed=i)
+        nbytes += b
+    secs = time.perf_counter() - t0
+    value = nbytes / secs / 1e9
+    line = {
+        "impl": "reference",
+        "metric": "w4a16_m1_gemv_hbm_gbs",
+        "value": round(value, 4),
+        "unit": "GB/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": min(args.warmup, 1),
+        "ms_per_step": round(secs * 1e3 / args.steps, 2),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "int4 weights, f16 activations, f32 accumulate",
+        "data": "synthetic",
+        "config": {
+            "workload": "gptq_llama8b_mlp_m1: GPTQ-Int4 act-order W4A16 GEMV, Llama-3.1-8B MLP shapes, M=1; each step is ONE layer (gate, up, down) of the 32-layer stack on the host cores",
+        },
+        "cpu_baseline": {
+            "value": round(value, 4),
+            "unit": "GB/s",
+            "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": "1 of 32 layers per step: numpy dequantize (g_idx gather) + fp16 torch CPU linear",
+        },
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

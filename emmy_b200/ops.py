@@ -1,0 +1,150 @@
+"""Operator-level calls on torch CUDA tensors, each one C-ABI call.
+
+Tensors are lent to the library as raw device pointers on torch's current
+stream, as the reference's torch.compile entry lends caller memory by
+(name, data_ptr, nbytes) (emmy/dynamo.py:58-68).  Outputs are allocated here
+with torch.empty; the kernels allocate nothing.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import lib as L
+
+_DTYPE = {torch.float16: L.EQ_F16, torch.bfloat16: L.EQ_BF16, torch.float32: L.EQ_F32}
+_FMT = {"awq": L.EQ_W4_AWQ, "gptq": L.EQ_W4_GPTQ}
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("emmy_b200 operators take CUDA tensors only; there is no CPU path")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("emmy_b200 operators take contiguous tensors")
+
+
+def unpack_int4(words: torch.Tensor, fmt: str, along_rows: bool = False) -> torch.Tensor:
+    _need_cuda(words)
+    rows, cols = words.shape
+    out = torch.empty((rows * 8, cols) if along_rows else (rows, cols * 8), dtype=torch.uint8, device=words.device)
+    L.check(L.load().eq_unpack_int4(_FMT[fmt], int(along_rows), _ptr(words), rows, cols, _ptr(out), _stream()))
+    return out
+
+
+def dequant_w4(qweight, qzeros, scales, group_size, fmt, g_idx=None, out_dtype=torch.float16, transpose=False):
+    """-> W[K, N] (or the HF orientation [N, K] when `transpose`), rounded once to out_dtype."""
+    _need_cuda(qweight, qzeros, scales, g_idx)
+    if fmt == "awq":
+        k, n = qweight.shape[0], qweight.shape[1] * 8
+    else:
+        k, n = qweight.shape[0] * 8, qweight.shape[1]
+    out = torch.empty((n, k) if transpose else (k, n), dtype=out_dtype, device=qweight.device)
+    L.check(
+        L.load().eq_dequant_w4(
+            _FMT[fmt], _ptr(qweight), _ptr(qzeros), _ptr(scales), _DTYPE[scales.dtype], _ptr(g_idx), k, n, group_size,
+            _DTYPE[out_dtype], int(transpose), _ptr(out), _stream(),
+        )
+    )
+    return out
+
+
+def dequant_fp8(bits, scale, out_dtype=torch.float32):
+    _need_cuda(bits, scale)
+    n, k = bits.shape
+    s = scale.reshape(1, 1) if scale.numel() == 1 else scale
+    if s.dim() == 1:
+        s = s.reshape(-1, 1)
+    out = torch.empty((n, k), dtype=out_dtype, device=bits.device)
+    L.check(L.load().eq_dequant_fp8(_ptr(bits), _ptr(s), n, k, s.shape[0], s.shape[1], _DTYPE[out_dtype], _ptr(out), _stream()))
+    return out
+
+
+def dequant_nvfp4(packed, scale_bits, scale_2, out_dtype=torch.float32):
+    _need_cuda(packed, scale_bits, scale_2)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    out = torch.empty((n, k), dtype=out_dtype, device=packed.device)
+    L.check(L.load().eq_dequant_nvfp4(_ptr(packed), _ptr(scale_bits), _ptr(scale_2), n, k, _DTYPE[out_dtype], _ptr(out), _stream()))
+    return out
+
+
+class W4Weight:
+    """A repacked int4 weight resident on the device."""
+
+    __slots__ = ("wq", "wm", "perm", "k", "n", "group", "scale_dtype", "fmt")
+
+    def nbytes(self) -> int:
+        return self.wq.numel() + self.wm.numel() + (self.perm.numel() * 4 if self.perm is not None else 0)
+
+
+def w4_repack(qweight, qzeros, scales, group_size, fmt, g_idx=None) -> W4Weight:
+    _need_cuda(qweight, qzeros, scales, g_idx)
+    lib = L.load()
+    if fmt == "awq":
+        k, n = qweight.shape[0], qweight.shape[1] * 8
+    else:
+        k, n = qweight.shape[0] * 8, qweight.shape[1]
+    a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    L.check(lib.eq_w4_repack_sizes(k, n, group_size, C.byref(a), C.byref(b), C.byref(c)))
+    dev = qweight.device
+    w = W4Weight()
+    w.wq = torch.empty(a.value, dtype=torch.uint8, device=dev)
+    w.wm = torch.empty(b.value, dtype=torch.uint8, device=dev)
+    perm = torch.empty(c.value // 4, dtype=torch.int32, device=dev) if g_idx is not None else None
+    uses = C.c_int(0)
+    L.check(
+        lib.eq_w4_repack(
+            _FMT[fmt], _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), k, n, group_size, _ptr(w.wq), _ptr(w.wm),
+            _ptr(perm), C.byref(uses), _stream(),
+        )
+    )
+    w.perm = perm if uses.value else None
+    w.k, w.n, w.group, w.scale_dtype, w.fmt = k, n, (k if group_size == -1 else group_size), scales.dtype, fmt
+    return w
+
+
+def w4_unpack_repacked(w: W4Weight) -> torch.Tensor:
+    out = torch.empty((w.k, w.n), dtype=torch.uint8, device=w.wq.device)
+    L.check(L.load().eq_w4_unpack_repacked(_ptr(w.wq), w.k, w.n, _ptr(out), _stream()))
+    return out
+
+
+_workspaces: dict = {}
+
+
+def w4a16_workspace(m: int, n: int, device) -> torch.Tensor:
+    """A zeroed scratch buffer per (device, stream); grown on demand, reused by calls on that stream."""
+    need = L.load().eq_w4a16_workspace_bytes(m, n)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def w4a16_linear(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """y[M, N] = x[M, K] @ W, x and y in f16 or bf16."""
+    _need_cuda(x)
+    m, k = x.shape
+    if k != w.k:
+        raise ValueError(f"x has {k} features, the weight takes {w.k}")
+    y = out if out is not None else torch.empty((m, w.n), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else w4a16_workspace(m, w.n, x.device)
+    L.check(
+        L.load().eq_w4a16_linear(
+            _ptr(w.wq), _ptr(w.wm), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, w.n, w.group, _ptr(x), m, _DTYPE[x.dtype],
+            _ptr(y), _ptr(ws), ws.numel(), _stream(),
+        )
+    )
+    return y

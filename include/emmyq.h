@@ -1,0 +1,121 @@
+/*
+ * emmyq — C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * This is the boundary a host program binds instead of the reference's
+ * compiled-program runtime for the quantized linear operator.  Conventions,
+ * kept from the reference's runtime boundary (crates/emmy-runtime-py/src/lib.rs:168-361,
+ * crates/emmy-runtime/ARCHITECTURE.md:216-227):
+ *   - every pointer is a DEVICE pointer that the caller owns and keeps alive
+ *     and unwritten until the work queued on `stream` has finished; nothing
+ *     here frees or retains caller memory;
+ *   - all work is enqueued on the caller's stream (`stream` is a
+ *     cudaStream_t passed as void*; NULL is the legacy default stream);
+ *   - nothing allocates: scratch memory is sized by a *_workspace_bytes()
+ *     query and handed in by the caller;
+ *   - every entry point returns an int status, EQ_OK (0) or a negative
+ *     EQ_ERR_* code; nothing aborts or throws across the boundary;
+ *     eq_last_error() gives the calling thread's last message.
+ *
+ * Tensor names and layouts are the checkpoint's own
+ * (emmy/compiler/loader/quant.py:99-133, 136-144, 1120-1194):
+ *   AWQ   qweight int32 [K, N/8] (nibble order 0,2,4,6,1,3,5,7), qzeros int32 [K/G, N/8], scales f16 [K/G, N]
+ *   GPTQ  qweight int32 [K/8, N] (sequential down K), qzeros int32 [K/G, N/8] (zero = stored + 1),
+ *         scales f16 [K/G, N], g_idx int32 [K] (optional)
+ *   FP8   weight u8 e4m3fn [N, K], weight_scale f32 [N] (multiplier)
+ *   NVFP4 weight u8 [N, K/2] (low nibble = even k), weight_scale u8 e4m3 [N, K/16], weight_scale_2 f32 [1]
+ * K = in features, N = out features, G = group size, y[M,N] = x[M,K] @ W[K,N].
+ */
+#ifndef EMMYQ_H
+#define EMMYQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    EQ_OK = 0,
+    EQ_ERR_BAD_ARG = -1,     /* null pointer, non-positive extent, unknown enum */
+    EQ_ERR_BAD_ALIGN = -2,   /* pointer or extent not aligned as the kernel needs */
+    EQ_ERR_UNSUPPORTED = -3, /* a shape / group size / dtype this build has no kernel for */
+    EQ_ERR_CUDA = -4,        /* a CUDA runtime call or launch failed */
+    EQ_ERR_NCCL = -5,
+    EQ_ERR_TIMEOUT = -6,     /* a bounded device-side wait ran out */
+    EQ_ERR_WORKSPACE = -7    /* workspace missing or too small */
+};
+
+enum { EQ_W4_AWQ = 0, EQ_W4_GPTQ = 1 };           /* packed-int4 family */
+enum { EQ_F16 = 0, EQ_BF16 = 1, EQ_F32 = 2 };     /* element types of activations / outputs / scales */
+
+/* Library version (major*10000 + minor*100 + patch) and message of the calling thread's last failure. */
+int eq_version(void);
+const char* eq_last_error(void);
+const char* eq_status_name(int status);
+
+/* ------------------------------------------------------------------ decode (bit-exact) */
+
+/* int32 words -> uint8 nibbles in [0,15], eight per word, in logical order.
+ * along_rows = 0: out[r, 8c+i] (AWQ qweight, both families' qzeros); 1: out[8r+i, c] (GPTQ qweight).
+ * Replaces unpack_int4 (emmy/compiler/loader/quant.py:515-530). */
+int eq_unpack_int4(int fmt, int along_rows, const int32_t* words, int64_t rows, int64_t cols, uint8_t* out, void* stream);
+
+/* Packed int4 linear -> value matrix, (q - (z + bias)) * s computed exactly in f32 and rounded ONCE to out_dtype.
+ * g_idx may be NULL (group of row k is k / G).  G = -1 means one group.  scale_dtype is EQ_F16 or EQ_BF16.
+ * transpose = 0 writes W[K, N]; 1 writes the HF orientation W[N, K].
+ * Replaces dequantize_packed_int4 (emmy/compiler/loader/quant.py:533-555) followed by the eager cast
+ * (emmy/compiler/trace/huggingface.py:2908-2910). */
+int eq_dequant_w4(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, int scale_dtype,
+                  const int32_t* g_idx, int64_t K, int64_t N, int64_t G, int out_dtype, int transpose, void* out,
+                  void* stream);
+
+/* e4m3 weight [N, K] times a multiplier scale [scale_rows, scale_cols] whose extents divide N and K
+ * (1x1 per tensor, Nx1 per output channel, 2-D blocks) -> out_dtype [N, K].
+ * Replaces decode_f8 + dequantize (emmy/compiler/dtype.py:236-238, emmy/compiler/loader/quant.py:147-170). */
+int eq_dequant_fp8(const uint8_t* bits, const float* scale, int64_t N, int64_t K, int64_t scale_rows,
+                   int64_t scale_cols, int out_dtype, void* out, void* stream);
+
+/* NVFP4 weight -> out_dtype [N, K]: e2m1 value times f32(f16(e4m3(scale) * scale_2)).
+ * Replaces dequantize_nvfp4 (emmy/compiler/loader/quant.py:173-197). */
+int eq_dequant_nvfp4(const uint8_t* packed, const uint8_t* scale_bits, const float* scale_2, int64_t N, int64_t K,
+                     int out_dtype, void* out, void* stream);
+
+/* ------------------------------------------------------------------ load-time repack (W4) */
+
+/* The reference binds checkpoint bytes verbatim and lets its compiler pick a folded or source layout per weight
+ * (emmy/compiler/loader/binder.py:19-131, emmy/compiler/pipeline/passes/tile/_layout.py:47-65).  Here the
+ * load-time step re-tiles the int4 words once into the order the tensor-core fragments read:
+ *   wq  u8  [N/16][K/64][32 lanes][16 B]   one 16x64 tile per 512 B, a lane's four words are four k16 steps
+ *   wm  8 B [N/16][K/G][8]                 per column pair (g, g+8): two 16-bit scales (scale dtype kept) and two
+ *                                          zero points with the family's bias added (0..16)
+ *   perm int32 [K + 4]                     row order, used only when g_idx is not constant on aligned G-blocks:
+ *                                          row k' of the repacked weight is input feature perm[k'] (rows sorted by
+ *                                          group); the four trailing words are status words of the repack itself
+ * With g_idx the scale/zero rows are gathered so that repacked group index is k' / G.
+ * Requires K % 64 == 0, N % 16 == 0, G % 64 == 0 (or G = -1), every group holding exactly G rows. */
+int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t* wm_bytes, size_t* perm_bytes);
+/* *uses_perm (host int) is set to 1 when `perm` must be passed to the linear call; the call synchronizes the
+ * stream once to read that flag.  `perm` may be NULL when g_idx is NULL. */
+int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, const int32_t* g_idx,
+                 int64_t K, int64_t N, int64_t G, void* wq, void* wm, int32_t* perm, int* uses_perm, void* stream);
+/* Inverse view for round-trip checks: repacked blob -> uint8 nibbles [K, N] in repacked row order. */
+int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, void* stream);
+
+/* ------------------------------------------------------------------ W4A16 linear */
+
+/* Scratch for eq_w4a16_linear: f32 partial sums and per-tile arrival counters.  The buffer must be zero the
+ * first time it is used; every call leaves it zero again, so it can be reused by calls on one stream. */
+size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N);
+/* y[M, N] = x[M, K] @ W on repacked weights; x and y are act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
+ * The operator the reference spells as int4 decode algebra in front of a LinearOp
+ * (emmy/compiler/loader/quant.py:1235-1435) and evaluates eagerly as dequantize + F.linear
+ * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it. */
+int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, const int32_t* perm, int64_t K, int64_t N,
+                    int64_t G, const void* x, int64_t M, int act_dtype, void* y, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMMYQ_H */

@@ -1,0 +1,60 @@
+"""CPU-side checks of the C-ABI library: it builds, loads, exports every symbol the header declares, and
+argument validation answers with status codes (no kernel is launched here)."""
+
+import ctypes as C
+
+import pytest
+
+from emmy_b200 import lib as L
+
+
+@pytest.fixture(scope="module")
+def eq():
+    from emmy_b200.build import build
+
+    build()
+    return L.load()
+
+
+def test_exports_every_declared_symbol(eq):
+    names = L.declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(eq, name), f"libemmyq.so does not export {name}"
+    assert set(names) == set(eq._eq_signatures), "lib.py binds a different set of symbols than the header declares"
+
+
+def test_version_and_status_names(eq):
+    assert eq.eq_version() >= 100
+    assert eq.eq_status_name(0) == b"EQ_OK"
+    assert eq.eq_status_name(L.EQ_ERR_WORKSPACE) == b"EQ_ERR_WORKSPACE"
+    assert eq.eq_status_name(-99) == b"EQ_ERR_UNKNOWN"
+
+
+def test_bad_arguments_return_codes_not_crashes(eq):
+    null = C.c_void_p(0)
+    one = C.c_void_p(16)  # never dereferenced: validation fails first
+    assert eq.eq_unpack_int4(7, 0, one, 1, 1, one, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_unpack_int4(0, 0, null, 1, 1, one, null) == L.EQ_ERR_BAD_ARG
+    assert b"null" in eq.eq_last_error()
+    # group geometry that does not cover K (the reference raises ValueError: quant.py:546-547)
+    assert eq.eq_dequant_w4(0, one, one, one, 0, null, 256, 64, 100, 0, 0, one, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_dequant_fp8(one, one, 16, 64, 3, 1, 2, one, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_dequant_nvfp4(one, one, one, 4, 20, 2, one, null) == L.EQ_ERR_BAD_ARG
+    a = C.c_size_t()
+    assert eq.eq_w4_repack_sizes(100, 64, 128, C.byref(a), None, None) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4_repack_sizes(4096, 4096, 32, C.byref(a), None, None) == L.EQ_ERR_UNSUPPORTED
+    assert eq.eq_w4_repack_sizes(4096, 4096, 128, C.byref(a), None, None) == 0 and a.value == 4096 * 4096 // 2
+    # linear: workspace too small, misaligned weights
+    assert eq.eq_w4a16_linear(one, one, 0, null, 4096, 4096, 128, one, 1, 0, one, null, 0, null) == L.EQ_ERR_WORKSPACE
+    assert eq.eq_w4a16_linear(C.c_void_p(8), one, 0, null, 4096, 4096, 128, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ALIGN
+    assert eq.eq_w4a16_linear(one, one, 0, null, 4096, 4096, 128, one, 1, 2, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4a16_workspace_bytes(1, 4096) == 4096 * 4 + 257 * 4
+
+
+def test_ops_refuse_cpu_tensors():
+    torch = pytest.importorskip("torch")
+    from emmy_b200 import ops
+
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.unpack_int4(torch.zeros(2, 2, dtype=torch.int32), "awq")

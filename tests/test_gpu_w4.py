@@ -1,0 +1,255 @@
+"""W4 (AWQ / GPTQ) on the GPU against the CPU oracle, through the C ABI."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as fm
+from oracle import linear as ol
+from oracle import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2  # max|err| <= TOL * max|ref|, f32 accumulation on both sides
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def act(x, dtype):
+    t = torch.from_numpy(x).cuda()
+    return t.half() if dtype == "f16" else t.bfloat16()
+
+
+def check_close(y, ref):
+    got = y.float().cpu().numpy()
+    err = np.abs(got - ref).max()
+    bound = TOL * np.abs(ref).max()
+    assert np.isfinite(got).all()
+    assert err <= bound, f"max err {err} > {bound}"
+    return err / np.abs(ref).max()
+
+
+@pytest.mark.parametrize("fmt,along", [("awq", False), ("gptq", True), ("gptq", False)])
+def test_unpack_bit_exact(fmt, along):
+    from emmy_b200 import ops
+
+    words = np.random.default_rng(5).integers(-(2**31), 2**31, (40, 24), dtype=np.int64).astype(np.int32)
+    got = ops.unpack_int4(dev(words), fmt, along_rows=along).cpu().numpy()
+    np.testing.assert_array_equal(got, fm.unpack_int4(words, fmt, along_rows=along).astype(np.uint8))
+
+
+def test_unpack_golden(golden):
+    from emmy_b200 import ops
+
+    for name in ("awq", "gptq"):
+        rows = name == "gptq"
+        got = ops.unpack_int4(dev(golden[f"{name}_qweight"]), name, along_rows=rows).cpu().numpy()
+        np.testing.assert_array_equal(got, golden[f"{name}_unpacked"].astype(np.uint8))
+
+
+@pytest.mark.parametrize("name", ["awq", "gptq", "awq_g32", "gptq_g32"])
+@pytest.mark.parametrize("transpose", [False, True])
+def test_dequant_golden_bit_exact(golden, name, transpose):
+    from emmy_b200 import ops
+
+    fmt = name.split("_")[0]
+    out = ops.dequant_w4(
+        dev(golden[f"{name}_qweight"]), dev(golden[f"{name}_qzeros"]), dev(golden[f"{name}_scales"]),
+        int(golden[f"{name}_group"]), fmt, out_dtype=torch.float32, transpose=transpose,
+    ).cpu().numpy()
+    ref = golden[f"{name}_dequant"]
+    np.testing.assert_array_equal(out, ref.T if transpose else ref)
+
+
+@pytest.mark.parametrize("fmt", ["awq", "gptq"])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_dequant_rounds_once_bit_exact(fmt, dtype):
+    """The dequantised weight in the model dtype equals the oracle's single rounding of the exact f32 product."""
+    from emmy_b200 import ops
+
+    k, n = 512, 384
+    if fmt == "awq":
+        qw, qz, sc = synth.awq_linear(k, n, seed=3)
+        gi = None
+    else:
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=3)
+    tdt = torch.float16 if dtype == "f16" else torch.bfloat16
+    out = ops.dequant_w4(dev(qw), dev(qz), dev(sc), 128, fmt, g_idx=None if gi is None else dev(gi), out_dtype=tdt, transpose=True)
+    ref = fm.cast_weight(fm.dequant_w4(qw, qz, sc, 128, fmt, gi), dtype).T
+    np.testing.assert_array_equal(out.float().cpu().numpy(), ref)
+
+
+def test_dequant_scattered_g_idx_bit_exact():
+    from emmy_b200 import ops
+
+    k, n, g = 256, 64, 64
+    qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=9)
+    gi = np.random.default_rng(1).permutation(np.arange(k) // g).astype(np.int32)
+    out = ops.dequant_w4(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi), out_dtype=torch.float32).cpu().numpy()
+    np.testing.assert_array_equal(out, fm.dequant_w4(qw, qz, sc, g, "gptq", gi))
+
+
+def test_dequant_single_group():
+    from emmy_b200 import ops
+
+    qw, qz, sc = synth.awq_linear(128, 32, group=128, seed=2)
+    out = ops.dequant_w4(dev(qw), dev(qz), dev(sc), -1, "awq", out_dtype=torch.float32).cpu().numpy()
+    np.testing.assert_array_equal(out, fm.dequant_w4(qw, qz, sc, -1, "awq"))
+
+
+@pytest.mark.parametrize("fmt", ["awq", "gptq"])
+def test_repack_round_trip_bit_exact(fmt):
+    """unpack(repack(w)) == unpack(w): the load-time re-tiling loses nothing."""
+    from emmy_b200 import ops
+
+    k, n = 512, 96
+    if fmt == "awq":
+        qw, qz, sc = synth.awq_linear(k, n, seed=4)
+        w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, fmt)
+    else:
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=4)
+        w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, fmt, g_idx=dev(gi))
+        assert w.perm is None  # block-constant g_idx needs no row permutation
+    got = ops.w4_unpack_repacked(w).cpu().numpy()
+    np.testing.assert_array_equal(got, fm.unpack_int4(qw, fmt, along_rows=(fmt == "gptq")).astype(np.uint8))
+
+
+def test_repack_scattered_g_idx_sorts_rows():
+    from emmy_b200 import ops
+
+    k, n, g = 256, 32, 64
+    qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=6)
+    gi = np.random.default_rng(2).permutation(np.arange(k) // g).astype(np.int32)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
+    assert w.perm is not None
+    perm = w.perm.cpu().numpy()[:k]
+    np.testing.assert_array_equal(perm, np.argsort(gi, kind="stable"))
+    got = ops.w4_unpack_repacked(w).cpu().numpy()
+    np.testing.assert_array_equal(got, fm.unpack_int4(qw, "gptq", along_rows=True).astype(np.uint8)[perm])
+
+
+def test_repack_rejects_unbalanced_groups():
+    from emmy_b200 import ops
+    from emmy_b200.lib import EmmyqError
+
+    k, n, g = 256, 32, 64
+    qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=6)
+    gi = np.zeros(k, dtype=np.int32)
+    gi[::3] = 1
+    with pytest.raises(EmmyqError) as e:
+        ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
+    assert e.value.status_name == "EQ_ERR_UNSUPPORTED"
+    gi[0] = 99
+    with pytest.raises(EmmyqError) as e:
+        ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
+    assert e.value.status_name == "EQ_ERR_BAD_ARG"
+
+
+@pytest.mark.parametrize("m", [1, 16])
+def test_awq_linear_config1(m):
+    """AWQ K=N=4096, group 128, fp16, M in {1, 16}."""
+    from emmy_b200 import ops
+
+    k = n = 4096
+    qw, qz, sc = synth.awq_linear(k, n, seed=0)
+    x = synth.activations(m, k, "f16", seed=1)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "awq")
+    y = ops.w4a16_linear(act(x, "f16"), w)
+    check_close(y, ol.w4a16_linear(x, qw, qz, sc, 128, "awq", "f16"))
+
+
+@pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096)])
+@pytest.mark.parametrize("m", [1, 4, 16])
+def test_gptq_act_order_llama_mlp(shape, m):
+    """GPTQ act-order, Llama-3.1-8B MLP shapes, decode-shaped M."""
+    from emmy_b200 import ops
+
+    k, n = shape
+    qw, qz, sc, gi = synth.gptq_linear(k, n, seed=0)
+    x = synth.activations(m, k, "f16", seed=m)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi))
+    y = ops.w4a16_linear(act(x, "f16"), w)
+    check_close(y, ol.w4a16_linear(x, qw, qz, sc, 128, "gptq", "f16", gi))
+
+
+@pytest.mark.parametrize("m", [64, 256])
+def test_gptq_act_order_prefill_rows(m):
+    from emmy_b200 import ops
+
+    k, n = 4096, 2048
+    qw, qz, sc, gi = synth.gptq_linear(k, n, seed=2)
+    x = synth.activations(m, k, "f16", seed=3)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi))
+    y = ops.w4a16_linear(act(x, "f16"), w)
+    check_close(y, ol.w4a16_linear(x, qw, qz, sc, 128, "gptq", "f16", gi))
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 7, 8, 9, 15, 17, 31, 33, 64, 65, 130])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_ragged_row_counts(m, dtype):
+    from emmy_b200 import ops
+
+    k, n = 768, 272  # 12 chunks, 17 column tiles: spans straddle tiles
+    qw, qz, sc = synth.awq_linear(k, n, seed=m)
+    x = synth.activations(m, k, dtype, seed=m + 1)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "awq")
+    y = ops.w4a16_linear(act(x, dtype), w)
+    check_close(y, ol.w4a16_linear(x, qw, qz, sc, 128, "awq", dtype))
+
+
+def test_smallest_shape_and_empty_batch():
+    from emmy_b200 import ops
+
+    qw, qz, sc = synth.awq_linear(64, 16, group=64, seed=1)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 64, "awq")
+    x = synth.activations(2, 64, "f16")
+    check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, 64, "awq", "f16"))
+    y = ops.w4a16_linear(torch.empty(0, 64, dtype=torch.float16, device="cuda"), w)
+    assert y.shape == (0, 16)
+
+
+def test_scattered_act_order_linear():
+    """A g_idx whose groups are scattered over K: rows are sorted at load time and x gathered at run time."""
+    from emmy_b200 import ops
+
+    k, n, g = 1024, 256, 128
+    qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=8)
+    gi = np.random.default_rng(3).permutation(np.arange(k) // g).astype(np.int32)
+    for m in (1, 5):
+        x = synth.activations(m, k, "f16", seed=m)
+        w = ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
+        y = ops.w4a16_linear(act(x, "f16"), w)
+        check_close(y, ol.w4a16_linear(x, qw, qz, sc, g, "gptq", "f16", gi))
+
+
+def test_workspace_is_left_zero_and_calls_repeat():
+    from emmy_b200 import ops
+
+    k, n = 2048, 1024
+    qw, qz, sc = synth.awq_linear(k, n, seed=0)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "awq")
+    x = act(synth.activations(4, k, "f16"), "f16")
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    y1 = ops.w4a16_linear(x, w, workspace=ws)
+    torch.cuda.synchronize()
+    assert int(ws.count_nonzero()) == 0
+    y2 = ops.w4a16_linear(x, w, workspace=ws)
+    assert float((y1.float() - y2.float()).abs().max()) <= 1e-2 * float(y1.float().abs().max())
+    assert int(ws.count_nonzero()) == 0
+
+
+def test_linearity_at_full_size():
+    """A size-independent property at the full down-projection size: W(a x1 + x2) == a W x1 + W x2 up to rounding."""
+    from emmy_b200 import ops
+
+    k, n = 14336, 4096
+    qw, qz, sc, gi = synth.gptq_linear(k, n, seed=11)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi))
+    x1 = act(synth.activations(1, k, "f16", seed=1), "f16")
+    x2 = act(synth.activations(1, k, "f16", seed=2), "f16")
+    y1, y2 = ops.w4a16_linear(x1, w).float(), ops.w4a16_linear(x2, w).float()
+    y12 = ops.w4a16_linear((x1.float() * 0.5 + x2.float()).half(), w).float()
+    ref = 0.5 * y1 + y2
+    assert float((y12 - ref).abs().max()) <= TOL * float(ref.abs().max())
