@@ -1,19 +1,29 @@
 // W4A16 linear for decode-shaped calls (and, in 64-row blocks, for any M): y[M,N] = x[M,K] @ W, W int4 group-wise.
 //
-// A bandwidth kernel.  The repacked weight (w4_repack.cu) is one flat run of 512-byte tiles, [n-tile][k-chunk], a
-// tile being 16 output columns x 64 input rows.  The grid is persistent-sized (a multiple of the SM count) and
-// every CTA takes an EQUAL contiguous span of that run, whatever the tile boundaries (stream-K), so all SMs stream
-// the same number of bytes.  Inside a CTA each warp takes an equal sub-span.  Per tile-chunk a lane issues one
-// 16-byte streaming load (a warp: 512 contiguous bytes), turns its four words into four m16n8k16 A fragments with
-// lop3 + one f16x2 subtract/fma per pair of nibbles (exact: (1024+q) - (1024+z)), and feeds mma.sync with the
-// activations as the B operand, f32 accumulators.  The per-group scale multiplies the group's partial sum once
-// (sum_k x*(q-z) is exact integer-times-activation work; s is applied in f32).
+// A bandwidth kernel.  The repacked weight (w4_repack.cu) is one flat run of 1088-byte ITEM records, [n-tile][item]:
+// 16 output columns x 128 input rows of nibbles plus that group's scales and zero points.  The grid is
+// persistent-sized (a multiple of the SM count) and every CTA takes an EQUAL contiguous span of items, whatever the
+// tile boundaries (stream-K), so all SMs stream the same number of bytes.  Inside a CTA each warp takes an equal
+// sub-span and keeps its own ring of kRing slots in shared memory.  A slot holds a BATCH of up to two consecutive
+// items and is filled by one bulk asynchronous copy (cp.async.bulk, the 1-D TMA path) that lane 0 issues kRing
+// batches ahead and that signals the slot's mbarrier: a warp keeps ~8 KB of weight bytes in flight without holding
+// them in registers.
+//
+// Per item a lane reads its 2 x 16 bytes and turns each word into one m16n8k16 A fragment with five integer
+// instructions (one shift, four lop3): (w & 0x000F000F) | 0x64006400 is the f16 pair {1024 + q, 1024 + q'}.  The
+// offset is NOT subtracted per element.  With the activations as the B operand (those of the k-slots that carry
+// 1024 + 16 q are stored pre-divided by 16) the tensor core returns
+//     acc = sum_k x_k q_k + 1024 * S1,     S1 = sum of the stored B values of the item,
+// and the item's contribution is  s * (acc - 1024 S1 - z S2),  S2 = sum_k x_k, with S1 and S2 computed once per
+// CTA while the activations are staged.  (bf16: 128 + q is exact, no pre-division, S1 = S2.)  The two items of a
+// batch and the k16 steps of an item accumulate into independent registers, so the tensor-core latency overlaps.
 //
 // Partial sums of one output tile meet in two levels: warps of a CTA add into shared-memory accumulators and the
 // warp that completes the CTA's share of a tile either stores y (tile wholly inside the CTA span, single K slice)
 // or adds the CTA's sum into the f32 workspace; the CTA whose contribution completes the tile converts, stores y
 // and leaves workspace and counter zero for the next call.  Nobody waits on anybody: "last arriver finishes".
 // A CTA handles the tiles it shares with its neighbours FIRST, so that second level is off the tail of the kernel.
+// The only waits are on a warp's own copies; they are bounded, and a wait that runs out sets a status word.
 //
 // K is cut into S slices only when the activations of a whole K run do not fit shared memory (M > 1 and large K).
 #include "common.cuh"
@@ -22,26 +32,28 @@ namespace eq {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kDepth = 4;  // tile-chunks in flight per warp (registers)
+constexpr int kRing = 4;                 // batch slots per warp
+constexpr int kBatch = 2;                // items per batch
+constexpr int kItemBytes = 1088;         // 1024 B of nibbles + 64 B of scales / zero points
+constexpr int kSlotBytes = kBatch * kItemBytes;
+constexpr int kXRegs = 8;                // activation vectors a thread loads before it starts the weight stream
+constexpr long long kWaitCycles = 2000000000LL;  // about a second: far beyond any real copy latency
 
 struct W4Params {
-    const uint4* wq;       // [n_tiles][chunks][32] lanes
-    const uint2* wm;       // [n_tiles][groups][8]: {s[g] | s[g+8] << 16, z[g] | z[g+8] << 8}
-    const int32_t* perm;   // optional [K]
-    const void* x;         // [M][K]
-    void* y;               // [M][N]
-    float* wsp;            // [M][N] partial sums (zero between calls)
-    int* counters;         // [n_tiles] chunks arrived (zero between calls)
+    const unsigned char* wq;  // [n_tiles][items][1088]
+    const int32_t* perm;      // optional [K]
+    const void* x;            // [M][K]
+    void* y;                  // [M][N]
+    float* wsp;               // [M][N] partial sums (zero between calls)
+    int* counters;            // [n_tiles] items arrived (zero between calls), then one status word
     int K, N, M;
-    int chunks;            // K / 64
-    int chunks_per_group;  // G / 64
-    int groups;            // K / G
-    int n_tiles;           // N / 16
-    int slices;            // S
-    int cs;                // chunks per slice
-    int ctas_per_slice;    // P
-    int rows;              // activation rows kept per 8-row m-tile in shared memory (M for M < 8, else 8)
-    int slots;             // shared accumulator slots (max tiles a CTA span touches)
+    int items;                // K / 128
+    int n_tiles;              // N / 16
+    int slices;               // S
+    int cs;                   // items per slice
+    int ctas_per_slice;       // P
+    int rows;                 // activation rows kept per 8-row m-tile in shared memory (M for M < 8, else 8)
+    int slots;                // shared accumulator slots (max tiles a CTA span touches)
     int scale_dtype;
 };
 
@@ -50,67 +62,99 @@ struct Frag;
 
 template <>
 struct Frag<__half> {
-    // four words of one lane -> A fragment registers of k16 step `w`, zero point removed
-    static __device__ __forceinline__ void dequant(uint32_t w, uint32_t zlo, uint32_t zhi, uint32_t nzlo, uint32_t nzhi,
-                                                   uint32_t (&a)[4]) {
-        constexpr uint32_t kMagic = 0x64006400u;  // 1024.0 | 1024.0: (w & mask) | magic == 1024 + q (or 1024 + 16 q)
-        const uint32_t h0 = lop3<0xEA>(w, 0x000F000Fu, kMagic);
-        const uint32_t h1 = lop3<0xEA>(w, 0x00F000F0u, kMagic);
+    static constexpr float kOffset = 1024.f;
+    static constexpr bool kPrescaleHi = true;
+    // one word of a lane -> A fragment registers {1024+q} (a0, a1) and {1024+16q} (a2, a3)
+    static __device__ __forceinline__ void expand(uint32_t w, uint32_t (&a)[4]) {
+        constexpr uint32_t kMagic = 0x64006400u;
+        a[0] = lop3<0xEA>(w, 0x000F000Fu, kMagic);
+        a[2] = lop3<0xEA>(w, 0x00F000F0u, kMagic);
         const uint32_t w8 = w >> 8;
-        const uint32_t h2 = lop3<0xEA>(w8, 0x000F000Fu, kMagic);
-        const uint32_t h3 = lop3<0xEA>(w8, 0x00F000F0u, kMagic);
-        constexpr uint32_t kSixteenth = 0x2C002C00u;  // 1/16 | 1/16
-        asm("sub.f16x2 %0, %1, %2;" : "=r"(a[0]) : "r"(h0), "r"(zlo));
-        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[2]) : "r"(h1), "r"(kSixteenth), "r"(nzlo));
-        asm("sub.f16x2 %0, %1, %2;" : "=r"(a[1]) : "r"(h2), "r"(zhi));
-        asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[3]) : "r"(h3), "r"(kSixteenth), "r"(nzhi));
-    }
-    // zero point z (0..16) -> {1024 + z} pair and {-(64 + z)} pair
-    static __device__ __forceinline__ void zero_consts(uint32_t z, uint32_t& sub, uint32_t& fma) {
-        const __half2 s = __half2half2(__ushort_as_half(static_cast<unsigned short>(0x6400u)));  // 1024
-        const __half2 zz = __half2half2(__uint2half_rn(z));
-        const __half2 a = __hadd2(s, zz);
-        const __half2 b = __hneg2(__hadd2(__half2half2(__float2half_rn(64.f)), zz));
-        sub = *reinterpret_cast<const uint32_t*>(&a);
-        fma = *reinterpret_cast<const uint32_t*>(&b);
+        a[1] = lop3<0xEA>(w8, 0x000F000Fu, kMagic);
+        a[3] = lop3<0xEA>(w8, 0x00F000F0u, kMagic);
     }
     static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t sixteenth(uint32_t pair) {
+        uint32_t r;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(pair), "r"(0x2C002C00u));
+        return r;
+    }
+    static __device__ __forceinline__ float pair_sum(uint32_t pair) {
+        const __half2 h = *reinterpret_cast<const __half2*>(&pair);
+        return __low2float(h) + __high2float(h);
     }
 };
 
 template <>
 struct Frag<__nv_bfloat16> {
-    static __device__ __forceinline__ void dequant(uint32_t w, uint32_t zlo, uint32_t zhi, uint32_t, uint32_t,
-                                                   uint32_t (&a)[4]) {
-        constexpr uint32_t kMagic = 0x43004300u;  // 128.0 | 128.0: 128 + q is exact in bf16
-        const uint32_t t0 = lop3<0xEA>(w, 0x000F000Fu, kMagic);
-        const uint32_t t1 = lop3<0xEA>(w >> 4, 0x000F000Fu, kMagic);
-        const uint32_t t2 = lop3<0xEA>(w >> 8, 0x000F000Fu, kMagic);
-        const uint32_t t3 = lop3<0xEA>(w >> 12, 0x000F000Fu, kMagic);
-        asm("sub.bf16x2 %0, %1, %2;" : "=r"(a[0]) : "r"(t0), "r"(zlo));
-        asm("sub.bf16x2 %0, %1, %2;" : "=r"(a[2]) : "r"(t1), "r"(zlo));
-        asm("sub.bf16x2 %0, %1, %2;" : "=r"(a[1]) : "r"(t2), "r"(zhi));
-        asm("sub.bf16x2 %0, %1, %2;" : "=r"(a[3]) : "r"(t3), "r"(zhi));
-    }
-    static __device__ __forceinline__ void zero_consts(uint32_t z, uint32_t& sub, uint32_t& fma) {
-        const __nv_bfloat162 a = __float2bfloat162_rn(128.f + static_cast<float>(z));
-        sub = *reinterpret_cast<const uint32_t*>(&a);
-        fma = 0;
+    static constexpr float kOffset = 128.f;
+    static constexpr bool kPrescaleHi = false;
+    static __device__ __forceinline__ void expand(uint32_t w, uint32_t (&a)[4]) {
+        constexpr uint32_t kMagic = 0x43004300u;  // 128 + q is exact in bf16
+        a[0] = lop3<0xEA>(w, 0x000F000Fu, kMagic);
+        a[2] = lop3<0xEA>(w >> 4, 0x000F000Fu, kMagic);
+        a[1] = lop3<0xEA>(w >> 8, 0x000F000Fu, kMagic);
+        a[3] = lop3<0xEA>(w >> 12, 0x000F000Fu, kMagic);
     }
     static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
             : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
+    static __device__ __forceinline__ uint32_t sixteenth(uint32_t pair) { return pair; }
+    static __device__ __forceinline__ float pair_sum(uint32_t pair) {
+        return __uint_as_float(pair << 16) + __uint_as_float(pair & 0xFFFF0000u);
+    }
 };
 
-// Position q of a CTA's processing order -> item index.  Order: the partial tile at the head of the span, the
-// partial tile at its tail, then the whole tiles between them.
+// ---- mbarrier / bulk copy ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+#ifdef EQ_W4_TRACE
+__device__ unsigned long long g_w4_trace[4096 * 8];
+__device__ __forceinline__ unsigned long long trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define EQ_TRACE(slot)                                                                         \
+    do {                                                                                       \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x * kWarps + (threadIdx.x >> 5) < 4096)        \
+            g_w4_trace[(blockIdx.x * kWarps + (threadIdx.x >> 5)) * 8 + (slot)] = trace_now(); \
+    } while (0)
+#else
+#define EQ_TRACE(slot) \
+    do {               \
+    } while (0)
+#endif
+
+// A CTA's span of items, visited in the order: partial tile at the head of the span, partial tile at its tail,
+// then the whole tiles between them.  Position q of that order maps to an item index.
 struct SpanOrder {
     int i0, i1, nh, nt;
     __device__ __forceinline__ int item(int q) const {
@@ -118,70 +162,232 @@ struct SpanOrder {
         if (q < nh + nt) return i1 - nt + (q - nh);
         return i0 + nh + (q - nh - nt);
     }
+    __device__ __forceinline__ int next_jump(int q) const {
+        if (q < nh) return nh;
+        if (q < nh + nt) return nh + nt;
+        return 0x7FFFFFFF;
+    }
 };
 
+struct Batch {
+    int t0, cl0, t1, cl1, n;
+};
+
+// Walks a warp's positions batch by batch.  Consecutive positions are consecutive items except at the two jumps of
+// SpanOrder; the second item joins the first's batch when its record follows the first's in memory.
+struct BatchIter {
+    int q, q_end, jump, t, cl;
+    __device__ __forceinline__ void seek(const SpanOrder& o, int q_, int cs) {
+        q = q_;
+        const int it = o.item(q);
+        t = it / cs;
+        cl = it - t * cs;
+        jump = o.next_jump(q);
+    }
+    __device__ __forceinline__ Batch next(const SpanOrder& o, int cs, bool single_slice) {
+        Batch b;
+        b.t0 = t;
+        b.cl0 = cl;
+        b.n = 1;
+        ++q;
+        bool contiguous = (q < q_end) && (q != jump);
+        if (q < q_end) {
+            if (q == jump) {
+                seek(o, q, cs);
+            } else if (++cl == cs) {
+                cl = 0;
+                ++t;
+                contiguous = contiguous && single_slice;
+            }
+        }
+        b.t1 = t;
+        b.cl1 = cl;
+        if (contiguous) {
+            b.n = 2;
+            ++q;
+            if (q < q_end) {
+                if (q == jump) {
+                    seek(o, q, cs);
+                } else if (++cl == cs) {
+                    cl = 0;
+                    ++t;
+                }
+            }
+        }
+        return b;
+    }
+    __device__ __forceinline__ bool more() const { return q < q_end; }
+};
+
+struct CtaView {
+    float* accs;
+    int* slot_cnt;
+    int first_tile, i0, i1;
+};
+
+// Hand one warp's sum for tile `t` to the CTA's slot; the warp that completes the CTA's share finishes the tile.
 template <typename ActT, int MT>
-__global__ void __launch_bounds__(kThreads, (MT <= 2 ? 3 : 1)) w4a16_streamk_kernel(const W4Params p) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __noinline__ void flush_tile(const W4Params& p, const CtaView& v, float (&yacc)[MT][4], int t, int nitems) {
+    const int lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
+    const int slot = t - v.first_tile;
+    float* a = v.accs + slot * MT * 128;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int m = 8 * mt + 2 * j + (e & 1);
+            const int n = g + ((e & 2) ? 8 : 0);
+            if (m < p.M) atomicAdd(a + m * 16 + n, yacc[mt][e]);
+            yacc[mt][e] = 0.f;
+        }
+    }
+    __syncwarp();
+    const int lo = max(v.i0, t * p.cs), hi = min(v.i1, (t + 1) * p.cs);
+    const int share = hi - lo;  // this CTA's items of tile t
+    int last = 0;
+    if (lane == 0) {
+        __threadfence_block();
+        last = (atomicAdd(v.slot_cnt + slot, nitems) + nitems == share);
+    }
+    last = __shfl_sync(0xFFFFFFFFu, last, 0);
+    if (!last) return;
+    __threadfence_block();
+    ActT* y = static_cast<ActT*>(p.y);
+    const int n_base = t * 16;
+    if (share == p.cs && p.slices == 1) {
+        for (int idx = lane; idx < p.M * 16; idx += 32) {
+            const int m = idx >> 4, n = idx & 15;
+            y[static_cast<size_t>(m) * p.N + n_base + n] = from_float<ActT>(a[m * 16 + n]);
+        }
+        return;
+    }
+    // second level: add the CTA's sum into the workspace, then count the CTA's items in
+    for (int idx = lane; idx < p.M * 16; idx += 32) {
+        const int m = idx >> 4, n = idx & 15;
+        atomicAdd(p.wsp + static_cast<size_t>(m) * p.N + n_base + n, a[m * 16 + n]);
+    }
+    __syncwarp();
+    int finisher = 0;
+    if (lane == 0) {
+        __threadfence();
+        finisher = (atomicAdd(p.counters + t, share) + share == p.items);
+    }
+    finisher = __shfl_sync(0xFFFFFFFFu, finisher, 0);
+    if (!finisher) return;
+    __threadfence();
+    for (int idx = lane; idx < p.M * 16; idx += 32) {
+        const int m = idx >> 4, n = idx & 15;
+        float* w = p.wsp + static_cast<size_t>(m) * p.N + n_base + n;
+        y[static_cast<size_t>(m) * p.N + n_base + n] = from_float<ActT>(__ldcg(w));
+        __stcg(w, 0.f);
+    }
+    if (lane == 0) p.counters[t] = 0;
+}
+
+// 128 input rows x 16 columns against MT m-tiles of activations: eight k16 steps spread over NCH accumulator chains.
+template <typename ActT, int MT, int NCH>
+__device__ __forceinline__ void item_mma(const unsigned char* rec, const uint4* xs_item, int rows, int lane,
+                                         float (&acc)[NCH][MT][4]) {
+    const int g = lane >> 2, j = lane & 3;
+    const uint4 w_lo = *reinterpret_cast<const uint4*>(rec + lane * 16);
+    const uint4 w_hi = *reinterpret_cast<const uint4*>(rec + 512 + lane * 16);
+    const uint32_t words[8] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w, w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+    for (int hs = 0; hs < 4; ++hs) {  // half-chunks: two k16 steps each
+        uint32_t a0[4], a1[4];
+        Frag<ActT>::expand(words[2 * hs], a0);
+        Frag<ActT>::expand(words[2 * hs + 1], a1);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (g < rows) b = xs_item[((((hs >> 1) * MT + mt) * 2 + (hs & 1)) * rows + g) * 4 + j];
+            Frag<ActT>::mma(acc[(2 * hs) % NCH][mt], a0, b.x, b.y);
+            Frag<ActT>::mma(acc[(2 * hs + 1) % NCH][mt], a1, b.z, b.w);
+        }
+    }
+}
+
+// yacc += s * (sum of chains - offset * S1 - z * S2) for one item
+template <typename ActT, int MT, int NCH>
+__device__ __forceinline__ void item_fold(const unsigned char* rec, const float2* xsum_item, int lane, int scale_dtype,
+                                          float (&acc)[NCH][MT][4], float (&yacc)[MT][4]) {
+    const int g = lane >> 2, j = lane & 3;
+    const uint2 meta = *reinterpret_cast<const uint2*>(rec + 1024 + g * 8);
+    const float slo = scale16_to_float(static_cast<uint16_t>(meta.x & 0xFFFF), scale_dtype);
+    const float shi = scale16_to_float(static_cast<uint16_t>(meta.x >> 16), scale_dtype);
+    const float zlo = static_cast<float>(meta.y & 0xFF), zhi = static_cast<float>((meta.y >> 8) & 0xFF);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        float c[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            c[e] = acc[0][mt][e];
+#pragma unroll
+            for (int ch = 1; ch < NCH; ++ch) c[e] += acc[ch][mt][e];
+        }
+        const float4 s = *reinterpret_cast<const float4*>(xsum_item + mt * 8 + 2 * j);  // {S1,S2}[m0], {S1,S2}[m1]
+        const float c0 = fmaf(-Frag<ActT>::kOffset, s.x, c[0]), c1 = fmaf(-Frag<ActT>::kOffset, s.z, c[1]);
+        const float c2 = fmaf(-Frag<ActT>::kOffset, s.x, c[2]), c3 = fmaf(-Frag<ActT>::kOffset, s.z, c[3]);
+        yacc[mt][0] = fmaf(slo, fmaf(-zlo, s.y, c0), yacc[mt][0]);
+        yacc[mt][1] = fmaf(slo, fmaf(-zlo, s.w, c1), yacc[mt][1]);
+        yacc[mt][2] = fmaf(shi, fmaf(-zhi, s.y, c2), yacc[mt][2]);
+        yacc[mt][3] = fmaf(shi, fmaf(-zhi, s.w, c3), yacc[mt][3]);
+    }
+}
+
+template <typename ActT, int MT>
+__global__ void __launch_bounds__(kThreads, (MT <= 2 ? 2 : 1)) w4a16_streamk_kernel(const W4Params p) {
+    constexpr int NCH = MT == 1 ? 4 : MT == 2 ? 2 : 1;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     const int slice = blockIdx.x / p.ctas_per_slice;
     const int part = blockIdx.x % p.ctas_per_slice;
-    const long long items = static_cast<long long>(p.n_tiles) * p.cs;
-    const int i0 = static_cast<int>(items * part / p.ctas_per_slice);
-    const int i1 = static_cast<int>(items * (part + 1) / p.ctas_per_slice);
+    const long long all_items = static_cast<long long>(p.n_tiles) * p.cs;
+    const int i0 = static_cast<int>(all_items * part / p.ctas_per_slice);
+    const int i1 = static_cast<int>(all_items * (part + 1) / p.ctas_per_slice);
+    EQ_TRACE(0);
 
-    // shared memory: activations in B-fragment order, accumulator slots, slot counters
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw);
-    const int xs_vecs = p.cs * MT * 2 * p.rows * 4;
-    float* accs = reinterpret_cast<float*>(xs + xs_vecs);           // [slots][MT*8][16]
-    int* slot_cnt = reinterpret_cast<int*>(accs + p.slots * MT * 128);  // [slots]
-
-    for (int i = threadIdx.x; i < p.slots * MT * 128; i += kThreads) accs[i] = 0.f;
-    for (int i = threadIdx.x; i < p.slots; i += kThreads) slot_cnt[i] = 0;
-
-    // ---- stage this slice of x: word (chunk, mt, half, r, j, wi) = {x[m][k], x[m][k+1]},
-    //      k = 64 chunk + 16 (2 half + wi/2) + 8 (wi & 1) + 2 j, m = 8 mt + r
-    {
-        uint32_t* xw = reinterpret_cast<uint32_t*>(xs);
-        const ActT* x = static_cast<const ActT*>(p.x);
-        const int total = xs_vecs * 4;
-        const int kbase = slice * p.cs * 64;
-        for (int idx = threadIdx.x; idx < total; idx += kThreads) {
-            const int wi = idx & 3, jj = (idx >> 2) & 3;
-            int rest = idx >> 4;
-            const int r = rest % p.rows;
-            rest /= p.rows;
-            const int half = rest & 1;
-            rest >>= 1;
-            const int mt = rest % MT;
-            const int chunk = rest / MT;
-            const int k = kbase + 64 * chunk + 16 * (2 * half + (wi >> 1)) + 8 * (wi & 1) + 2 * jj;
-            const int m = 8 * mt + r;
-            uint32_t v = 0;
-            if (m < p.M) {
-                if (p.perm) {
-                    const ActT lo = x[static_cast<size_t>(m) * p.K + p.perm[k]];
-                    const ActT hi = x[static_cast<size_t>(m) * p.K + p.perm[k + 1]];
-                    v = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&lo)) |
-                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
-                } else {
-                    v = *reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(m) * p.K + k);
-                }
+    // ---- activations: the first vectors are requested now, their latency overlaps the start of the weight stream
+    const ActT* x = static_cast<const ActT*>(p.x);
+    const int kbase = slice * p.cs * 128;
+    const int m_rows = min(p.M, MT * 8);
+    const int vec_per_row = p.cs * 16;  // uint4 = 8 activations = one (chunk, step, b)
+    const int total_vecs = m_rows * vec_per_row;
+    uint4 xr[kXRegs];
+    if (!p.perm) {
+#pragma unroll
+        for (int u = 0; u < kXRegs; ++u) {
+            const int idx = threadIdx.x + u * kThreads;
+            if (idx < total_vecs) {
+                const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+                xr[u] = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * p.K + kbase + v * 8);
             }
-            xw[idx] = v;
         }
     }
-    __syncthreads();
+
+    // ---- shared memory carve-up
+    unsigned char* ring = smem_raw + warp * (kRing * kSlotBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + kWarps * kRing * kSlotBytes) + warp * kRing;
+    uint4* xs = reinterpret_cast<uint4*>(smem_raw + kWarps * kRing * kSlotBytes + kWarps * kRing * 8);
+    const int xs_vecs = p.cs * 2 * MT * 2 * p.rows * 4;                 // [chunk64][mt][half][row][j]
+    float2* xsum = reinterpret_cast<float2*>(xs + xs_vecs);             // [item][MT*8] {S1, S2}
+    float* accs = reinterpret_cast<float*>(xsum + p.cs * MT * 8);       // [slots][MT*8][16]
+    int* slot_cnt = reinterpret_cast<int*>(accs + p.slots * MT * 128);  // [slots]
 
     // ---- this warp's share of the CTA span
-    const int first_tile = i0 / p.cs;
+    CtaView view;
+    view.accs = accs;
+    view.slot_cnt = slot_cnt;
+    view.first_tile = i0 / p.cs;
+    view.i0 = i0;
+    view.i1 = i1;
     SpanOrder order;
     order.i0 = i0;
     order.i1 = i1;
     {
-        const int head_end = min(i1, (first_tile + 1) * p.cs);
+        const int head_end = min(i1, (view.first_tile + 1) * p.cs);
         order.nh = (i0 % p.cs) ? head_end - i0 : 0;
         const int tail_start = (i1 / p.cs) * p.cs;
         order.nt = (i1 % p.cs && tail_start >= i0 + order.nh) ? i1 - max(tail_start, i0 + order.nh) : 0;
@@ -189,155 +395,188 @@ __global__ void __launch_bounds__(kThreads, (MT <= 2 ? 3 : 1)) w4a16_streamk_ker
     const int span = i1 - i0;
     const int q0 = static_cast<int>(static_cast<long long>(span) * warp / kWarps);
     const int q1 = static_cast<int>(static_cast<long long>(span) * (warp + 1) / kWarps);
+    const bool single = p.slices == 1;
 
-    // register pipeline
-    uint4 wbuf[kDepth];
-    uint2 mbuf[kDepth];
-    int tbuf[kDepth], cbuf[kDepth];
-
-    auto issue = [&](int slot, int q) {
-        if (q < q1) {
-            const int it = order.item(q);
-            const int t = it / p.cs;
-            const int c = slice * p.cs + (it - t * p.cs);
-            tbuf[slot] = t;
-            cbuf[slot] = c;
-            wbuf[slot] = ld_stream_v4(p.wq + (static_cast<size_t>(t) * p.chunks + c) * 32 + lane);
-            mbuf[slot] = __ldg(p.wm + (static_cast<size_t>(t) * p.groups + c / p.chunks_per_group) * 8 + g);
-        }
-    };
-
-    float acc[MT][4], yacc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[mt][e] = yacc[mt][e] = 0.f;
-
-    int cur_t = -1, cur_grp = -1, done_chunks = 0;
-    float slo = 0.f, shi = 0.f;
-    uint32_t zlo = 0, zhi = 0, nzlo = 0, nzhi = 0;
-
-    auto fold_group = [&]() {
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-            yacc[mt][0] = fmaf(slo, acc[mt][0], yacc[mt][0]);
-            yacc[mt][1] = fmaf(slo, acc[mt][1], yacc[mt][1]);
-            yacc[mt][2] = fmaf(shi, acc[mt][2], yacc[mt][2]);
-            yacc[mt][3] = fmaf(shi, acc[mt][3], yacc[mt][3]);
-            acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-        }
-    };
-
-    // Hand this warp's sum for tile `t` to the CTA's slot; the warp that completes the CTA's share finishes it.
-    auto flush_tile = [&](int t, int nchunks) {
-        const int slot = t - first_tile;
-        float* a = accs + slot * MT * 128;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int m = 8 * mt + 2 * j + (e & 1);
-                const int n = g + ((e & 2) ? 8 : 0);
-                if (m < p.M) atomicAdd(a + m * 16 + n, yacc[mt][e]);
-                yacc[mt][e] = 0.f;
-            }
-        }
-        __syncwarp();
-        // this CTA's share of tile t, in chunks
-        const int lo = max(i0, t * p.cs), hi = min(i1, (t + 1) * p.cs);
-        const int share = hi - lo;
-        int last = 0;
+    // ---- start the weight stream: lane 0 arms the slot barriers and issues the first kRing batches
+    if (lane == 0) {
+        for (int s = 0; s < kRing; ++s) mbar_init(smem_addr(bars + s), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    BatchIter load_it;
+    load_it.q = load_it.q_end = q1;
+    if (q0 < q1) {
+        load_it.q_end = q1;
+        load_it.seek(order, q0, p.cs);
+    }
+    auto produce = [&](int slot) {
+        // every lane tracks the iterator; lane 0 issues
+        const Batch b = load_it.next(order, p.cs, single);
         if (lane == 0) {
-            __threadfence_block();
-            last = (atomicAdd(slot_cnt + slot, nchunks) + nchunks == share);
+            const uint32_t bar = smem_addr(bars + slot);
+            const uint32_t bytes = b.n * kItemBytes;
+            mbar_expect_tx(bar, bytes);
+            bulk_g2s(smem_addr(ring + slot * kSlotBytes),
+                     p.wq + (static_cast<size_t>(b.t0) * p.items + slice * p.cs + b.cl0) * kItemBytes, bytes, bar);
         }
-        last = __shfl_sync(0xFFFFFFFFu, last, 0);
-        if (!last) return;
-        __threadfence_block();
-        ActT* y = static_cast<ActT*>(p.y);
-        const int n_base = t * 16;
-        const bool whole = (share == p.cs) && (p.slices == 1);
-        if (whole) {
-            for (int idx = lane; idx < p.M * 16; idx += 32) {
-                const int m = idx >> 4, n = idx & 15;
-                y[static_cast<size_t>(m) * p.N + n_base + n] = from_float<ActT>(a[m * 16 + n]);
-            }
-            return;
-        }
-        // second level: add the CTA's sum into the workspace, then count the CTA's chunks in
-        for (int idx = lane; idx < p.M * 16; idx += 32) {
-            const int m = idx >> 4, n = idx & 15;
-            atomicAdd(p.wsp + static_cast<size_t>(m) * p.N + n_base + n, a[m * 16 + n]);
-        }
-        __syncwarp();
-        int finisher = 0;
-        if (lane == 0) {
-            __threadfence();
-            finisher = (atomicAdd(p.counters + t, share) + share == p.chunks);
-        }
-        finisher = __shfl_sync(0xFFFFFFFFu, finisher, 0);
-        if (!finisher) return;
-        __threadfence();
-        for (int idx = lane; idx < p.M * 16; idx += 32) {
-            const int m = idx >> 4, n = idx & 15;
-            float* w = p.wsp + static_cast<size_t>(m) * p.N + n_base + n;
-            y[static_cast<size_t>(m) * p.N + n_base + n] = from_float<ActT>(__ldcg(w));
-            __stcg(w, 0.f);
-        }
-        if (lane == 0) p.counters[t] = 0;
     };
+    for (int s = 0; s < kRing && load_it.more(); ++s) produce(s);
+    EQ_TRACE(1);
 
-    // prologue
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d) issue(d, q0 + d);
+    for (int i = threadIdx.x; i < p.slots * MT * 128; i += kThreads) accs[i] = 0.f;
+    for (int i = threadIdx.x; i < p.slots; i += kThreads) slot_cnt[i] = 0;
 
-    for (int qb = q0; qb < q1; qb += kDepth) {
+    // ---- stage this slice of x in B-fragment order.  Vector v of row m holds x[m][8v .. 8v+7]: one (chunk, step, b)
+    //      with k = 64 chunk + 16 step + 8 b + 2 j, j = 0..3.  Word j lands at
+    //      ((((chunk MT + mt) 2 + step/2) rows + r) 4 + j) 4 + 2 (step & 1) + b; b = 1 words are pre-divided by 16 (f16).
+    {
+        uint32_t* xw = reinterpret_cast<uint32_t*>(xs);
+        auto store_vec = [&](int idx, uint4 val) {
+            const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+            const int chunk = v >> 3, step = (v >> 1) & 3, b = v & 1;
+            if (Frag<ActT>::kPrescaleHi && b) {
+                val.x = Frag<ActT>::sixteenth(val.x);
+                val.y = Frag<ActT>::sixteenth(val.y);
+                val.z = Frag<ActT>::sixteenth(val.z);
+                val.w = Frag<ActT>::sixteenth(val.w);
+            }
+            const int mt = m >> 3, r = m & 7;
+            uint32_t* dst = xw + ((((chunk * MT + mt) * 2 + (step >> 1)) * p.rows + r) * 16) + 2 * (step & 1) + b;
+            dst[0] = val.x;
+            dst[4] = val.y;
+            dst[8] = val.z;
+            dst[12] = val.w;
+        };
+        if (!p.perm) {
 #pragma unroll
-        for (int d = 0; d < kDepth; ++d) {
-            const int q = qb + d;
-            if (q < q1) {
-                const uint4 w4 = wbuf[d];
-                const uint2 meta = mbuf[d];
-                const int t = tbuf[d], c = cbuf[d];
-                issue(d, q + kDepth);  // refill this register slot
-                const int grp = c / p.chunks_per_group;
-                if (t != cur_t || grp != cur_grp) {
-                    if (cur_t >= 0) fold_group();
-                    if (t != cur_t) {
-                        if (cur_t >= 0) flush_tile(cur_t, done_chunks);
-                        cur_t = t;
-                        done_chunks = 0;
-                    }
-                    cur_grp = grp;
-                    slo = scale16_to_float(static_cast<uint16_t>(meta.x & 0xFFFF), p.scale_dtype);
-                    shi = scale16_to_float(static_cast<uint16_t>(meta.x >> 16), p.scale_dtype);
-                    Frag<ActT>::zero_consts(meta.y & 0xFF, zlo, nzlo);
-                    Frag<ActT>::zero_consts((meta.y >> 8) & 0xFF, zhi, nzhi);
+            for (int u = 0; u < kXRegs; ++u) {
+                const int idx = threadIdx.x + u * kThreads;
+                if (idx < total_vecs) store_vec(idx, xr[u]);
+            }
+#pragma unroll 4
+            for (int idx = threadIdx.x + kXRegs * kThreads; idx < total_vecs; idx += kThreads) {
+                const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+                store_vec(idx, *reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * p.K + kbase + v * 8));
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < total_vecs; idx += kThreads) {
+                const int m = idx / vec_per_row, v = idx - m * vec_per_row;
+                uint32_t wds[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int k = kbase + v * 8 + 2 * jj;
+                    const ActT lo = x[static_cast<size_t>(m) * p.K + p.perm[k]];
+                    const ActT hi = x[static_cast<size_t>(m) * p.K + p.perm[k + 1]];
+                    wds[jj] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&lo)) |
+                              (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&hi)) << 16);
                 }
-                ++done_chunks;
-                // B fragments of the four k16 steps of this chunk
-                const int c_local = c - slice * p.cs;
-                const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-                const uint2* xs2 = reinterpret_cast<const uint2*>(xs);
+                store_vec(idx, make_uint4(wds[0], wds[1], wds[2], wds[3]));
+            }
+        }
+        // rows of the last m-tile beyond M read as zero
+        if (p.rows == 8) {
+            const int pad_vecs = (MT * 8 - m_rows) * vec_per_row;
+            for (int idx = threadIdx.x; idx < pad_vecs; idx += kThreads) store_vec(total_vecs + idx, make_uint4(0, 0, 0, 0));
+        }
+    }
+    __syncthreads();
+    EQ_TRACE(2);
+    // ---- per (item, row): S1 = sum of the stored B values, S2 = sum of x; eight lanes share one (item, row)
+    {
+        const uint32_t* xw = reinterpret_cast<const uint32_t*>(xs);
+        const int pairs = p.cs * MT * 8;
+        const int sub = threadIdx.x & 7;
+        for (int base = 0; base < pairs; base += kThreads / 8) {
+            const int idx = base + (threadIdx.x >> 3);
+            float s1 = 0.f, s2 = 0.f;
+            if (idx < pairs) {
+                const int it = idx / (MT * 8), m = idx - it * (MT * 8);
+                const int mt = m >> 3, r = m & 7;
+                if (r < p.rows) {
+                    // this lane: (chunk, half) = sub / 2, words 8 (sub & 1) .. +7 of that 16-word row
+                    const int ch = sub >> 2, half = (sub >> 1) & 1;
+                    const uint32_t* src = xw + (((((it * 2 + ch) * MT + mt) * 2 + half) * p.rows + r) * 16) + 8 * (sub & 1);
 #pragma unroll
-                for (int step = 0; step < 4; ++step) {
-                    uint32_t a[4];
-                    Frag<ActT>::dequant(words[step], zlo, zhi, nzlo, nzhi, a);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        uint2 b = make_uint2(0, 0);
-                        if (g < p.rows)
-                            b = xs2[(((((c_local * MT + mt) * 2 + (step >> 1)) * p.rows + g) * 4 + j) << 1) + (step & 1)];
-                        Frag<ActT>::mma(acc[mt], a, b.x, b.y);
+                    for (int wd = 0; wd < 8; ++wd) {
+                        const float v = Frag<ActT>::pair_sum(src[wd]);
+                        s1 += v;
+                        s2 += (Frag<ActT>::kPrescaleHi && (wd & 1)) ? 16.f * v : v;
                     }
                 }
             }
+#pragma unroll
+            for (int off = 1; off < 8; off <<= 1) {
+                s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, off);
+                s2 += __shfl_xor_sync(0xFFFFFFFFu, s2, off);
+            }
+            if (idx < pairs && sub == 0) xsum[idx] = make_float2(s1, s2);
         }
     }
-    if (cur_t >= 0) {
-        fold_group();
-        flush_tile(cur_t, done_chunks);
+    __syncthreads();
+    EQ_TRACE(3);
+
+    float yacc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) yacc[mt][0] = yacc[mt][1] = yacc[mt][2] = yacc[mt][3] = 0.f;
+
+    BatchIter it;
+    it.q = it.q_end = q1;
+    if (q0 < q1) it.seek(order, q0, p.cs);
+    int cur_t = -1, done = 0;
+    int* status = p.counters + p.n_tiles;
+
+    for (int i = 0; it.more(); ++i) {
+        const int slot = i % kRing;
+        const uint32_t bar = smem_addr(bars + slot);
+        const uint32_t parity = (i / kRing) & 1;
+        if (!mbar_try_wait(bar, parity)) {
+            const long long t_start = clock64();
+            bool ok = false;
+            while (!(ok = mbar_try_wait(bar, parity)) && clock64() - t_start < kWaitCycles) {
+            }
+            if (!ok) {  // a copy that never landed: report and stop this warp
+                if (lane == 0) atomicExch(status, 1);
+                return;
+            }
+        }
+        if (i == 0) EQ_TRACE(4);
+        const Batch b = it.next(order, p.cs, single);
+        const unsigned char* rec = ring + slot * kSlotBytes;
+
+        float acc0[NCH][MT][4], acc1[NCH][MT][4];
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc0[ch][mt][e] = acc1[ch][mt][e] = 0.f;
+        // both items are multiplied unconditionally (a missing second item is stale bytes, its result is dropped)
+        item_mma<ActT, MT, NCH>(rec, xs + static_cast<size_t>(b.cl0) * 2 * MT * 2 * p.rows * 4, p.rows, lane, acc0);
+        item_mma<ActT, MT, NCH>(rec + kItemBytes, xs + static_cast<size_t>(b.cl1) * 2 * MT * 2 * p.rows * 4, p.rows, lane, acc1);
+
+        if (b.t0 != cur_t) {
+            if (cur_t >= 0) flush_tile<ActT, MT>(p, view, yacc, cur_t, done);
+            cur_t = b.t0;
+            done = 0;
+        }
+        item_fold<ActT, MT, NCH>(rec, xsum + b.cl0 * MT * 8, lane, p.scale_dtype, acc0, yacc);
+        ++done;
+        if (b.n == 2) {
+            if (b.t1 != cur_t) {
+                flush_tile<ActT, MT>(p, view, yacc, cur_t, done);
+                cur_t = b.t1;
+                done = 0;
+            }
+            item_fold<ActT, MT, NCH>(rec + kItemBytes, xsum + b.cl1 * MT * 8, lane, p.scale_dtype, acc1, yacc);
+            ++done;
+        }
+        // the slot has been read by every lane: refill it
+        __syncwarp();
+        if (load_it.more()) produce(slot);
     }
+    EQ_TRACE(5);
+    if (cur_t >= 0) flush_tile<ActT, MT>(p, view, yacc, cur_t, done);
+    EQ_TRACE(6);
 }
 
 struct W4Plan {
@@ -345,35 +584,42 @@ struct W4Plan {
     size_t smem;
 };
 
+static size_t w4_smem_bytes(int cs, int mt, int rows, int slots) {
+    return static_cast<size_t>(kWarps) * kRing * (kSlotBytes + 8) + static_cast<size_t>(cs) * 2 * mt * 2 * rows * 4 * 16 +
+           static_cast<size_t>(cs) * mt * 8 * sizeof(float2) + static_cast<size_t>(slots) * mt * 128 * 4 +
+           static_cast<size_t>(slots) * 4 + 16;
+}
+
 static int plan_w4(int64_t K, int64_t N, int M, W4Plan& pl) {
-    const int chunks = static_cast<int>(K / 64), n_tiles = static_cast<int>(N / 16);
+    const int items = static_cast<int>(K / 128), n_tiles = static_cast<int>(N / 16);
     int mt = (M + 7) / 8;
     pl.mt = mt <= 1 ? 1 : mt <= 2 ? 2 : mt <= 4 ? 4 : 8;
     pl.rows = pl.mt == 1 ? (M < 8 ? M : 8) : 8;
-    const int xs_budget = pl.mt <= 2 ? 64 * 1024 : 96 * 1024;
-    const int cs_max = xs_budget / (128 * pl.mt * pl.rows);
+    // activations of one slice: cs items * 256 B * mt * rows
+    const int xs_budget = pl.mt <= 2 ? 36 * 1024 : 96 * 1024;
+    const int cs_max = xs_budget / (256 * pl.mt * pl.rows);
     EQ_REQUIRE(cs_max >= 1, EQ_ERR_UNSUPPORTED, "plan_w4: activation tile does not fit shared memory");
-    int s = static_cast<int>(ceil_div(chunks, cs_max));
-    while (chunks % s) ++s;
+    int s = static_cast<int>(ceil_div(items, cs_max));
+    while (items % s) ++s;
     pl.slices = s;
-    pl.cs = chunks / s;
-    const int occupancy = pl.mt <= 2 ? 3 : 1;
-    const long long items = static_cast<long long>(n_tiles) * pl.cs;
+    pl.cs = items / s;
+    const int occupancy = pl.mt <= 2 ? 2 : 1;
+    const long long all_items = static_cast<long long>(n_tiles) * pl.cs;
     int p = sm_count() * occupancy / s;
     if (p < 1) p = 1;
-    // keep at least one chunk per warp on average, and bound the accumulator slots of a CTA
-    if (static_cast<long long>(p) * kWarps > items) p = static_cast<int>(ceil_div(items, kWarps));
+    // keep at least one item per warp on average, and bound the accumulator slots of a CTA
+    if (static_cast<long long>(p) * kWarps > all_items) p = static_cast<int>(ceil_div(all_items, kWarps));
     const int max_slots = pl.mt <= 2 ? 32 : 8;
-    long long per_cta = ceil_div(items, p);
+    long long per_cta = ceil_div(all_items, p);
     if (ceil_div(per_cta, pl.cs) + 1 > max_slots) {
         per_cta = static_cast<long long>(max_slots - 1) * pl.cs;
-        p = static_cast<int>(ceil_div(items, per_cta));
+        p = static_cast<int>(ceil_div(all_items, per_cta));
     }
     pl.ctas_per_slice = p;
-    per_cta = ceil_div(items, p);
+    per_cta = ceil_div(all_items, p);
     pl.slots = static_cast<int>(ceil_div(per_cta, pl.cs) + 1);
-    pl.smem = static_cast<size_t>(pl.cs) * pl.mt * 2 * pl.rows * 4 * 16 + static_cast<size_t>(pl.slots) * pl.mt * 128 * 4 +
-              static_cast<size_t>(pl.slots) * 4;
+    pl.smem = w4_smem_bytes(pl.cs, pl.mt, pl.rows, pl.slots);
+    EQ_REQUIRE(pl.smem <= 220 * 1024, EQ_ERR_UNSUPPORTED, "plan_w4: %zu bytes of shared memory needed", pl.smem);
     return EQ_OK;
 }
 
@@ -381,7 +627,7 @@ template <typename ActT, int MT>
 static int launch_w4(const W4Params& p, const W4Plan& pl, cudaStream_t stream) {
     auto kernel = w4a16_streamk_kernel<ActT, MT>;
     if (pl.smem > 48 * 1024)
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     kernel<<<static_cast<unsigned>(pl.slices * pl.ctas_per_slice), kThreads, pl.smem, stream>>>(p);
     EQ_LAUNCH_OK("w4a16_streamk_kernel");
     return EQ_OK;
@@ -397,25 +643,25 @@ extern "C" size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N) {
     return static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16 + 1) * sizeof(int);
 }
 
-extern "C" int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, const int32_t* perm, int64_t K,
-                               int64_t N, int64_t G, const void* x, int64_t M, int act_dtype, void* y, void* workspace,
-                               size_t workspace_bytes, void* stream_) {
+extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
+                               const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                               void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    EQ_REQUIRE(wq && wm && x && y, EQ_ERR_BAD_ARG, "eq_w4a16_linear: null pointer");
+    EQ_REQUIRE(wq && (M == 0 || (x && y)), EQ_ERR_BAD_ARG, "eq_w4a16_linear: null pointer");
     EQ_REQUIRE(K > 0 && N > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_w4a16_linear: bad extents M=%lld K=%lld N=%lld", (long long)M,
                (long long)K, (long long)N);
     if (G == -1) G = K;
     EQ_REQUIRE(G > 0 && K % G == 0, EQ_ERR_BAD_ARG, "eq_w4a16_linear: group size %lld does not cover K=%lld", (long long)G,
                (long long)K);
-    EQ_REQUIRE(K % 64 == 0 && N % 16 == 0 && G % 64 == 0, EQ_ERR_UNSUPPORTED,
-               "eq_w4a16_linear: needs K %% 64 == 0, N %% 16 == 0, G %% 64 == 0 (K=%lld N=%lld G=%lld)", (long long)K,
+    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0 && G % 128 == 0, EQ_ERR_UNSUPPORTED,
+               "eq_w4a16_linear: needs K %% 128 == 0, N %% 16 == 0, G %% 128 == 0 (K=%lld N=%lld G=%lld)", (long long)K,
                (long long)N, (long long)G);
     EQ_REQUIRE(K < (1 << 24) && N < (1 << 24), EQ_ERR_UNSUPPORTED, "eq_w4a16_linear: extent too large");
     EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_w4a16_linear: activations must be f16 or bf16");
     EQ_REQUIRE(scale_dtype == EQ_F16 || scale_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_w4a16_linear: scales must be f16 or bf16");
-    EQ_REQUIRE(aligned(wq, 16) && aligned(wm, 8) && aligned(x, 4) && aligned(y, 2), EQ_ERR_BAD_ALIGN,
-               "eq_w4a16_linear: wq needs 16-byte, wm 8-byte, x 4-byte alignment");
     if (M == 0) return EQ_OK;
+    EQ_REQUIRE(aligned(wq, 16) && aligned(x, 16) && aligned(y, 2), EQ_ERR_BAD_ALIGN,
+               "eq_w4a16_linear: wq and x need 16-byte alignment");
     EQ_REQUIRE(workspace && workspace_bytes >= eq_w4a16_workspace_bytes(M, N), EQ_ERR_WORKSPACE,
                "eq_w4a16_linear: workspace of %zu bytes needed, %zu given", eq_w4a16_workspace_bytes(M, N), workspace_bytes);
     EQ_REQUIRE(aligned(workspace, 16), EQ_ERR_BAD_ALIGN, "eq_w4a16_linear: workspace must be 16-byte aligned");
@@ -427,8 +673,7 @@ extern "C" int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, 
         int st = plan_w4(K, N, mb, pl);
         if (st != EQ_OK) return st;
         W4Params p;
-        p.wq = static_cast<const uint4*>(wq);
-        p.wm = static_cast<const uint2*>(wm);
+        p.wq = static_cast<const unsigned char*>(wq);
         p.perm = perm;
         p.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * K * esz;
         p.y = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
@@ -438,9 +683,7 @@ extern "C" int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, 
         p.K = static_cast<int>(K);
         p.N = static_cast<int>(N);
         p.M = mb;
-        p.chunks = static_cast<int>(K / 64);
-        p.chunks_per_group = static_cast<int>(G / 64);
-        p.groups = static_cast<int>(K / G);
+        p.items = static_cast<int>(K / 128);
         p.n_tiles = static_cast<int>(N / 16);
         p.slices = pl.slices;
         p.cs = pl.cs;
@@ -448,8 +691,8 @@ extern "C" int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, 
         p.rows = pl.rows;
         p.slots = pl.slots;
         p.scale_dtype = scale_dtype;
-#define EQ_W4_CASE(MTV)                                                                       \
-    case MTV:                                                                                 \
+#define EQ_W4_CASE(MTV)                                                                                                  \
+    case MTV:                                                                                                            \
         st = act_dtype == EQ_F16 ? launch_w4<__half, MTV>(p, pl, stream) : launch_w4<__nv_bfloat16, MTV>(p, pl, stream); \
         break;
         switch (pl.mt) {
@@ -464,3 +707,21 @@ extern "C" int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, 
     }
     return EQ_OK;
 }
+
+extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && M > 0 && N > 0, EQ_ERR_BAD_ARG, "eq_w4a16_status: bad arguments");
+    const int64_t ws_rows = M < 64 ? M : 64;
+    const int* status = reinterpret_cast<const int*>(static_cast<const float*>(workspace) + ws_rows * N) + N / 16;
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_w4a16_status: a device-side wait on a weight copy ran out");
+    return EQ_OK;
+}
+
+#ifdef EQ_W4_TRACE
+extern "C" int eq_debug_w4_trace(unsigned long long* host, int n) {
+    return cudaMemcpyFromSymbol(host, eq::g_w4_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -4;
+}
+#endif

@@ -1,12 +1,19 @@
-// Load-time re-tiling of AWQ / GPTQ int4 weights into the order the tensor-core fragments of the W4A16 kernels
-// read.  One 16(n) x 64(k) tile is 512 contiguous bytes: lane L = 4g + j of a warp owns 16 of them, word c of the
-// lane is k16 step c of the tile, and the eight nibbles p of a word are
+// Load-time re-tiling of AWQ / GPTQ int4 weights into the stream the W4A16 kernels read.
+//
+// The repacked weight is a flat run of 1088-byte ITEM records, [n-tile][item]: 16 output columns x 128 input rows.
+//   bytes    0..1023  two 16(n) x 64(k) tiles of nibbles, 512 B each
+//   bytes 1024..1087  the scales and zero points of the item's group: eight 8-byte records, one per column pair
+//                     (g, g+8): {scale[g] | scale[g+8] << 16 (raw 16-bit patterns), zero[g] | zero[g+8] << 8}
+//                     with the family's zero bias already added (0..16)
+// so one bulk copy brings everything a warp needs for 128 input rows of 16 columns, and a tile's whole K run is
+// contiguous.  (A group wider than 128 rows repeats its record in each of its items.)
+// Inside a 512-byte tile lane L = 4g + j of a warp owns 16 bytes, word c of the lane is k16 step c of the tile, and
+// the eight nibbles p of a word are
 //     p:      0        4        1        5        2        6        3        7
 //     k:     2j      2j+1     2j+8     2j+9      2j      2j+1     2j+8     2j+9      (within the k16 step)
 //     n:      g        g        g        g       g+8      g+8      g+8      g+8      (within the tile)
 // so that (w & 0x000F000F), (w & 0x00F000F0), ((w >> 8) & 0x000F000F), ((w >> 8) & 0x00F000F0) are the four
-// registers of an m16n8k16 A fragment.  Tiles are laid out [n-tile][k-chunk], i.e. a tile's whole K run is
-// contiguous.
+// registers of an m16n8k16 A fragment.
 #include "common.cuh"
 
 namespace eq {
@@ -20,9 +27,16 @@ __device__ __forceinline__ uint32_t read_nibble(int fmt, const uint32_t* __restr
     return (qweight[(k / 8) * N + n] >> (4 * (k & 7))) & 0xF;
 }
 
+constexpr int64_t kItemRecord = 1088;  // 1024 B of nibbles + 64 B of scales / zero points
+
+// byte offset of word (tile t, 64-row chunk c, lane, word wi) in the repacked stream
+__device__ __forceinline__ int64_t word_offset(int64_t K, int64_t t, int64_t c, int lane, int wi) {
+    return (t * (K / 128) + (c >> 1)) * kItemRecord + (c & 1) * 512 + lane * 16 + wi * 4;
+}
+
 // One thread per output word.
 __global__ void w4_repack_kernel(int fmt, const uint32_t* __restrict__ qweight, const int32_t* __restrict__ perm,
-                                 int64_t K, int64_t N, uint32_t* __restrict__ wq) {
+                                 int64_t K, int64_t N, unsigned char* __restrict__ wq) {
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (idx >= K * N / 8) return;
     const int wi = static_cast<int>(idx & 3);
@@ -40,21 +54,21 @@ __global__ void w4_repack_kernel(int fmt, const uint32_t* __restrict__ qweight, 
         const int64_t ksrc = perm ? perm[kk] : kk;
         w |= read_nibble(fmt, qweight, K, N, ksrc, n) << (4 * p);
     }
-    wq[idx] = w;
+    *reinterpret_cast<uint32_t*>(wq + word_offset(K, t, c, lane, wi)) = w;
 }
 
-// Scales and zero points, one 8-byte record per (n-tile, group, g): the two columns g and g+8 a lane owns.
-//   .x = scale[g] | scale[g+8] << 16 (raw 16-bit patterns), .y = zero[g] | zero[g+8] << 8 (family bias added)
+// Scales and zero points: one thread per (n-tile, item, g) writes the 8-byte record of columns g and g+8.
 // The source group of repacked group `grp` is g_idx[perm[grp * G]] when act-order information is present.
 __global__ void w4_repack_meta_kernel(int fmt, const uint32_t* __restrict__ qzeros, const uint16_t* __restrict__ scales,
                                       const int32_t* __restrict__ g_idx, const int32_t* __restrict__ perm, int64_t K,
-                                      int64_t N, int64_t G, uint2* __restrict__ wm) {
+                                      int64_t N, int64_t G, unsigned char* __restrict__ wq) {
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    const int64_t groups = K / G;
-    if (idx >= groups * (N / 2)) return;
+    const int64_t items = K / 128;
+    if (idx >= items * (N / 2)) return;
     const int g = static_cast<int>(idx & 7);
-    const int64_t tg = idx >> 3;
-    const int64_t t = tg / groups, grp = tg % groups;
+    const int64_t ti = idx >> 3;
+    const int64_t t = ti / items, item = ti % items;
+    const int64_t grp = item * 128 / G;
     int64_t src = grp;
     if (g_idx) src = g_idx[perm ? perm[grp * G] : grp * G];
     uint32_t sc = 0, zz = 0;
@@ -67,7 +81,7 @@ __global__ void w4_repack_meta_kernel(int fmt, const uint32_t* __restrict__ qzer
         sc |= static_cast<uint32_t>(scales[src * N + n]) << (16 * h);
         zz |= z << (8 * h);
     }
-    wm[idx] = make_uint2(sc, zz);
+    *reinterpret_cast<uint2*>(wq + ti * kItemRecord + 1024 + g * 8) = make_uint2(sc, zz);
 }
 
 // flags[0] |= 1 when some aligned G-block of g_idx is not constant; flags[1] |= 1 on an out-of-range entry.
@@ -110,7 +124,7 @@ __global__ void g_idx_sort_kernel(const int32_t* __restrict__ g_idx, int64_t K, 
     if (threadIdx.x == 0 && base != G) atomicOr(&flags[1], 2);
 }
 
-__global__ void w4_unpack_repacked_kernel(const uint32_t* __restrict__ wq, int64_t K, int64_t N,
+__global__ void w4_unpack_repacked_kernel(const unsigned char* __restrict__ wq, int64_t K, int64_t N,
                                           uint8_t* __restrict__ out) {
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (idx >= K * N / 8) return;
@@ -120,7 +134,7 @@ __global__ void w4_unpack_repacked_kernel(const uint32_t* __restrict__ wq, int64
     const int64_t chunks = K / 64;
     const int64_t t = tile_chunk / chunks, c = tile_chunk % chunks;
     const int g = lane >> 2, j = lane & 3;
-    const uint32_t w = wq[idx];
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(wq + word_offset(K, t, c, lane, wi));
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
         const int64_t kk = c * 64 + wi * 16 + 2 * j + ((p >> 2) & 1) + ((p & 1) ? 8 : 0);
@@ -133,9 +147,9 @@ static int check_geometry(const char* who, int64_t K, int64_t N, int64_t& G) {
     EQ_REQUIRE(K > 0 && N > 0, EQ_ERR_BAD_ARG, "%s: K and N must be positive", who);
     if (G == -1) G = K;
     EQ_REQUIRE(G > 0 && K % G == 0, EQ_ERR_BAD_ARG, "%s: group size %lld does not cover K=%lld", who, (long long)G, (long long)K);
-    EQ_REQUIRE(K % 64 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED, "%s: needs K %% 64 == 0 and N %% 16 == 0 (K=%lld N=%lld)", who,
+    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED, "%s: needs K %% 128 == 0 and N %% 16 == 0 (K=%lld N=%lld)", who,
                (long long)K, (long long)N);
-    EQ_REQUIRE(G % 64 == 0, EQ_ERR_UNSUPPORTED, "%s: group size %lld is not a multiple of 64", who, (long long)G);
+    EQ_REQUIRE(G % 128 == 0, EQ_ERR_UNSUPPORTED, "%s: group size %lld is not a multiple of 128", who, (long long)G);
     return EQ_OK;
 }
 
@@ -143,26 +157,24 @@ static int check_geometry(const char* who, int64_t K, int64_t N, int64_t& G) {
 
 using namespace eq;
 
-extern "C" int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t* wm_bytes,
-                                  size_t* perm_bytes) {
+extern "C" int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t* perm_bytes) {
     int st = check_geometry("eq_w4_repack_sizes", K, N, G);
     if (st != EQ_OK) return st;
-    if (wq_bytes) *wq_bytes = static_cast<size_t>(K) * N / 2;
-    if (wm_bytes) *wm_bytes = static_cast<size_t>(K / G) * (N / 2) * sizeof(uint2);
+    if (wq_bytes) *wq_bytes = static_cast<size_t>(N / 16) * (K / 128) * kItemRecord;
     // K row indices followed by four status words the repack itself uses
     if (perm_bytes) *perm_bytes = static_cast<size_t>(K + 4) * sizeof(int32_t);
     return EQ_OK;
 }
 
 extern "C" int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales,
-                            const int32_t* g_idx, int64_t K, int64_t N, int64_t G, void* wq, void* wm, int32_t* perm,
-                            int* uses_perm, void* stream_) {
+                            const int32_t* g_idx, int64_t K, int64_t N, int64_t G, void* wq, int32_t* perm, int* uses_perm,
+                            void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ, EQ_ERR_BAD_ARG, "eq_w4_repack: unknown format %d", fmt);
-    EQ_REQUIRE(qweight && qzeros && scales && wq && wm, EQ_ERR_BAD_ARG, "eq_w4_repack: null pointer");
+    EQ_REQUIRE(qweight && qzeros && scales && wq, EQ_ERR_BAD_ARG, "eq_w4_repack: null pointer");
     int st = check_geometry("eq_w4_repack", K, N, G);
     if (st != EQ_OK) return st;
-    EQ_REQUIRE(aligned(wq, 16) && aligned(wm, 8), EQ_ERR_BAD_ALIGN, "eq_w4_repack: wq needs 16-byte, wm 8-byte alignment");
+    EQ_REQUIRE(aligned(wq, 16), EQ_ERR_BAD_ALIGN, "eq_w4_repack: wq must be 16-byte aligned");
     if (uses_perm) *uses_perm = 0;
     const int32_t* row_perm = nullptr;
     if (g_idx) {
@@ -188,22 +200,22 @@ extern "C" int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzer
     }
     const int threads = 256;
     w4_repack_kernel<<<static_cast<unsigned>(ceil_div(K * N / 8, threads)), threads, 0, stream>>>(
-        fmt, reinterpret_cast<const uint32_t*>(qweight), row_perm, K, N, static_cast<uint32_t*>(wq));
+        fmt, reinterpret_cast<const uint32_t*>(qweight), row_perm, K, N, static_cast<unsigned char*>(wq));
     EQ_LAUNCH_OK("w4_repack_kernel");
-    w4_repack_meta_kernel<<<static_cast<unsigned>(ceil_div((K / G) * (N / 2), threads)), threads, 0, stream>>>(
+    w4_repack_meta_kernel<<<static_cast<unsigned>(ceil_div((K / 128) * (N / 2), threads)), threads, 0, stream>>>(
         fmt, reinterpret_cast<const uint32_t*>(qzeros), static_cast<const uint16_t*>(scales), g_idx, row_perm, K, N, G,
-        static_cast<uint2*>(wm));
+        static_cast<unsigned char*>(wq));
     EQ_LAUNCH_OK("w4_repack_meta_kernel");
     return EQ_OK;
 }
 
 extern "C" int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, void* stream) {
     EQ_REQUIRE(wq && out, EQ_ERR_BAD_ARG, "eq_w4_unpack_repacked: null pointer");
-    EQ_REQUIRE(K > 0 && N > 0 && K % 64 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED,
-               "eq_w4_unpack_repacked: needs K %% 64 == 0 and N %% 16 == 0");
+    EQ_REQUIRE(K > 0 && N > 0 && K % 128 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED,
+               "eq_w4_unpack_repacked: needs K %% 128 == 0 and N %% 16 == 0");
     const int threads = 256;
     w4_unpack_repacked_kernel<<<static_cast<unsigned>(ceil_div(K * N / 8, threads)), threads, 0,
-                                static_cast<cudaStream_t>(stream)>>>(static_cast<const uint32_t*>(wq), K, N, out);
+                                static_cast<cudaStream_t>(stream)>>>(static_cast<const unsigned char*>(wq), K, N, out);
     EQ_LAUNCH_OK("w4_unpack_repacked_kernel");
     return EQ_OK;
 }

@@ -81,10 +81,10 @@ def dequant_nvfp4(packed, scale_bits, scale_2, out_dtype=torch.float32):
 class W4Weight:
     """A repacked int4 weight resident on the device."""
 
-    __slots__ = ("wq", "wm", "perm", "k", "n", "group", "scale_dtype", "fmt")
+    __slots__ = ("wq", "perm", "k", "n", "group", "scale_dtype", "fmt")
 
     def nbytes(self) -> int:
-        return self.wq.numel() + self.wm.numel() + (self.perm.numel() * 4 if self.perm is not None else 0)
+        return self.wq.numel() + (self.perm.numel() * 4 if self.perm is not None else 0)
 
 
 def w4_repack(qweight, qzeros, scales, group_size, fmt, g_idx=None) -> W4Weight:
@@ -94,18 +94,17 @@ def w4_repack(qweight, qzeros, scales, group_size, fmt, g_idx=None) -> W4Weight:
         k, n = qweight.shape[0], qweight.shape[1] * 8
     else:
         k, n = qweight.shape[0] * 8, qweight.shape[1]
-    a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
-    L.check(lib.eq_w4_repack_sizes(k, n, group_size, C.byref(a), C.byref(b), C.byref(c)))
+    a, c = C.c_size_t(), C.c_size_t()
+    L.check(lib.eq_w4_repack_sizes(k, n, group_size, C.byref(a), C.byref(c)))
     dev = qweight.device
     w = W4Weight()
     w.wq = torch.empty(a.value, dtype=torch.uint8, device=dev)
-    w.wm = torch.empty(b.value, dtype=torch.uint8, device=dev)
     perm = torch.empty(c.value // 4, dtype=torch.int32, device=dev) if g_idx is not None else None
     uses = C.c_int(0)
     L.check(
         lib.eq_w4_repack(
-            _FMT[fmt], _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), k, n, group_size, _ptr(w.wq), _ptr(w.wm),
-            _ptr(perm), C.byref(uses), _stream(),
+            _FMT[fmt], _ptr(qweight), _ptr(qzeros), _ptr(scales), _ptr(g_idx), k, n, group_size, _ptr(w.wq), _ptr(perm),
+            C.byref(uses), _stream(),
         )
     )
     w.perm = perm if uses.value else None
@@ -143,8 +142,13 @@ def w4a16_linear(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = 
     ws = workspace if workspace is not None else w4a16_workspace(m, w.n, x.device)
     L.check(
         L.load().eq_w4a16_linear(
-            _ptr(w.wq), _ptr(w.wm), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, w.n, w.group, _ptr(x), m, _DTYPE[x.dtype],
+            _ptr(w.wq), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, w.n, w.group, _ptr(x), m, _DTYPE[x.dtype],
             _ptr(y), _ptr(ws), ws.numel(), _stream(),
         )
     )
     return y
+
+
+def w4a16_status(workspace: torch.Tensor, m: int, n: int) -> None:
+    """Raises EmmyqError(EQ_ERR_TIMEOUT) if a bounded device-side wait of an earlier call ran out."""
+    L.check(L.load().eq_w4a16_status(_ptr(workspace), m, n, _stream()))

@@ -86,19 +86,20 @@ int eq_dequant_nvfp4(const uint8_t* packed, const uint8_t* scale_bits, const flo
 /* The reference binds checkpoint bytes verbatim and lets its compiler pick a folded or source layout per weight
  * (emmy/compiler/loader/binder.py:19-131, emmy/compiler/pipeline/passes/tile/_layout.py:47-65).  Here the
  * load-time step re-tiles the int4 words once into the order the tensor-core fragments read:
- *   wq  u8  [N/16][K/64][32 lanes][16 B]   one 16x64 tile per 512 B, a lane's four words are four k16 steps
- *   wm  8 B [N/16][K/G][8]                 per column pair (g, g+8): two 16-bit scales (scale dtype kept) and two
- *                                          zero points with the family's bias added (0..16)
+ *   wq  u8  [N/16][K/128][1088 B]          one record per 16 columns x 128 input rows: two 16x64 nibble tiles
+ *                                          (512 B each; a lane of a warp owns 16 B, its four words are four k16
+ *                                          steps) followed by 64 B of that group's scales (dtype kept) and zero
+ *                                          points (family bias added, 0..16), one 8-byte entry per column pair
  *   perm int32 [K + 4]                     row order, used only when g_idx is not constant on aligned G-blocks:
  *                                          row k' of the repacked weight is input feature perm[k'] (rows sorted by
  *                                          group); the four trailing words are status words of the repack itself
  * With g_idx the scale/zero rows are gathered so that repacked group index is k' / G.
- * Requires K % 64 == 0, N % 16 == 0, G % 64 == 0 (or G = -1), every group holding exactly G rows. */
-int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t* wm_bytes, size_t* perm_bytes);
+ * Requires K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1), every group holding exactly G rows. */
+int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t* perm_bytes);
 /* *uses_perm (host int) is set to 1 when `perm` must be passed to the linear call; the call synchronizes the
  * stream once to read that flag.  `perm` may be NULL when g_idx is NULL. */
 int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, const int32_t* g_idx,
-                 int64_t K, int64_t N, int64_t G, void* wq, void* wm, int32_t* perm, int* uses_perm, void* stream);
+                 int64_t K, int64_t N, int64_t G, void* wq, int32_t* perm, int* uses_perm, void* stream);
 /* Inverse view for round-trip checks: repacked blob -> uint8 nibbles [K, N] in repacked row order. */
 int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, void* stream);
 
@@ -110,10 +111,16 @@ size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N);
 /* y[M, N] = x[M, K] @ W on repacked weights; x and y are act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * The operator the reference spells as int4 decode algebra in front of a LinearOp
  * (emmy/compiler/loader/quant.py:1235-1435) and evaluates eagerly as dequantize + F.linear
- * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it. */
-int eq_w4a16_linear(const void* wq, const void* wm, int scale_dtype, const int32_t* perm, int64_t K, int64_t N,
-                    int64_t G, const void* x, int64_t M, int act_dtype, void* y, void* workspace,
-                    size_t workspace_bytes, void* stream);
+ * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it.
+ * Needs K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1); x and wq 16-byte aligned. */
+int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
+                    const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                    void* stream);
+/* The kernel's only device-side waits are on its own weight copies and are bounded; one that runs out sets a status
+ * word in the workspace and the affected outputs are left unwritten.  This call synchronizes the stream, reads the
+ * word and returns EQ_ERR_TIMEOUT if it is set (the reference's counterpart is the host-side hung-launch deadline,
+ * crates/emmy-runtime/src/cuda.rs:1401-1451).  M and N as given to eq_w4a16_linear. */
+int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 
 #ifdef __cplusplus
 }

@@ -42,13 +42,14 @@ def test_bad_arguments_return_codes_not_crashes(eq):
     assert eq.eq_dequant_fp8(one, one, 16, 64, 3, 1, 2, one, null) == L.EQ_ERR_BAD_ARG
     assert eq.eq_dequant_nvfp4(one, one, one, 4, 20, 2, one, null) == L.EQ_ERR_BAD_ARG
     a = C.c_size_t()
-    assert eq.eq_w4_repack_sizes(100, 64, 128, C.byref(a), None, None) == L.EQ_ERR_BAD_ARG
-    assert eq.eq_w4_repack_sizes(4096, 4096, 32, C.byref(a), None, None) == L.EQ_ERR_UNSUPPORTED
-    assert eq.eq_w4_repack_sizes(4096, 4096, 128, C.byref(a), None, None) == 0 and a.value == 4096 * 4096 // 2
+    assert eq.eq_w4_repack_sizes(100, 64, 128, C.byref(a), None) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4_repack_sizes(4096, 4096, 32, C.byref(a), None) == L.EQ_ERR_UNSUPPORTED
+    assert eq.eq_w4_repack_sizes(4096, 4096, 128, C.byref(a), None) == 0 and a.value == 256 * 32 * 1088
     # linear: workspace too small, misaligned weights
-    assert eq.eq_w4a16_linear(one, one, 0, null, 4096, 4096, 128, one, 1, 0, one, null, 0, null) == L.EQ_ERR_WORKSPACE
-    assert eq.eq_w4a16_linear(C.c_void_p(8), one, 0, null, 4096, 4096, 128, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ALIGN
-    assert eq.eq_w4a16_linear(one, one, 0, null, 4096, 4096, 128, one, 1, 2, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 128, one, 1, 0, one, null, 0, null) == L.EQ_ERR_WORKSPACE
+    assert eq.eq_w4a16_linear(C.c_void_p(8), 0, null, 4096, 4096, 128, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ALIGN
+    assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 128, one, 1, 2, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 64, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_UNSUPPORTED
     assert eq.eq_w4a16_workspace_bytes(1, 4096) == 4096 * 4 + 257 * 4
 
 

@@ -119,7 +119,7 @@ def test_repack_round_trip_bit_exact(fmt):
 def test_repack_scattered_g_idx_sorts_rows():
     from emmy_b200 import ops
 
-    k, n, g = 256, 32, 64
+    k, n, g = 512, 32, 128
     qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=6)
     gi = np.random.default_rng(2).permutation(np.arange(k) // g).astype(np.int32)
     w = ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
@@ -134,7 +134,7 @@ def test_repack_rejects_unbalanced_groups():
     from emmy_b200 import ops
     from emmy_b200.lib import EmmyqError
 
-    k, n, g = 256, 32, 64
+    k, n, g = 256, 32, 128
     qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=6)
     gi = np.zeros(k, dtype=np.int32)
     gi[::3] = 1
@@ -202,12 +202,32 @@ def test_ragged_row_counts(m, dtype):
 def test_smallest_shape_and_empty_batch():
     from emmy_b200 import ops
 
-    qw, qz, sc = synth.awq_linear(64, 16, group=64, seed=1)
-    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 64, "awq")
-    x = synth.activations(2, 64, "f16")
-    check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, 64, "awq", "f16"))
-    y = ops.w4a16_linear(torch.empty(0, 64, dtype=torch.float16, device="cuda"), w)
+    qw, qz, sc = synth.awq_linear(128, 16, group=128, seed=1)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "awq")
+    x = synth.activations(2, 128, "f16")
+    check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, 128, "awq", "f16"))
+    y = ops.w4a16_linear(torch.empty(0, 128, dtype=torch.float16, device="cuda"), w)
     assert y.shape == (0, 16)
+
+
+def test_single_group_and_wide_groups():
+    from emmy_b200 import ops
+
+    for group in (-1, 256):
+        qw, qz, sc = synth.awq_linear(512, 64, group=512 if group == -1 else group, seed=7)
+        w = ops.w4_repack(dev(qw), dev(qz), dev(sc), group, "awq")
+        x = synth.activations(3, 512, "f16")
+        check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, group, "awq", "f16"))
+
+
+def test_group_64_is_refused_with_a_status():
+    from emmy_b200 import ops
+    from emmy_b200.lib import EmmyqError
+
+    qw, qz, sc = synth.awq_linear(128, 16, group=64, seed=1)
+    with pytest.raises(EmmyqError) as e:
+        ops.w4_repack(dev(qw), dev(qz), dev(sc), 64, "awq")
+    assert e.value.status_name == "EQ_ERR_UNSUPPORTED"
 
 
 def test_scattered_act_order_linear():
@@ -235,6 +255,7 @@ def test_workspace_is_left_zero_and_calls_repeat():
     y1 = ops.w4a16_linear(x, w, workspace=ws)
     torch.cuda.synchronize()
     assert int(ws.count_nonzero()) == 0
+    ops.w4a16_status(ws, 4, n)
     y2 = ops.w4a16_linear(x, w, workspace=ws)
     assert float((y1.float() - y2.float()).abs().max()) <= 1e-2 * float(y1.float().abs().max())
     assert int(ws.count_nonzero()) == 0
