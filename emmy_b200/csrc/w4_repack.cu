@@ -3,7 +3,7 @@
 // The repacked weight is a flat run of 1088-byte ITEM records, [n-tile][item]: 16 output columns x 128 input rows.
 //   bytes    0..1023  two 16(n) x 64(k) tiles of nibbles, 512 B each
 //   bytes 1024..1087  the scales and zero points of the item's group: eight 8-byte records, one per column pair
-//                     (g, g+8): {scale[g] | scale[g+8] << 16 (raw 16-bit patterns), zero[g] | zero[g+8] << 8}
+//                     (g, g+8): {scale[g] | scale[g+8] << 16 (raw 16-bit patterns), f16(zero[g]) | f16(zero[g+8]) << 16}
 //                     with the family's zero bias already added (0..16)
 // so one bulk copy brings everything a warp needs for 128 input rows of 16 columns, and a tile's whole K run is
 // contiguous.  (A group wider than 128 rows repeats its record in each of its items.)
@@ -79,7 +79,7 @@ __global__ void w4_repack_meta_kernel(int fmt, const uint32_t* __restrict__ qzer
         const int sh = fmt == EQ_W4_AWQ ? ((ni & 1) * 16 + (ni >> 1) * 4) : 4 * ni;
         const uint32_t z = ((qzeros[src * (N / 8) + n / 8] >> sh) & 0xF) + (fmt == EQ_W4_GPTQ ? 1u : 0u);
         sc |= static_cast<uint32_t>(scales[src * N + n]) << (16 * h);
-        zz |= z << (8 * h);
+        zz |= static_cast<uint32_t>(__half_as_ushort(__uint2half_rn(z))) << (16 * h);
     }
     *reinterpret_cast<uint2*>(wq + ti * kItemRecord + 1024 + g * 8) = make_uint2(sc, zz);
 }
