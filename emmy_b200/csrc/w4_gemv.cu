@@ -799,6 +799,54 @@ extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void
     return EQ_OK;
 }
 
+// ---- entry point for callers that cannot allocate ------------------------------------------------------------
+// The scratch of eq_w4a16_linear (partial sums, arrival counters, status word) for up to kNoAllocMaxM rows and
+// kNoAllocMaxN columns, resident in every device that loads this library until the process exits.
+namespace {
+constexpr int64_t kNoAllocMaxM = 16;
+constexpr int64_t kNoAllocMaxN = 32768;
+constexpr size_t kNoAllocBytes = static_cast<size_t>(kNoAllocMaxM) * kNoAllocMaxN * sizeof(float) +
+                                 (static_cast<size_t>(kNoAllocMaxN) / 16 + 1) * sizeof(int) + 252;
+static __device__ __align__(256) unsigned char g_w4_noalloc_scratch[kNoAllocBytes];
+
+// Device address of the array above on the current device.  The array's name is only a host-side handle; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+int noalloc_scratch(void** out) {
+    static void* cached[64] = {nullptr};
+    int dev = -1;
+    EQ_CUDA_OK(cudaGetDevice(&dev));
+    EQ_REQUIRE(dev >= 0 && dev < 64, EQ_ERR_UNSUPPORTED, "eq_w4a16_linear_noalloc: device index %d out of range", dev);
+    void* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (!ptr) {
+        EQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_w4_noalloc_scratch));
+        EQ_REQUIRE(ptr != nullptr, EQ_ERR_CUDA, "eq_w4a16_linear_noalloc: no device address for the static scratch");
+        __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
+    }
+    *out = ptr;
+    return EQ_OK;
+}
+}  // namespace
+
+extern "C" int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N,
+                                       int64_t G, const void* x, int64_t M, int act_dtype, void* y, void* stream_) {
+    EQ_REQUIRE(M >= 0 && M <= kNoAllocMaxM, EQ_ERR_UNSUPPORTED,
+               "eq_w4a16_linear_noalloc: M=%lld exceeds the built-in scratch (at most %lld rows); use eq_w4a16_linear with "
+               "a caller workspace",
+               (long long)M, (long long)kNoAllocMaxM);
+    EQ_REQUIRE(N > 0 && N <= kNoAllocMaxN, EQ_ERR_UNSUPPORTED,
+               "eq_w4a16_linear_noalloc: N=%lld exceeds the built-in scratch (at most %lld columns); use eq_w4a16_linear "
+               "with a caller workspace",
+               (long long)N, (long long)kNoAllocMaxN);
+    if (M == 0) return EQ_OK;
+    void* scratch = nullptr;
+    int st = noalloc_scratch(&scratch);
+    if (st != EQ_OK) return st;
+    const size_t used = eq_w4a16_workspace_bytes(M, N);
+    // all calls share the one array: whatever an earlier (possibly failed) call left there is cleared first
+    EQ_CUDA_OK(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream_)));
+    return eq_w4a16_linear(wq, scale_dtype, perm, K, N, G, x, M, act_dtype, y, scratch, used, stream_);
+}
+
 #ifdef EQ_W4_TRACE
 extern "C" int eq_debug_w4_trace(unsigned long long* host, int n) {
     return cudaMemcpyFromSymbol(host, eq::g_w4_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -4;

@@ -66,6 +66,7 @@ def load() -> C.CDLL:
         "eq_w4a16_workspace_bytes": (sz, [i64, i64]),
         "eq_w4a16_linear": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_w4a16_status": (i, [p, i64, i64, p]),
+        "eq_w4a16_linear_noalloc": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

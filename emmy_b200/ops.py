@@ -152,3 +152,19 @@ def w4a16_linear(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = 
 def w4a16_status(workspace: torch.Tensor, m: int, n: int) -> None:
     """Raises EmmyqError(EQ_ERR_TIMEOUT) if a bounded device-side wait of an earlier call ran out."""
     L.check(L.load().eq_w4a16_status(_ptr(workspace), m, n, _stream()))
+
+
+def w4a16_linear_noalloc(x: torch.Tensor, w: W4Weight, out: torch.Tensor):
+    """The W4A16 linear for callers that may not allocate: scratch lives inside the library (M <= 16, N <= 32768)
+    and `out` must be given.  Calls on one device must not overlap."""
+    _need_cuda(x, out)
+    m, k = x.shape
+    if k != w.k:
+        raise ValueError(f"x has {k} features, the weight takes {w.k}")
+    L.check(
+        L.load().eq_w4a16_linear_noalloc(
+            _ptr(w.wq), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, w.n, w.group, _ptr(x), m, _DTYPE[x.dtype], _ptr(out),
+            _stream(),
+        )
+    )
+    return out

@@ -122,6 +122,21 @@ int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_
  * crates/emmy-runtime/src/cuda.rs:1401-1451).  M and N as given to eq_w4a16_linear. */
 int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 
+/* eq_w4a16_linear for hosts that cannot hand over scratch memory.  (No counterpart in the reference: its runtime
+ * owns all device memory itself.)  Some callers of this library run where device allocation is off limits: a
+ * serving engine that has already given every byte to its KV-cache pool and forbids cudaMalloc afterwards, code on
+ * a latency-critical decode path where an allocation would synchronize the device, or a plug-in loaded into a
+ * process whose allocator it may not touch.  This variant takes inputs and outputs only.  Its partial sums and
+ * counters live in one array built into the library (about 2 MiB, present on every GPU that loads the library
+ * until the process exits), which limits it to M <= 16 rows and N <= 32768 columns; larger calls are refused with
+ * EQ_ERR_UNSUPPORTED and should use eq_w4a16_linear.  It calls no allocating routine.
+ * The first call on each device looks up the array's device address (the device must be current); make that call
+ * before starting a stream capture.  Every call clears the part of the array it uses and all calls share it, so
+ * two calls that overlap on the GPU (different streams, or different threads without ordering) race: keep calls on
+ * one device ordered. */
+int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
+                            const void* x, int64_t M, int act_dtype, void* y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
