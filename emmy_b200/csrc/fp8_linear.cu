@@ -1,0 +1,352 @@
+// FP8-E4M3 W8A8 linear: per-token dynamic activation quantize, then (sum_k q_x q_w) * s_x[m] * s_w[n].
+//
+//   quant_fp8_rows_kernel   x[M,K] f16/bf16/f32 -> e4m3 bits + one f32 scale per row.  s = max(amax, 1e-12) / 448
+//                           and q = e4m3_rne_satfinite(x / s), both with round-to-nearest f32 division: bit-exact
+//                           against the numpy rule the reference spells (emmy/compiler/loader/quant.py:1655-1735).
+//   fp8_smallm_kernel       M <= 64 (decode-shaped): a bandwidth kernel.  Weights [N,K] are read as stored, 16 bytes
+//                           per lane, straight into m16n8k32 e4m3 A fragments (no dequant instruction at all);
+//                           eight warps of a CTA split K for one 16-column tile and meet in shared memory.
+//   fp8_gemm_tc_kernel      M > 64 (prefill-shaped): tcgen05.mma kind::f8f6f4, 128x256 output tile per CTA, K-major
+//                           operands brought by TMA with the 128-byte swizzle through a 4-stage mbarrier ring,
+//                           f32 accumulators in TMEM, one producer warp, one MMA warp, four epilogue warps that read
+//                           TMEM with tcgen05.ld, apply both scales and store bf16/f16.
+// Both scales are hoisted out of the contraction, as in the reference's own native FP8 path
+// (tests/compiler/passes/test_fp8_mma.py:111-120).
+#include "tc_common.cuh"
+
+namespace eq {
+
+// ------------------------------------------------------------------------------------------------ activation quantize
+template <typename InT>
+__device__ __forceinline__ float load_as_float(const InT* p) {
+    return to_float(*p);
+}
+
+__device__ __forceinline__ uint16_t e4m3x2_satfinite(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));  // first source -> upper byte
+    return r;
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(256) quant_fp8_rows_kernel(const InT* __restrict__ x, int64_t K, uint8_t* __restrict__ q,
+                                                             float* __restrict__ scale) {
+    __shared__ float warp_max[8];
+    __shared__ float row_scale;
+    const int64_t row = blockIdx.x;
+    const InT* xr = x + row * K;
+    float amax = 0.f;
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(load_as_float(xr + k)));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float m = warp_max[0];
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+        const float s = __fdiv_rn(fmaxf(m, 1e-12f), 448.0f);
+        row_scale = s;
+        scale[row] = s;
+    }
+    __syncthreads();
+    const float s = row_scale;
+    uint8_t* qr = q + row * K;
+    // two elements per thread per step; K is even (K % 16 == 0 is required by the callers)
+    for (int64_t k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x) {
+        const float a = __fdiv_rn(load_as_float(xr + k), s), b = __fdiv_rn(load_as_float(xr + k + 1), s);
+        *reinterpret_cast<uint16_t*>(qr + k) = e4m3x2_satfinite(a, b);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ decode-shaped
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kSmallWarps = 8;
+
+// One CTA per 16 output columns; warp w takes the w-th eighth of K.  A lane's 16 weight bytes of row g (and g+8)
+// feed two k32 MMAs; which actual k a fragment slot means is irrelevant as long as the activation fragment uses the
+// same bytes, so both are simply the lane's 16 consecutive bytes.
+template <typename OutT, int MT>
+__global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
+                                                                       const uint8_t* __restrict__ qx, const float* __restrict__ sx,
+                                                                       OutT* __restrict__ y, int M, int N, int K) {
+    __shared__ float red[kSmallWarps][MT][16][8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, j = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const int steps = K / 64;
+    const int s0 = steps * warp / kSmallWarps, s1 = steps * (warp + 1) / kSmallWarps;
+    const uint8_t* wr_lo = w + static_cast<size_t>(n0 + g) * K + 16 * j;
+    const uint8_t* wr_hi = wr_lo + static_cast<size_t>(8) * K;
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+
+    constexpr int U = 4;  // steps in flight per warp
+    for (int sb = s0; sb < s1; sb += U) {
+        uint4 a_lo[U], a_hi[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (sb + u < s1) {
+                a_lo[u] = ld_stream_v4(wr_lo + static_cast<size_t>(sb + u) * 64);
+                a_hi[u] = ld_stream_v4(wr_hi + static_cast<size_t>(sb + u) * 64);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (sb + u < s1) {
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    const int m = mt * 8 + g;
+                    uint4 b = make_uint4(0, 0, 0, 0);
+                    if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u) * 64 + 16 * j));
+                    mma_e4m3(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
+                    mma_e4m3(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        red[warp][mt][g][2 * j] = acc[mt][0];
+        red[warp][mt][g][2 * j + 1] = acc[mt][1];
+        red[warp][mt][g + 8][2 * j] = acc[mt][2];
+        red[warp][mt][g + 8][2 * j + 1] = acc[mt][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MT * 128; idx += kSmallWarps * 32) {
+        const int mt = idx >> 7, n = (idx >> 3) & 15, mm = idx & 7;
+        const int m = mt * 8 + mm;
+        if (m < M) {
+            float s = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < kSmallWarps; ++wv) s += red[wv][mt][n][mm];
+            y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ prefill-shaped
+constexpr int kBM = 128, kBN = 256, kBK = 128;  // tile; kBK in bytes = e4m3 elements
+constexpr int kStages = 4;
+constexpr int kTileA = kBM * kBK, kTileB = kBN * kBK;
+constexpr int kGemmThreads = 192;
+constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const float* __restrict__ sx, const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K,
+                       int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    // the swizzled tiles need 1024-byte alignment
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_a = smem;
+    unsigned char* tiles_b = smem + kStages * kTileA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kTileA + kTileB));
+    uint64_t* full = bars;                 // [kStages] TMA -> MMA
+    uint64_t* empty = bars + kStages;      // [kStages] MMA -> TMA
+    uint64_t* acc_ready = bars + 2 * kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    const int k_blocks = K / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kBN);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_a);
+            tc::tma_prefetch_desc(&map_b);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                tc::mbar_expect_tx(bar, kTileA + kTileB);
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBK, m0, bar);
+                tc::tma_load_2d(tc::smem_u32(tiles_b + s * kTileB), &map_b, kb * kBK, n0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc(0, 0, kBM, kBN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % kStages;
+                ok = tc::mbar_wait(tc::smem_u32(full + s), (kb / kStages) & 1);
+                if (!ok) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles_a + s * kTileA), b_addr = tc::smem_u32(tiles_b + s * kTileB);
+#pragma unroll
+                for (int ks = 0; ks < kBK / 32; ++ks) {
+                    // 32 bytes of K per instruction: step the descriptors' start address inside the swizzle atom
+                    const uint64_t da = tc::smem_desc_k_sw128(a_addr + ks * 32), db = tc::smem_desc_k_sw128(b_addr + ks * 32);
+                    tc::mma_f8f6f4(tmem_base, da, db, idesc, kb > 0 || ks > 0);
+                }
+                tc::mma_commit(tc::smem_u32(empty + s));  // stage is free once these MMAs have read it
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too, so that the epilogue does not sit out its wait
+        }
+    } else {
+        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok) {
+            const float row_scale = m < M ? sx[m] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
+                tc::tmem_ld_wait();
+                if (m < M) {
+                    OutT* dst = y + static_cast<size_t>(m) * N + n0 + c;
+                    if (n0 + c + 32 <= N) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float v0 = __uint_as_float(r[2 * i]) * row_scale * sw[n0 + c + 2 * i];
+                            const float v1 = __uint_as_float(r[2 * i + 1]) * row_scale * sw[n0 + c + 2 * i + 1];
+                            const OutT o0 = from_float<OutT>(v0), o1 = from_float<OutT>(v1);
+                            packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && n0 + c + i < N; ++i)
+                            dst[i] = from_float<OutT>(__uint_as_float(r[i]) * row_scale * sw[n0 + c + i]);
+                    }
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, kBN);
+    }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace eq
+
+using namespace eq;
+
+extern "C" int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(M >= 0 && K > 0, EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: bad extents M=%lld K=%lld", (long long)M, (long long)K);
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(x && q && scale, EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: null pointer");
+    EQ_REQUIRE(K % 2 == 0 && aligned(q, 2), EQ_ERR_BAD_ALIGN, "eq_quant_fp8_per_token: K must be even and q 2-byte aligned");
+    const unsigned grid = static_cast<unsigned>(M);
+    switch (in_dtype) {
+        case EQ_F16: quant_fp8_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), K, q, scale); break;
+        case EQ_BF16: quant_fp8_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), K, q, scale); break;
+        case EQ_F32: quant_fp8_rows_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), K, q, scale); break;
+        default: return fail(EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: unknown dtype %d", in_dtype);
+    }
+    EQ_LAUNCH_OK("quant_fp8_rows_kernel");
+    return EQ_OK;
+}
+
+extern "C" size_t eq_fp8_workspace_bytes(int64_t M, int64_t K) {
+    if (M <= 0 || K <= 0) return 0;
+    return align_up(static_cast<size_t>(M) * K, 256) + align_up(static_cast<size_t>(M) * sizeof(float), 256) + 256;
+}
+
+template <typename OutT>
+static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
+                             OutT* y, int* status, cudaStream_t stream) {
+    if (M <= 64) {
+        const unsigned grid = static_cast<unsigned>(N / 16);
+        const int mt = static_cast<int>((M + 7) / 8);
+        const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
+        if (mt <= 1) fp8_smallm_kernel<OutT, 1><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
+        else if (mt <= 2) fp8_smallm_kernel<OutT, 2><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
+        else if (mt <= 4) fp8_smallm_kernel<OutT, 4><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
+        else fp8_smallm_kernel<OutT, 8><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
+        EQ_LAUNCH_OK("fp8_smallm_kernel");
+        return EQ_OK;
+    }
+    CUtensorMap map_a, map_b;
+    int st = make_tensor_map_2d(&map_a, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kBN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    auto kernel = fp8_gemm_tc_kernel<OutT>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
+    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
+    kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N),
+                                                     static_cast<int>(K), status);
+    EQ_LAUNCH_OK("fp8_gemm_tc_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
+                             int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_fp8_linear: bad extents M=%lld K=%lld N=%lld", (long long)M,
+               (long long)K, (long long)N);
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(weight && weight_scale && x && y, EQ_ERR_BAD_ARG, "eq_fp8_linear: null pointer");
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_fp8_linear: activations must be f16 or bf16");
+    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED, "eq_fp8_linear: needs K %% 128 == 0 and N %% 16 == 0 (K=%lld N=%lld)",
+               (long long)K, (long long)N);
+    EQ_REQUIRE(aligned(weight, 16) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "eq_fp8_linear: weight and y must be 16-byte aligned");
+    EQ_REQUIRE(workspace && workspace_bytes >= eq_fp8_workspace_bytes(M, K), EQ_ERR_WORKSPACE,
+               "eq_fp8_linear: workspace of %zu bytes needed, %zu given", eq_fp8_workspace_bytes(M, K), workspace_bytes);
+    EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "eq_fp8_linear: workspace must be 256-byte aligned");
+    uint8_t* qx = static_cast<uint8_t*>(workspace);
+    float* sx = reinterpret_cast<float*>(qx + align_up(static_cast<size_t>(M) * K, 256));
+    int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + align_up(static_cast<size_t>(M) * sizeof(float), 256));
+    EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    int st = eq_quant_fp8_per_token(x, M, K, act_dtype, qx, sx, stream_);
+    if (st != EQ_OK) return st;
+    if (act_dtype == EQ_F16) return fp8_linear_launch<__half>(weight, weight_scale, N, K, qx, sx, M, static_cast<__half*>(y), status, stream);
+    return fp8_linear_launch<__nv_bfloat16>(weight, weight_scale, N, K, qx, sx, M, static_cast<__nv_bfloat16*>(y), status, stream);
+}
+
+extern "C" int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && M > 0 && K > 0, EQ_ERR_BAD_ARG, "eq_fp8_status: bad arguments");
+    const unsigned char* base = static_cast<const unsigned char*>(workspace);
+    const int* status = reinterpret_cast<const int*>(base + align_up(static_cast<size_t>(M) * K, 256) +
+                                                     align_up(static_cast<size_t>(M) * sizeof(float), 256));
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_fp8_status: a bounded pipeline wait ran out (code %d)", host);
+    return EQ_OK;
+}

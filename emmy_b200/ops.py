@@ -168,3 +168,42 @@ def w4a16_linear_noalloc(x: torch.Tensor, w: W4Weight, out: torch.Tensor):
         )
     )
     return out
+
+
+# ---------------------------------------------------------------------------------------------- FP8 W8A8
+
+
+def quant_fp8_per_token(x: torch.Tensor):
+    """x [M, K] (f16 / bf16 / f32) -> (bits uint8 [M, K], scale f32 [M, 1])."""
+    _need_cuda(x)
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((m, 1), dtype=torch.float32, device=x.device)
+    L.check(L.load().eq_quant_fp8_per_token(_ptr(x), m, k, _DTYPE[x.dtype], _ptr(q), _ptr(s), _stream()))
+    return q, s
+
+
+def fp8_workspace(m: int, k: int, device) -> torch.Tensor:
+    need = L.load().eq_fp8_workspace_bytes(m, k)
+    return torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
+
+
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None):
+    """y[M, N] = x @ (weight * scale).T with x quantized per token; weight uint8 e4m3 bits [N, K], scale f32 [N]."""
+    _need_cuda(x, weight, weight_scale)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise ValueError(f"x has {k} features, the weight takes {weight.shape[1]}")
+    y = out if out is not None else torch.empty((m, n), dtype=x.dtype, device=x.device)
+    ws = workspace if workspace is not None else fp8_workspace(m, k, x.device)
+    L.check(
+        L.load().eq_fp8_linear(
+            _ptr(weight), _ptr(weight_scale), n, k, _ptr(x), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()
+        )
+    )
+    return y
+
+
+def fp8_status(workspace: torch.Tensor, m: int, k: int) -> None:
+    L.check(L.load().eq_fp8_status(_ptr(workspace), m, k, _stream()))

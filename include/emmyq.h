@@ -137,6 +137,29 @@ int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                             const void* x, int64_t M, int act_dtype, void* y, void* stream);
 
+/* ------------------------------------------------------------------ FP8-E4M3 W8A8 linear */
+
+/* Dynamic per-token activation quantize: scale[m] = max(amax_k |x[m,k]|, 1e-12) / 448 (f32), q = e4m3 (round to
+ * nearest even, saturating to +-448) of x / scale with an f32 division.  x is [M, K] of in_dtype (EQ_F16, EQ_BF16 or
+ * EQ_F32), q is [M, K] bytes, scale [M] f32.  Bit-exact with the rule the reference spells into its graphs
+ * (_spell_dynamic_activation, emmy/compiler/loader/quant.py:1655-1735).  Applied to a weight's rows it is the
+ * per-output-channel weight quantizer. */
+int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream);
+
+/* Scratch of eq_fp8_linear: the quantized activations, their scales and a status word. */
+size_t eq_fp8_workspace_bytes(int64_t M, int64_t K);
+/* y[M, N] = (sum_k q_x[m,k] q_w[n,k]) * s_x[m] * s_w[n] in act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
+ * weight: e4m3 bits [N, K] as the checkpoint stores them, weight_scale: f32 [N] multiplier.  The activation is
+ * quantized per token inside the call.  M <= 64 runs a weight-streaming kernel, larger M the tcgen05 tensor path.
+ * The operator the reference spells as FP8 decode + dynamic activation round trip in front of a LinearOp
+ * (emmy/compiler/loader/quant.py:1581-1768) and runs natively with both scales hoisted
+ * (tests/compiler/passes/test_fp8_mma.py:111-120).  Needs K % 128 == 0, N % 16 == 0; workspace 256-byte aligned. */
+int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
+                  int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* Synchronizes the stream and returns EQ_ERR_TIMEOUT if a bounded pipeline wait of the last eq_fp8_linear call on
+ * this workspace ran out (same role as eq_w4a16_status). */
+int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
