@@ -7,11 +7,11 @@
 //                     with the family's zero bias already added (0..16)
 // so one bulk copy brings everything a warp needs for 128 input rows of 16 columns, and a tile's whole K run is
 // contiguous.  (A group wider than 128 rows repeats its record in each of its items.)
-// Inside a 512-byte tile lane L = 4g + j of a warp owns 16 bytes, word c of the lane is k16 step c of the tile, and
-// the eight nibbles p of a word are
-//     p:      0        4        1        5        2        6        3        7
-//     k:     2j      2j+1     2j+8     2j+9      2j      2j+1     2j+8     2j+9      (within the k16 step)
-//     n:      g        g        g        g       g+8      g+8      g+8      g+8      (within the tile)
+// Inside a 512-byte tile lane L = 4g + j of a warp owns 16 bytes, word c of the lane is k16 step s = 4 tile + c of
+// the item, and the eight nibbles p of a word are
+//     p:        0          4          1           5           2          6          3           5+2
+//     row:  32j+2s     32j+2s+1   32j+16+2s   32j+17+2s    32j+2s     32j+2s+1   32j+16+2s   32j+17+2s   (in the item)
+//     n:        g          g          g           g          g+8        g+8        g+8         g+8       (in the tile)
 // so that (w & 0x000F000F), (w & 0x00F000F0), ((w >> 8) & 0x000F000F), ((w >> 8) & 0x00F000F0) are the four
 // registers of an m16n8k16 A fragment.
 #include "common.cuh"
@@ -25,6 +25,16 @@ __device__ __forceinline__ uint32_t read_nibble(int fmt, const uint32_t* __restr
         return (qweight[k * (N / 8) + n / 8] >> ((i & 1) * 16 + (i >> 1) * 4)) & 0xF;
     }
     return (qweight[(k / 8) * N + n] >> (4 * (k & 7))) & 0xF;
+}
+
+// Input row of nibble p of word wi (k16 step s = 4 (c & 1) + wi of the item) in lane j.  The rows of an item are
+// dealt to the four lane columns j in blocks of 32; inside a block the first 16 rows are the "low" fragment slots
+// (k-slots 2j, 2j+1 of the steps), the last 16 the "high" ones (k-slots 2j+8, 2j+9), two rows per step:
+//     row = 128 item + 32 j + 16 high + 2 s + odd
+// so the activations one lane needs for a whole item are 64 contiguous bytes of x.
+__device__ __forceinline__ int64_t item_row(int64_t c, int wi, int j, int p) {
+    const int s = 4 * static_cast<int>(c & 1) + wi;
+    return (c >> 1) * 128 + 32 * j + ((p & 1) ? 16 : 0) + 2 * s + ((p >> 2) & 1);
 }
 
 constexpr int64_t kItemRecord = 1088;  // 1024 B of nibbles + 64 B of scales / zero points
@@ -45,11 +55,10 @@ __global__ void w4_repack_kernel(int fmt, const uint32_t* __restrict__ qweight, 
     const int64_t chunks = K / 64;
     const int64_t t = tile_chunk / chunks, c = tile_chunk % chunks;
     const int g = lane >> 2, j = lane & 3;
-    const int64_t kb = c * 64 + wi * 16;
     uint32_t w = 0;
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-        const int64_t kk = kb + 2 * j + ((p >> 2) & 1) + ((p & 1) ? 8 : 0);
+        const int64_t kk = item_row(c, wi, j, p);
         const int64_t n = t * 16 + g + ((p & 2) ? 8 : 0);
         const int64_t ksrc = perm ? perm[kk] : kk;
         w |= read_nibble(fmt, qweight, K, N, ksrc, n) << (4 * p);
@@ -137,7 +146,7 @@ __global__ void w4_unpack_repacked_kernel(const unsigned char* __restrict__ wq, 
     const uint32_t w = *reinterpret_cast<const uint32_t*>(wq + word_offset(K, t, c, lane, wi));
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
-        const int64_t kk = c * 64 + wi * 16 + 2 * j + ((p >> 2) & 1) + ((p & 1) ? 8 : 0);
+        const int64_t kk = item_row(c, wi, j, p);
         const int64_t n = t * 16 + g + ((p & 2) ? 8 : 0);
         out[kk * N + n] = (w >> (4 * p)) & 0xF;
     }
