@@ -1,0 +1,352 @@
+// NVFP4 (e2m1 codes, e4m3 scale per 16 elements of K, f32 global scale) W4A4 linear.
+//
+//   nvfp4_amax_kernel / nvfp4_scale2_kernel  calibrate-on-the-sample input scale: max(amax, 1e-12) / (6 * 448)
+//   quant_nvfp4_act_kernel   static-scale activation quantize, the f32 algebra the reference spells
+//                            (emmy/compiler/loader/quant.py:1968-2139, tests/compiler/loader/test_quant.py:1776-1784):
+//                            ratio = (amax_blk * f32(1/6)) * f32(1/s2); sbits = e4m3(ratio); fused = dec(sbits) * s2;
+//                            codes = e2m1(blk / max(fused, 1e-12)), all round-to-nearest f32.  Bit-exact.
+//   nvfp4_tile_scales_kernel re-tiles a plain [rows, K/16] scale matrix into the 512-byte atoms the tensor core's
+//                            scale-factor copy reads (load time for weights, inside the quantize for activations)
+//   nvfp4_gemm_tc_kernel     tcgen05.mma kind::mxf4nvf4.block_scale.scale_vec::4X: codes come by TMA (128-byte
+//                            swizzle, 256 elements of K per row), scale atoms by bulk copy and then tcgen05.cp into
+//                            TMEM, f32 accumulators in TMEM; the epilogue multiplies by the two global scales.
+// The hardware applies the raw e4m3 block scale and the global scales are factored out into the epilogue, whereas
+// the reference's value path applies f16(block * global) per element: a relative difference of at most 2^-11 per
+// operand, far inside the output tolerance; the dequantised-weight export (eq_dequant_nvfp4) stays bit-exact.
+#include "tc_common.cuh"
+
+namespace eq {
+
+// ------------------------------------------------------------------------------------------------ calibration
+template <typename InT>
+__global__ void nvfp4_amax_kernel(const InT* __restrict__ x, int64_t n, unsigned int* __restrict__ amax_bits) {
+    float m = 0.f;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        m = fmaxf(m, fabsf(to_float(x[i])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    if ((threadIdx.x & 31) == 0) atomicMax(amax_bits, __float_as_uint(m));  // non-negative floats order like their bits
+}
+__global__ void nvfp4_scale2_kernel(const unsigned int* __restrict__ amax_bits, float* __restrict__ scale2) {
+    const double amax = fmax(static_cast<double>(__uint_as_float(*amax_bits)), 1e-12);
+    *scale2 = static_cast<float>(amax / (6.0 * 448.0));
+}
+
+// ------------------------------------------------------------------------------------------------ scale atoms
+// Tiled scale layout: [row block of 128][k block of 64 elements][512 B]; inside an atom the scale of (row r, 16-block
+// i of the k block) sits at byte (r % 32) * 16 + (r / 32) * 4 + i.  Rows beyond `rows` are zero.
+__device__ __forceinline__ size_t sf_tiled_offset(int64_t row, int64_t blk16, int64_t k64_blocks) {
+    const int64_t rb = row >> 7, r = row & 127, kb = blk16 >> 2, i = blk16 & 3;
+    return static_cast<size_t>((rb * k64_blocks + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4 + i);
+}
+
+__global__ void nvfp4_tile_scales_kernel(const uint8_t* __restrict__ plain, int64_t rows, int64_t K, uint8_t* __restrict__ tiled) {
+    const int64_t blocks16 = K / 16, k64 = K / 64;
+    const int64_t padded_rows = (rows + 127) / 128 * 128;
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= padded_rows * blocks16) return;
+    const int64_t row = idx / blocks16, b = idx % blocks16;
+    tiled[sf_tiled_offset(row, b, k64)] = row < rows ? plain[row * blocks16 + b] : 0;
+}
+
+// ------------------------------------------------------------------------------------------------ activation quantize
+__device__ __forceinline__ uint8_t e4m3_satfinite(float v) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(0.f), "f"(v));
+    return static_cast<uint8_t>(r & 0xFF);
+}
+// two f32 -> one byte: low nibble = code(lo), high nibble = code(hi)
+__device__ __forceinline__ uint8_t e2m1x2_satfinite(float lo, float hi) {
+    uint16_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return static_cast<uint8_t>(r);
+}
+
+// One thread per 16-element block.  Writes the packed codes [M, K/2], the plain scales [M, K/16] (optional) and the
+// tiled scales (optional).
+template <typename InT>
+__global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int64_t K, const float* __restrict__ scale2,
+                                       uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_tiled) {
+    const int64_t blocks16 = K / 16;
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= M * blocks16) return;
+    const int64_t row = idx / blocks16, b = idx % blocks16;
+    const InT* src = x + row * K + b * 16;
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        v[i] = to_float(src[i]);
+        amax = fmaxf(amax, fabsf(v[i]));
+    }
+    const float s2 = scale2[0];
+    const float ratio = __fmul_rn(__fmul_rn(amax, __fdiv_rn(1.0f, 6.0f)), __fdiv_rn(1.0f, s2));
+    const uint8_t sbits = e4m3_satfinite(ratio);
+    const float fused = __fmul_rn(e4m3_to_float(sbits), s2);
+    const float div = fmaxf(fused, 1e-12f);
+    uint32_t w[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint8_t byte = e2m1x2_satfinite(__fdiv_rn(v[2 * i], div), __fdiv_rn(v[2 * i + 1], div));
+        w[i >> 2] |= static_cast<uint32_t>(byte) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(codes + row * (K / 2) + b * 8) = make_uint2(w[0], w[1]);
+    if (sf_plain) sf_plain[idx] = sbits;
+    if (sf_tiled) sf_tiled[sf_tiled_offset(row, b, K / 64)] = sbits;
+}
+
+// ------------------------------------------------------------------------------------------------ tensor path
+constexpr int kBM = 128, kBN = 256;
+constexpr int kBKBytes = 128;                 // 256 e2m1 elements of K per stage row
+constexpr int kStages = 4;
+constexpr int kTileA = kBM * kBKBytes, kTileB = kBN * kBKBytes;
+constexpr int kSfA = 4 * 512, kSfB = 2 * 4 * 512;  // four k64 atoms per stage, one / two row blocks
+constexpr int kStageBytes = kTileA + kTileB + kSfA + kSfB;
+constexpr int kGemmThreads = 192;
+constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+constexpr uint32_t kTmemCols = 512;           // 256 accumulator columns + 16 (SFA) + 32 (SFB), rounded to a power of two
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ gx,
+                         const float* __restrict__ gw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_a = smem;
+    unsigned char* tiles_b = tiles_a + kStages * kTileA;
+    unsigned char* sfs_a = tiles_b + kStages * kTileB;
+    unsigned char* sfs_b = sfs_a + kStages * kSfA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sfs_b + kStages * kSfB);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kStages;
+    uint64_t* acc_ready = bars + 2 * kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    const int k_blocks = K / 256;   // stages of 256 elements
+    const int k64_blocks = K / 64;  // scale atoms along K
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_sfa = tmem_base + kBN;        // 4 columns per k64 step
+    const uint32_t tmem_sfb = tmem_base + kBN + 16;   // 8 columns per k64 step
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_a);
+            tc::tma_prefetch_desc(&map_b);
+            const int rb_a = m0 / 128, rb_b = n0 / 128;
+            const int n_rb = (N + 127) / 128;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                // the second row block of B may lie beyond N (N not a multiple of 256): it is then not copied
+                const bool second = rb_b + 1 < n_rb;
+                tc::mbar_expect_tx(bar, kTileA + kTileB + kSfA + (second ? kSfB : kSfB / 2));
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBKBytes, m0, bar);
+                tc::tma_load_2d(tc::smem_u32(tiles_b + s * kTileB), &map_b, kb * kBKBytes, n0, bar);
+                bulk_g2s(tc::smem_u32(sfs_a + s * kSfA), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfA, bar);
+                bulk_g2s(tc::smem_u32(sfs_b + s * kSfB), sfb + (static_cast<size_t>(rb_b) * k64_blocks + kb * 4) * 512, kSfB / 2, bar);
+                if (second)
+                    bulk_g2s(tc::smem_u32(sfs_b + s * kSfB + kSfB / 2),
+                             sfb + (static_cast<size_t>(rb_b + 1) * k64_blocks + kb * 4) * 512, kSfB / 2, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc_nvfp4(kBM, kBN, 0, 0);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kStages) & 1)) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles_a + s * kTileA), b_addr = tc::smem_u32(tiles_b + s * kTileB);
+                const uint32_t sfa_addr = tc::smem_u32(sfs_a + s * kSfA), sfb_addr = tc::smem_u32(sfs_b + s * kSfB);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    // scale atoms of this k64 step -> TMEM: A rows 0..127 (4 columns), B rows 0..127 and 128..255
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfa + ks * 4, tc::smem_desc_sf(sfa_addr + ks * 512));
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8, tc::smem_desc_sf(sfb_addr + ks * 512));
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8 + 4, tc::smem_desc_sf(sfb_addr + kSfB / 2 + ks * 512));
+                    const uint64_t da = tc::smem_desc_k_sw128(a_addr + ks * 32), db = tc::smem_desc_k_sw128(b_addr + ks * 32);
+                    tc::mma_mxf4nvf4(tmem_base, da, db, idesc, tmem_sfa + ks * 4, tmem_sfb + ks * 8, kb > 0 || ks > 0);
+                }
+                tc::mma_commit(tc::smem_u32(empty + s));
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok) {
+            const float g = gx[0] * gw[0];
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
+                tc::tmem_ld_wait();
+                if (m < M) {
+                    OutT* dst = y + static_cast<size_t>(m) * N + n0 + c;
+                    for (int i = 0; i < 32 && n0 + c + i < N; i += 2) {
+                        const OutT o0 = from_float<OutT>(__uint_as_float(r[i]) * g), o1 = from_float<OutT>(__uint_as_float(r[i + 1]) * g);
+                        *reinterpret_cast<uint32_t*>(dst + i) = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                                                (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                    }
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t sf_tiled_bytes(int64_t rows, int64_t K) { return static_cast<size_t>((rows + 127) / 128) * (K / 64) * 512; }
+
+}  // namespace eq
+
+using namespace eq;
+
+extern "C" size_t eq_nvfp4_tiled_scale_bytes(int64_t rows, int64_t K) {
+    if (rows <= 0 || K <= 0 || K % 64) return 0;
+    return sf_tiled_bytes(rows, K);
+}
+
+extern "C" int eq_nvfp4_tile_scales(const uint8_t* scale_bits, int64_t rows, int64_t K, uint8_t* tiled, void* stream) {
+    EQ_REQUIRE(scale_bits && tiled, EQ_ERR_BAD_ARG, "eq_nvfp4_tile_scales: null pointer");
+    EQ_REQUIRE(rows > 0 && K > 0 && K % 64 == 0, EQ_ERR_UNSUPPORTED, "eq_nvfp4_tile_scales: needs K %% 64 == 0 (K=%lld)", (long long)K);
+    const int64_t total = (rows + 127) / 128 * 128 * (K / 16);
+    nvfp4_tile_scales_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(scale_bits, rows, K, tiled);
+    EQ_LAUNCH_OK("nvfp4_tile_scales_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_nvfp4_global_scale(const void* x, int64_t M, int64_t K, int in_dtype, float* scale2, unsigned int* scratch_u32,
+                                     void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(x && scale2 && scratch_u32 && M > 0 && K > 0, EQ_ERR_BAD_ARG, "eq_nvfp4_global_scale: bad arguments");
+    EQ_CUDA_OK(cudaMemsetAsync(scratch_u32, 0, sizeof(unsigned int), stream));
+    const int64_t n = M * K;
+    const unsigned grid = static_cast<unsigned>(n / 256 / 8 + 1 < 1184 ? n / 256 / 8 + 1 : 1184);
+    switch (in_dtype) {
+        case EQ_F16: nvfp4_amax_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), n, scratch_u32); break;
+        case EQ_BF16: nvfp4_amax_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), n, scratch_u32); break;
+        case EQ_F32: nvfp4_amax_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), n, scratch_u32); break;
+        default: return fail(EQ_ERR_BAD_ARG, "eq_nvfp4_global_scale: unknown dtype %d", in_dtype);
+    }
+    EQ_LAUNCH_OK("nvfp4_amax_kernel");
+    nvfp4_scale2_kernel<<<1, 1, 0, stream>>>(scratch_u32, scale2);
+    EQ_LAUNCH_OK("nvfp4_scale2_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const float* input_scale, uint8_t* codes,
+                                  uint8_t* scale_bits, uint8_t* scale_tiled, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(M >= 0 && K > 0, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: bad extents");
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(x && input_scale && codes, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: null pointer");
+    EQ_REQUIRE(K % 16 == 0 && (!scale_tiled || K % 64 == 0), EQ_ERR_UNSUPPORTED, "eq_quant_nvfp4_act: K must be a multiple of 16 (64 with tiled scales)");
+    EQ_REQUIRE(aligned(codes, 8), EQ_ERR_BAD_ALIGN, "eq_quant_nvfp4_act: codes must be 8-byte aligned");
+    if (scale_tiled) EQ_CUDA_OK(cudaMemsetAsync(scale_tiled, 0, sf_tiled_bytes(M, K), stream));  // rows beyond M
+    const int64_t total = M * (K / 16);
+    const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
+    switch (in_dtype) {
+        case EQ_F16: quant_nvfp4_act_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
+        case EQ_BF16: quant_nvfp4_act_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
+        case EQ_F32: quant_nvfp4_act_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
+        default: return fail(EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: unknown dtype %d", in_dtype);
+    }
+    EQ_LAUNCH_OK("quant_nvfp4_act_kernel");
+    return EQ_OK;
+}
+
+extern "C" size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K) {
+    if (M <= 0 || K <= 0) return 0;
+    return align_up(static_cast<size_t>(M) * K / 2, 256) + align_up(sf_tiled_bytes(M, K), 256) + 256;
+}
+
+extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N,
+                               int64_t K, const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace,
+                               size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: bad extents M=%lld K=%lld N=%lld", (long long)M, (long long)K, (long long)N);
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(weight && weight_scale_tiled && weight_scale_2 && x && input_scale && y, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: null pointer");
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: activations must be f16 or bf16");
+    EQ_REQUIRE(K % 256 == 0 && N % 8 == 0, EQ_ERR_UNSUPPORTED, "eq_nvfp4_linear: needs K %% 256 == 0 and N %% 8 == 0 (K=%lld N=%lld)", (long long)K, (long long)N);
+    EQ_REQUIRE(aligned(weight, 16) && aligned(weight_scale_tiled, 16) && aligned(y, 4), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: weight and scales must be 16-byte aligned");
+    EQ_REQUIRE(workspace && workspace_bytes >= eq_nvfp4_workspace_bytes(M, K), EQ_ERR_WORKSPACE, "eq_nvfp4_linear: workspace of %zu bytes needed, %zu given",
+               eq_nvfp4_workspace_bytes(M, K), workspace_bytes);
+    EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: workspace must be 256-byte aligned");
+    uint8_t* codes = static_cast<uint8_t*>(workspace);
+    uint8_t* sfa = codes + align_up(static_cast<size_t>(M) * K / 2, 256);
+    int* status = reinterpret_cast<int*>(sfa + align_up(sf_tiled_bytes(M, K), 256));
+    EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    int st = eq_quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, stream_);
+    if (st != EQ_OK) return st;
+    CUtensorMap map_a, map_b;
+    // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
+    st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, kBN, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
+    if (act_dtype == EQ_F16) {
+        auto kernel = nvfp4_gemm_tc_kernel<__half>;
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
+        kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2,
+                                                         static_cast<__half*>(y), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+    } else {
+        auto kernel = nvfp4_gemm_tc_kernel<__nv_bfloat16>;
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
+        kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2,
+                                                         static_cast<__nv_bfloat16*>(y), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+    }
+    EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && M > 0 && K > 0, EQ_ERR_BAD_ARG, "eq_nvfp4_status: bad arguments");
+    const unsigned char* base = static_cast<const unsigned char*>(workspace);
+    const int* status = reinterpret_cast<const int*>(base + align_up(static_cast<size_t>(M) * K / 2, 256) + align_up(sf_tiled_bytes(M, K), 256));
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_nvfp4_status: a bounded pipeline wait ran out (code %d)", host);
+    return EQ_OK;
+}

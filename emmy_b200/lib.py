@@ -70,6 +70,13 @@ def load() -> C.CDLL:
         "eq_fp8_workspace_bytes": (sz, [i64, i64]),
         "eq_fp8_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_fp8_status": (i, [p, i64, i64, p]),
+        "eq_nvfp4_global_scale": (i, [p, i64, i64, i, p, p, p]),
+        "eq_quant_nvfp4_act": (i, [p, i64, i64, i, p, p, p, p, p]),
+        "eq_nvfp4_tiled_scale_bytes": (sz, [i64, i64]),
+        "eq_nvfp4_tile_scales": (i, [p, i64, i64, p, p]),
+        "eq_nvfp4_workspace_bytes": (sz, [i64, i64]),
+        "eq_nvfp4_linear": (i, [p, p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
+        "eq_nvfp4_status": (i, [p, i64, i64, p]),
         "eq_w4a16_linear_noalloc": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p]),
     }
     for name, (res, args) in sig.items():

@@ -160,6 +160,37 @@ int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, i
  * this workspace ran out (same role as eq_w4a16_status). */
 int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream);
 
+/* ------------------------------------------------------------------ NVFP4 W4A4 linear */
+
+/* The input scale calibrated on the sample itself: max(amax |x|, 1e-12) / (6 * 448), computed in f64 and rounded to
+ * f32 (emmy/compiler/loader/synthesize.py:181-183; the same rule gives weight_scale_2 in quantize_nvfp4,
+ * emmy/compiler/loader/quant.py:221-226).  scale2: device f32 [1]; scratch_u32: device uint32 [1]. */
+int eq_nvfp4_global_scale(const void* x, int64_t M, int64_t K, int in_dtype, float* scale2, unsigned int* scratch_u32,
+                          void* stream);
+/* Static-scale NVFP4 activation quantize, bit-exact with the algebra the reference spells
+ * (_spell_static_fp4_quantize, emmy/compiler/loader/quant.py:1968-2139; pinned by _static_quantize_ref,
+ * tests/compiler/loader/test_quant.py:1776-1784).  codes: [M, K/2] bytes (low nibble = even k); scale_bits: optional
+ * plain e4m3 scales [M, K/16]; scale_tiled: optional scales in the tensor core's atom order (size from
+ * eq_nvfp4_tiled_scale_bytes).  input_scale: device f32 [1]. */
+int eq_quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const float* input_scale, uint8_t* codes,
+                       uint8_t* scale_bits, uint8_t* scale_tiled, void* stream);
+/* Load-time re-tiling of a checkpoint's weight_scale [rows, K/16] into 512-byte atoms: [row block of 128][64
+ * elements of K][512 B], scale of (row r, block i) at byte (r % 32) * 16 + (r / 32) * 4 + i; rows padded to 128 with
+ * zeros.  (The reference binds these bytes verbatim, emmy/compiler/loader/binder.py:124-130; here the scale-factor
+ * copy into tensor memory wants this order.)  Needs K % 64 == 0. */
+size_t eq_nvfp4_tiled_scale_bytes(int64_t rows, int64_t K);
+int eq_nvfp4_tile_scales(const uint8_t* scale_bits, int64_t rows, int64_t K, uint8_t* tiled, void* stream);
+/* y[M, N] = input_scale * weight_scale_2 * sum_blocks s_x s_w sum_k c_x c_w in act_dtype: the native block-scaled
+ * product (tcgen05.mma kind::mxf4nvf4).  weight: packed e2m1 [N, K/2] as stored; weight_scale_tiled: from
+ * eq_nvfp4_tile_scales; weight_scale_2, input_scale: device f32 [1].  The activation is quantized inside the call.
+ * The operator the reference spells as NVFP4 decode + static activation quantize in front of a LinearOp
+ * (emmy/compiler/loader/quant.py:2142-2209, 1968-2139).  Needs K % 256 == 0, N % 8 == 0. */
+size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K);
+int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N,
+                    int64_t K, const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace,
+                    size_t workspace_bytes, void* stream);
+int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
