@@ -1,0 +1,441 @@
+// Mixture-of-experts layer on W4A16 (AWQ / GPTQ int4) experts: router, token permute, grouped expert FFN, combine.
+// Everything is decided on the device: no host read of the routing, every launch has a host-known grid, so the
+// whole layer can sit in a CUDA graph at any token count.
+//
+//   moe_route_kernel      softmax in f32 over the router logits, top-k with ties to the lowest expert id, picked
+//                         probabilities renormalised, picks of a row sorted by ascending expert id (the order the
+//                         combine adds them in).  Follows emmy/serving/native/prepare.py:424-463 and the routed
+//                         combine's ordering, emmy/serving/gen_runner.py:263-279.
+//   moe_count / moe_plan / moe_scatter
+//                         histogram of rows per expert, exclusive scan, the list of (expert, first row, rows) row
+//                         blocks, and each row's position in expert order: the device-side form of the reference's
+//                         stable argsort + counts.tolist() (gen_runner.py:276-283).
+//   moe_expert_gemm_kernel  grouped W4A16 GEMM: grid = (column tiles, row blocks); a row block is at most kRowBlock
+//                         rows of ONE expert, its weights are that expert's slice of the stacked repacked tensor.
+//                         Rows are gathered (first GEMM) / scattered (second GEMM) through index arrays, nothing is
+//                         copied.  Body: the W4A16 tile code of w4_tile.cuh.
+//   moe_swiglu_kernel     h = silu(gate) * up with the roundings of the eager form
+//                         (emmy/compiler/trace/huggingface.py:1663-1669).
+//   moe_combine_kernel    out[t] = dtype(sum_j f32(score_j) * f32(expert_j(x_t))), picks in ascending expert order,
+//                         products and sum in f32, one rounding (gen_runner.py:235-287).
+#include "w4_tile.cuh"
+
+namespace eq {
+
+constexpr int kMaxTopK = 16;
+
+// ------------------------------------------------------------------------------------------------ router
+// One warp per token.  E <= 1024.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int topk, int renorm, int32_t* __restrict__ ids,
+                                 float* __restrict__ scores) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= T) return;
+    const float* lg = logits + static_cast<size_t>(warp) * E;
+    // softmax statistics
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    // top-k by repeated arg-max on the logits (they order the experts as the probabilities do); ties -> lowest id
+    int pick_id[kMaxTopK];
+    float pick_p[kMaxTopK];
+    unsigned long long taken_lo = 0;  // this lane's experts already picked (bit = (e - lane) / 32)
+    float psum = 0.f;
+    for (int j = 0; j < topk; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7FFFFFFF;
+        for (int e = lane, b = 0; e < E; e += 32, ++b) {
+            if ((taken_lo >> b) & 1ull) continue;
+            const float v = lg[e];
+            if (v > best || (v == best && e < best_e)) {
+                best = v;
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
+            if (ov > best || (ov == best && oe < best_e)) {
+                best = ov;
+                best_e = oe;
+            }
+        }
+        if (best_e < E && (best_e & 31) == lane) taken_lo |= 1ull << (best_e >> 5);
+        const float pr = best_e < E ? expf(best - mx) / sum : 0.f;
+        pick_id[j] = best_e < E ? best_e : E - 1;
+        pick_p[j] = pr;
+        psum += pr;
+    }
+    if (lane == 0) {
+        // ascending expert id (insertion sort of at most 16 picks)
+        for (int a = 1; a < topk; ++a) {
+            const int id = pick_id[a];
+            const float pv = pick_p[a];
+            int b = a - 1;
+            while (b >= 0 && pick_id[b] > id) {
+                pick_id[b + 1] = pick_id[b];
+                pick_p[b + 1] = pick_p[b];
+                --b;
+            }
+            pick_id[b + 1] = id;
+            pick_p[b + 1] = pv;
+        }
+        for (int j = 0; j < topk; ++j) {
+            ids[static_cast<size_t>(warp) * topk + j] = pick_id[j];
+            scores[static_cast<size_t>(warp) * topk + j] = renorm ? pick_p[j] / psum : pick_p[j];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ permute
+struct RowBlock {
+    int32_t expert, row0, rows, pad;
+};
+
+__global__ void moe_count_kernel(const int32_t* __restrict__ eid, int R, int E, int32_t* __restrict__ counts, int32_t* status) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int e = eid[r];
+    if (e < 0 || e >= E) {
+        atomicExch(status, 4);  // an expert id outside [0, E): the row is dropped, the caller is told
+        return;
+    }
+    atomicAdd(counts + e, 1);
+}
+
+// One CTA: exclusive scan of the counts, row blocks of at most `block_rows` rows, cursors reset.
+__global__ void moe_plan_kernel(const int32_t* __restrict__ counts, int E, int block_rows, int32_t* __restrict__ offsets,
+                                int32_t* __restrict__ cursor, RowBlock* __restrict__ blocks, int32_t* __restrict__ n_blocks,
+                                int max_blocks) {
+    extern __shared__ int32_t sh[];  // [E] counts -> offsets, [E] block offsets
+    int32_t* off = sh;
+    int32_t* boff = sh + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        off[e] = counts[e];
+        boff[e] = (counts[e] + block_rows - 1) / block_rows;
+        cursor[e] = 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t run = 0, brun = 0;
+        for (int e = 0; e < E; ++e) {
+            const int32_t c = off[e], b = boff[e];
+            off[e] = run;
+            boff[e] = brun;
+            run += c;
+            brun += b;
+        }
+        offsets[E] = run;
+        *n_blocks = brun < max_blocks ? brun : max_blocks;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        offsets[e] = off[e];
+        const int32_t c = counts[e];
+        for (int32_t b = 0, r = 0; r < c; ++b, r += block_rows) {
+            if (boff[e] + b < max_blocks) {
+                RowBlock rb;
+                rb.expert = e;
+                rb.row0 = off[e] + r;
+                rb.rows = min(block_rows, c - r);
+                rb.pad = 0;
+                blocks[boff[e] + b] = rb;
+            }
+        }
+    }
+}
+
+// pos_of[r]: position of row r in expert order; src_of[pos]: the activation row that feeds position pos; dst_of[pos] = r.
+__global__ void moe_scatter_kernel(const int32_t* __restrict__ eid, const int32_t* __restrict__ src_row, int R, int E,
+                                   const int32_t* __restrict__ offsets, int32_t* __restrict__ cursor, int32_t* __restrict__ src_of,
+                                   int32_t* __restrict__ dst_of) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int e = eid[r];
+    if (e < 0 || e >= E) return;
+    const int pos = offsets[e] + atomicAdd(cursor + e, 1);
+    src_of[pos] = src_row ? src_row[r] : r;
+    dst_of[pos] = r;
+}
+
+// ------------------------------------------------------------------------------------------------ grouped GEMM
+struct GroupedParams {
+    const unsigned char* wq;      // [E][n_tiles][items][1088]
+    size_t expert_stride;         // bytes between experts
+    const void* x;                // activations (rows addressed through x_rows, or contiguous in expert order)
+    void* y;                      // outputs (rows addressed through y_rows, or contiguous in expert order)
+    const int32_t* x_rows;        // optional [R] gather index in expert order
+    const int32_t* y_rows;        // optional [R] scatter index in expert order
+    const RowBlock* blocks;
+    const int32_t* n_blocks;
+    int K, N, scale_dtype;
+};
+
+template <typename ActT, int MT, bool ONE>
+__global__ void __launch_bounds__(kTileThreads) moe_expert_gemm_kernel(const GroupedParams gp) {
+    __shared__ float red[kTileWarps][MT * 8][16];
+    __shared__ int last_flag;
+    if (static_cast<int>(blockIdx.y) >= *gp.n_blocks) return;
+    const RowBlock rb = gp.blocks[blockIdx.y];
+    W4Params p;
+    p.wq = gp.wq + static_cast<size_t>(rb.expert) * gp.expert_stride;
+    p.perm = nullptr;
+    p.K = gp.K;
+    p.N = gp.N;
+    p.M = rb.rows;
+    p.items = gp.K / 128;
+    p.splits = 1;
+    p.scale_dtype = gp.scale_dtype;
+    p.wsp = nullptr;
+    p.counters = nullptr;
+    if (gp.x_rows) {
+        p.x = gp.x;
+        p.x_rows = gp.x_rows + rb.row0;
+    } else {
+        p.x = static_cast<const ActT*>(gp.x) + static_cast<size_t>(rb.row0) * gp.K;
+        p.x_rows = nullptr;
+    }
+    if (gp.y_rows) {
+        p.y = gp.y;
+        p.y_rows = gp.y_rows + rb.row0;
+    } else {
+        p.y = static_cast<ActT*>(gp.y) + static_cast<size_t>(rb.row0) * gp.N;
+        p.y_rows = nullptr;
+    }
+    w4_tile<ActT, MT, ONE>(p, blockIdx.x, 0, red, &last_flag);
+}
+
+// h[r][i] = act( silu(gate[r][i]) ) * up[r][i], gate = gu[r][i], up = gu[r][I + i]; silu in f32, rounded to the
+// activation dtype before the product, product rounded again: the eager form's two roundings.
+template <typename ActT>
+__global__ void moe_swiglu_kernel(const ActT* __restrict__ gu, const int32_t* __restrict__ total_rows, int I, ActT* __restrict__ h) {
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t r = idx / I, i = idx % I;
+    if (r >= *total_rows) return;
+    const float g = to_float(gu[r * 2 * I + i]), u = to_float(gu[r * 2 * I + I + i]);
+    const ActT s = from_float<ActT>(g / (1.f + expf(-g)));
+    h[idx] = from_float<ActT>(to_float(s) * u);
+}
+
+// One thread per output element: f32 products and sum over the row's picks in their stored (ascending id) order.
+template <typename ActT>
+__global__ void moe_combine_kernel(const ActT* __restrict__ out_rows, const float* __restrict__ scores, int T, int topk, int H,
+                                   ActT* __restrict__ y) {
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= static_cast<int64_t>(T) * H) return;
+    const int64_t t = idx / H, hcol = idx % H;
+    float acc = 0.f;
+    for (int j = 0; j < topk; ++j) {
+        // the reference casts the scores to the activation dtype first (gen_runner.py:263)
+        const float sc = to_float(from_float<ActT>(scores[t * topk + j]));
+        acc = fmaf(sc, to_float(out_rows[(t * topk + j) * H + hcol]), acc);
+    }
+    y[idx] = from_float<ActT>(acc);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct MoeWorkspace {
+    int32_t *counts, *offsets, *cursor, *n_blocks, *status, *src_of, *dst_of, *ids, *src_row;
+    float* scores;
+    RowBlock* blocks;
+    unsigned char *h1, *h, *out;
+    int max_blocks;
+    size_t bytes;
+};
+
+static int block_rows_for(int64_t R) { return R <= 64 ? 8 : R <= 256 ? 16 : 64; }
+
+static MoeWorkspace carve(void* base, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I) {
+    MoeWorkspace w;
+    const int64_t R = T * topk;
+    unsigned char* p = static_cast<unsigned char*>(base);
+    size_t o = 0;
+    auto take = [&](size_t bytes) {
+        unsigned char* r = p ? p + o : nullptr;
+        o += align_up(bytes, 256);
+        return r;
+    };
+    w.counts = reinterpret_cast<int32_t*>(take(E * 4));
+    w.offsets = reinterpret_cast<int32_t*>(take((E + 1) * 4));
+    w.cursor = reinterpret_cast<int32_t*>(take(E * 4));
+    w.n_blocks = reinterpret_cast<int32_t*>(take(4));
+    w.status = reinterpret_cast<int32_t*>(take(4));
+    w.max_blocks = static_cast<int>(R / block_rows_for(R) + E + 1);
+    w.blocks = reinterpret_cast<RowBlock*>(take(sizeof(RowBlock) * w.max_blocks));
+    w.src_of = reinterpret_cast<int32_t*>(take(R * 4));
+    w.dst_of = reinterpret_cast<int32_t*>(take(R * 4));
+    w.ids = reinterpret_cast<int32_t*>(take(R * 4));
+    w.src_row = reinterpret_cast<int32_t*>(take(R * 4));
+    w.scores = reinterpret_cast<float*>(take(R * 4));
+    w.h1 = take(R * 2 * I * 2);
+    w.h = take(R * I * 2);
+    w.out = take(R * H * 2);
+    w.bytes = o;
+    return w;
+}
+
+template <typename ActT>
+static int launch_grouped(const GroupedParams& gp, int block_rows, int max_blocks, cudaStream_t stream) {
+    dim3 grid(static_cast<unsigned>(gp.N / 16), static_cast<unsigned>(max_blocks));
+    if (block_rows <= 8) moe_expert_gemm_kernel<ActT, 1, false><<<grid, kTileThreads, 0, stream>>>(gp);
+    else if (block_rows <= 16) moe_expert_gemm_kernel<ActT, 2, false><<<grid, kTileThreads, 0, stream>>>(gp);
+    else moe_expert_gemm_kernel<ActT, 8, false><<<grid, kTileThreads, 0, stream>>>(gp);
+    EQ_LAUNCH_OK("moe_expert_gemm_kernel");
+    return EQ_OK;
+}
+
+// Grouped expert FFN over R rows: row r is activation row src_row[r] (or r) of x and belongs to expert eid[r];
+// out[r] = down_e( silu(gate_e(x)) * up_e(x) ).
+template <typename ActT>
+static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H,
+                           int64_t I, const void* x, const int32_t* src_row, const int32_t* eid, int64_t R, void* out,
+                           cudaStream_t stream) {
+    const int br = block_rows_for(R);
+    EQ_CUDA_OK(cudaMemsetAsync(w.counts, 0, E * 4, stream));
+    moe_count_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, static_cast<int>(R), static_cast<int>(E), w.counts, w.status);
+    EQ_LAUNCH_OK("moe_count_kernel");
+    moe_plan_kernel<<<1, 256, 2 * E * sizeof(int32_t), stream>>>(w.counts, static_cast<int>(E), br, w.offsets, w.cursor, w.blocks, w.n_blocks,
+                                                                 w.max_blocks);
+    EQ_LAUNCH_OK("moe_plan_kernel");
+    moe_scatter_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, src_row, static_cast<int>(R), static_cast<int>(E), w.offsets,
+                                                                                  w.cursor, w.src_of, w.dst_of);
+    EQ_LAUNCH_OK("moe_scatter_kernel");
+    GroupedParams g1;
+    g1.wq = static_cast<const unsigned char*>(wq_gate_up);
+    g1.expert_stride = static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes;
+    g1.x = x;
+    g1.y = w.h1;
+    g1.x_rows = w.src_of;
+    g1.y_rows = nullptr;
+    g1.blocks = w.blocks;
+    g1.n_blocks = w.n_blocks;
+    g1.K = static_cast<int>(H);
+    g1.N = static_cast<int>(2 * I);
+    g1.scale_dtype = scale_dtype;
+    int st = launch_grouped<ActT>(g1, br, w.max_blocks, stream);
+    if (st != EQ_OK) return st;
+    moe_swiglu_kernel<ActT><<<static_cast<unsigned>(ceil_div(R * I, 256)), 256, 0, stream>>>(reinterpret_cast<const ActT*>(w.h1), w.offsets + E,
+                                                                                          static_cast<int>(I), reinterpret_cast<ActT*>(w.h));
+    EQ_LAUNCH_OK("moe_swiglu_kernel");
+    GroupedParams g2 = g1;
+    g2.wq = static_cast<const unsigned char*>(wq_down);
+    g2.expert_stride = static_cast<size_t>(H / 16) * (I / 128) * kItemBytes;
+    g2.x = w.h;
+    g2.y = out;
+    g2.x_rows = nullptr;
+    g2.y_rows = w.dst_of;
+    g2.K = static_cast<int>(I);
+    g2.N = static_cast<int>(H);
+    return launch_grouped<ActT>(g2, br, w.max_blocks, stream);
+}
+
+static int check_moe_shapes(const char* who, int64_t E, int64_t topk, int64_t H, int64_t I, int64_t G) {
+    EQ_REQUIRE(E > 0 && E <= 1024 && topk > 0 && topk <= kMaxTopK && topk <= E, EQ_ERR_UNSUPPORTED, "%s: needs 0 < top-k <= 16 and E <= 1024", who);
+    if (G == -1) G = 128;
+    EQ_REQUIRE(H % 128 == 0 && I % 128 == 0 && G == 128, EQ_ERR_UNSUPPORTED, "%s: needs hidden and intermediate sizes that are multiples of 128 and group 128", who);
+    return EQ_OK;
+}
+
+}  // namespace eq
+
+using namespace eq;
+
+extern "C" int eq_moe_route(const float* logits, int64_t T, int64_t E, int64_t topk, int renorm, int32_t* ids, float* scores, void* stream) {
+    EQ_REQUIRE(T >= 0 && E > 0 && E <= 1024 && topk > 0 && topk <= kMaxTopK && topk <= E, EQ_ERR_UNSUPPORTED,
+               "eq_moe_route: needs 0 < top-k <= 16 and E <= 1024");
+    if (T == 0) return EQ_OK;
+    EQ_REQUIRE(logits && ids && scores, EQ_ERR_BAD_ARG, "eq_moe_route: null pointer");
+    moe_route_kernel<<<static_cast<unsigned>(ceil_div(T * 32, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, static_cast<int>(T), static_cast<int>(E), static_cast<int>(topk), renorm, ids, scores);
+    EQ_LAUNCH_OK("moe_route_kernel");
+    return EQ_OK;
+}
+
+extern "C" size_t eq_moe_workspace_bytes(int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I) {
+    if (T <= 0 || E <= 0 || topk <= 0 || H <= 0 || I <= 0) return 0;
+    return carve(nullptr, T, E, topk, H, I).bytes;
+}
+
+extern "C" int eq_moe_experts_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H, int64_t I, int64_t G,
+                                    const void* x, const int32_t* src_row, const int32_t* expert_ids, int64_t R, int act_dtype, void* out,
+                                    void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_moe_shapes("eq_moe_experts_w4a16", E, 1, H, I, G);
+    if (st != EQ_OK) return st;
+    if (R == 0) return EQ_OK;
+    EQ_REQUIRE(R > 0 && wq_gate_up && wq_down && x && expert_ids && out, EQ_ERR_BAD_ARG, "eq_moe_experts_w4a16: null pointer or negative row count");
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_moe_experts_w4a16: activations must be f16 or bf16");
+    EQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= eq_moe_workspace_bytes(R, E, 1, H, I), EQ_ERR_WORKSPACE,
+               "eq_moe_experts_w4a16: workspace of %zu bytes (256-byte aligned) needed, %zu given", eq_moe_workspace_bytes(R, E, 1, H, I), workspace_bytes);
+    MoeWorkspace w = carve(workspace, R, E, 1, H, I);
+    EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
+    if (act_dtype == EQ_F16)
+        return experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, stream);
+    return experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, stream);
+}
+
+__global__ void moe_src_rows_kernel(int32_t* src_row, int R, int topk) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < R) src_row[r] = r / topk;
+}
+
+extern "C" int eq_moe_combine(const void* out_rows, const float* scores, int64_t T, int64_t topk, int64_t H, int act_dtype, void* y, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(T >= 0 && topk > 0 && H > 0, EQ_ERR_BAD_ARG, "eq_moe_combine: bad extents");
+    if (T == 0) return EQ_OK;
+    EQ_REQUIRE(out_rows && scores && y, EQ_ERR_BAD_ARG, "eq_moe_combine: null pointer");
+    const unsigned grid = static_cast<unsigned>(ceil_div(T * H, 256));
+    if (act_dtype == EQ_F16)
+        moe_combine_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(out_rows), scores, static_cast<int>(T), static_cast<int>(topk),
+                                                             static_cast<int>(H), static_cast<__half*>(y));
+    else if (act_dtype == EQ_BF16)
+        moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(out_rows), scores, static_cast<int>(T),
+                                                                    static_cast<int>(topk), static_cast<int>(H), static_cast<__nv_bfloat16*>(y));
+    else
+        return fail(EQ_ERR_BAD_ARG, "eq_moe_combine: activations must be f16 or bf16");
+    EQ_LAUNCH_OK("moe_combine_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t topk, int64_t H, int64_t I, int64_t G,
+                            const void* x, const float* router_logits, int64_t T, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                            void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = check_moe_shapes("eq_moe_w4a16", E, topk, H, I, G);
+    if (st != EQ_OK) return st;
+    if (T == 0) return EQ_OK;
+    EQ_REQUIRE(T > 0 && wq_gate_up && wq_down && x && router_logits && y, EQ_ERR_BAD_ARG, "eq_moe_w4a16: null pointer or negative token count");
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_moe_w4a16: activations must be f16 or bf16");
+    EQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= eq_moe_workspace_bytes(T, E, topk, H, I), EQ_ERR_WORKSPACE,
+               "eq_moe_w4a16: workspace of %zu bytes (256-byte aligned) needed, %zu given", eq_moe_workspace_bytes(T, E, topk, H, I), workspace_bytes);
+    MoeWorkspace w = carve(workspace, T, E, topk, H, I);
+    const int64_t R = T * topk;
+    EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
+    st = eq_moe_route(router_logits, T, E, topk, 1, w.ids, w.scores, stream_);
+    if (st != EQ_OK) return st;
+    moe_src_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(w.src_row, static_cast<int>(R), static_cast<int>(topk));
+    EQ_LAUNCH_OK("moe_src_rows_kernel");
+    if (act_dtype == EQ_F16)
+        st = experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, stream);
+    else
+        st = experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, stream);
+    if (st != EQ_OK) return st;
+    return eq_moe_combine(w.out, w.scores, T, topk, H, act_dtype, y, stream_);
+}
+
+extern "C" int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && T > 0, EQ_ERR_BAD_ARG, "eq_moe_status: bad arguments");
+    MoeWorkspace w = carve(const_cast<void*>(workspace), T, E, topk, H, I);
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, w.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host == 0, EQ_ERR_BAD_ARG, "eq_moe_status: an expert id outside [0, E) was met (code %d)", host);
+    return EQ_OK;
+}

@@ -77,6 +77,12 @@ def load() -> C.CDLL:
         "eq_nvfp4_workspace_bytes": (sz, [i64, i64]),
         "eq_nvfp4_linear": (i, [p, p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
         "eq_nvfp4_status": (i, [p, i64, i64, p]),
+        "eq_moe_route": (i, [p, i64, i64, i64, i, p, p, p]),
+        "eq_moe_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),
+        "eq_moe_experts_w4a16": (i, [p, p, i, i64, i64, i64, i64, p, p, p, i64, i, p, p, sz, p]),
+        "eq_moe_combine": (i, [p, p, i64, i64, i64, i, p, p]),
+        "eq_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, i64, i, p, p, sz, p]),
+        "eq_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),
         "eq_w4a16_linear_noalloc": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p]),
     }
     for name, (res, args) in sig.items():

@@ -191,6 +191,39 @@ int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scale_tiled, co
                     size_t workspace_bytes, void* stream);
 int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream);
 
+/* ------------------------------------------------------------------ MoE on W4A16 experts */
+
+/* Router: softmax in f32 over logits [T, E], top-k with ties to the lowest expert id, picked probabilities
+ * renormalised when renorm != 0.  ids int32 [T, k] and scores f32 [T, k] come out sorted by ascending expert id per
+ * row, the order the combine adds them in.  Follows the router of emmy/serving/native/prepare.py:424-463 (contract
+ * of the fused router in emmy/serving/gen_runner.py:3175-3197).  E <= 1024, k <= 16. */
+int eq_moe_route(const float* logits, int64_t T, int64_t E, int64_t topk, int renorm, int32_t* ids, float* scores, void* stream);
+
+/* Scratch of the MoE calls for T tokens (for eq_moe_experts_w4a16: T = rows, topk = 1). */
+size_t eq_moe_workspace_bytes(int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I);
+
+/* Grouped expert FFN over R rows: row r reads activation row src_row[r] of x (src_row NULL: row r) and belongs to
+ * expert expert_ids[r]; out[r] = down_e( silu(gate_e(x_r)) * up_e(x_r) ) in act_dtype.  wq_gate_up / wq_down: the
+ * experts' repacked int4 weights (eq_w4_repack) stacked expert-major; gate_up is K = H, N = 2 I (gate columns then up
+ * columns), down is K = I, N = H.  The expert algebra of ExpertFFN.forward (emmy/compiler/trace/huggingface.py:1663-1669)
+ * over the row lists the reference builds with a stable argsort and a host read of the counts
+ * (emmy/serving/gen_runner.py:276-283, 3359-3479); here counts, offsets and row blocks stay on the device.
+ * This is also the local step of expert-parallel serving: the rows are the tokens received from all ranks. */
+int eq_moe_experts_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H, int64_t I, int64_t G,
+                         const void* x, const int32_t* src_row, const int32_t* expert_ids, int64_t R, int act_dtype, void* out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* y[t] = dtype( sum_j f32(dtype(score[t, j])) * f32(out_rows[t k + j]) ): products and sum in f32 in the stored pick
+ * order, one rounding (combine_routed_experts, emmy/serving/gen_runner.py:235-287). */
+int eq_moe_combine(const void* out_rows, const float* scores, int64_t T, int64_t topk, int64_t H, int act_dtype, void* y, void* stream);
+
+/* Whole routed layer on one device: route (renormalised top-k), grouped expert FFN, combine. */
+int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t topk, int64_t H, int64_t I, int64_t G,
+                 const void* x, const float* router_logits, int64_t T, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                 void* stream);
+/* Synchronizes the stream; EQ_ERR_BAD_ARG if the last call met an expert id outside [0, E) (such rows are dropped). */
+int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
