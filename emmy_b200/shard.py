@@ -1,0 +1,182 @@
+"""Sharding of the quantized-linear path over the GPUs of one node (one process per GPU, torch.distributed).
+
+Three partitions, as the path shards naturally:
+
+* column-parallel linear: rank r keeps output columns [r N/W, (r+1) N/W) of every checkpoint tensor; x is replicated,
+  activation quantization is the same on every rank, there is no collective (outputs stay column-sharded, or are
+  all-gathered on request);
+* row-parallel linear: rank r keeps input rows [r K/W, (r+1) K/W) on group boundaries, computes a full [M, N]
+  partial from its slice of x, and the partials are summed by one all-reduce over NVLink;
+* expert-parallel MoE: expert e lives on rank e // (E / W); picks are dispatched to their experts' ranks by one
+  all-to-all, run through the local grouped expert FFN, returned by a second all-to-all and combined at the source
+  in ascending expert order in f32.
+
+The reference shards differently -- every rank holds a 1/W slice of EVERY expert's intermediate axis and the
+partials are all-reduced (expert_intermediate_slice / slice_routed_experts,
+emmy/compiler/trace/huggingface.py:1071-1124; emmy/serving/vllm_model_gen.py:986-991).  `expert_intermediate_slice`
+below restates that slicing too: its partial sums must equal the expert-parallel result up to f32 summation order,
+which the tests use as a cross-check.
+
+The compute steps are passed in as callables, so the partition and exchange logic runs unchanged on CPU tensors
+with the gloo backend (that is how it is tested without GPUs); on GPUs the callables are the C-ABI operators.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+# ---------------------------------------------------------------------------------------------- slicing
+
+
+def _cols(n: int, rank: int, world: int, unit: int) -> slice:
+    if n % (world * unit):
+        raise ValueError(f"{n} output columns do not split into {world} shards of whole {unit}-column units")
+    w = n // world
+    return slice(rank * w, (rank + 1) * w)
+
+
+def column_slice_w4(fmt: str, qweight, qzeros, scales, g_idx, rank: int, world: int):
+    """Output-column shard of an AWQ / GPTQ linear (checkpoint layouts).  16-column units keep the shard tileable."""
+    n = scales.shape[1]
+    c = _cols(n, rank, world, 16)
+    c8 = slice(c.start // 8, c.stop // 8)
+    qw = qweight[:, c8] if fmt == "awq" else qweight[:, c]
+    return qw.contiguous(), qzeros[:, c8].contiguous(), scales[:, c].contiguous(), g_idx
+
+
+def row_slice_w4(fmt: str, qweight, qzeros, scales, g_idx, group: int, rank: int, world: int):
+    """Input-row shard of an AWQ / GPTQ linear on group boundaries.  With act-order information the shard keeps the
+    scale / zero rows of the groups its rows name, renumbered from zero."""
+    k = scales.shape[0] * group
+    if k % (world * group):
+        raise ValueError(f"{k} input rows do not split into {world} shards of whole groups of {group}")
+    kw = k // world
+    rows = slice(rank * kw, (rank + 1) * kw)
+    qw = qweight[rows] if fmt == "awq" else qweight[rows.start // 8 : rows.stop // 8]
+    if g_idx is None:
+        groups = slice(rows.start // group, rows.stop // group)
+        return qw.contiguous(), qzeros[groups].contiguous(), scales[groups].contiguous(), None, rows
+    local = g_idx[rows]
+    used, renumbered = torch.unique(local, sorted=True, return_inverse=True)
+    if used.numel() * group != kw:
+        raise ValueError("row shard does not hold whole act-order groups")
+    return (qw.contiguous(), qzeros[used.long()].contiguous(), scales[used.long()].contiguous(), renumbered.to(g_idx.dtype), rows)
+
+
+def column_slice_fp8(weight, weight_scale, rank: int, world: int):
+    """Rows of the [N, K] e4m3 weight and of its per-channel scale."""
+    c = _cols(weight.shape[0], rank, world, 16)
+    return weight[c].contiguous(), weight_scale.reshape(-1)[c].contiguous()
+
+
+def column_slice_nvfp4(weight, weight_scale, weight_scale_2, rank: int, world: int):
+    """Rows of the packed [N, K/2] weight and of its [N, K/16] block scales; the global scale is shared."""
+    c = _cols(weight.shape[0], rank, world, 8)
+    return weight[c].contiguous(), weight_scale[c].contiguous(), weight_scale_2
+
+
+def expert_intermediate_slice(name: str, tensor, rank: int, world: int, *, stacked: bool = False):
+    """The reference's tensor-parallel slice of one expert tensor along the intermediate axis
+    (emmy/compiler/trace/huggingface.py:1071-1089): gate and up keep rows, down keeps columns, a concatenated
+    w_gate_up keeps the same rows of each half, an extent-1 scale stays whole."""
+    axis = (1 if name.startswith("w_down") else 0) + int(stacked)
+    halves = 2 if name.startswith("w_gate_up") else 1
+    extent = tensor.shape[axis] // halves
+    if extent == 1:
+        return tensor
+    if extent % world:
+        raise ValueError(f"expert input {name!r} has {extent} intermediate entries on axis {axis}, not divisible by {world} ranks")
+    width = extent // world
+    parts = [tensor.narrow(axis, half * extent + rank * width, width) for half in range(halves)]
+    return torch.cat(parts, dim=axis).contiguous()
+
+
+def expert_owner(expert_ids: torch.Tensor, num_experts: int, world: int) -> torch.Tensor:
+    """Rank that holds each expert: contiguous blocks of E / W experts."""
+    if num_experts % world:
+        raise ValueError(f"{num_experts} experts do not split over {world} ranks")
+    return expert_ids // (num_experts // world)
+
+
+# ---------------------------------------------------------------------------------------------- linears
+
+
+class ColumnParallelLinear:
+    """y_local[M, N/W] = linear_fn(x); `gather=True` all-gathers the column shards into [M, N]."""
+
+    def __init__(self, linear_fn: Callable[[torch.Tensor], torch.Tensor], group=None):
+        self.linear_fn, self.group = linear_fn, group
+
+    def __call__(self, x: torch.Tensor, gather: bool = False) -> torch.Tensor:
+        y = self.linear_fn(x)
+        if not gather:
+            return y
+        world = dist.get_world_size(self.group)
+        parts = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(parts, y.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
+
+
+class RowParallelLinear:
+    """y[M, N] = all_reduce_sum( linear_fn(x[:, rows]) ).  `rows` is this rank's input-feature slice."""
+
+    def __init__(self, linear_fn: Callable[[torch.Tensor], torch.Tensor], rows: slice, group=None, reduce_dtype=torch.float32):
+        self.linear_fn, self.rows, self.group, self.reduce_dtype = linear_fn, rows, group, reduce_dtype
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        partial = self.linear_fn(x[:, self.rows].contiguous())
+        acc = partial.to(self.reduce_dtype)
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.group)
+        return acc.to(partial.dtype)
+
+
+# ---------------------------------------------------------------------------------------------- expert parallel
+
+
+def ep_moe_forward(
+    x: torch.Tensor,
+    ids: torch.Tensor,
+    scores: torch.Tensor,
+    num_experts: int,
+    experts_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+    combine_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+    group=None,
+) -> torch.Tensor:
+    """One routed MoE layer with the experts spread over the ranks of `group`.
+
+    x [T, H]: this rank's tokens; ids int [T, k] / scores f32 [T, k]: their picks, ascending expert id per row.
+    experts_fn(rows [R, H], local_expert_ids int32 [R]) -> [R, H]: the local grouped expert FFN.
+    combine_fn(out_rows [T k, H], scores [T, k]) -> [T, H]: the f32 weighted sum in stored pick order.
+
+    The counts exchange is the one host read of the layer (the reference has one too, emmy/serving/gen_runner.py:283);
+    the token exchange is two all-to-alls of [picks, H] rows."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    t, k = ids.shape
+    per_rank = num_experts // world
+    flat = ids.reshape(-1).long()
+    owner = expert_owner(flat, num_experts, world)
+    order = torch.argsort(owner, stable=True)  # picks grouped by destination rank, token order kept inside
+    send_counts = torch.bincount(owner, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    send_list, recv_list = send_counts.tolist(), recv_counts.tolist()
+
+    send_rows = x[(order // k)].contiguous()
+    send_eid = (flat[order] - owner[order] * per_rank).to(torch.int32).contiguous()
+    recv_rows = x.new_empty((sum(recv_list), x.shape[1]))
+    recv_eid = send_eid.new_empty(sum(recv_list))
+    dist.all_to_all_single(recv_rows, send_rows, recv_list, send_list, group=group)
+    dist.all_to_all_single(recv_eid, send_eid, recv_list, send_list, group=group)
+
+    done = experts_fn(recv_rows, recv_eid) if recv_rows.shape[0] else recv_rows
+    back = x.new_empty((t * k, x.shape[1]))
+    dist.all_to_all_single(back, done.contiguous(), send_list, recv_list, group=group)
+
+    out_rows = torch.empty_like(back)
+    out_rows[order] = back  # undo the grouping by destination
+    del rank
+    return combine_fn(out_rows, scores)
