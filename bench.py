@@ -253,7 +253,7 @@ def run_ours(args, rank, world, local_rank):
             "frac": round(achieved / peak, 4),
             "peak_kind": peak_kind,
             "traffic": TRAFFIC_PER_LAUNCH,
-            "kernel": "w4a16_tile_kernel<__half,1,true>",
+            "kernel": "w4a16_stream_kernel<__half,1,true>",
             "avg_launch_us": round(per_launch_us, 3),
         },
         "clocks": clocks.summary(),

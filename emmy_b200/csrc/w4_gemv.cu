@@ -23,6 +23,8 @@
 
 namespace eq {
 
+int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream);  // w4_stream.cu
+
 template <typename ActT, int MT, bool ONE>
 __global__ void __launch_bounds__(kTileThreads) w4a16_tile_kernel(const W4Params p) {
     __shared__ float red[kTileWarps][MT * 8][16];
@@ -124,7 +126,11 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         p.scale_dtype = scale_dtype;
         p.x_rows = nullptr;
         p.y_rows = nullptr;
-        const int st = act_dtype == EQ_F16 ? launch_w4<__half>(p, stream) : launch_w4<__nv_bfloat16>(p, stream);
+        int st;
+        if (mb <= 16 && static_cast<long long>(N / 16) * (K / 128) < (1LL << 30))
+            st = w4_stream_launch(p, act_dtype, stream);  // decode-shaped: one wave of equal spans
+        else
+            st = act_dtype == EQ_F16 ? launch_w4<__half>(p, stream) : launch_w4<__nv_bfloat16>(p, stream);
         if (st != EQ_OK) return st;
     }
     return EQ_OK;

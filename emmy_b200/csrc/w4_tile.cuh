@@ -22,6 +22,7 @@ struct W4Params {
     int items;                // K / 128
     int splits;               // K splits per tile
     int scale_dtype;
+    int span_base, span_rem;  // stream kernel: items per warp, plus one for the first span_rem warps
     const int32_t* x_rows;    // optional: activation row m of the problem is row x_rows[m] of x (gather)
     const int32_t* y_rows;    // optional: output row m of the problem is row y_rows[m] of y (scatter)
 };
@@ -126,6 +127,60 @@ __device__ __forceinline__ void load_x(const ActT* xrow, const int32_t* perm, in
     }
 }
 
+// One item (128 input rows x 16 columns) of a tile against the rows of x: yacc += s * sum_k x_k (q_k - z).
+// wl / wh: the lane's 16 bytes of the item's two nibble tiles; meta: its scale / zero entry (columns g, g+8).
+template <typename ActT, int MT, bool ONE>
+__device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it, const uint4& wl, const uint4& wh, const uint2& mt_,
+                                        int g, int j, float (&yacc)[MT][4]) {
+    float s_lo, s_hi;
+    if (p.scale_dtype == EQ_F16) {
+        const __half2 s = *reinterpret_cast<const __half2*>(&mt_.x);
+        s_lo = __low2float(s);
+        s_hi = __high2float(s);
+    } else {
+        s_lo = __uint_as_float(mt_.x << 16);
+        s_hi = __uint_as_float(mt_.x & 0xFFFF0000u);
+    }
+    const typename Frag<ActT>::Zero z_lo = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x1010));
+    const typename Frag<ActT>::Zero z_hi = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x3232));
+    const uint32_t words[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
+    uint4 xv[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int m = ONE ? 0 : mt * 8 + g;
+        if (ONE || m < p.M) {
+            const size_t xr = p.x_rows ? static_cast<size_t>(p.x_rows[m]) : static_cast<size_t>(m);
+            load_x<ActT>(x + xr * p.K, p.perm, it * 128 + 32 * j, xv[mt]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[mt][i] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    // even and odd k16 steps accumulate into separate registers: two chains of four MMAs instead of one of eight
+    float acc[2][MT][4];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        uint32_t a[4];
+        Frag<ActT>::expand(words[s], z_lo, z_hi, a);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t* lo = reinterpret_cast<const uint32_t*>(&xv[mt][0]);  // 8 words: steps 0..7, low slots
+            const uint32_t* hi = reinterpret_cast<const uint32_t*>(&xv[mt][2]);  // high slots
+            if (s < 2)
+                Frag<ActT>::mma0(acc[s & 1][mt], a, lo[s], hi[s]);
+            else
+                Frag<ActT>::mma(acc[s & 1][mt], a, lo[s], hi[s]);
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        yacc[mt][0] = fmaf(s_lo, acc[0][mt][0] + acc[1][mt][0], yacc[mt][0]);
+        yacc[mt][1] = fmaf(s_lo, acc[0][mt][1] + acc[1][mt][1], yacc[mt][1]);
+        yacc[mt][2] = fmaf(s_hi, acc[0][mt][2] + acc[1][mt][2], yacc[mt][2]);
+        yacc[mt][3] = fmaf(s_hi, acc[0][mt][3] + acc[1][mt][3], yacc[mt][3]);
+    }
+}
+
 // One output tile (16 columns) x one K split, for a problem (wq, x, y, M).  ONE: a single activation row; every lane
 // then reads row 0, the m = 1..7 columns of the product are copies of column 0 and are never looked at.
 template <typename ActT, int MT, bool ONE>
@@ -171,53 +226,7 @@ __device__ __forceinline__ void w4_tile(const W4Params& p, int tile, int split, 
                     w_hi[d] = ld_stream_v4(rec0 + off + 512);
                     meta[d] = __ldg(reinterpret_cast<const uint2*>(meta0 + off));
                 }
-                // scale and zero point of the two columns g, g+8
-                float s_lo, s_hi;
-                if (p.scale_dtype == EQ_F16) {
-                    const __half2 s = *reinterpret_cast<const __half2*>(&mt_.x);
-                    s_lo = __low2float(s);
-                    s_hi = __high2float(s);
-                } else {
-                    s_lo = __uint_as_float(mt_.x << 16);
-                    s_hi = __uint_as_float(mt_.x & 0xFFFF0000u);
-                }
-                const typename Frag<ActT>::Zero z_lo = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x1010));
-                const typename Frag<ActT>::Zero z_hi = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x3232));
-                const uint32_t words[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
-                uint4 xv[MT][4];
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int m = ONE ? 0 : mt * 8 + g;
-                    if (ONE || m < p.M) {
-                        const size_t xr = p.x_rows ? static_cast<size_t>(p.x_rows[m]) : static_cast<size_t>(m);
-                        load_x<ActT>(x + xr * p.K, p.perm, it * 128 + 32 * j, xv[mt]);
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) xv[mt][i] = make_uint4(0, 0, 0, 0);
-                    }
-                }
-                float acc[MT][4];
-#pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    uint32_t a[4];
-                    Frag<ActT>::expand(words[s], z_lo, z_hi, a);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const uint32_t* lo = reinterpret_cast<const uint32_t*>(&xv[mt][0]);  // 8 words: steps 0..7, low slots
-                        const uint32_t* hi = reinterpret_cast<const uint32_t*>(&xv[mt][2]);  // high slots
-                        if (s == 0)
-                            Frag<ActT>::mma0(acc[mt], a, lo[s], hi[s]);
-                        else
-                            Frag<ActT>::mma(acc[mt], a, lo[s], hi[s]);
-                    }
-                }
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    yacc[mt][0] = fmaf(s_lo, acc[mt][0], yacc[mt][0]);
-                    yacc[mt][1] = fmaf(s_lo, acc[mt][1], yacc[mt][1]);
-                    yacc[mt][2] = fmaf(s_hi, acc[mt][2], yacc[mt][2]);
-                    yacc[mt][3] = fmaf(s_hi, acc[mt][3], yacc[mt][3]);
-                }
+                w4_item<ActT, MT, ONE>(p, x, it, wl, wh, mt_, g, j, yacc);
             }
         }
     }
