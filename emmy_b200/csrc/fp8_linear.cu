@@ -6,9 +6,9 @@
 //   fp8_smallm_kernel       M <= 64 (decode-shaped): a bandwidth kernel.  Weights [N,K] are read as stored, 16 bytes
 //                           per lane, straight into m16n8k32 e4m3 A fragments (no dequant instruction at all);
 //                           eight warps of a CTA split K for one 16-column tile and meet in shared memory.
-//   fp8_gemm_tc_kernel      M > 64 (prefill-shaped): tcgen05.mma kind::f8f6f4, 128x256 output tile per CTA, K-major
-//                           operands brought by TMA with the 128-byte swizzle through a 4-stage mbarrier ring,
-//                           f32 accumulators in TMEM, one producer warp, one MMA warp, four epilogue warps that read
+//   fp8_gemm_tc_kernel      M > 64 (prefill-shaped): tcgen05.mma kind::f8f6f4, 256x256 output tile per CTA, K-major
+//                           operands brought by TMA with the 128-byte swizzle through a 3-stage mbarrier ring,
+//                           f32 accumulators in TMEM, one producer warp, one MMA warp, eight epilogue warps that read
 //                           TMEM with tcgen05.ld, apply both scales and store bf16/f16.
 // Both scales are hoisted out of the contraction, as in the reference's own native FP8 path
 // (tests/compiler/passes/test_fp8_mma.py:111-120).
@@ -132,11 +132,16 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
 }
 
 // ------------------------------------------------------------------------------------------------ prefill-shaped
-constexpr int kBM = 128, kBN = 256, kBK = 128;  // tile; kBK in bytes = e4m3 elements
-constexpr int kStages = 4;
+// A CTA computes a 256 x 256 output tile as two 128-row MMAs that share one B tile in shared memory: per byte
+// brought in from L2 that is 256 flop, against 170 for a 128 x 256 tile, and L2 -> SM bandwidth is what bounds
+// this kernel (a 128 x 256 tile needs ~19 TB/s of it at the tensor peak).  The two f32 accumulators fill TMEM.
+constexpr int kBM = 256, kBN = 256, kBK = 128;  // tile; kBK in bytes = e4m3 elements
+constexpr int kStages = 3;
 constexpr int kTileA = kBM * kBK, kTileB = kBN * kBK;
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kGemmThreads = (2 + kEpilogueWarps) * 32;
 constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;
 
 template <typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -157,6 +162,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
     const int k_blocks = K / kBK;
+    const bool two_halves = M - m0 > 128;  // the second 128 rows hold real rows
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -166,7 +172,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tc::mbar_init(tc::smem_u32(acc_ready), 1);
         tc::mbar_fence_init();
     }
-    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kBN);
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kTmemCols);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -192,12 +198,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     } else if (warp == 1) {
         // ---- MMA issuer
         if (tc::elect_one()) {
-            constexpr uint32_t idesc = tc::instr_desc(0, 0, kBM, kBN);
-            bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+            constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, kBN);
+            for (int kb = 0; kb < k_blocks; ++kb) {
                 const int s = kb % kStages;
-                ok = tc::mbar_wait(tc::smem_u32(full + s), (kb / kStages) & 1);
-                if (!ok) {
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kStages) & 1)) {
                     atomicExch(status, 2);
                     break;
                 }
@@ -206,26 +210,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
                 for (int ks = 0; ks < kBK / 32; ++ks) {
                     // 32 bytes of K per instruction: step the descriptors' start address inside the swizzle atom
-                    const uint64_t da = tc::smem_desc_k_sw128(a_addr + ks * 32), db = tc::smem_desc_k_sw128(b_addr + ks * 32);
-                    tc::mma_f8f6f4(tmem_base, da, db, idesc, kb > 0 || ks > 0);
+                    const uint64_t db = tc::smem_desc_k_sw128(b_addr + ks * 32);
+                    tc::mma_f8f6f4(tmem_base, tc::smem_desc_k_sw128(a_addr + ks * 32), db, idesc, kb > 0 || ks > 0);
+                    if (two_halves)
+                        tc::mma_f8f6f4(tmem_base + kBN, tc::smem_desc_k_sw128(a_addr + 128 * kBK + ks * 32), db, idesc, kb > 0 || ks > 0);
                 }
                 tc::mma_commit(tc::smem_u32(empty + s));  // stage is free once these MMAs have read it
             }
             tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too, so that the epilogue does not sit out its wait
         }
     } else {
-        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31
+        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31; warps 2..5 take rows 0..127, 6..9 rows 128..255
         const int quarter = warp & 3;
-        const int m = m0 + quarter * 32 + lane;
+        const int half = (warp - 2) >> 2;
+        const int m = m0 + half * 128 + quarter * 32 + lane;
         const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
-        if (ok) {
+        if (ok && (half == 0 || two_halves)) {
             const float row_scale = m < M ? sx[m] : 0.f;
 #pragma unroll 1
             for (int c = 0; c < kBN; c += 32) {
                 uint32_t r[32];
-                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
+                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kBN + c, r);
                 tc::tmem_ld_wait();
                 if (m < M) {
                     OutT* dst = y + static_cast<size_t>(m) * N + n0 + c;
@@ -254,7 +261,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     if (warp == 1) {
         tc::fence_after_sync();
-        tc::tmem_dealloc(tmem_base, kBN);
+        tc::tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
