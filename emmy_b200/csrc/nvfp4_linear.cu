@@ -187,12 +187,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 tc::fence_after_sync();
                 const uint32_t a_addr = tc::smem_u32(tiles_a + s * kTileA), b_addr = tc::smem_u32(tiles_b + s * kTileB);
                 const uint32_t sfa_addr = tc::smem_u32(sfs_a + s * kSfA), sfb_addr = tc::smem_u32(sfs_b + s * kSfB);
+                // scale atoms of the stage's four k64 steps -> TMEM: A rows 0..127 (4 columns per step), B rows 0..127
+                // and 128..255 (8 columns per step); all twelve copies are queued before the first MMA
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    // scale atoms of this k64 step -> TMEM: A rows 0..127 (4 columns), B rows 0..127 and 128..255
                     tc::tmem_cp_32x128b_warpx4(tmem_sfa + ks * 4, tc::smem_desc_sf(sfa_addr + ks * 512));
                     tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8, tc::smem_desc_sf(sfb_addr + ks * 512));
                     tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8 + 4, tc::smem_desc_sf(sfb_addr + kSfB / 2 + ks * 512));
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
                     const uint64_t da = tc::smem_desc_k_sw128(a_addr + ks * 32), db = tc::smem_desc_k_sw128(b_addr + ks * 32);
                     tc::mma_mxf4nvf4(tmem_base, da, db, idesc, tmem_sfa + ks * 4, tmem_sfb + ks * 8, kb > 0 || ks > 0);
                 }
@@ -215,10 +219,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 tc::tmem_ld_wait();
                 if (m < M) {
                     OutT* dst = y + static_cast<size_t>(m) * N + n0 + c;
-                    for (int i = 0; i < 32 && n0 + c + i < N; i += 2) {
-                        const OutT o0 = from_float<OutT>(__uint_as_float(r[i]) * g), o1 = from_float<OutT>(__uint_as_float(r[i + 1]) * g);
-                        *reinterpret_cast<uint32_t*>(dst + i) = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
-                                                                (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                    if (n0 + c + 32 <= N) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const OutT o0 = from_float<OutT>(__uint_as_float(r[2 * i]) * g), o1 = from_float<OutT>(__uint_as_float(r[2 * i + 1]) * g);
+                            packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && n0 + c + i < N; ++i) dst[i] = from_float<OutT>(__uint_as_float(r[i]) * g);
                     }
                 }
             }
@@ -307,7 +320,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     EQ_REQUIRE(weight && weight_scale_tiled && weight_scale_2 && x && input_scale && y, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: null pointer");
     EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: activations must be f16 or bf16");
     EQ_REQUIRE(K % 256 == 0 && N % 8 == 0, EQ_ERR_UNSUPPORTED, "eq_nvfp4_linear: needs K %% 256 == 0 and N %% 8 == 0 (K=%lld N=%lld)", (long long)K, (long long)N);
-    EQ_REQUIRE(aligned(weight, 16) && aligned(weight_scale_tiled, 16) && aligned(y, 4), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: weight and scales must be 16-byte aligned");
+    EQ_REQUIRE(aligned(weight, 16) && aligned(weight_scale_tiled, 16) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: weight and scales must be 16-byte aligned");
     EQ_REQUIRE(workspace && workspace_bytes >= eq_nvfp4_workspace_bytes(M, K), EQ_ERR_WORKSPACE, "eq_nvfp4_linear: workspace of %zu bytes needed, %zu given",
                eq_nvfp4_workspace_bytes(M, K), workspace_bytes);
     EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: workspace must be 256-byte aligned");
