@@ -250,8 +250,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         for (int v = 0; v < 4; ++v)
                             reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
                     } else {
-                        for (int i = 0; i < 32 && n0 + c + i < N; ++i)
-                            dst[i] = from_float<OutT>(__uint_as_float(r[i]) * row_scale * sw[n0 + c + i]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c + i < N) dst[i] = from_float<OutT>(__uint_as_float(r[i]) * row_scale * sw[n0 + c + i]);
                     }
                 }
             }

@@ -1,0 +1,434 @@
+// W4A16 linear for prefill-shaped calls (M > 16): y[M,N] = x[M,K] @ W on the tcgen05 tensor cores.
+//
+// The int4 weight never exists as a 16-bit matrix in global memory.  A CTA owns a tile of 128 or 256 activation
+// rows by BN output columns and walks K in steps of 64:
+//   warp 0        TMA producer: the 64-wide slice of the x rows, 128-byte swizzle, into the stage's A tile
+//   warp 1        MMA issuer: tcgen05.mma kind::f16, 128 x BN x 16 per instruction, f32 accumulators in TMEM (one
+//                 accumulator per 128 activation rows; both read the same B tile)
+//   warps 2..     dequant producers, then the epilogue.  A producer warp reads the packed nibbles of one 16-column
+//                 weight tile straight from global memory into registers (one 16-byte load per lane and K step,
+//                 issued kAhead steps early), expands them exactly as the decode kernel does (lop3 to 1024 + q, one
+//                 subtract / fma removes 1024 and the zero point), multiplies by the group scale in the activation
+//                 dtype, which is the value the reference's dequantize-then-matmul path feeds its matmul
+//                 (emmy/compiler/loader/quant.py:402-470), and writes the stage's B tile in the same 128-byte-swizzled
+//                 K-major layout TMA would have produced.  fence.proxy.async makes the writes visible to the tensor
+//                 core; one arrive per warp completes the stage.
+// The repack (w4_repack.cu) deals the 128 input rows of an item to lanes so that a lane's four words of one half-tile
+// hold, for columns g and g + 8, two runs of eight consecutive rows: exactly two 16-byte chunks of a swizzled row per
+// column.  Lanes (g, h, jj) of a warp take the pieces of rows 64 t + 32 jj + 8 h (+16) of K step t of the item, so one
+// K step of the MMA is 64 consecutive input rows and x needs no reordering.  Act-order weights (a row permutation)
+// gather the columns of x into the workspace first.
+#include "tc_common.cuh"
+#include "w4_tile.cuh"
+
+namespace eq {
+
+namespace {
+
+constexpr int kGK = 64;             // K per stage: 128 bytes of 16-bit elements
+constexpr int kRowBytes = 128;
+
+// HALVES: 128-row activation blocks per CTA; BN: output columns per CTA; DW: dequant (and epilogue) warps;
+// AHEAD: items (two K steps each) whose packed bytes are in a warp's registers ahead of use.
+template <int HALVES, int BN, int DW, int AHEAD>
+struct GemmCfg {
+    static constexpr int kDequantWarps = DW;
+    static constexpr int kAhead = AHEAD;
+    static constexpr int kEpiGroups = DW / 4 / HALVES;       // warp quartets per accumulator
+    static constexpr int kEpiCols = BN / kEpiGroups;          // accumulator columns per quartet
+    static constexpr int kTilesPerWarp = BN / 16 / kDequantWarps;
+    static constexpr int kThreads = 64 + 32 * kDequantWarps;
+    static constexpr int kTileA = HALVES * 128 * kRowBytes;
+    static constexpr int kTileB = BN * kRowBytes;
+    static constexpr int kStageBytes = kTileA + kTileB;
+    static constexpr int kStages = (196608 / kStageBytes) < 4 ? (196608 / kStageBytes) : 4;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+    static constexpr uint32_t kTmemCols = HALVES * BN < 32 ? 32 : HALVES * BN;
+    static_assert(kTilesPerWarp >= 1 && kTilesPerWarp * 16 * kDequantWarps == BN, "every dequant warp needs whole weight tiles");
+    static_assert(kEpiGroups >= 1 && kEpiCols % 32 == 0, "the epilogue reads 32 accumulator columns at a time");
+    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns: a power of two up to 512");
+};
+
+#ifdef EQ_W4G_TRACE
+__device__ unsigned long long g_w4g_trace[16];
+#define TR_DECL(n) long long tr_##n = 0
+#define TR_BEGIN(n) const long long tb_##n = clock64()
+#define TR_END(n) tr_##n += clock64() - tb_##n
+#define TR_FLUSH(slot, n) atomicAdd(&g_w4g_trace[slot], static_cast<unsigned long long>(tr_##n))
+#else
+#define TR_DECL(n)
+#define TR_BEGIN(n)
+#define TR_END(n)
+#define TR_FLUSH(slot, n)
+#endif
+
+// 8-byte read-only load that stays where it is written (issued kAhead steps before its use).
+__device__ __forceinline__ uint2 ld_pinned_v2(const void* p) {
+    uint2 r;
+    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <typename ActT>
+struct ScaleMul;
+template <>
+struct ScaleMul<__half> {
+    static constexpr uint32_t kFmt = 0;
+    static __device__ __forceinline__ uint32_t pair(uint16_t raw, int scale_dtype) {
+        uint16_t b = raw;
+        if (scale_dtype != EQ_F16) b = __half_as_ushort(__float2half_rn(__uint_as_float(static_cast<uint32_t>(raw) << 16)));
+        return static_cast<uint32_t>(b) * 0x00010001u;
+    }
+    static __device__ __forceinline__ uint32_t mul(uint32_t v, uint32_t s) {
+        uint32_t r;
+        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(s));
+        return r;
+    }
+};
+template <>
+struct ScaleMul<__nv_bfloat16> {
+    static constexpr uint32_t kFmt = 1;
+    static __device__ __forceinline__ uint32_t pair(uint16_t raw, int scale_dtype) {
+        uint16_t b = raw;
+        if (scale_dtype == EQ_F16) b = __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(__ushort_as_half(raw))));
+        return static_cast<uint32_t>(b) * 0x00010001u;
+    }
+    static __device__ __forceinline__ uint32_t mul(uint32_t v, uint32_t s) {
+        uint32_t r;
+        asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(s));
+        return r;
+    }
+};
+
+// xg[m][k'] = x[m][perm[k']]
+template <typename ActT>
+__global__ void gather_cols_kernel(const ActT* __restrict__ x, const int32_t* __restrict__ perm, int64_t M, int64_t K,
+                                   ActT* __restrict__ xg) {
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= M * K) return;
+    const int64_t m = idx / K, k = idx - m * K;
+    xg[idx] = x[m * K + perm[k]];
+}
+
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD>
+__global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
+    w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const unsigned char* __restrict__ wq, ActT* __restrict__ y,
+                         int M, int N, int K, int scale_dtype, int* __restrict__ status) {
+    using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
+    constexpr int kStages = Cfg::kStages;
+    constexpr int kAhead = Cfg::kAhead;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_a = smem;
+    unsigned char* tiles_b = smem + kStages * Cfg::kTileA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes);
+    uint64_t* full_a = bars;                  // [kStages] TMA -> MMA
+    uint64_t* full_b = bars + kStages;        // [kStages] dequant warps -> MMA
+    uint64_t* empty = bars + 2 * kStages;     // [kStages] MMA -> producers
+    uint64_t* acc_ready = bars + 3 * kStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * HALVES);
+    const int k_blocks = K / kGK;
+    const int items = K / 128;
+    const bool two_halves = HALVES == 2 && M - m0 > 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full_a + s), 1);
+            tc::mbar_init(tc::smem_u32(full_b + s), Cfg::kDequantWarps);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), Cfg::kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer of the activation tiles
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_x);
+            TR_DECL(tma_wait);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                TR_BEGIN(tma_wait);
+                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                TR_END(tma_wait);
+                const uint32_t bar = tc::smem_u32(full_a + s);
+                tc::mbar_expect_tx(bar, Cfg::kTileA);
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * Cfg::kTileA), &map_x, kb * kGK, m0, bar);
+            }
+            TR_FLUSH(0, tma_wait);
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc(ScaleMul<ActT>::kFmt, ScaleMul<ActT>::kFmt, 128, BN);
+            TR_DECL(mma_wa);
+            TR_DECL(mma_wb);
+            TR_DECL(mma_total);
+            TR_BEGIN(mma_total);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t parity = (kb / kStages) & 1;
+                TR_BEGIN(mma_wa);
+                const bool got_a = tc::mbar_wait(tc::smem_u32(full_a + s), parity);
+                TR_END(mma_wa);
+                TR_BEGIN(mma_wb);
+                const bool got_b = got_a && tc::mbar_wait(tc::smem_u32(full_b + s), parity);
+                TR_END(mma_wb);
+                if (!got_b) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles_a + s * Cfg::kTileA), b_addr = tc::smem_u32(tiles_b + s * Cfg::kTileB);
+#pragma unroll
+                for (int ks = 0; ks < kGK / 16; ++ks) {
+                    const uint64_t db = tc::smem_desc_k_sw128(b_addr + ks * 32);
+                    tc::mma_f16(tmem_base, tc::smem_desc_k_sw128(a_addr + ks * 32), db, idesc, kb > 0 || ks > 0);
+                    if (two_halves)
+                        tc::mma_f16(tmem_base + BN, tc::smem_desc_k_sw128(a_addr + 128 * kRowBytes + ks * 32), db, idesc, kb > 0 || ks > 0);
+                }
+                tc::mma_commit(tc::smem_u32(empty + s));
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too: the epilogue must not sit out its wait
+            TR_END(mma_total);
+            TR_FLUSH(1, mma_wa);
+            TR_FLUSH(2, mma_wb);
+            TR_FLUSH(3, mma_total);
+        }
+    } else {
+        // ---- dequant producers
+        const int dw = warp - 2;
+        const int g = lane & 7, h = (lane >> 3) & 1, jj = lane >> 4;
+        // Shared-memory byte offsets of the lane's four 16-byte chunks inside a B tile: row r = 16 tile + g (+8) is an
+        // output column, chunk q = 4 jj + 2 high + h of its 128 bytes is swizzled with r & 7 = g.
+        const uint32_t b_base = tc::smem_u32(tiles_b);
+        const unsigned char* wp[Cfg::kTilesPerWarp];   // the lane's 16 bytes of K step 0 of item 0; K step 1 is 32 bytes on
+        const unsigned char* mp[Cfg::kTilesPerWarp];   // its scale / zero record of item 0
+        uint32_t off_lo[Cfg::kTilesPerWarp];
+        bool live[Cfg::kTilesPerWarp];
+#pragma unroll
+        for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
+            const int tile_in_cta = dw * Cfg::kTilesPerWarp + nt;
+            const int tile = n0 / 16 + tile_in_cta;
+            live[nt] = tile < N / 16;
+            const unsigned char* rec = wq + static_cast<size_t>(live[nt] ? tile : 0) * items * kItemBytes;
+            wp[nt] = rec + h * 512 + (4 * g + jj) * 16;
+            mp[nt] = rec + 1024 + g * 8;
+            off_lo[nt] = static_cast<uint32_t>((tile_in_cta * 16 + g) * kRowBytes + (((4 * jj + h) ^ g) << 4));
+        }
+        // register ring of whole items (two K steps each)
+        uint4 w0[kAhead][Cfg::kTilesPerWarp], w1[kAhead][Cfg::kTilesPerWarp];
+        uint2 meta[kAhead][Cfg::kTilesPerWarp];
+#pragma unroll
+        for (int d = 0; d < kAhead; ++d) {
+            if (d < items) {
+#pragma unroll
+                for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
+                    w0[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes);
+                    w1[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes + 32);
+                    meta[d][nt] = ld_pinned_v2(mp[nt] + static_cast<size_t>(d) * kItemBytes);
+                }
+            }
+        }
+        bool broken = false;
+        int stage = 0, round = 0;
+        TR_DECL(dq_wait);
+        TR_DECL(dq_work);
+        for (int it0 = 0; it0 < items && !broken; it0 += kAhead) {
+#pragma unroll
+            for (int d = 0; d < kAhead; ++d) {
+                const int it = it0 + d;
+                if (it >= items || broken) continue;
+                // the item's constants: exact-dequant zero terms and the scale pair of columns g and g + 8
+                typename Frag<ActT>::Zero z_lo[Cfg::kTilesPerWarp], z_hi[Cfg::kTilesPerWarp];
+                uint32_t s_lo[Cfg::kTilesPerWarp], s_hi[Cfg::kTilesPerWarp];
+#pragma unroll
+                for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
+                    const uint2 mt = meta[d][nt];
+                    z_lo[nt] = Frag<ActT>::zero(__byte_perm(mt.y, 0, 0x1010));
+                    z_hi[nt] = Frag<ActT>::zero(__byte_perm(mt.y, 0, 0x3232));
+                    s_lo[nt] = ScaleMul<ActT>::pair(static_cast<uint16_t>(mt.x & 0xFFFF), scale_dtype);
+                    s_hi[nt] = ScaleMul<ActT>::pair(static_cast<uint16_t>(mt.x >> 16), scale_dtype);
+                }
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (broken) continue;
+                    TR_BEGIN(dq_wait);
+                    if (round > 0 && !tc::mbar_wait(tc::smem_u32(empty + stage), (round - 1) & 1)) {
+                        if (lane == 0) atomicExch(status, 4);
+                        broken = true;
+                        continue;
+                    }
+                    TR_END(dq_wait);
+                    TR_BEGIN(dq_work);
+                    const uint32_t tile_addr = b_base + stage * Cfg::kTileB;
+#pragma unroll
+                    for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
+                        const uint4 w = t == 0 ? w0[d][nt] : w1[d][nt];
+                        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+                        uint32_t a[4][4];
+#pragma unroll
+                        for (int wi = 0; wi < 4; ++wi) Frag<ActT>::expand(wv[wi], z_lo[nt], z_hi[nt], a[wi]);
+                        // a[wi][0]: column g, low run; [2]: column g, high run; [1] / [3]: the same for column g + 8
+                        if (live[nt]) {
+                            const uint32_t addr = tile_addr + off_lo[nt];
+                            st_shared_v4(addr, ScaleMul<ActT>::mul(a[0][0], s_lo[nt]), ScaleMul<ActT>::mul(a[1][0], s_lo[nt]),
+                                         ScaleMul<ActT>::mul(a[2][0], s_lo[nt]), ScaleMul<ActT>::mul(a[3][0], s_lo[nt]));
+                            st_shared_v4(addr ^ 32u, ScaleMul<ActT>::mul(a[0][2], s_lo[nt]), ScaleMul<ActT>::mul(a[1][2], s_lo[nt]),
+                                         ScaleMul<ActT>::mul(a[2][2], s_lo[nt]), ScaleMul<ActT>::mul(a[3][2], s_lo[nt]));
+                            st_shared_v4(addr + 8 * kRowBytes, ScaleMul<ActT>::mul(a[0][1], s_hi[nt]), ScaleMul<ActT>::mul(a[1][1], s_hi[nt]),
+                                         ScaleMul<ActT>::mul(a[2][1], s_hi[nt]), ScaleMul<ActT>::mul(a[3][1], s_hi[nt]));
+                            st_shared_v4((addr ^ 32u) + 8 * kRowBytes, ScaleMul<ActT>::mul(a[0][3], s_hi[nt]), ScaleMul<ActT>::mul(a[1][3], s_hi[nt]),
+                                         ScaleMul<ActT>::mul(a[2][3], s_hi[nt]), ScaleMul<ActT>::mul(a[3][3], s_hi[nt]));
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) tc::mbar_arrive(tc::smem_u32(full_b + stage));
+                    if (++stage == kStages) {
+                        stage = 0;
+                        ++round;
+                    }
+                    TR_END(dq_work);
+                }
+                if (it + kAhead < items) {  // refill this ring slot
+#pragma unroll
+                    for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
+                        const size_t off = static_cast<size_t>(it + kAhead) * kItemBytes;
+                        w0[d][nt] = ld_stream_v4(wp[nt] + off);
+                        w1[d][nt] = ld_stream_v4(wp[nt] + off + 32);
+                        meta[d][nt] = ld_pinned_v2(mp[nt] + off);
+                    }
+                }
+            }
+        }
+        TR_DECL(epi_wait);
+        TR_DECL(epi_work);
+        TR_BEGIN(epi_wait);
+
+        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31
+        const int quarter = warp & 3;
+        const int quartet = dw >> 2;
+        const int half = quartet / Cfg::kEpiGroups;
+        const int c_begin = (quartet % Cfg::kEpiGroups) * Cfg::kEpiCols;
+        const int m = m0 + half * 128 + quarter * 32 + lane;
+        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        TR_END(epi_wait);
+        TR_BEGIN(epi_work);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok && (half == 0 || two_halves)) {
+#pragma unroll 1
+            for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c, r);
+                tc::tmem_ld_wait();
+                if (m < M && n0 + c < N) {
+                    ActT* dst = y + static_cast<size_t>(m) * N + n0 + c;
+                    if (n0 + c + 32 <= N) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const ActT o0 = from_float<ActT>(__uint_as_float(r[2 * i])), o1 = from_float<ActT>(__uint_as_float(r[2 * i + 1]));
+                            packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c + i < N) dst[i] = from_float<ActT>(__uint_as_float(r[i]));
+                    }
+                }
+            }
+        }
+        TR_END(epi_work);
+        if (lane == 0 && dw == 0) {
+            TR_FLUSH(4, dq_wait);
+            TR_FLUSH(5, dq_work);
+            TR_FLUSH(6, epi_wait);
+            TR_FLUSH(7, epi_work);
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD>
+int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y, int64_t M, int64_t N, int64_t K, int* status,
+               cudaStream_t stream) {
+    using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
+    CUtensorMap map_x;
+    const CUtensorMapDataType elem = sizeof(ActT) == 2 && ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * HALVES, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    auto kernel = w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, 128 * HALVES)));
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                                                        scale_dtype, status);
+    EQ_LAUNCH_OK("w4a16_gemm_tc_kernel");
+    return EQ_OK;
+}
+
+template <typename ActT>
+int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, const ActT* x, ActT* y, int64_t M, int64_t N,
+                 int64_t K, ActT* gathered, int* status, cudaStream_t stream) {
+    if (perm) {
+        const int64_t total = M * K;
+        gather_cols_kernel<ActT><<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, stream>>>(x, perm, M, K, gathered);
+        EQ_LAUNCH_OK("gather_cols_kernel");
+        x = gathered;
+    }
+    if (M <= 128) return launch_cfg<ActT, 1, 64, 4, 4>(wq, scale_dtype, x, y, M, N, K, status, stream);
+    if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count()) return launch_cfg<ActT, 2, 256, 16, 2>(wq, scale_dtype, x, y, M, N, K, status, stream);
+    return launch_cfg<ActT, 2, 128, 8, 3>(wq, scale_dtype, x, y, M, N, K, status, stream);
+}
+
+}  // namespace
+
+// gathered: M * K elements of scratch when perm is given.  status: one word, set by a bounded wait that ran out.
+int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
+                      int64_t K, int act_dtype, void* gathered, int* status, cudaStream_t stream) {
+    if (act_dtype == EQ_F16)
+        return launch_typed<__half>(wq, scale_dtype, perm, static_cast<const __half*>(x), static_cast<__half*>(y), M, N, K,
+                                    static_cast<__half*>(gathered), status, stream);
+    return launch_typed<__nv_bfloat16>(wq, scale_dtype, perm, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), M,
+                                       N, K, static_cast<__nv_bfloat16*>(gathered), status, stream);
+}
+
+}  // namespace eq
+
+#ifdef EQ_W4G_TRACE
+extern "C" int eq_debug_w4g_trace(unsigned long long* out, int reset) {
+    if (cudaMemcpyFromSymbol(out, eq::g_w4g_trace, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+    if (reset) {
+        unsigned long long zero[16] = {0};
+        if (cudaMemcpyToSymbol(eq::g_w4g_trace, zero, sizeof(zero)) != cudaSuccess) return -1;
+    }
+    return 0;
+}
+#endif

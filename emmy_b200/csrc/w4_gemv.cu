@@ -24,6 +24,8 @@
 namespace eq {
 
 int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream);  // w4_stream.cu
+int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
+                      int64_t K, int act_dtype, void* gathered, int* status, cudaStream_t stream);  // w4_gemm.cu
 
 template <typename ActT, int MT, bool ONE>
 __global__ void __launch_bounds__(kTileThreads) w4a16_tile_kernel(const W4Params p) {
@@ -78,10 +80,18 @@ static int launch_w4(const W4Params& p, cudaStream_t stream) {
 
 using namespace eq;
 
-extern "C" size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N) {
-    if (M <= 0 || N <= 0) return 0;
-    const int64_t rows = M < 64 ? M : 64;  // larger M runs in 64-row blocks that reuse the scratch
+// Front part: f32 partial sums of up to 64 rows, one arrival counter per 16-column tile, one status word.  Calls with
+// M > 16 add room for the column-gathered copy of x that act-order weights need on the tensor path.
+static size_t w4_front_bytes(int64_t M, int64_t N) {
+    const int64_t rows = M < 64 ? M : 64;
     return static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16 + 1) * sizeof(int);
+}
+static size_t w4_gather_offset(int64_t M, int64_t N) { return (w4_front_bytes(M, N) + 255) / 256 * 256; }
+
+extern "C" size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if (M <= 16) return w4_front_bytes(M, N);
+    return w4_gather_offset(M, N) + static_cast<size_t>(M) * K * 2;
 }
 
 extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
@@ -103,9 +113,18 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     if (M == 0) return EQ_OK;
     EQ_REQUIRE(aligned(wq, 16) && aligned(x, 16) && aligned(y, 2), EQ_ERR_BAD_ALIGN,
                "eq_w4a16_linear: wq and x need 16-byte alignment");
-    EQ_REQUIRE(workspace && workspace_bytes >= eq_w4a16_workspace_bytes(M, N), EQ_ERR_WORKSPACE,
-               "eq_w4a16_linear: workspace of %zu bytes needed, %zu given", eq_w4a16_workspace_bytes(M, N), workspace_bytes);
+    EQ_REQUIRE(workspace && workspace_bytes >= eq_w4a16_workspace_bytes(M, N, K), EQ_ERR_WORKSPACE,
+               "eq_w4a16_linear: workspace of %zu bytes needed, %zu given", eq_w4a16_workspace_bytes(M, N, K), workspace_bytes);
     EQ_REQUIRE(aligned(workspace, 16), EQ_ERR_BAD_ALIGN, "eq_w4a16_linear: workspace must be 16-byte aligned");
+
+    if (M > 16 && aligned(y, 16)) {
+        // prefill-shaped: the tcgen05 kernel; its bounded waits report through the workspace's status word
+        const int64_t ws_rows = M < 64 ? M : 64;
+        int* status = reinterpret_cast<int*>(static_cast<float*>(workspace) + ws_rows * N) + N / 16;
+        void* gathered = static_cast<unsigned char*>(workspace) + w4_gather_offset(M, N);
+        return w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
+                                 stream);
+    }
 
     const size_t esz = 2;
     for (int64_t m0 = 0; m0 < M; m0 += 64) {
@@ -136,8 +155,8 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     return EQ_OK;
 }
 
-// The kernel has no device-side wait; the status word of the workspace is kept for the boundary's sake and is
-// always clear.
+// The decode kernels have no device-side wait; the tensor-path kernel sets the status word when one of its bounded
+// pipeline waits ran out.
 extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     EQ_REQUIRE(workspace && M > 0 && N > 0, EQ_ERR_BAD_ARG, "eq_w4a16_status: bad arguments");
@@ -192,7 +211,7 @@ extern "C" int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const in
     void* scratch = nullptr;
     int st = noalloc_scratch(&scratch);
     if (st != EQ_OK) return st;
-    const size_t used = eq_w4a16_workspace_bytes(M, N);
+    const size_t used = eq_w4a16_workspace_bytes(M, N, K);
     // all calls share the one array: whatever an earlier (possibly failed) call left there is cleared first
     EQ_CUDA_OK(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream_)));
     return eq_w4a16_linear(wq, scale_dtype, perm, K, N, G, x, M, act_dtype, y, scratch, used, stream_);

@@ -121,9 +121,9 @@ def w4_unpack_repacked(w: W4Weight) -> torch.Tensor:
 _workspaces: dict = {}
 
 
-def w4a16_workspace(m: int, n: int, device) -> torch.Tensor:
+def w4a16_workspace(m: int, n: int, device, k: int = 1) -> torch.Tensor:
     """A zeroed scratch buffer per (device, stream); grown on demand, reused by calls on that stream."""
-    need = L.load().eq_w4a16_workspace_bytes(m, n)
+    need = L.load().eq_w4a16_workspace_bytes(m, n, k)
     key = (device.index if device.index is not None else torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < need:
@@ -139,7 +139,7 @@ def w4a16_linear(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = 
     if k != w.k:
         raise ValueError(f"x has {k} features, the weight takes {w.k}")
     y = out if out is not None else torch.empty((m, w.n), dtype=x.dtype, device=x.device)
-    ws = workspace if workspace is not None else w4a16_workspace(m, w.n, x.device)
+    ws = workspace if workspace is not None else w4a16_workspace(m, w.n, x.device, w.k)
     L.check(
         L.load().eq_w4a16_linear(
             _ptr(w.wq), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, w.n, w.group, _ptr(x), m, _DTYPE[x.dtype],

@@ -105,19 +105,22 @@ int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, vo
 
 /* ------------------------------------------------------------------ W4A16 linear */
 
-/* Scratch for eq_w4a16_linear: f32 partial sums and per-tile arrival counters.  The buffer must be zero the
- * first time it is used; every call leaves it zero again, so it can be reused by calls on one stream. */
-size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N);
+/* Scratch for eq_w4a16_linear: f32 partial sums, per-tile arrival counters and a status word, plus, for M > 16,
+ * room for a column-gathered copy of x (used when the weight carries a row permutation).  The buffer must be zero
+ * the first time it is used; every call leaves its counters and sums zero again, so it can be reused by calls on one
+ * stream. */
+size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /* y[M, N] = x[M, K] @ W on repacked weights; x and y are act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * The operator the reference spells as int4 decode algebra in front of a LinearOp
  * (emmy/compiler/loader/quant.py:1235-1435) and evaluates eagerly as dequantize + F.linear
  * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it.
- * Needs K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1); x and wq 16-byte aligned. */
+ * Needs K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1); x and wq 16-byte aligned.
+ * M <= 16 runs the bandwidth kernels; M > 16 runs the tcgen05 kernel, which dequantises into shared memory. */
 int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                     const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
                     void* stream);
-/* The kernel's only device-side waits are on its own weight copies and are bounded; one that runs out sets a status
- * word in the workspace and the affected outputs are left unwritten.  This call synchronizes the stream, reads the
+/* The only device-side waits are the tensor-path kernel's pipeline barriers and they are bounded; one that runs out
+ * sets a status word in the workspace and the affected outputs are undefined.  This call synchronizes the stream, reads the
  * word and returns EQ_ERR_TIMEOUT if it is set (the reference's counterpart is the host-side hung-launch deadline,
  * crates/emmy-runtime/src/cuda.rs:1401-1451).  M and N as given to eq_w4a16_linear. */
 int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);

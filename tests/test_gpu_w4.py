@@ -274,3 +274,48 @@ def test_linearity_at_full_size():
     y12 = ops.w4a16_linear((x1.float() * 0.5 + x2.float()).half(), w).float()
     ref = 0.5 * y1 + y2
     assert float((y12 - ref).abs().max()) <= TOL * float(ref.abs().max())
+
+
+# ---------------------------------------------------------------------------------------------- tensor path (M > 16)
+@pytest.mark.parametrize("m,n,k", [(200, 272, 768), (300, 1040, 256), (2560, 4096, 256), (2700, 4112, 128)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_prefill_tiles_and_tails(m, n, k, dtype):
+    """Row counts and widths that leave ragged tiles in each of the tensor-path tilings."""
+    from emmy_b200 import ops
+
+    qw, qz, sc = synth.awq_linear(k, n, seed=m)
+    x = synth.activations(m, k, dtype, seed=n)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "awq")
+    ws = ops.w4a16_workspace(m, n, torch.device("cuda"), k)
+    y = ops.w4a16_linear(act(x, dtype), w, workspace=ws)
+    ops.w4a16_status(ws, m, n)
+    check_close(y, ol.w4a16_linear(x, qw, qz, sc, 128, "awq", dtype))
+
+
+def test_prefill_scattered_act_order():
+    from emmy_b200 import ops
+
+    k, n, g = 1024, 256, 128
+    qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=8)
+    gi = np.random.default_rng(3).permutation(np.arange(k) // g).astype(np.int32)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))
+    for m in (40, 333):
+        x = synth.activations(m, k, "bf16", seed=m)
+        y = ops.w4a16_linear(act(x, "bf16"), w)
+        check_close(y, ol.w4a16_linear(x, qw, qz, sc, g, "gptq", "bf16", gi))
+
+
+@pytest.mark.parametrize("m", [64, 256, 4096])
+def test_prefill_matches_dequantised_matmul_at_full_size(m):
+    """Llama-3.1-8B gate/up shape: the tensor path against an f32 matmul on the bit-exact dequantised weight."""
+    from emmy_b200 import ops
+
+    k, n = 4096, 14336
+    qw, qz, sc, gi = synth.gptq_linear(k, n, seed=0)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi))
+    wd = ops.dequant_w4(dev(qw), dev(qz), dev(sc), 128, "gptq", out_dtype=torch.float16, g_idx=dev(gi))  # [K, N]
+    x = act(synth.activations(m, k, "f16", seed=m), "f16")
+    y = ops.w4a16_linear(x, w)
+    ref = x.float() @ wd.float()
+    err = float((y.float() - ref).abs().max())
+    assert err <= 4e-3 * float(ref.abs().max())
