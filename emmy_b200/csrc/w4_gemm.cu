@@ -80,10 +80,11 @@ struct ScaleMul;
 template <>
 struct ScaleMul<__half> {
     static constexpr uint32_t kFmt = 0;
-    static __device__ __forceinline__ uint32_t pair(uint16_t raw, int scale_dtype) {
-        uint16_t b = raw;
-        if (scale_dtype != EQ_F16) b = __half_as_ushort(__float2half_rn(__uint_as_float(static_cast<uint32_t>(raw) << 16)));
-        return static_cast<uint32_t>(b) * 0x00010001u;
+    // raw scale bits -> the same value twice in the activation dtype; CVT: the scales are stored in the other 16-bit type
+    template <bool CVT>
+    static __device__ __forceinline__ uint32_t pair(uint32_t raw) {
+        if constexpr (CVT) raw = __half_as_ushort(__float2half_rn(__uint_as_float(raw << 16)));
+        return __byte_perm(raw, 0, 0x1010);
     }
     static __device__ __forceinline__ uint32_t mul(uint32_t v, uint32_t s) {
         uint32_t r;
@@ -94,10 +95,10 @@ struct ScaleMul<__half> {
 template <>
 struct ScaleMul<__nv_bfloat16> {
     static constexpr uint32_t kFmt = 1;
-    static __device__ __forceinline__ uint32_t pair(uint16_t raw, int scale_dtype) {
-        uint16_t b = raw;
-        if (scale_dtype == EQ_F16) b = __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(__ushort_as_half(raw))));
-        return static_cast<uint32_t>(b) * 0x00010001u;
+    template <bool CVT>
+    static __device__ __forceinline__ uint32_t pair(uint32_t raw) {
+        if constexpr (CVT) raw = __bfloat16_as_ushort(__float2bfloat16_rn(__half2float(__ushort_as_half(static_cast<unsigned short>(raw)))));
+        return __byte_perm(raw, 0, 0x1010);
     }
     static __device__ __forceinline__ uint32_t mul(uint32_t v, uint32_t s) {
         uint32_t r;
@@ -116,10 +117,10 @@ __global__ void gather_cols_kernel(const ActT* __restrict__ x, const int32_t* __
     xg[idx] = x[m * K + perm[k]];
 }
 
-template <typename ActT, int HALVES, int BN, int DW, int AHEAD>
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD, bool CVT>
 __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const unsigned char* __restrict__ wq, ActT* __restrict__ y,
-                         int M, int N, int K, int scale_dtype, int* __restrict__ status) {
+                         int M, int N, int K, int* __restrict__ status) {
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAhead = Cfg::kAhead;
@@ -154,23 +155,33 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // shared-window addresses, computed once: barrier s of a ring sits 8 s bytes on
+    const uint32_t full_a_addr = tc::smem_u32(full_a), full_b_addr = tc::smem_u32(full_b), empty_addr = tc::smem_u32(empty);
+    const uint32_t a_base = tc::smem_u32(tiles_a), b_base = tc::smem_u32(tiles_b);
 
     if (warp == 0) {
         // ---- TMA producer of the activation tiles
         if (tc::elect_one()) {
             tc::tma_prefetch_desc(&map_x);
             TR_DECL(tma_wait);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool first = true;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % kStages;
                 TR_BEGIN(tma_wait);
-                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                if (!first && !tc::mbar_wait(empty_addr + 8 * stage, phase ^ 1)) {
                     atomicExch(status, 1);
                     break;
                 }
                 TR_END(tma_wait);
-                const uint32_t bar = tc::smem_u32(full_a + s);
+                const uint32_t bar = full_a_addr + 8 * stage;
                 tc::mbar_expect_tx(bar, Cfg::kTileA);
-                tc::tma_load_2d(tc::smem_u32(tiles_a + s * Cfg::kTileA), &map_x, kb * kGK, m0, bar);
+                tc::tma_load_2d(a_base + stage * Cfg::kTileA, &map_x, kb * kGK, m0, bar);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                    first = false;
+                }
             }
             TR_FLUSH(0, tma_wait);
         }
@@ -182,21 +193,21 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
             TR_DECL(mma_wb);
             TR_DECL(mma_total);
             TR_BEGIN(mma_total);
+            int stage = 0;
+            uint32_t phase = 0;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % kStages;
-                const uint32_t parity = (kb / kStages) & 1;
                 TR_BEGIN(mma_wa);
-                const bool got_a = tc::mbar_wait(tc::smem_u32(full_a + s), parity);
+                const bool got_a = tc::mbar_wait(full_a_addr + 8 * stage, phase);
                 TR_END(mma_wa);
                 TR_BEGIN(mma_wb);
-                const bool got_b = got_a && tc::mbar_wait(tc::smem_u32(full_b + s), parity);
+                const bool got_b = got_a && tc::mbar_wait(full_b_addr + 8 * stage, phase);
                 TR_END(mma_wb);
                 if (!got_b) {
                     atomicExch(status, 2);
                     break;
                 }
                 tc::fence_after_sync();
-                const uint32_t a_addr = tc::smem_u32(tiles_a + s * Cfg::kTileA), b_addr = tc::smem_u32(tiles_b + s * Cfg::kTileB);
+                const uint32_t a_addr = a_base + stage * Cfg::kTileA, b_addr = b_base + stage * Cfg::kTileB;
 #pragma unroll
                 for (int ks = 0; ks < kGK / 16; ++ks) {
                     const uint64_t db = tc::smem_desc_k_sw128(b_addr + ks * 32);
@@ -204,7 +215,11 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     if (two_halves)
                         tc::mma_f16(tmem_base + BN, tc::smem_desc_k_sw128(a_addr + 128 * kRowBytes + ks * 32), db, idesc, kb > 0 || ks > 0);
                 }
-                tc::mma_commit(tc::smem_u32(empty + s));
+                tc::mma_commit(empty_addr + 8 * stage);
+                if (++stage == kStages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
             }
             tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too: the epilogue must not sit out its wait
             TR_END(mma_total);
@@ -218,7 +233,6 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         const int g = lane & 7, h = (lane >> 3) & 1, jj = lane >> 4;
         // Shared-memory byte offsets of the lane's four 16-byte chunks inside a B tile: row r = 16 tile + g (+8) is an
         // output column, chunk q = 4 jj + 2 high + h of its 128 bytes is swizzled with r & 7 = g.
-        const uint32_t b_base = tc::smem_u32(tiles_b);
         const unsigned char* wp[Cfg::kTilesPerWarp];   // the lane's 16 bytes of K step 0 of item 0; K step 1 is 32 bytes on
         const unsigned char* mp[Cfg::kTilesPerWarp];   // its scale / zero record of item 0
         uint32_t off_lo[Cfg::kTilesPerWarp];
@@ -247,16 +261,20 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 }
             }
         }
-        bool broken = false;
-        int stage = 0, round = 0;
+        bool broken = false, first = true;
+        int stage = 0;
+        uint32_t phase = 0;
         TR_DECL(dq_wait);
         TR_DECL(dq_work);
+        TR_DECL(dq_const);
+        TR_DECL(dq_refill);
         for (int it0 = 0; it0 < items && !broken; it0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
                 const int it = it0 + d;
                 if (it >= items || broken) continue;
                 // the item's constants: exact-dequant zero terms and the scale pair of columns g and g + 8
+                TR_BEGIN(dq_const);
                 typename Frag<ActT>::Zero z_lo[Cfg::kTilesPerWarp], z_hi[Cfg::kTilesPerWarp];
                 uint32_t s_lo[Cfg::kTilesPerWarp], s_hi[Cfg::kTilesPerWarp];
 #pragma unroll
@@ -264,14 +282,18 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     const uint2 mt = meta[d][nt];
                     z_lo[nt] = Frag<ActT>::zero(__byte_perm(mt.y, 0, 0x1010));
                     z_hi[nt] = Frag<ActT>::zero(__byte_perm(mt.y, 0, 0x3232));
-                    s_lo[nt] = ScaleMul<ActT>::pair(static_cast<uint16_t>(mt.x & 0xFFFF), scale_dtype);
-                    s_hi[nt] = ScaleMul<ActT>::pair(static_cast<uint16_t>(mt.x >> 16), scale_dtype);
+                    s_lo[nt] = ScaleMul<ActT>::template pair<CVT>(mt.x & 0xFFFFu);
+                    s_hi[nt] = ScaleMul<ActT>::template pair<CVT>(mt.x >> 16);
                 }
+#ifdef EQ_W4G_TRACE
+                asm volatile("" ::"r"(s_hi[0]), "r"(z_hi[0].sub) : "memory");
+#endif
+                TR_END(dq_const);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (broken) continue;
                     TR_BEGIN(dq_wait);
-                    if (round > 0 && !tc::mbar_wait(tc::smem_u32(empty + stage), (round - 1) & 1)) {
+                    if (!first && !tc::mbar_wait(empty_addr + 8 * stage, phase ^ 1)) {
                         if (lane == 0) atomicExch(status, 4);
                         broken = true;
                         continue;
@@ -301,13 +323,15 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) tc::mbar_arrive(tc::smem_u32(full_b + stage));
+                    if (lane == 0) tc::mbar_arrive(full_b_addr + 8 * stage);
                     if (++stage == kStages) {
                         stage = 0;
-                        ++round;
+                        phase ^= 1;
+                        first = false;
                     }
                     TR_END(dq_work);
                 }
+                TR_BEGIN(dq_refill);
                 if (it + kAhead < items) {  // refill this ring slot
 #pragma unroll
                     for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
@@ -317,6 +341,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         meta[d][nt] = ld_pinned_v2(mp[nt] + off);
                     }
                 }
+                TR_END(dq_refill);
             }
         }
         TR_DECL(epi_wait);
@@ -367,6 +392,8 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
             TR_FLUSH(5, dq_work);
             TR_FLUSH(6, epi_wait);
             TR_FLUSH(7, epi_work);
+            TR_FLUSH(8, dq_const);
+            TR_FLUSH(9, dq_refill);
         }
     }
     tc::fence_before_sync();
@@ -385,11 +412,11 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
     const CUtensorMapDataType elem = sizeof(ActT) == 2 && ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * HALVES, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    auto kernel = w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD>;
+    const bool cvt = scale_dtype != (ScaleMul<ActT>::kFmt == 0 ? EQ_F16 : EQ_BF16);
+    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
     dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, 128 * HALVES)));
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
-                                                        scale_dtype, status);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
     EQ_LAUNCH_OK("w4a16_gemm_tc_kernel");
     return EQ_OK;
 }
