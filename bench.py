@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME [--m ROWS]]
 
 Default workload (`gptq_llama8b_mlp_m1`): the W4A16 M=1 GEMV on GPTQ act-order weights with the
 Llama-3.1-8B MLP shapes (gate/up K=4096 N=14336, down K=14336 N=4096, group 128) -- one step is one pass
@@ -50,6 +50,15 @@ def peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def tensor_peaks():
+    """(burst, sustained) dense bf16 TFLOP/s; FP8 runs at twice and NVFP4 at four times these."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -266,6 +275,290 @@ def run_ours(args, rank, world, local_rank):
 TRAFFIC_PER_LAUNCH = None
 
 
+# --------------------------------------------------------------------------------------------- other workloads
+#
+# The same contract for the other calls of the path; `--workload NAME [--m ROWS]`.  One step = `copies` calls on distinct
+# weight copies (so that weights come from HBM, not L2), captured in one CUDA graph where the call has no host read.
+
+GEMM_K, GEMM_N = 5120, 17408
+
+
+def _wl_fp8(device, rank, m):
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(100 + rank)
+    copies = 2
+    ws = []
+    for _ in range(copies):
+        w = (torch.randn(GEMM_N, GEMM_K, device=device, generator=gen) * 0.02)
+        s = w.abs().amax(dim=1).clamp_min(1e-12) / 448.0
+        ws.append(((w / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s.float().contiguous()))
+    x_host = torch.randn(m, GEMM_K, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, GEMM_N, dtype=torch.bfloat16, device=device)
+    wsp = ops.fp8_workspace(m, GEMM_K, device)
+
+    def step():
+        for w, s in ws:
+            ops.fp8_linear(x, w, s, workspace=wsp, out=y)
+
+    return dict(
+        step=step, flops=2.0 * m * GEMM_K * GEMM_N * copies, calls=copies, kernels_per_call=2, x=x, x_host=x_host, y=y, graph=True,
+        metric="fp8_w8a8_gemm_tflops", dtype="e4m3 weights and activations, f32 accumulate, bf16 out", peak_mult=2.0,
+        kernel="fp8_gemm_tc_kernel<__nv_bfloat16>" if m > 64 else "fp8_smallm_kernel",
+        status=lambda: ops.fp8_status(wsp, m, GEMM_K),
+        workload=f"fp8_gemm: FP8-E4M3 W8A8, per-channel weight scale, dynamic per-token activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}, bf16 out",
+        alg_bytes=GEMM_N * GEMM_K + GEMM_N * 4 + m * GEMM_K * 2 + m * GEMM_N * 2,
+    )
+
+
+def _wl_nvfp4(device, rank, m):
+    from emmy_b200 import ops_nvfp4 as o4
+
+    gen = torch.Generator(device=device).manual_seed(200 + rank)
+    copies = 3
+    ws = []
+    for _ in range(copies):
+        w = torch.randint(0, 256, (GEMM_N, GEMM_K // 2), dtype=torch.uint8, device=device, generator=gen)
+        sf = torch.randint(0x28, 0x40, (GEMM_N, GEMM_K // 16), dtype=torch.uint8, device=device, generator=gen)
+        ws.append((w, o4.nvfp4_tile_scales(sf, GEMM_K), torch.tensor([2.0e-5], device=device)))
+    x_host = torch.randn(m, GEMM_K, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
+    x = x_host.to(device)
+    s2 = o4.nvfp4_global_scale(x)
+    y = torch.empty(m, GEMM_N, dtype=torch.bfloat16, device=device)
+    wsp = o4.nvfp4_workspace(m, GEMM_K, device)
+
+    def step():
+        for w, sf, g in ws:
+            o4.nvfp4_linear(x, w, sf, g, s2, workspace=wsp, out=y)
+
+    return dict(
+        step=step, flops=2.0 * m * GEMM_K * GEMM_N * copies, calls=copies, kernels_per_call=2, x=x, x_host=x_host, y=y, graph=True,
+        metric="nvfp4_gemm_tflops", dtype="e2m1 weights and activations with e4m3 block scales, f32 accumulate, bf16 out", peak_mult=4.0,
+        kernel="nvfp4_gemm_tc_kernel<__nv_bfloat16>", status=lambda: o4.nvfp4_status(wsp, m, GEMM_K),
+        workload=f"nvfp4_gemm: NVFP4 block-scaled W4A4 (codes uniform, block scales uniform 0x28..0x3F: synthetic codes stand in for quantized N(0,0.02) weights), static activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}, bf16 out",
+        alg_bytes=GEMM_N * GEMM_K // 2 + GEMM_N * GEMM_K // 16 + 4 + m * GEMM_K * 2 + m * GEMM_N * 2,
+    )
+
+
+def _wl_w4_prefill(device, rank, m):
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(300 + rank)
+    k, n = SHAPES["gate"]
+    copies = 4
+    ws = []
+    for _ in range(copies):
+        qweight = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, device=device, generator=gen)
+        qzeros = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32, device=device)
+        scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+        perm = torch.randperm(k // GROUP, device=device, generator=gen)
+        g_idx = perm[torch.arange(k, device=device) // GROUP].int()
+        ws.append(ops.w4_repack(qweight, qzeros, scales, GROUP, "gptq", g_idx=g_idx))
+    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).half().pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, n, dtype=torch.float16, device=device)
+    wsp = torch.zeros(ops.L.load().eq_w4a16_workspace_bytes(m, n, k) + 256, dtype=torch.uint8, device=device)
+
+    def step():
+        for w in ws:
+            ops.w4a16_linear(x, w, workspace=wsp, out=y)
+
+    return dict(
+        step=step, flops=2.0 * m * k * n * copies, calls=copies, kernels_per_call=1, x=x, x_host=x_host, y=y, graph=True,
+        metric="w4a16_gemm_tflops", dtype="int4 weights dequantised to f16 in shared memory, f16 activations, f32 accumulate", peak_mult=1.0,
+        kernel="w4a16_gemm_tc_kernel<__half>", status=lambda: ops.w4a16_status(wsp, m, n),
+        workload=f"w4a16_prefill: GPTQ-Int4 act-order W4A16, Llama-3.1-8B gate/up shape K={k} N={n} group 128, M={m}",
+        alg_bytes=algorithmic_bytes(k, n, m),
+    )
+
+
+def _wl_moe(device, rank, world, t):
+    """Qwen3-30B-A3B expert shapes; with N > 1 ranks the experts are sharded E/N per rank and tokens travel by all-to-all."""
+    from emmy_b200 import ops_moe as om
+    from emmy_b200 import shard
+
+    e, topk, hidden, inter = 128, 8, 2048, 768
+    local_e = e // world
+    gen = torch.Generator(device=device).manual_seed(400 + rank)
+
+    def stack(k, n):
+        qw = torch.randint(-(2**31), 2**31 - 1, (local_e, k, n // 8), dtype=torch.int32, device=device, generator=gen)
+        qz = torch.randint(-(2**31), 2**31 - 1, (local_e, k // GROUP, n // 8), dtype=torch.int32, device=device, generator=gen)
+        sc = (torch.rand((local_e, k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+        return qw, qz, sc
+
+    w = om.moe_repack(stack(hidden, 2 * inter), stack(inter, hidden))
+    hg = torch.Generator().manual_seed(rank)
+    x_host = torch.randn(t, hidden, generator=hg).bfloat16().pin_memory()
+    logits = torch.randn(t, e, generator=hg).to(device)
+    x = x_host.to(device)
+    y = torch.empty(t, hidden, dtype=torch.bfloat16, device=device)
+    if world == 1:
+        wsp = om.moe_workspace(t, w, topk, device)
+
+        def step():
+            om.moe_forward(x, logits, w, topk, workspace=wsp, out=y)
+
+        status = lambda: om.moe_status(wsp, t, w, topk)
+    else:
+        def step():
+            ids, scores = om.moe_route(logits, topk)
+            out = shard.ep_moe_forward(x, ids, scores, e, lambda rows, eid: om.moe_experts(rows, eid, w),
+                                       lambda rows, sc: om.moe_combine(rows, sc, topk))
+            y.copy_(out)
+
+        status = lambda: None
+    return dict(
+        step=step, flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), calls=1, kernels_per_call=8, x=x, x_host=x_host,
+        y=y, graph=world == 1, metric="moe_w4a16_tflops", dtype="int4 expert weights, bf16 activations, f32 accumulate and combine",
+        peak_mult=1.0, kernel="moe_expert_gemm_kernel", status=status,
+        workload=f"moe: routed W4A16 expert layer, Qwen3-30B-A3B shapes (128 experts, top-8, hidden 2048, intermediate 768, AWQ group 128), T={t} tokens per rank"
+        + (f", experts sharded {local_e} per rank, all-to-all dispatch and return over NCCL" if world > 1 else ""),
+        alg_bytes=None,
+    )
+
+
+def cpu_sample(name, m):
+    """The oracle port on a bounded sample of the workload's rows; (units, seconds, description)."""
+    from oracle import linear as ol
+    from oracle import moe as omoe
+    from oracle import synth
+
+    if name == "fp8_gemm":
+        rows = min(m, 16)
+        wb, wsc = synth.fp8_weight(GEMM_N, GEMM_K, seed=0)
+        x = synth.activations(rows, GEMM_K, "bf16")
+        t0 = time.perf_counter()
+        ol.fp8_linear(x, wb, wsc)
+        return 2.0 * rows * GEMM_K * GEMM_N, time.perf_counter() - t0, f"{rows} of {m} rows: numpy dequantize, per-token round trip, f32 matmul"
+    if name == "nvfp4_gemm":
+        rows = min(m, 16)
+        packed, sb, s2 = synth.nvfp4_weight(2048, GEMM_K, seed=0)
+        x = synth.activations(rows, GEMM_K, "bf16")
+        from oracle import activations as oa
+
+        t0 = time.perf_counter()
+        ol.nvfp4_linear(x, packed, sb, s2, oa.nvfp4_global_scale(x))
+        return 2.0 * rows * GEMM_K * 2048, time.perf_counter() - t0, f"{rows} of {m} rows, 2048 of {GEMM_N} output channels: numpy dequantize, static activation round trip, f32 matmul"
+    if name == "w4a16_prefill":
+        rows = min(m, 16)
+        k, n = SHAPES["gate"]
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=0)
+        x = synth.activations(rows, k, "f16")
+        t0 = time.perf_counter()
+        ol.w4a16_linear(x, qw, qz, sc, GROUP, "gptq", "f16", gi)
+        return 2.0 * rows * k * n, time.perf_counter() - t0, f"{rows} of {m} rows: numpy dequantize (g_idx gather) + f32 matmul"
+    # moe: one token's eight experts, dense dequantised
+    hidden, inter = 2048, 768
+    gu = [synth.awq_linear(hidden, 2 * inter, seed=2 * i) for i in range(8)]
+    dn = [synth.awq_linear(inter, hidden, seed=2 * i + 1) for i in range(8)]
+    ex = {"gate_up": tuple(np.stack([p[j] for p in gu]) for j in range(3)), "down": tuple(np.stack([p[j] for p in dn]) for j in range(3))}
+    x = torch.from_numpy(synth.activations(1, hidden, "bf16")).bfloat16()
+    logits = torch.randn(1, 8, generator=torch.Generator().manual_seed(0))
+    t0 = time.perf_counter()
+    wgu, wdn = omoe.dequant_expert_weights(ex, torch.bfloat16)
+    omoe.moe_layer(x, logits, wgu, wdn, 8)
+    return 8 * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), time.perf_counter() - t0, "1 token, its 8 experts: numpy dequantize + bf16 torch CPU expert FFN + f32 combine"
+
+
+def run_other(args, rank, world, local_rank):
+    from emmy_b200.build import build
+
+    if not (ROOT / "emmy_b200" / "libemmyq.so").exists():
+        build()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    name = args.workload
+    default_m = {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
+    m = args.m or default_m
+    wl = _wl_moe(device, rank, world, m) if name == "moe" else {"fp8_gemm": _wl_fp8, "nvfp4_gemm": _wl_nvfp4, "w4a16_prefill": _wl_w4_prefill}[name](device, rank, m)
+    step = wl["step"]
+    stream = torch.cuda.Stream(device)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        wl["status"]()
+        run = step
+        if wl["graph"]:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            graph.replay()
+            stream.synchronize()
+            run = graph.replay
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            start.record(stream)
+            for _ in range(args.steps):
+                run()
+            end.record(stream)
+            end.synchronize()
+            dev_ms = start.elapsed_time(end)
+            if dev_ms < 400:
+                t_end = time.time() + 0.4
+                while time.time() < t_end:
+                    run()
+                stream.synchronize()
+        barrier()
+        # end to end: the step's activations come from pinned host memory, its result goes back
+        y_host = torch.empty(wl["y"].shape, dtype=wl["y"].dtype).pin_memory()
+        e2e_steps = max(1, min(args.steps, 5))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            wl["x"].copy_(wl["x_host"], non_blocking=True)
+            run()
+            y_host.copy_(wl["y"], non_blocking=True)
+            stream.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        barrier()
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+    if rank != 0:
+        return
+    burst, sustained, kind = tensor_peaks()
+    step_ms = dev_ms / args.steps
+    value = wl["flops"] * world / (step_ms * 1e-3) / 1e12
+    per_call_us = step_ms * 1e3 / wl["calls"]
+    achieved = wl["flops"] / wl["calls"] / (per_call_us * 1e-6) / 1e12
+    peak = sustained * wl["peak_mult"]
+    units, secs, what = cpu_sample(name, m)
+    line = {
+        "metric": wl["metric"], "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+        "config": {"workload": wl["workload"], "flops_per_step": wl["flops"], "calls_per_step": wl["calls"],
+                   "l2": "weights rotate over distinct copies and activations plus outputs exceed L2",
+                   "launch": "one CUDA graph per step" if wl["graph"] else "eager calls (the expert-parallel exchange reads its counts on the host)"},
+        "e2e": {"value": round(wl["flops"] * world / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(wl["x_host"].numel() * wl["x_host"].element_size()),
+                "d2h_bytes_per_step": int(y_host.numel() * y_host.element_size())},
+        "gpu_launches": wl["calls"] * wl["kernels_per_call"] * args.steps,
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
+                     "frac": round(achieved / peak, 4), "peak_kind": f"{kind}: {wl['peak_mult']:g} x sustained bf16 {sustained} (burst {burst})",
+                     "frac_of_burst": round(achieved / (burst * wl["peak_mult"]), 4), "traffic": None, "kernel": wl["kernel"],
+                     "avg_call_us": round(per_call_us, 2), "includes": "activation quantize and the GEMM of each call"},
+        "clocks": clocks.summary(),
+        "cpu_baseline": {"value": round(units / secs / 1e12, 6), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": f"{what}, {secs:.1f} s"},
+    }
+    if wl["alg_bytes"]:
+        line["config"]["algorithmic_bytes_per_call"] = wl["alg_bytes"]
+        line["roofline"]["hbm_gbs"] = round(wl["alg_bytes"] / (per_call_us * 1e-6) / 1e9, 1)
+    print(json.dumps(line), flush=True)
+
+
 # --------------------------------------------------------------------------------------------- CPU arm
 
 
@@ -350,6 +643,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gptq_llama8b_mlp_m1",
+                    choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "nvfp4_gemm", "moe"])
+    ap.add_argument("--m", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -362,7 +658,10 @@ def main():
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "gptq_llama8b_mlp_m1":
+            run_ours(args, rank, world, local_rank)
+        else:
+            run_other(args, rank, world, local_rank)
     finally:
         if world > 1:
             torch.distributed.destroy_process_group()

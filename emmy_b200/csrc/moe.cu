@@ -14,15 +14,25 @@
 //                         rows of ONE expert, its weights are that expert's slice of the stacked repacked tensor.
 //                         Rows are gathered (first GEMM) / scattered (second GEMM) through index arrays, nothing is
 //                         copied.  Body: the W4A16 tile code of w4_tile.cuh.
+//                         With many rows per expert the two GEMMs run on the tensor path instead (w4_gemm.cu): rows are
+//                         first copied into expert order (moe_gather_rows_kernel) so that TMA can read them, row
+//                         blocks are 256 rows, and SwiGLU is fused into the first GEMM's epilogue.
 //   moe_swiglu_kernel     h = silu(gate) * up with the roundings of the eager form
 //                         (emmy/compiler/trace/huggingface.py:1663-1669).
 //   moe_combine_kernel    out[t] = dtype(sum_j f32(score_j) * f32(expert_j(x_t))), picks in ascending expert order,
 //                         products and sum in f32, one rounding (gen_runner.py:235-287).
+#include <type_traits>
+
 #include "w4_tile.cuh"
 
 namespace eq {
 
+int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
+                              int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
+                              const int32_t* y_rows, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
+
 constexpr int kMaxTopK = 16;
+constexpr int kBadExpertId = 16;  // status code of a row whose expert id is out of range (1..4 are the tensor path's waits)
 
 // ------------------------------------------------------------------------------------------------ router
 // One warp per token.  E <= 1024.
@@ -93,16 +103,12 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 }
 
 // ------------------------------------------------------------------------------------------------ permute
-struct RowBlock {
-    int32_t expert, row0, rows, pad;
-};
-
 __global__ void moe_count_kernel(const int32_t* __restrict__ eid, int R, int E, int32_t* __restrict__ counts, int32_t* status) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= R) return;
     const int e = eid[r];
     if (e < 0 || e >= E) {
-        atomicExch(status, 4);  // an expert id outside [0, E): the row is dropped, the caller is told
+        atomicExch(status, kBadExpertId);  // the row is dropped, the caller is told
         return;
     }
     atomicAdd(counts + e, 1);
@@ -161,6 +167,15 @@ __global__ void moe_scatter_kernel(const int32_t* __restrict__ eid, const int32_
     const int pos = offsets[e] + atomicAdd(cursor + e, 1);
     src_of[pos] = src_row ? src_row[r] : r;
     dst_of[pos] = r;
+}
+
+// xp[pos][:] = x[src_of[pos]][:], 16 bytes per thread.
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ src_of, const int32_t* __restrict__ total_rows,
+                                       int row_vec, uint4* __restrict__ xp) {
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const int64_t pos = idx / row_vec, v = idx - pos * row_vec;
+    if (pos >= *total_rows) return;
+    xp[idx] = x[static_cast<int64_t>(src_of[pos]) * row_vec + v];
 }
 
 // ------------------------------------------------------------------------------------------------ grouped GEMM
@@ -249,7 +264,9 @@ struct MoeWorkspace {
     size_t bytes;
 };
 
-static int block_rows_for(int64_t R) { return R <= 64 ? 8 : R <= 256 ? 16 : 64; }
+// Rows per expert at which the grouped GEMMs move to the tensor path (256-row blocks).
+static bool tensor_path(int64_t R, int64_t E) { return R >= 2 * E; }
+static int block_rows_for(int64_t R, int64_t E) { return tensor_path(R, E) ? 256 : R <= 64 ? 8 : R <= 256 ? 16 : 64; }
 
 static MoeWorkspace carve(void* base, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I) {
     MoeWorkspace w;
@@ -266,7 +283,7 @@ static MoeWorkspace carve(void* base, int64_t T, int64_t E, int64_t topk, int64_
     w.cursor = reinterpret_cast<int32_t*>(take(E * 4));
     w.n_blocks = reinterpret_cast<int32_t*>(take(4));
     w.status = reinterpret_cast<int32_t*>(take(4));
-    w.max_blocks = static_cast<int>(R / block_rows_for(R) + E + 1);
+    w.max_blocks = static_cast<int>(R / block_rows_for(R, E) + E + 1);
     w.blocks = reinterpret_cast<RowBlock*>(take(sizeof(RowBlock) * w.max_blocks));
     w.src_of = reinterpret_cast<int32_t*>(take(R * 4));
     w.dst_of = reinterpret_cast<int32_t*>(take(R * 4));
@@ -296,7 +313,7 @@ template <typename ActT>
 static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H,
                            int64_t I, const void* x, const int32_t* src_row, const int32_t* eid, int64_t R, void* out,
                            cudaStream_t stream) {
-    const int br = block_rows_for(R);
+    const int br = block_rows_for(R, E);
     EQ_CUDA_OK(cudaMemsetAsync(w.counts, 0, E * 4, stream));
     moe_count_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, static_cast<int>(R), static_cast<int>(E), w.counts, w.status);
     EQ_LAUNCH_OK("moe_count_kernel");
@@ -306,6 +323,22 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
     moe_scatter_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, src_row, static_cast<int>(R), static_cast<int>(E), w.offsets,
                                                                                   w.cursor, w.src_of, w.dst_of);
     EQ_LAUNCH_OK("moe_scatter_kernel");
+    if (tensor_path(R, E)) {
+        // rows into expert order (the region of the second GEMM's output in the workspace is free until then)
+        const int act = sizeof(ActT) == 2 && std::is_same<ActT, __half>::value ? EQ_F16 : EQ_BF16;
+        const int row_vec = static_cast<int>(H * 2 / 16);
+        EQ_REQUIRE(aligned(x, 16) && aligned(out, 16), EQ_ERR_BAD_ALIGN, "grouped expert GEMM: activations and outputs must be 16-byte aligned");
+        moe_gather_rows_kernel<<<static_cast<unsigned>(ceil_div(R * row_vec, 256)), 256, 0, stream>>>(
+            static_cast<const uint4*>(x), w.src_of, w.offsets + E, row_vec, reinterpret_cast<uint4*>(w.out));
+        EQ_LAUNCH_OK("moe_gather_rows_kernel");
+        int st = w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_gate_up), static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes,
+                                           scale_dtype, w.out, w.h, R, 2 * I, H, act, w.blocks, w.n_blocks, w.max_blocks, nullptr, true, w.status,
+                                           stream);
+        if (st != EQ_OK) return st;
+        return w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_down), static_cast<size_t>(H / 16) * (I / 128) * kItemBytes,
+                                         scale_dtype, w.h, out, R, H, I, act, w.blocks, w.n_blocks, w.max_blocks, w.dst_of, false, w.status,
+                                         stream);
+    }
     GroupedParams g1;
     g1.wq = static_cast<const unsigned char*>(wq_gate_up);
     g1.expert_stride = static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes;
@@ -436,6 +469,7 @@ extern "C" int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_
     int host = 0;
     EQ_CUDA_OK(cudaMemcpyAsync(&host, w.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     EQ_CUDA_OK(cudaStreamSynchronize(stream));
-    EQ_REQUIRE(host == 0, EQ_ERR_BAD_ARG, "eq_moe_status: an expert id outside [0, E) was met (code %d)", host);
+    EQ_REQUIRE(host != kBadExpertId, EQ_ERR_BAD_ARG, "eq_moe_status: an expert id outside [0, E) was met");
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_moe_status: a bounded pipeline wait of the tensor path ran out (code %d)", host);
     return EQ_OK;
 }

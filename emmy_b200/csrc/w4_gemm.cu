@@ -117,10 +117,24 @@ __global__ void gather_cols_kernel(const ActT* __restrict__ x, const int32_t* __
     xg[idx] = x[m * K + perm[k]];
 }
 
-template <typename ActT, int HALVES, int BN, int DW, int AHEAD, bool CVT>
+// MODE: kPlain: one weight, CTA row tile = blockIdx.y.  kGrouped: blockIdx.y walks a device-side list of row blocks, each
+// a run of rows of ONE expert in an expert-ordered activation matrix; the weight is that expert's slice of a stacked
+// tensor and output rows may be scattered through y_rows.  kGroupedSwiGLU: the same, with the first 128 columns of the
+// CTA's B tile taken from the gate half and the last 128 from the up half of a [gate | up] weight, and the epilogue
+// writing act(silu(gate)) * up (emmy/compiler/trace/huggingface.py:1663-1669) into a matrix of N / 2 columns.
+enum GemmMode { kPlain = 0, kGrouped = 1, kGroupedSwiGLU = 2 };
+
+struct GroupArgs {
+    const RowBlock* blocks;
+    const int32_t* n_blocks;
+    const int32_t* y_rows;   // optional: output row m goes to row y_rows[m]
+    size_t expert_stride;    // bytes between the experts' repacked weights
+};
+
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD, bool CVT, int MODE>
 __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const unsigned char* __restrict__ wq, ActT* __restrict__ y,
-                         int M, int N, int K, int* __restrict__ status) {
+                         int M, int N, int K, int* __restrict__ status, const GroupArgs grp) {
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAhead = Cfg::kAhead;
@@ -136,10 +150,18 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * HALVES);
+    const int n0 = blockIdx.x * BN;
+    int m0 = blockIdx.y * (128 * HALVES), m_end = M;
+    if constexpr (MODE != kPlain) {
+        if (static_cast<int>(blockIdx.y) >= *grp.n_blocks) return;  // the whole CTA, before any barrier exists
+        const RowBlock rb = grp.blocks[blockIdx.y];
+        m0 = rb.row0;
+        m_end = rb.row0 + rb.rows;
+        wq += static_cast<size_t>(rb.expert) * grp.expert_stride;
+    }
     const int k_blocks = K / kGK;
     const int items = K / 128;
-    const bool two_halves = HALVES == 2 && M - m0 > 128;
+    const bool two_halves = HALVES == 2 && m_end - m0 > 128;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -240,7 +262,12 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
 #pragma unroll
         for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
             const int tile_in_cta = dw * Cfg::kTilesPerWarp + nt;
-            const int tile = n0 / 16 + tile_in_cta;
+            int tile = n0 / 16 + tile_in_cta;
+            if constexpr (MODE == kGroupedSwiGLU) {
+                constexpr int kHalfTiles = BN / 32;  // gate tiles of this CTA, then as many up tiles
+                const int col_tile = n0 / 32 + (tile_in_cta % kHalfTiles);
+                tile = col_tile < N / 32 ? col_tile + (tile_in_cta / kHalfTiles) * (N / 32) : N / 16;
+            }
             live[nt] = tile < N / 16;
             const unsigned char* rec = wq + static_cast<size_t>(live[nt] ? tile : 0) * items * kItemBytes;
             wp[nt] = rec + h * 512 + (4 * g + jj) * 16;
@@ -359,29 +386,74 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         TR_BEGIN(epi_work);
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
-        if (ok && (half == 0 || two_halves)) {
+        if (ok && (half == 0 || two_halves)) {  // warp-uniform: the TMEM loads below are warp-wide instructions
+            const bool row_ok = m < m_end;
+            size_t out_row = static_cast<size_t>(m);
+            if constexpr (MODE != kPlain) {
+                if (row_ok && grp.y_rows) out_row = static_cast<size_t>(grp.y_rows[m]);
+            }
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN;
+            if constexpr (MODE == kGroupedSwiGLU) {
+                // gate columns [0, BN/2) and up columns [BN/2, BN) of the accumulator -> BN/2 columns of the output
+                const int out_n = N / 2, out0 = n0 / 2;
+                constexpr int kCols = BN / 2 / Cfg::kEpiGroups;
+                const int cb = (quartet % Cfg::kEpiGroups) * kCols;
 #pragma unroll 1
-            for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
-                uint32_t r[32];
-                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c, r);
-                tc::tmem_ld_wait();
-                if (m < M && n0 + c < N) {
-                    ActT* dst = y + static_cast<size_t>(m) * N + n0 + c;
-                    if (n0 + c + 32 <= N) {
+                for (int c = cb; c < cb + kCols; c += 32) {
+                    uint32_t rg[32], ru[32];
+                    tc::tmem_ld_32x32(t_row + c, rg);
+                    tc::tmem_ld_32x32(t_row + BN / 2 + c, ru);
+                    tc::tmem_ld_wait();
+                    if (row_ok && out0 + c < out_n) {
+                        ActT* dst = y + out_row * out_n + out0 + c;
                         uint32_t packed[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const ActT o0 = from_float<ActT>(__uint_as_float(r[2 * i])), o1 = from_float<ActT>(__uint_as_float(r[2 * i + 1]));
-                            packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
-                                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        for (int i = 0; i < 32; ++i) {
+                            const float g = to_float(from_float<ActT>(__uint_as_float(rg[i])));
+                            const float u = to_float(from_float<ActT>(__uint_as_float(ru[i])));
+                            const ActT sg = from_float<ActT>(g / (1.f + expf(-g)));
+                            const ActT o = from_float<ActT>(to_float(sg) * u);
+                            const uint32_t bits = *reinterpret_cast<const uint16_t*>(&o);
+                            if (i & 1)
+                                packed[i >> 1] |= bits << 16;
+                            else
+                                packed[i >> 1] = bits;
                         }
+                        if (out0 + c + 32 <= out_n) {
 #pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    } else {
+                            for (int v = 0; v < 4; ++v)
+                                reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (n0 + c + i < N) dst[i] = from_float<ActT>(__uint_as_float(r[i]));
+                            for (int i = 0; i < 32; ++i)
+                                if (out0 + c + i < out_n) reinterpret_cast<uint16_t*>(dst)[i] = static_cast<uint16_t>(packed[i >> 1] >> (16 * (i & 1)));
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(t_row + c, r);
+                    tc::tmem_ld_wait();
+                    if (row_ok && n0 + c < N) {
+                        ActT* dst = y + out_row * N + n0 + c;
+                        if (n0 + c + 32 <= N) {
+                            uint32_t packed[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const ActT o0 = from_float<ActT>(__uint_as_float(r[2 * i])), o1 = from_float<ActT>(__uint_as_float(r[2 * i + 1]));
+                                packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                            (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                            }
+#pragma unroll
+                            for (int v = 0; v < 4; ++v)
+                                reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n0 + c + i < N) dst[i] = from_float<ActT>(__uint_as_float(r[i]));
+                        }
                     }
                 }
             }
@@ -404,19 +476,19 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     }
 }
 
-template <typename ActT, int HALVES, int BN, int DW, int AHEAD>
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD, int MODE>
 int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y, int64_t M, int64_t N, int64_t K, int* status,
-               cudaStream_t stream) {
+               const GroupArgs& grp, unsigned grid_y, cudaStream_t stream) {
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     CUtensorMap map_x;
-    const CUtensorMapDataType elem = sizeof(ActT) == 2 && ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * HALVES, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const bool cvt = scale_dtype != (ScaleMul<ActT>::kFmt == 0 ? EQ_F16 : EQ_BF16);
-    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false>;
+    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true, MODE> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false, MODE>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
-    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, 128 * HALVES)));
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), grid_y);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, grp);
     EQ_LAUNCH_OK("w4a16_gemm_tc_kernel");
     return EQ_OK;
 }
@@ -430,9 +502,12 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
         EQ_LAUNCH_OK("gather_cols_kernel");
         x = gathered;
     }
-    if (M <= 128) return launch_cfg<ActT, 1, 64, 4, 4>(wq, scale_dtype, x, y, M, N, K, status, stream);
-    if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count()) return launch_cfg<ActT, 2, 256, 16, 2>(wq, scale_dtype, x, y, M, N, K, status, stream);
-    return launch_cfg<ActT, 2, 128, 8, 3>(wq, scale_dtype, x, y, M, N, K, status, stream);
+    const GroupArgs none = {nullptr, nullptr, nullptr, 0};
+    if (M <= 128)
+        return launch_cfg<ActT, 1, 64, 4, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 128)), stream);
+    if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
+        return launch_cfg<ActT, 2, 256, 16, 2, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
+    return launch_cfg<ActT, 2, 128, 8, 3, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
 }
 
 }  // namespace
@@ -445,6 +520,26 @@ int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* p
                                     static_cast<__half*>(gathered), status, stream);
     return launch_typed<__nv_bfloat16>(wq, scale_dtype, perm, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), M,
                                        N, K, static_cast<__nv_bfloat16*>(gathered), status, stream);
+}
+
+// Grouped expert GEMM on the tensor path.  x: [R][K] activations in expert order; blocks / n_blocks: device-side list of
+// row blocks of at most 256 rows; wq: E stacked repacked weights expert_stride bytes apart, each [N][K] logical.
+// swiglu: N is the width of the [gate | up] weight and y has N / 2 columns.  max_blocks bounds the grid.
+int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
+                              int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
+                              const int32_t* y_rows, bool swiglu, int* status, cudaStream_t stream) {
+    const GroupArgs grp = {blocks, n_blocks, y_rows, expert_stride};
+    const unsigned gy = static_cast<unsigned>(max_blocks);
+    if (act_dtype == EQ_F16) {
+        const __half* xa = static_cast<const __half*>(x);
+        __half* ya = static_cast<__half*>(y);
+        return swiglu ? launch_cfg<__half, 2, 256, 16, 2, kGroupedSwiGLU>(wq, scale_dtype, xa, ya, R, N, K, status, grp, gy, stream)
+                      : launch_cfg<__half, 2, 256, 16, 2, kGrouped>(wq, scale_dtype, xa, ya, R, N, K, status, grp, gy, stream);
+    }
+    const __nv_bfloat16* xa = static_cast<const __nv_bfloat16*>(x);
+    __nv_bfloat16* ya = static_cast<__nv_bfloat16*>(y);
+    return swiglu ? launch_cfg<__nv_bfloat16, 2, 256, 16, 2, kGroupedSwiGLU>(wq, scale_dtype, xa, ya, R, N, K, status, grp, gy, stream)
+                  : launch_cfg<__nv_bfloat16, 2, 256, 16, 2, kGrouped>(wq, scale_dtype, xa, ya, R, N, K, status, grp, gy, stream);
 }
 
 }  // namespace eq

@@ -27,6 +27,11 @@ struct W4Params {
     const int32_t* y_rows;    // optional: output row m of the problem is row y_rows[m] of y (scatter)
 };
 
+// A run of rows of one expert in an expert-ordered row list (grouped expert GEMMs).
+struct RowBlock {
+    int32_t expert, row0, rows, pad;
+};
+
 template <typename ActT>
 struct Frag;
 

@@ -110,3 +110,27 @@ def test_expert_ids_out_of_range_are_reported():
     om.moe_experts(x, torch.tensor([0, 9, 1], dtype=torch.int32, device="cuda"), w, workspace=ws)
     with pytest.raises(EmmyqError):
         om.moe_status(ws, 3, w, 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_moe_layer_tensor_path_ragged_shapes(dtype):
+    """Enough rows per expert for the tcgen05 grouped GEMMs; widths that leave partial column tiles, experts with
+    more than one 256-row block and experts with none."""
+    from emmy_b200 import ops_moe as om
+
+    e, h, inter, k, t = 8, 640, 384, 2, 1500
+    ex = make_experts(e, h, inter, seed=300)
+    w = om.moe_repack(tuple(dev(a) for a in ex["gate_up"]), tuple(dev(a) for a in ex["down"]))
+    wgu, wdn = omoe.dequant_expert_weights(ex, dtype)
+    name = "bf16" if dtype == torch.bfloat16 else "f16"
+    x = torch.from_numpy(synth.activations(t, h, name, seed=t)).to(dtype)
+    logits = torch.randn(t, e, generator=torch.Generator().manual_seed(t))
+    logits[:, 5] = -50.0  # nobody picks expert 5
+    logits[:, 2] += 2.0   # expert 2 is crowded
+    ws = om.moe_workspace(t, w, k, torch.device("cuda"))
+    y = om.moe_forward(x.cuda(), logits.cuda(), w, k, workspace=ws)
+    om.moe_status(ws, t, w, k)
+    ref = omoe.moe_layer(x, logits, wgu, wdn, k).float()
+    got = y.float().cpu()
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max()) <= TOL * float(ref.abs().max())
