@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME [--m ROWS]]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME [--rows ROWS]]
 
 Default workload (`gptq_llama8b_mlp_m1`): the W4A16 M=1 GEMV on GPTQ act-order weights with the
 Llama-3.1-8B MLP shapes (gate/up K=4096 N=14336, down K=14336 N=4096, group 128) -- one step is one pass
@@ -277,7 +277,7 @@ TRAFFIC_PER_LAUNCH = None
 
 # --------------------------------------------------------------------------------------------- other workloads
 #
-# The same contract for the other calls of the path; `--workload NAME [--m ROWS]`.  One step = `copies` calls on distinct
+# The same contract for the other calls of the path; `--workload NAME [--rows ROWS]`.  One step = `copies` calls on distinct
 # weight copies (so that weights come from HBM, not L2), captured in one CUDA graph where the call has no host read.
 
 GEMM_K, GEMM_N = 5120, 17408
@@ -471,7 +471,7 @@ def run_other(args, rank, world, local_rank):
     torch.cuda.set_device(device)
     name = args.workload
     default_m = {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
-    m = args.m or default_m
+    m = args.rows or default_m
     wl = _wl_moe(device, rank, world, m) if name == "moe" else {"fp8_gemm": _wl_fp8, "nvfp4_gemm": _wl_nvfp4, "w4a16_prefill": _wl_w4_prefill}[name](device, rank, m)
     step = wl["step"]
     stream = torch.cuda.Stream(device)
@@ -645,7 +645,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptq_llama8b_mlp_m1",
                     choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "nvfp4_gemm", "moe"])
-    ap.add_argument("--m", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
+    ap.add_argument("--rows", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
