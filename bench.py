@@ -373,7 +373,7 @@ def _wl_w4_prefill(device, rank, m):
     )
 
 
-def _wl_moe(device, rank, world, t):
+def _wl_moe(device, rank, world, t, exchange="peer"):
     """Qwen3-30B-A3B expert shapes; with N > 1 ranks the experts are sharded E/N per rank and tokens travel by all-to-all."""
     from emmy_b200 import ops_moe as om
     from emmy_b200 import shard
@@ -401,7 +401,7 @@ def _wl_moe(device, rank, world, t):
             om.moe_forward(x, logits, w, topk, workspace=wsp, out=y)
 
         status = lambda: om.moe_status(wsp, t, w, topk)
-    else:
+    elif exchange == "nccl":
         def step():
             ids, scores = om.moe_route(logits, topk)
             out = shard.ep_moe_forward(x, ids, scores, e, lambda rows, eid: om.moe_experts(rows, eid, w),
@@ -409,12 +409,22 @@ def _wl_moe(device, rank, world, t):
             y.copy_(out)
 
         status = lambda: None
+    else:
+        ep = shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device)
+
+        def step():
+            ids, scores = om.moe_route(logits, topk)
+            ep.forward(x, ids, scores, w, out=y)
+
+        status = ep.status
     return dict(
         step=step, flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), calls=1, kernels_per_call=8, x=x, x_host=x_host,
         y=y, graph=world == 1, metric="moe_w4a16_tflops", dtype="int4 expert weights, bf16 activations, f32 accumulate and combine",
         peak_mult=1.0, kernel="moe_expert_gemm_kernel", status=status,
         workload=f"moe: routed W4A16 expert layer, Qwen3-30B-A3B shapes (128 experts, top-8, hidden 2048, intermediate 768, AWQ group 128), T={t} tokens per rank"
-        + (f", experts sharded {local_e} per rank, all-to-all dispatch and return over NCCL" if world > 1 else ""),
+        + (f", experts sharded {local_e} per rank, " + ("all-to-all dispatch and return over NCCL" if exchange == "nccl" else
+            "rows stored into the owner's receive buffer and results stored back from the second GEMM's epilogue over NVLink peer memory")
+           if world > 1 else ""),
         alg_bytes=None,
     )
 
@@ -472,7 +482,7 @@ def run_other(args, rank, world, local_rank):
     name = args.workload
     default_m = {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
     m = args.rows or default_m
-    wl = _wl_moe(device, rank, world, m) if name == "moe" else {"fp8_gemm": _wl_fp8, "nvfp4_gemm": _wl_nvfp4, "w4a16_prefill": _wl_w4_prefill}[name](device, rank, m)
+    wl = _wl_moe(device, rank, world, m, args.exchange) if name == "moe" else {"fp8_gemm": _wl_fp8, "nvfp4_gemm": _wl_nvfp4, "w4a16_prefill": _wl_w4_prefill}[name](device, rank, m)
     step = wl["step"]
     stream = torch.cuda.Stream(device)
 
@@ -541,7 +551,7 @@ def run_other(args, rank, world, local_rank):
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": {"workload": wl["workload"], "flops_per_step": wl["flops"], "calls_per_step": wl["calls"],
                    "l2": "weights rotate over distinct copies and activations plus outputs exceed L2",
-                   "launch": "one CUDA graph per step" if wl["graph"] else "eager calls (the expert-parallel exchange reads its counts on the host)"},
+                   "launch": "one CUDA graph per step" if wl["graph"] else "eager calls"},
         "e2e": {"value": round(wl["flops"] * world / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
                 "h2d_bytes_per_step": int(wl["x_host"].numel() * wl["x_host"].element_size()),
                 "d2h_bytes_per_step": int(y_host.numel() * y_host.element_size())},
@@ -645,6 +655,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptq_llama8b_mlp_m1",
                     choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "nvfp4_gemm", "moe"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="moe workload at N > 1: who moves the tokens")
     ap.add_argument("--rows", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -29,7 +29,7 @@ namespace eq {
 
 int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
                               int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
-                              const int32_t* y_rows, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
+                              const int32_t* y_rows, const uint64_t* y_ptrs, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
 
 constexpr int kMaxTopK = 16;
 constexpr int kBadExpertId = 16;  // status code of a row whose expert id is out of range (1..4 are the tensor path's waits)
@@ -107,6 +107,7 @@ __global__ void moe_count_kernel(const int32_t* __restrict__ eid, int R, int E, 
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= R) return;
     const int e = eid[r];
+    if (e == -1) return;  // an empty slot of an expert-parallel receive buffer
     if (e < 0 || e >= E) {
         atomicExch(status, kBadExpertId);  // the row is dropped, the caller is told
         return;
@@ -157,9 +158,10 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ counts, int E, int b
 }
 
 // pos_of[r]: position of row r in expert order; src_of[pos]: the activation row that feeds position pos; dst_of[pos] = r.
+// row_ptr (optional): the address output row r goes to; dst_ptr[pos] carries it into expert order.
 __global__ void moe_scatter_kernel(const int32_t* __restrict__ eid, const int32_t* __restrict__ src_row, int R, int E,
                                    const int32_t* __restrict__ offsets, int32_t* __restrict__ cursor, int32_t* __restrict__ src_of,
-                                   int32_t* __restrict__ dst_of) {
+                                   int32_t* __restrict__ dst_of, const uint64_t* __restrict__ row_ptr, uint64_t* __restrict__ dst_ptr) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= R) return;
     const int e = eid[r];
@@ -167,6 +169,7 @@ __global__ void moe_scatter_kernel(const int32_t* __restrict__ eid, const int32_
     const int pos = offsets[e] + atomicAdd(cursor + e, 1);
     src_of[pos] = src_row ? src_row[r] : r;
     dst_of[pos] = r;
+    if (row_ptr) dst_ptr[pos] = row_ptr[r];
 }
 
 // xp[pos][:] = x[src_of[pos]][:], 16 bytes per thread.
@@ -186,6 +189,7 @@ struct GroupedParams {
     void* y;                      // outputs (rows addressed through y_rows, or contiguous in expert order)
     const int32_t* x_rows;        // optional [R] gather index in expert order
     const int32_t* y_rows;        // optional [R] scatter index in expert order
+    const uint64_t* y_ptrs;       // optional [R] destination address of each row in expert order (overrides y / y_rows)
     const RowBlock* blocks;
     const int32_t* n_blocks;
     int K, N, scale_dtype;
@@ -215,6 +219,7 @@ __global__ void __launch_bounds__(kTileThreads) moe_expert_gemm_kernel(const Gro
         p.x = static_cast<const ActT*>(gp.x) + static_cast<size_t>(rb.row0) * gp.K;
         p.x_rows = nullptr;
     }
+    p.y_ptrs = gp.y_ptrs ? gp.y_ptrs + rb.row0 : nullptr;
     if (gp.y_rows) {
         p.y = gp.y;
         p.y_rows = gp.y_rows + rb.row0;
@@ -258,6 +263,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct MoeWorkspace {
     int32_t *counts, *offsets, *cursor, *n_blocks, *status, *src_of, *dst_of, *ids, *src_row;
     float* scores;
+    uint64_t* dst_ptr;
     RowBlock* blocks;
     unsigned char *h1, *h, *out;
     int max_blocks;
@@ -290,6 +296,7 @@ static MoeWorkspace carve(void* base, int64_t T, int64_t E, int64_t topk, int64_
     w.ids = reinterpret_cast<int32_t*>(take(R * 4));
     w.src_row = reinterpret_cast<int32_t*>(take(R * 4));
     w.scores = reinterpret_cast<float*>(take(R * 4));
+    w.dst_ptr = reinterpret_cast<uint64_t*>(take(R * 8));
     w.h1 = take(R * 2 * I * 2);
     w.h = take(R * I * 2);
     w.out = take(R * H * 2);
@@ -312,7 +319,7 @@ static int launch_grouped(const GroupedParams& gp, int block_rows, int max_block
 template <typename ActT>
 static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H,
                            int64_t I, const void* x, const int32_t* src_row, const int32_t* eid, int64_t R, void* out,
-                           cudaStream_t stream) {
+                           const uint64_t* row_ptr, cudaStream_t stream) {
     const int br = block_rows_for(R, E);
     EQ_CUDA_OK(cudaMemsetAsync(w.counts, 0, E * 4, stream));
     moe_count_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, static_cast<int>(R), static_cast<int>(E), w.counts, w.status);
@@ -321,7 +328,7 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
                                                                  w.max_blocks);
     EQ_LAUNCH_OK("moe_plan_kernel");
     moe_scatter_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, src_row, static_cast<int>(R), static_cast<int>(E), w.offsets,
-                                                                                  w.cursor, w.src_of, w.dst_of);
+                                                                                  w.cursor, w.src_of, w.dst_of, row_ptr, w.dst_ptr);
     EQ_LAUNCH_OK("moe_scatter_kernel");
     if (tensor_path(R, E)) {
         // rows into expert order (the region of the second GEMM's output in the workspace is free until then)
@@ -332,12 +339,12 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
             static_cast<const uint4*>(x), w.src_of, w.offsets + E, row_vec, reinterpret_cast<uint4*>(w.out));
         EQ_LAUNCH_OK("moe_gather_rows_kernel");
         int st = w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_gate_up), static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes,
-                                           scale_dtype, w.out, w.h, R, 2 * I, H, act, w.blocks, w.n_blocks, w.max_blocks, nullptr, true, w.status,
-                                           stream);
+                                           scale_dtype, w.out, w.h, R, 2 * I, H, act, w.blocks, w.n_blocks, w.max_blocks, nullptr, nullptr, true,
+                                           w.status, stream);
         if (st != EQ_OK) return st;
         return w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_down), static_cast<size_t>(H / 16) * (I / 128) * kItemBytes,
-                                         scale_dtype, w.h, out, R, H, I, act, w.blocks, w.n_blocks, w.max_blocks, w.dst_of, false, w.status,
-                                         stream);
+                                         scale_dtype, w.h, out, R, H, I, act, w.blocks, w.n_blocks, w.max_blocks, w.dst_of,
+                                         row_ptr ? w.dst_ptr : nullptr, false, w.status, stream);
     }
     GroupedParams g1;
     g1.wq = static_cast<const unsigned char*>(wq_gate_up);
@@ -346,6 +353,7 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
     g1.y = w.h1;
     g1.x_rows = w.src_of;
     g1.y_rows = nullptr;
+    g1.y_ptrs = nullptr;
     g1.blocks = w.blocks;
     g1.n_blocks = w.n_blocks;
     g1.K = static_cast<int>(H);
@@ -363,9 +371,147 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
     g2.y = out;
     g2.x_rows = nullptr;
     g2.y_rows = w.dst_of;
+    g2.y_ptrs = row_ptr ? w.dst_ptr : nullptr;
     g2.K = static_cast<int>(I);
     g2.N = static_cast<int>(H);
     return launch_grouped<ActT>(g2, br, w.max_blocks, stream);
+}
+
+
+// ------------------------------------------------------------------------------------------------ expert parallel
+// Experts sharded E / world per rank; every rank holds T tokens.  The token exchange is done by the kernels themselves
+// over peer memory (NVLink): the dispatch stores each picked row straight into the owner's receive buffer, the second
+// expert GEMM stores each result row straight into the token's rank (per-row destination addresses), and epoch
+// flags written with release / read with acquire at system scope order the two.  No host read, no NCCL call.
+//   rank r's receive buffer: [world sources][cap rows][H]; source s fills its own region in arrival order
+//   flags of rank r: [0][s] = epoch of the last dispatch that source s completed into r's buffer
+//                    [1][d] = epoch of the last call whose results destination d has stored into r's `back`
+// Waits are bounded (about a second) and report through the status word.
+constexpr int kEpOverflow = 32;   // a source had more rows for one destination than `cap`
+constexpr int kEpWaitReady = 64;  // a peer's dispatch did not arrive in time
+constexpr int kEpWaitDone = 65;   // a peer's results did not arrive in time
+constexpr long long kEpWaitCycles = 2000000000LL;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One warp per pick: copy the token's row into the owner's receive region of this rank and record (local expert,
+// return slot).  The last CTA to finish publishes the row counts and raises this rank's flag at every destination.
+__global__ void ep_dispatch_kernel(const eq_ep_peers pe, const uint4* __restrict__ x, const int32_t* __restrict__ ids, int picks, int topk,
+                                   int per_rank, int row_vec, int32_t* __restrict__ send_cursor, int32_t* __restrict__ cta_done,
+                                   uint32_t epoch, int32_t* __restrict__ status) {
+    __shared__ int s_last;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp < picks) {
+        const int id = ids[warp];
+        if (id < 0 || id >= per_rank * pe.world) {
+            if (lane == 0) atomicExch(status, kBadExpertId);
+        } else {
+            const int dest = id / per_rank, le = id - dest * per_rank;
+            int slot = 0;
+            if (lane == 0) slot = atomicAdd(send_cursor + dest, 1);
+            slot = __shfl_sync(0xFFFFFFFFu, slot, 0);
+            if (slot >= pe.cap) {
+                if (lane == 0) atomicExch(status, kEpOverflow);
+            } else {
+                const size_t row = static_cast<size_t>(pe.rank) * pe.cap + slot;
+                uint4* dst = static_cast<uint4*>(pe.recv_x[dest]) + row * row_vec;
+                const uint4* src = x + static_cast<size_t>(warp / topk) * row_vec;
+                for (int v = lane; v < row_vec; v += 32) dst[v] = src[v];
+                if (lane == 0) *reinterpret_cast<int2*>(pe.recv_meta[dest] + 2 * row) = make_int2(le, warp);
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(cta_done, 1) == static_cast<int>(gridDim.x) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (static_cast<int>(threadIdx.x) < pe.world) {
+        const int d = threadIdx.x;
+        const int sent = atomicExch(send_cursor + d, 0);
+        pe.recv_count[d][pe.rank] = sent < pe.cap ? sent : static_cast<int>(pe.cap);
+        __threadfence_system();
+        st_release_sys(pe.flags[d] + pe.rank, epoch);
+    }
+    if (threadIdx.x == 0) *cta_done = 0;
+}
+
+// which = 0: wait for every source's dispatch; 1: for every destination's results.
+__global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int world, int which, uint32_t epoch, int32_t* __restrict__ status) {
+    if (static_cast<int>(threadIdx.x) >= world) return;
+    const uint32_t* f = flags + which * world + threadIdx.x;
+    const long long start = clock64();
+    while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
+        if (clock64() - start > kEpWaitCycles) {
+            atomicExch(status, which == 0 ? kEpWaitReady : kEpWaitDone);
+            return;
+        }
+    }
+}
+
+// The received rows as a row list for the grouped FFN: row r = (source r / cap, slot r % cap).
+__global__ void ep_build_rows_kernel(const eq_ep_peers pe, const int32_t* __restrict__ meta, const int32_t* __restrict__ counts, int e_local,
+                                     size_t row_bytes, int32_t* __restrict__ eid, int32_t* __restrict__ src_row, uint64_t* __restrict__ row_ptr,
+                                     int32_t* __restrict__ status) {
+    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (r >= static_cast<int64_t>(pe.world) * pe.cap) return;
+    const int s = static_cast<int>(r / pe.cap);
+    const int64_t i = r - static_cast<int64_t>(s) * pe.cap;
+    int e = -1;
+    uint64_t ptr = 0;
+    if (i < counts[s]) {
+        const int2 m = *reinterpret_cast<const int2*>(meta + 2 * r);
+        if (m.x >= 0 && m.x < e_local) {
+            e = m.x;
+            ptr = reinterpret_cast<uint64_t>(static_cast<unsigned char*>(pe.back[s]) + static_cast<size_t>(m.y) * row_bytes);
+        } else {
+            atomicExch(status, kBadExpertId);
+        }
+    }
+    eid[r] = e;
+    src_row[r] = static_cast<int32_t>(r);
+    row_ptr[r] = ptr;
+}
+
+__global__ void ep_signal_done_kernel(const eq_ep_peers pe, uint32_t epoch) {
+    if (static_cast<int>(threadIdx.x) >= pe.world) return;
+    __threadfence_system();
+    st_release_sys(pe.flags[threadIdx.x] + pe.world + pe.rank, epoch);
+}
+
+struct EpWorkspace {
+    MoeWorkspace moe;
+    int32_t *send_cursor, *cta_done, *eid, *src_row;
+    uint64_t* row_ptr;
+    size_t bytes;
+};
+
+static EpWorkspace carve_ep(void* base, int64_t world, int64_t cap, int64_t e_local, int64_t H, int64_t I) {
+    EpWorkspace w;
+    const int64_t R = world * cap;
+    w.moe = carve(base, R, e_local, 1, H, I);
+    unsigned char* p = static_cast<unsigned char*>(base);
+    size_t o = w.moe.bytes;
+    auto take = [&](size_t bytes) {
+        unsigned char* r = p ? p + o : nullptr;
+        o += align_up(bytes, 256);
+        return r;
+    };
+    w.send_cursor = reinterpret_cast<int32_t*>(take(EQ_EP_MAX_RANKS * 4));
+    w.cta_done = reinterpret_cast<int32_t*>(take(4));
+    w.eid = reinterpret_cast<int32_t*>(take(R * 4));
+    w.src_row = reinterpret_cast<int32_t*>(take(R * 4));
+    w.row_ptr = reinterpret_cast<uint64_t*>(take(R * 8));
+    w.bytes = o;
+    return w;
 }
 
 static int check_moe_shapes(const char* who, int64_t E, int64_t topk, int64_t H, int64_t I, int64_t G) {
@@ -409,8 +555,8 @@ extern "C" int eq_moe_experts_w4a16(const void* wq_gate_up, const void* wq_down,
     MoeWorkspace w = carve(workspace, R, E, 1, H, I);
     EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
     if (act_dtype == EQ_F16)
-        return experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, stream);
-    return experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, stream);
+        return experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, nullptr, stream);
+    return experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, nullptr, stream);
 }
 
 __global__ void moe_src_rows_kernel(int32_t* src_row, int R, int topk) {
@@ -455,9 +601,9 @@ extern "C" int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int sca
     moe_src_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(w.src_row, static_cast<int>(R), static_cast<int>(topk));
     EQ_LAUNCH_OK("moe_src_rows_kernel");
     if (act_dtype == EQ_F16)
-        st = experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, stream);
+        st = experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, nullptr, stream);
     else
-        st = experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, stream);
+        st = experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, nullptr, stream);
     if (st != EQ_OK) return st;
     return eq_moe_combine(w.out, w.scores, T, topk, H, act_dtype, y, stream_);
 }
@@ -471,5 +617,76 @@ extern "C" int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_
     EQ_CUDA_OK(cudaStreamSynchronize(stream));
     EQ_REQUIRE(host != kBadExpertId, EQ_ERR_BAD_ARG, "eq_moe_status: an expert id outside [0, E) was met");
     EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_moe_status: a bounded pipeline wait of the tensor path ran out (code %d)", host);
+    return EQ_OK;
+}
+
+extern "C" size_t eq_ep_moe_workspace_bytes(int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I) {
+    if (world <= 0 || world > EQ_EP_MAX_RANKS || cap <= 0 || E_local <= 0 || H <= 0 || I <= 0) return 0;
+    return carve_ep(nullptr, world, cap, E_local, H, I).bytes;
+}
+
+extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E_local, int64_t topk, int64_t H, int64_t I,
+                               int64_t G, const void* x, const int32_t* ids, const float* scores, int64_t T, int act_dtype, void* y,
+                               const eq_ep_peers* peers, uint32_t epoch, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(peers && peers->world >= 1 && peers->world <= EQ_EP_MAX_RANKS && peers->rank >= 0 && peers->rank < peers->world && peers->cap > 0,
+               EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: bad peer description");
+    const int64_t world = peers->world, cap = peers->cap;
+    int st = check_moe_shapes("eq_ep_moe_w4a16", E_local * world, topk, H, I, G);
+    if (st != EQ_OK) return st;
+    EQ_REQUIRE(T >= 0 && epoch != 0, EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: negative token count or epoch 0");
+    EQ_REQUIRE(wq_gate_up && wq_down && (T == 0 || (x && ids && scores && y)), EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: null pointer");
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: activations must be f16 or bf16");
+    EQ_REQUIRE(T == 0 || aligned(x, 16), EQ_ERR_BAD_ALIGN, "eq_ep_moe_w4a16: x must be 16-byte aligned");
+    for (int r = 0; r < world; ++r)
+        EQ_REQUIRE(peers->recv_x[r] && peers->recv_meta[r] && peers->recv_count[r] && peers->back[r] && peers->flags[r] &&
+                       aligned(peers->recv_x[r], 16) && aligned(peers->back[r], 16) && aligned(peers->recv_meta[r], 8),
+                   EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: peer %d has a null or misaligned buffer", r);
+    EQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= eq_ep_moe_workspace_bytes(world, cap, E_local, H, I), EQ_ERR_WORKSPACE,
+               "eq_ep_moe_w4a16: workspace of %zu bytes (256-byte aligned, zero on first use) needed, %zu given",
+               eq_ep_moe_workspace_bytes(world, cap, E_local, H, I), workspace_bytes);
+    EpWorkspace w = carve_ep(workspace, world, cap, E_local, H, I);
+    const int me = peers->rank;
+    const int64_t picks = T * topk, R = world * cap;
+    const int row_vec = static_cast<int>(H * 2 / 16);
+    EQ_CUDA_OK(cudaMemsetAsync(w.moe.status, 0, 4, stream));
+    // every rank launches the dispatch, with or without tokens of its own: its flag is what the others wait for
+    const unsigned dgrid = static_cast<unsigned>(picks > 0 ? ceil_div(picks * 32, 256) : 1);
+    ep_dispatch_kernel<<<dgrid, 256, 0, stream>>>(*peers, static_cast<const uint4*>(x), ids, static_cast<int>(picks), static_cast<int>(topk),
+                                                  static_cast<int>(E_local), row_vec, w.send_cursor, w.cta_done, epoch, w.moe.status);
+    EQ_LAUNCH_OK("ep_dispatch_kernel");
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 0, epoch, w.moe.status);
+    EQ_LAUNCH_OK("ep_wait_kernel");
+    ep_build_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(*peers, peers->recv_meta[me], peers->recv_count[me],
+                                                                                      static_cast<int>(E_local), static_cast<size_t>(H) * 2, w.eid,
+                                                                                      w.src_row, w.row_ptr, w.moe.status);
+    EQ_LAUNCH_OK("ep_build_rows_kernel");
+    if (act_dtype == EQ_F16)
+        st = experts_forward<__half>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, w.eid, R, w.moe.out,
+                                     w.row_ptr, stream);
+    else
+        st = experts_forward<__nv_bfloat16>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, w.eid, R,
+                                            w.moe.out, w.row_ptr, stream);
+    if (st != EQ_OK) return st;
+    ep_signal_done_kernel<<<1, 32, 0, stream>>>(*peers, epoch);
+    EQ_LAUNCH_OK("ep_signal_done_kernel");
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 1, epoch, w.moe.status);
+    EQ_LAUNCH_OK("ep_wait_kernel");
+    if (T == 0) return EQ_OK;
+    return eq_moe_combine(peers->back[me], scores, T, topk, H, act_dtype, y, stream_);
+}
+
+extern "C" int eq_ep_moe_status(const void* workspace, int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && world > 0 && world <= EQ_EP_MAX_RANKS && cap > 0, EQ_ERR_BAD_ARG, "eq_ep_moe_status: bad arguments");
+    EpWorkspace w = carve_ep(const_cast<void*>(workspace), world, cap, E_local, H, I);
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, w.moe.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host != kBadExpertId, EQ_ERR_BAD_ARG, "eq_ep_moe_status: an expert id out of range was met");
+    EQ_REQUIRE(host != kEpOverflow, EQ_ERR_UNSUPPORTED, "eq_ep_moe_status: a rank had more rows for one destination than the receive capacity; rows were dropped");
+    EQ_REQUIRE(host != kEpWaitReady && host != kEpWaitDone, EQ_ERR_TIMEOUT, "eq_ep_moe_status: a peer's %s did not arrive within the wait bound",
+               host == kEpWaitReady ? "dispatch" : "results");
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_ep_moe_status: a bounded pipeline wait of the tensor path ran out (code %d)", host);
     return EQ_OK;
 }

@@ -128,6 +128,7 @@ struct GroupArgs {
     const RowBlock* blocks;
     const int32_t* n_blocks;
     const int32_t* y_rows;   // optional: output row m goes to row y_rows[m]
+    const uint64_t* y_ptrs;  // optional: output row m starts at address y_ptrs[m] (0 = drop the row); may be a peer GPU's memory
     size_t expert_stride;    // bytes between the experts' repacked weights
 };
 
@@ -387,10 +388,18 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
         if (ok && (half == 0 || two_halves)) {  // warp-uniform: the TMEM loads below are warp-wide instructions
-            const bool row_ok = m < m_end;
+            bool row_ok = m < m_end;
             size_t out_row = static_cast<size_t>(m);
+            ActT* out_base = y;
             if constexpr (MODE != kPlain) {
-                if (row_ok && grp.y_rows) out_row = static_cast<size_t>(grp.y_rows[m]);
+                if (row_ok && grp.y_ptrs) {
+                    // the row's own destination: results go straight to the rank that owns the token
+                    out_base = reinterpret_cast<ActT*>(grp.y_ptrs[m]);
+                    out_row = 0;
+                    row_ok = out_base != nullptr;
+                } else if (row_ok && grp.y_rows) {
+                    out_row = static_cast<size_t>(grp.y_rows[m]);
+                }
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN;
             if constexpr (MODE == kGroupedSwiGLU) {
@@ -405,7 +414,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     tc::tmem_ld_32x32(t_row + BN / 2 + c, ru);
                     tc::tmem_ld_wait();
                     if (row_ok && out0 + c < out_n) {
-                        ActT* dst = y + out_row * out_n + out0 + c;
+                        ActT* dst = out_base + out_row * out_n + out0 + c;
                         uint32_t packed[16];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -437,7 +446,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     tc::tmem_ld_32x32(t_row + c, r);
                     tc::tmem_ld_wait();
                     if (row_ok && n0 + c < N) {
-                        ActT* dst = y + out_row * N + n0 + c;
+                        ActT* dst = out_base + out_row * N + n0 + c;
                         if (n0 + c + 32 <= N) {
                             uint32_t packed[16];
 #pragma unroll
@@ -502,7 +511,7 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
         EQ_LAUNCH_OK("gather_cols_kernel");
         x = gathered;
     }
-    const GroupArgs none = {nullptr, nullptr, nullptr, 0};
+    const GroupArgs none = {nullptr, nullptr, nullptr, nullptr, 0};
     if (M <= 128)
         return launch_cfg<ActT, 1, 64, 4, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 128)), stream);
     if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
@@ -527,8 +536,8 @@ int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* p
 // swiglu: N is the width of the [gate | up] weight and y has N / 2 columns.  max_blocks bounds the grid.
 int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
                               int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
-                              const int32_t* y_rows, bool swiglu, int* status, cudaStream_t stream) {
-    const GroupArgs grp = {blocks, n_blocks, y_rows, expert_stride};
+                              const int32_t* y_rows, const uint64_t* y_ptrs, bool swiglu, int* status, cudaStream_t stream) {
+    const GroupArgs grp = {blocks, n_blocks, y_rows, y_ptrs, expert_stride};
     const unsigned gy = static_cast<unsigned>(max_blocks);
     if (act_dtype == EQ_F16) {
         const __half* xa = static_cast<const __half*>(x);

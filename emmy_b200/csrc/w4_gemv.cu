@@ -145,6 +145,7 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         p.scale_dtype = scale_dtype;
         p.x_rows = nullptr;
         p.y_rows = nullptr;
+        p.y_ptrs = nullptr;
         int st;
         if (mb <= 16 && static_cast<long long>(N / 16) * (K / 128) < (1LL << 30))
             st = w4_stream_launch(p, act_dtype, stream);  // decode-shaped: one wave of equal spans

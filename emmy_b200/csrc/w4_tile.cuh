@@ -25,6 +25,7 @@ struct W4Params {
     int span_base, span_rem;  // stream kernel: items per warp, plus one for the first span_rem warps
     const int32_t* x_rows;    // optional: activation row m of the problem is row x_rows[m] of x (gather)
     const int32_t* y_rows;    // optional: output row m of the problem is row y_rows[m] of y (scatter)
+    const uint64_t* y_ptrs;   // optional (unsplit tiles only): output row m starts at address y_ptrs[m], possibly on a peer GPU
 };
 
 // A run of rows of one expert in an expert-ordered row list (grouped expert GEMMs).
@@ -250,8 +251,12 @@ __device__ __forceinline__ void w4_tile(const W4Params& p, int tile, int split, 
         for (int idx = threadIdx.x; idx < cells; idx += kTileThreads) {
             const int m = idx >> 4, n = idx & 15;
             const float v = red[0][m][n] + red[1][m][n] + red[2][m][n] + red[3][m][n];
-            const size_t yr = p.y_rows ? static_cast<size_t>(p.y_rows[m]) : static_cast<size_t>(m);
-            y[yr * p.N + n_base + n] = from_float<ActT>(v);
+            if (p.y_ptrs) {
+                reinterpret_cast<ActT*>(p.y_ptrs[m])[n_base + n] = from_float<ActT>(v);
+            } else {
+                const size_t yr = p.y_rows ? static_cast<size_t>(p.y_rows[m]) : static_cast<size_t>(m);
+                y[yr * p.N + n_base + n] = from_float<ActT>(v);
+            }
         }
         return;
     }

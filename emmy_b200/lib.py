@@ -22,6 +22,24 @@ EQ_W4_AWQ, EQ_W4_GPTQ = 0, 1
 EQ_F16, EQ_BF16, EQ_F32 = 0, 1, 2
 
 
+EQ_EP_MAX_RANKS = 8
+
+
+class EpPeers(C.Structure):
+    """struct eq_ep_peers of include/emmyq.h."""
+
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("cap", C.c_int64),
+        ("recv_x", C.c_void_p * EQ_EP_MAX_RANKS),
+        ("recv_meta", C.c_void_p * EQ_EP_MAX_RANKS),
+        ("recv_count", C.c_void_p * EQ_EP_MAX_RANKS),
+        ("back", C.c_void_p * EQ_EP_MAX_RANKS),
+        ("flags", C.c_void_p * EQ_EP_MAX_RANKS),
+    ]
+
+
 class EmmyqError(RuntimeError):
     """A C-ABI call returned a negative status."""
 
@@ -84,6 +102,9 @@ def load() -> C.CDLL:
         "eq_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, i64, i, p, p, sz, p]),
         "eq_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),
         "eq_w4a16_linear_noalloc": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p]),
+        "eq_ep_moe_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),
+        "eq_ep_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, p, i64, i, p, C.POINTER(EpPeers), C.c_uint32, p, sz, p]),
+        "eq_ep_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -7,9 +7,11 @@ Three partitions, as the path shards naturally:
   all-gathered on request);
 * row-parallel linear: rank r keeps input rows [r K/W, (r+1) K/W) on group boundaries, computes a full [M, N]
   partial from its slice of x, and the partials are summed by one all-reduce over NVLink;
-* expert-parallel MoE: expert e lives on rank e // (E / W); picks are dispatched to their experts' ranks by one
-  all-to-all, run through the local grouped expert FFN, returned by a second all-to-all and combined at the source
-  in ascending expert order in f32.
+* expert-parallel MoE: expert e lives on rank e // (E / W); picks are dispatched to their experts' ranks, run
+  through the local grouped expert FFN, returned and combined at the source in ascending expert order in f32.
+  Two exchanges exist: `ep_moe_forward` uses NCCL all-to-alls (and runs on gloo for the CPU tests); `EpMoe` lets the
+  CUDA kernels do the exchange themselves over NVLink peer mappings (eq_ep_moe_w4a16): no host read, no NCCL call on
+  the data path.
 
 The reference shards differently -- every rank holds a 1/W slice of EVERY expert's intermediate axis and the
 partials are all-reduced (expert_intermediate_slice / slice_routed_experts,
@@ -180,3 +182,82 @@ def ep_moe_forward(
     out_rows[order] = back  # undo the grouping by destination
     del rank
     return combine_fn(out_rows, scores)
+
+
+# ---------------------------------------------------------------------------------------------- peer-memory exchange
+
+
+class EpMoe:
+    """Expert-parallel W4A16 MoE whose token exchange is done by the kernels over peer memory (eq_ep_moe_w4a16).
+
+    Owns one symmetric buffer per rank (receive rows, their metadata and counts, returned rows, epoch flags), mapped
+    into every rank of `group` through torch symmetric memory, and a local workspace.  `t_max` bounds the tokens of a
+    call on any rank; `cap` (rows one source may send to one destination) defaults to twice the balanced share plus
+    slack, or all picks when the group is small; rows beyond it are dropped and reported by `status()`."""
+
+    def __init__(self, group, t_max: int, topk: int, hidden: int, inter: int, experts_local: int, dtype, device, cap: int | None = None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only, no NVLS binding
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import lib as L
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > L.EQ_EP_MAX_RANKS:
+            raise ValueError(f"at most {L.EQ_EP_MAX_RANKS} ranks")
+        picks = t_max * topk
+        if cap is None:
+            cap = picks if self.world <= 2 else min(picks, 2 * picks // self.world + 256)
+        self.cap, self.t_max, self.topk, self.hidden, self.inter, self.experts_local = cap, t_max, topk, hidden, inter, experts_local
+        self.dtype, self.device = dtype, device
+        esz = 2
+        al = lambda v: (v + 255) // 256 * 256
+        sizes = [al(self.world * cap * hidden * esz), al(self.world * cap * 8), al(self.world * 4), al(picks * hidden * esz), al(2 * self.world * 4)]
+        offs = [0]
+        for sz in sizes[:-1]:
+            offs.append(offs[-1] + sz)
+        self.buf = symm_mem.empty(offs[-1] + sizes[-1], dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        torch.cuda.synchronize(device)
+        self.handle.barrier()
+        peers = L.EpPeers()
+        peers.world, peers.rank, peers.cap = self.world, self.rank, cap
+        for r in range(self.world):
+            base = int(self.handle.buffer_ptrs[r])
+            peers.recv_x[r], peers.recv_meta[r], peers.recv_count[r] = base + offs[0], base + offs[1], base + offs[2]
+            peers.back[r], peers.flags[r] = base + offs[3], base + offs[4]
+        self.peers = peers
+        self.lib = L
+        need = L.load().eq_ep_moe_workspace_bytes(self.world, cap, experts_local, hidden, inter)
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)
+        self.epoch = 0
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, w, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x [T, H] this rank's tokens; ids int32 [T, k] / scores f32 [T, k] over all experts; w: the local experts."""
+        import ctypes as C
+
+        from .ops import _DTYPE, _ptr, _stream
+
+        t = x.shape[0]
+        if t > self.t_max:
+            raise ValueError(f"{t} tokens exceed the t_max={self.t_max} the buffers were sized for")
+        y = out if out is not None else torch.empty((t, self.hidden), dtype=x.dtype, device=x.device)
+        self.epoch += 1
+        L = self.lib
+        L.check(
+            L.load().eq_ep_moe_w4a16(
+                _ptr(w.gate_up), _ptr(w.down), _DTYPE[w.scale_dtype], self.experts_local, self.topk, self.hidden, self.inter, w.group,
+                _ptr(x), _ptr(ids), _ptr(scores), t, _DTYPE[x.dtype], _ptr(y), C.byref(self.peers), self.epoch, _ptr(self.workspace),
+                self.workspace.numel(), _stream(),
+            )
+        )
+        return y
+
+    def status(self) -> None:
+        """Synchronizes the stream; raises if a peer wait ran out or rows overflowed the receive capacity."""
+        from .ops import _ptr, _stream
+
+        self.lib.check(self.lib.load().eq_ep_moe_status(_ptr(self.workspace), self.world, self.cap, self.experts_local, self.hidden, self.inter, _stream()))

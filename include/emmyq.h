@@ -227,6 +227,35 @@ int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, i
 /* Synchronizes the stream; EQ_ERR_BAD_ARG if the last call met an expert id outside [0, E) (such rows are dropped). */
 int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I, void* stream);
 
+/* ------------------------------------------------------------------ expert-parallel MoE over peer memory */
+
+/* Experts sharded E_local per rank over `world` GPUs of one node.  The token exchange of the reference's expert
+ * sharding (tests/serving/test_expert_sharding.py:49-165 pin its host-side split; the dispatch itself is an NCCL
+ * all-to-all in the reference's stack) is done here by the kernels: rows are stored into the owner's receive buffer
+ * and results stored back into the token's rank over NVLink peer mappings, ordered by epoch flags.  Every pointer
+ * below is a device address valid ON THE CALLING RANK (its own buffer, or a peer's buffer mapped into this
+ * process, e.g. through CUDA IPC or torch symmetric memory); entry r describes rank r's buffers. */
+#define EQ_EP_MAX_RANKS 8
+typedef struct eq_ep_peers {
+    int32_t world, rank;
+    int64_t cap;                          /* rows one source may send to one destination in one call */
+    void* recv_x[EQ_EP_MAX_RANKS];        /* [world][cap][H] activation rows, written by the sources */
+    int32_t* recv_meta[EQ_EP_MAX_RANKS];  /* [world][cap][2]: local expert id, return slot (pick index at the source) */
+    int32_t* recv_count[EQ_EP_MAX_RANKS]; /* [world]: rows each source sent */
+    void* back[EQ_EP_MAX_RANKS];          /* [T_max * topk][H]: expert outputs in the owner's pick order */
+    uint32_t* flags[EQ_EP_MAX_RANKS];     /* [2][world] uint32, zero before the first call */
+} eq_ep_peers;
+
+size_t eq_ep_moe_workspace_bytes(int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I);
+/* One routed layer on this rank's T tokens (ids / scores as eq_moe_route returns them, over all E_local * world
+ * experts).  Collective: every rank of the group calls it with the same epoch, which must grow by one per call and
+ * start at 1.  The workspace is local, zero on first use.  Waits on peers are bounded (about one second). */
+int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E_local, int64_t topk, int64_t H,
+                    int64_t I, int64_t G, const void* x, const int32_t* ids, const float* scores, int64_t T, int act_dtype,
+                    void* y, const eq_ep_peers* peers, uint32_t epoch, void* workspace, size_t workspace_bytes, void* stream);
+/* EQ_ERR_TIMEOUT when a peer did not arrive in time, EQ_ERR_UNSUPPORTED when rows overflowed `cap`. */
+int eq_ep_moe_status(const void* workspace, int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

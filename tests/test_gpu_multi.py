@@ -44,6 +44,20 @@ def _worker(rank, world, port, ret):
                                  lambda out_rows, sc: om.moe_combine(out_rows, sc, k)).float()
         ret[rank] = float((y - ref).abs().max() / ref.abs().max())
 
+        # the same layer with the exchange done by the kernels over peer memory, twice (the epoch flags must carry over)
+        ep = shard.EpMoe(None, 300, k, h, inter, per, torch.bfloat16, torch.device("cuda", rank))
+        y1 = ep.forward(x, ids, scores, local).float()
+        ep.status()
+        ret[30 + rank] = float((y1 - ref).abs().max() / ref.abs().max())
+        t2 = 300 - 7 * rank  # ranks need not hold the same number of tokens
+        x2 = torch.from_numpy(synth.activations(t2, h, "bf16", seed=70 + rank)).bfloat16().cuda()
+        logits2 = torch.randn(t2, e, generator=torch.Generator().manual_seed(80 + rank)).cuda()
+        ref2 = om.moe_forward(x2, logits2, full, k).float()
+        ids2, scores2 = om.moe_route(logits2, k)
+        y2 = ep.forward(x2, ids2, scores2, local).float()
+        ep.status()
+        ret[40 + rank] = float((y2 - ref2).abs().max() / ref2.abs().max())
+
         kk, n = 512, 256
         qw, qz, sc, gi = synth.gptq_linear(kk, n, seed=9)
         tq = [torch.from_numpy(a) for a in (qw, qz, sc, gi)]
@@ -72,5 +86,6 @@ def test_sharded_paths_on_two_gpus():
         mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
         out = dict(ret)
     assert all(out[r] < 1e-2 for r in range(world)), out            # EP == single device up to f32 summation order
+    assert all(out[30 + r] < 1e-2 and out[40 + r] < 1e-2 for r in range(world)), out  # peer-memory exchange
     assert all(out[10 + r] == 0.0 for r in range(world)), out      # column shards are the same columns
     assert all(out[20 + r] < 1e-2 for r in range(world)), out      # row partials summed in f32
