@@ -271,8 +271,9 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-# dram bytes per launch of the GEMV kernel from the ncu capture summarised under profiles/ (None until captured)
-TRAFFIC_PER_LAUNCH = None
+# dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of three launches of this
+# workload) from the ncu capture summarised in profiles/w4a16_stream_kernel_gptq_m1.md
+TRAFFIC_PER_LAUNCH = 31224000
 
 
 # --------------------------------------------------------------------------------------------- other workloads
