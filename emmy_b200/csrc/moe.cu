@@ -161,15 +161,76 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ counts, int E, int b
 // row_ptr (optional): the address output row r goes to; dst_ptr[pos] carries it into expert order.
 __global__ void moe_scatter_kernel(const int32_t* __restrict__ eid, const int32_t* __restrict__ src_row, int R, int E,
                                    const int32_t* __restrict__ offsets, int32_t* __restrict__ cursor, int32_t* __restrict__ src_of,
-                                   int32_t* __restrict__ dst_of, const uint64_t* __restrict__ row_ptr, uint64_t* __restrict__ dst_ptr) {
+                                   int32_t* __restrict__ dst_of, const uint64_t* __restrict__ row_ptr, uint64_t* __restrict__ dst_ptr,
+                                   int src_div) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= R) return;
     const int e = eid[r];
     if (e < 0 || e >= E) return;
     const int pos = offsets[e] + atomicAdd(cursor + e, 1);
-    src_of[pos] = src_row ? src_row[r] : r;
+    src_of[pos] = src_row ? src_row[r] : (src_div > 0 ? r / src_div : r);
     dst_of[pos] = r;
     if (row_ptr) dst_ptr[pos] = row_ptr[r];
+}
+
+// The three kernels above in one CTA, for row counts where the launches cost more than the work.
+constexpr int kSmallPlanRows = 8192;
+__global__ void moe_plan_small_kernel(const int32_t* __restrict__ eid, const int32_t* __restrict__ src_row, int src_div, int R, int E, int block_rows,
+                                      int32_t* __restrict__ offsets, RowBlock* __restrict__ blocks, int32_t* __restrict__ n_blocks, int max_blocks,
+                                      int32_t* __restrict__ src_of, int32_t* __restrict__ dst_of, const uint64_t* __restrict__ row_ptr,
+                                      uint64_t* __restrict__ dst_ptr, int32_t* __restrict__ status) {
+    extern __shared__ int32_t sh[];  // counts -> cursors [E], offsets [E], block offsets [E]
+    int32_t* cnt = sh;
+    int32_t* off = sh + E;
+    int32_t* boff = sh + 2 * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+        const int e = eid[r];
+        if (e == -1) continue;
+        if (e < 0 || e >= E)
+            atomicExch(status, kBadExpertId);
+        else
+            atomicAdd(cnt + e, 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t run = 0, brun = 0;
+        for (int e = 0; e < E; ++e) {
+            off[e] = run;
+            boff[e] = brun;
+            run += cnt[e];
+            brun += (cnt[e] + block_rows - 1) / block_rows;
+        }
+        offsets[E] = run;
+        *n_blocks = brun < max_blocks ? brun : max_blocks;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        offsets[e] = off[e];
+        const int32_t c = cnt[e];
+        for (int32_t b = 0, r = 0; r < c; ++b, r += block_rows) {
+            if (boff[e] + b < max_blocks) {
+                RowBlock rb;
+                rb.expert = e;
+                rb.row0 = off[e] + r;
+                rb.rows = min(block_rows, c - r);
+                rb.pad = 0;
+                blocks[boff[e] + b] = rb;
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;  // now the cursors
+    __syncthreads();
+    for (int r = threadIdx.x; r < R; r += blockDim.x) {
+        const int e = eid[r];
+        if (e < 0 || e >= E) continue;
+        const int pos = off[e] + atomicAdd(cnt + e, 1);
+        src_of[pos] = src_row ? src_row[r] : (src_div > 0 ? r / src_div : r);
+        dst_of[pos] = r;
+        if (row_ptr) dst_ptr[pos] = row_ptr[r];
+    }
 }
 
 // xp[pos][:] = x[src_of[pos]][:], 16 bytes per thread.
@@ -318,18 +379,25 @@ static int launch_grouped(const GroupedParams& gp, int block_rows, int max_block
 // out[r] = down_e( silu(gate_e(x)) * up_e(x) ).
 template <typename ActT>
 static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t H,
-                           int64_t I, const void* x, const int32_t* src_row, const int32_t* eid, int64_t R, void* out,
+                           int64_t I, const void* x, const int32_t* src_row, int src_div, const int32_t* eid, int64_t R, void* out,
                            const uint64_t* row_ptr, cudaStream_t stream) {
     const int br = block_rows_for(R, E);
-    EQ_CUDA_OK(cudaMemsetAsync(w.counts, 0, E * 4, stream));
-    moe_count_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, static_cast<int>(R), static_cast<int>(E), w.counts, w.status);
-    EQ_LAUNCH_OK("moe_count_kernel");
-    moe_plan_kernel<<<1, 256, 2 * E * sizeof(int32_t), stream>>>(w.counts, static_cast<int>(E), br, w.offsets, w.cursor, w.blocks, w.n_blocks,
-                                                                 w.max_blocks);
-    EQ_LAUNCH_OK("moe_plan_kernel");
-    moe_scatter_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, src_row, static_cast<int>(R), static_cast<int>(E), w.offsets,
-                                                                                  w.cursor, w.src_of, w.dst_of, row_ptr, w.dst_ptr);
-    EQ_LAUNCH_OK("moe_scatter_kernel");
+    if (R <= kSmallPlanRows) {
+        moe_plan_small_kernel<<<1, 1024, 3 * E * sizeof(int32_t), stream>>>(eid, src_row, src_div, static_cast<int>(R), static_cast<int>(E), br, w.offsets,
+                                                                            w.blocks, w.n_blocks, w.max_blocks, w.src_of, w.dst_of, row_ptr, w.dst_ptr,
+                                                                            w.status);
+        EQ_LAUNCH_OK("moe_plan_small_kernel");
+    } else {
+        EQ_CUDA_OK(cudaMemsetAsync(w.counts, 0, E * 4, stream));
+        moe_count_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, static_cast<int>(R), static_cast<int>(E), w.counts, w.status);
+        EQ_LAUNCH_OK("moe_count_kernel");
+        moe_plan_kernel<<<1, 256, 2 * E * sizeof(int32_t), stream>>>(w.counts, static_cast<int>(E), br, w.offsets, w.cursor, w.blocks, w.n_blocks,
+                                                                     w.max_blocks);
+        EQ_LAUNCH_OK("moe_plan_kernel");
+        moe_scatter_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(eid, src_row, static_cast<int>(R), static_cast<int>(E), w.offsets,
+                                                                                      w.cursor, w.src_of, w.dst_of, row_ptr, w.dst_ptr, src_div);
+        EQ_LAUNCH_OK("moe_scatter_kernel");
+    }
     if (tensor_path(R, E)) {
         // rows into expert order (the region of the second GEMM's output in the workspace is free until then)
         const int act = sizeof(ActT) == 2 && std::is_same<ActT, __half>::value ? EQ_F16 : EQ_BF16;
@@ -555,13 +623,8 @@ extern "C" int eq_moe_experts_w4a16(const void* wq_gate_up, const void* wq_down,
     MoeWorkspace w = carve(workspace, R, E, 1, H, I);
     EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
     if (act_dtype == EQ_F16)
-        return experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, nullptr, stream);
-    return experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, expert_ids, R, out, nullptr, stream);
-}
-
-__global__ void moe_src_rows_kernel(int32_t* src_row, int R, int topk) {
-    const int r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r < R) src_row[r] = r / topk;
+        return experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, 0, expert_ids, R, out, nullptr, stream);
+    return experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, src_row, 0, expert_ids, R, out, nullptr, stream);
 }
 
 extern "C" int eq_moe_combine(const void* out_rows, const float* scores, int64_t T, int64_t topk, int64_t H, int act_dtype, void* y, void* stream_) {
@@ -598,12 +661,10 @@ extern "C" int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int sca
     EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
     st = eq_moe_route(router_logits, T, E, topk, 1, w.ids, w.scores, stream_);
     if (st != EQ_OK) return st;
-    moe_src_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(w.src_row, static_cast<int>(R), static_cast<int>(topk));
-    EQ_LAUNCH_OK("moe_src_rows_kernel");
     if (act_dtype == EQ_F16)
-        st = experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, nullptr, stream);
+        st = experts_forward<__half>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, nullptr, static_cast<int>(topk), w.ids, R, w.out, nullptr, stream);
     else
-        st = experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, w.src_row, w.ids, R, w.out, nullptr, stream);
+        st = experts_forward<__nv_bfloat16>(w, wq_gate_up, wq_down, scale_dtype, E, H, I, x, nullptr, static_cast<int>(topk), w.ids, R, w.out, nullptr, stream);
     if (st != EQ_OK) return st;
     return eq_moe_combine(w.out, w.scores, T, topk, H, act_dtype, y, stream_);
 }
@@ -662,10 +723,10 @@ extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int 
                                                                                       w.src_row, w.row_ptr, w.moe.status);
     EQ_LAUNCH_OK("ep_build_rows_kernel");
     if (act_dtype == EQ_F16)
-        st = experts_forward<__half>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, w.eid, R, w.moe.out,
+        st = experts_forward<__half>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, 0, w.eid, R, w.moe.out,
                                      w.row_ptr, stream);
     else
-        st = experts_forward<__nv_bfloat16>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, w.eid, R,
+        st = experts_forward<__nv_bfloat16>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, 0, w.eid, R,
                                             w.moe.out, w.row_ptr, stream);
     if (st != EQ_OK) return st;
     ep_signal_done_kernel<<<1, 32, 0, stream>>>(*peers, epoch);

@@ -132,10 +132,22 @@ struct GroupArgs {
     size_t expert_stride;    // bytes between the experts' repacked weights
 };
 
-template <typename ActT, int HALVES, int BN, int DW, int AHEAD, bool CVT, int MODE>
+// SPLIT (plain mode only): gridDim.z CTAs share one output tile, each contracting a run of whole items of K.  Partial
+// sums meet in an f32 scratch [M][N] by vector reductions; the CTA whose arrival completes the tile converts it, stores y
+// and leaves scratch and counter zero.  Nobody waits.
+struct SplitArgs {
+    float* partial;     // [M][N], zero between calls
+    int* counters;      // one per column tile of this kernel, zero between calls
+};
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <typename ActT, int HALVES, int BN, int DW, int AHEAD, bool CVT, int MODE, bool SPLIT = false>
 __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const unsigned char* __restrict__ wq, ActT* __restrict__ y,
-                         int M, int N, int K, int* __restrict__ status, const GroupArgs grp) {
+                         int M, int N, int K, int* __restrict__ status, const GroupArgs grp, const SplitArgs split) {
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     constexpr int kStages = Cfg::kStages;
     constexpr int kAhead = Cfg::kAhead;
@@ -160,8 +172,15 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         m_end = rb.row0 + rb.rows;
         wq += static_cast<size_t>(rb.expert) * grp.expert_stride;
     }
-    const int k_blocks = K / kGK;
     const int items = K / 128;
+    // this CTA's run of items (all of K unless SPLIT), in K steps of 64
+    int item_lo = 0, item_hi = items;
+    if constexpr (SPLIT) {
+        item_lo = static_cast<int>(static_cast<long long>(items) * blockIdx.z / gridDim.z);
+        item_hi = static_cast<int>(static_cast<long long>(items) * (blockIdx.z + 1) / gridDim.z);
+    }
+    const int kb_lo = 2 * item_lo;
+    const int k_blocks = 2 * (item_hi - item_lo);
     const bool two_halves = HALVES == 2 && m_end - m0 > 128;
 
     if (threadIdx.x == 0) {
@@ -199,7 +218,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 TR_END(tma_wait);
                 const uint32_t bar = full_a_addr + 8 * stage;
                 tc::mbar_expect_tx(bar, Cfg::kTileA);
-                tc::tma_load_2d(a_base + stage * Cfg::kTileA, &map_x, kb * kGK, m0, bar);
+                tc::tma_load_2d(a_base + stage * Cfg::kTileA, &map_x, (kb_lo + kb) * kGK, m0, bar);
                 if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1;
@@ -271,16 +290,17 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
             }
             live[nt] = tile < N / 16;
             const unsigned char* rec = wq + static_cast<size_t>(live[nt] ? tile : 0) * items * kItemBytes;
-            wp[nt] = rec + h * 512 + (4 * g + jj) * 16;
-            mp[nt] = rec + 1024 + g * 8;
+            wp[nt] = rec + static_cast<size_t>(item_lo) * kItemBytes + h * 512 + (4 * g + jj) * 16;
+            mp[nt] = rec + static_cast<size_t>(item_lo) * kItemBytes + 1024 + g * 8;
             off_lo[nt] = static_cast<uint32_t>((tile_in_cta * 16 + g) * kRowBytes + (((4 * jj + h) ^ g) << 4));
         }
         // register ring of whole items (two K steps each)
         uint4 w0[kAhead][Cfg::kTilesPerWarp], w1[kAhead][Cfg::kTilesPerWarp];
         uint2 meta[kAhead][Cfg::kTilesPerWarp];
+        const int my_items = item_hi - item_lo;
 #pragma unroll
         for (int d = 0; d < kAhead; ++d) {
-            if (d < items) {
+            if (d < my_items) {
 #pragma unroll
                 for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
                     w0[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes);
@@ -296,11 +316,11 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         TR_DECL(dq_work);
         TR_DECL(dq_const);
         TR_DECL(dq_refill);
-        for (int it0 = 0; it0 < items && !broken; it0 += kAhead) {
+        for (int it0 = 0; it0 < my_items && !broken; it0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
                 const int it = it0 + d;
-                if (it >= items || broken) continue;
+                if (it >= my_items || broken) continue;
                 // the item's constants: exact-dequant zero terms and the scale pair of columns g and g + 8
                 TR_BEGIN(dq_const);
                 typename Frag<ActT>::Zero z_lo[Cfg::kTilesPerWarp], z_hi[Cfg::kTilesPerWarp];
@@ -360,7 +380,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     TR_END(dq_work);
                 }
                 TR_BEGIN(dq_refill);
-                if (it + kAhead < items) {  // refill this ring slot
+                if (it + kAhead < my_items) {  // refill this ring slot
 #pragma unroll
                     for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
                         const size_t off = static_cast<size_t>(it + kAhead) * kItemBytes;
@@ -439,6 +459,26 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         }
                     }
                 }
+            } else if constexpr (SPLIT) {
+#pragma unroll 1
+                for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(t_row + c, r);
+                    tc::tmem_ld_wait();
+                    if (row_ok && n0 + c < N) {
+                        float* dst = split.partial + static_cast<size_t>(m) * N + n0 + c;
+                        if (n0 + c + 32 <= N) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                red_add_v4(dst + 4 * v, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
+                                           __uint_as_float(r[4 * v + 3]));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n0 + c + i < N) atomicAdd(dst + i, __uint_as_float(r[i]));
+                        }
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
@@ -465,6 +505,31 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         }
                     }
                 }
+            }
+        }
+        if constexpr (SPLIT) {
+            // the epilogue warps of this CTA meet, one of them counts the CTA in; the last CTA of the tile finishes it
+            __shared__ int s_last;
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(Cfg::kDequantWarps * 32) : "memory");
+            if (dw == 0 && lane == 0) s_last = atomicAdd(split.counters + blockIdx.x, 1) == static_cast<int>(gridDim.z) - 1;
+            asm volatile("bar.sync 1, %0;" ::"n"(Cfg::kDequantWarps * 32) : "memory");
+            if (s_last) {
+                __threadfence();
+                const int rows = min(m_end - m0, 128 * HALVES);
+                const int cols = min(BN, N - n0);  // multiples of 16
+                for (int idx = (dw * 32 + lane) * 4; idx < rows * cols; idx += Cfg::kDequantWarps * 32 * 4) {
+                    const int rr = idx / cols, cc = idx - rr * cols;
+                    float4* src = reinterpret_cast<float4*>(split.partial + static_cast<size_t>(m0 + rr) * N + n0 + cc);
+                    const float4 v = __ldcg(src);
+                    __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+                    const ActT o0 = from_float<ActT>(v.x), o1 = from_float<ActT>(v.y), o2 = from_float<ActT>(v.z), o3 = from_float<ActT>(v.w);
+                    uint2 pk;
+                    pk.x = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) | (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                    pk.y = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o2)) | (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o3)) << 16);
+                    *reinterpret_cast<uint2*>(y + static_cast<size_t>(m0 + rr) * N + n0 + cc) = pk;
+                }
+                if (dw == 0 && lane == 0) split.counters[blockIdx.x] = 0;
             }
         }
         TR_END(epi_work);
@@ -497,14 +562,46 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
     auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true, MODE> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false, MODE>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
     dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), grid_y);
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, grp);
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, grp,
+                                                        SplitArgs{nullptr, nullptr});
     EQ_LAUNCH_OK("w4a16_gemm_tc_kernel");
+    return EQ_OK;
+}
+
+// M <= 128: 128 x 256 tiles with K split over gridDim.z so that about one CTA per SM runs.
+template <typename ActT>
+int launch_split(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y, int64_t M, int64_t N, int64_t K, int* status,
+                 float* partial, int* counters, cudaStream_t stream) {
+    using Cfg = GemmCfg<1, 256, 16, 2>;
+    CUtensorMap map_x;
+    const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    const int64_t tiles = ceil_div(N, 256), items = K / 128;
+    int64_t splits = sm_count() / tiles;
+    if (splits > items) splits = items;
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
+    const bool cvt = scale_dtype != (ScaleMul<ActT>::kFmt == 0 ? EQ_F16 : EQ_BF16);
+    const GroupArgs none = {nullptr, nullptr, nullptr, nullptr, 0};
+    const SplitArgs sp = {partial, counters};
+    dim3 grid(static_cast<unsigned>(tiles), 1, static_cast<unsigned>(splits));
+    if (splits == 1) {
+        auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, false> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, false>;
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+        kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, none, sp);
+    } else {
+        auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, true> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, true>;
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+        kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, none, sp);
+    }
+    EQ_LAUNCH_OK("w4a16_gemm_tc_kernel (split K)");
     return EQ_OK;
 }
 
 template <typename ActT>
 int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, const ActT* x, ActT* y, int64_t M, int64_t N,
-                 int64_t K, ActT* gathered, int* status, cudaStream_t stream) {
+                 int64_t K, ActT* gathered, int* status, float* partial, int* counters, cudaStream_t stream) {
     if (perm) {
         const int64_t total = M * K;
         gather_cols_kernel<ActT><<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, stream>>>(x, perm, M, K, gathered);
@@ -512,8 +609,12 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
         x = gathered;
     }
     const GroupArgs none = {nullptr, nullptr, nullptr, nullptr, 0};
-    if (M <= 128)
-        return launch_cfg<ActT, 1, 64, 4, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 128)), stream);
+    if (M <= 128) {
+        // wide matrices fill the SMs with 64-column tiles; narrow ones split K over 256-column tiles instead
+        if (ceil_div(N, 64) >= sm_count())
+            return launch_cfg<ActT, 1, 64, 4, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, 1, stream);
+        return launch_split<ActT>(wq, scale_dtype, x, y, M, N, K, status, partial, counters, stream);
+    }
     if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
         return launch_cfg<ActT, 2, 256, 16, 2, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
     return launch_cfg<ActT, 2, 128, 8, 3, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
@@ -522,13 +623,14 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
 }  // namespace
 
 // gathered: M * K elements of scratch when perm is given.  status: one word, set by a bounded wait that ran out.
+// partial / counters: f32 [min(M, 128)][N] and one int per 256 columns, zero between calls (used when M <= 128).
 int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
-                      int64_t K, int act_dtype, void* gathered, int* status, cudaStream_t stream) {
+                      int64_t K, int act_dtype, void* gathered, int* status, float* partial, int* counters, cudaStream_t stream) {
     if (act_dtype == EQ_F16)
         return launch_typed<__half>(wq, scale_dtype, perm, static_cast<const __half*>(x), static_cast<__half*>(y), M, N, K,
-                                    static_cast<__half*>(gathered), status, stream);
+                                    static_cast<__half*>(gathered), status, partial, counters, stream);
     return launch_typed<__nv_bfloat16>(wq, scale_dtype, perm, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), M,
-                                       N, K, static_cast<__nv_bfloat16*>(gathered), status, stream);
+                                       N, K, static_cast<__nv_bfloat16*>(gathered), status, partial, counters, stream);
 }
 
 // Grouped expert GEMM on the tensor path.  x: [R][K] activations in expert order; blocks / n_blocks: device-side list of

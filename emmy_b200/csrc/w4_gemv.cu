@@ -25,7 +25,7 @@ namespace eq {
 
 int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream);  // w4_stream.cu
 int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
-                      int64_t K, int act_dtype, void* gathered, int* status, cudaStream_t stream);  // w4_gemm.cu
+                      int64_t K, int act_dtype, void* gathered, int* status, float* partial, int* counters, cudaStream_t stream);  // w4_gemm.cu
 
 template <typename ActT, int MT, bool ONE>
 __global__ void __launch_bounds__(kTileThreads) w4a16_tile_kernel(const W4Params p) {
@@ -80,10 +80,11 @@ static int launch_w4(const W4Params& p, cudaStream_t stream) {
 
 using namespace eq;
 
-// Front part: f32 partial sums of up to 64 rows, one arrival counter per 16-column tile, one status word.  Calls with
+// Front part: f32 partial sums of up to 128 rows, one arrival counter per 16-column tile, one status word.  Calls with
 // M > 16 add room for the column-gathered copy of x that act-order weights need on the tensor path.
+static int64_t w4_front_rows(int64_t M) { return M < 128 ? M : 128; }
 static size_t w4_front_bytes(int64_t M, int64_t N) {
-    const int64_t rows = M < 64 ? M : 64;
+    const int64_t rows = w4_front_rows(M);
     return static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16 + 1) * sizeof(int);
 }
 static size_t w4_gather_offset(int64_t M, int64_t N) { return (w4_front_bytes(M, N) + 255) / 256 * 256; }
@@ -119,11 +120,13 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
 
     if (M > 16 && aligned(y, 16)) {
         // prefill-shaped: the tcgen05 kernel; its bounded waits report through the workspace's status word
-        const int64_t ws_rows = M < 64 ? M : 64;
-        int* status = reinterpret_cast<int*>(static_cast<float*>(workspace) + ws_rows * N) + N / 16;
+        const int64_t ws_rows = w4_front_rows(M);
+        float* partial = static_cast<float*>(workspace);
+        int* counters = reinterpret_cast<int*>(partial + ws_rows * N);
+        int* status = counters + N / 16;
         void* gathered = static_cast<unsigned char*>(workspace) + w4_gather_offset(M, N);
         return w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
-                                 stream);
+                                 partial, counters, stream);
     }
 
     const size_t esz = 2;
@@ -135,7 +138,7 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         p.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * K * esz;
         p.y = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
         p.wsp = static_cast<float*>(workspace);
-        const int64_t ws_rows = M < 64 ? M : 64;
+        const int64_t ws_rows = w4_front_rows(M);
         p.counters = reinterpret_cast<int*>(static_cast<float*>(workspace) + ws_rows * N);
         p.K = static_cast<int>(K);
         p.N = static_cast<int>(N);
@@ -161,7 +164,7 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
 extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     EQ_REQUIRE(workspace && M > 0 && N > 0, EQ_ERR_BAD_ARG, "eq_w4a16_status: bad arguments");
-    const int64_t ws_rows = M < 64 ? M : 64;
+    const int64_t ws_rows = w4_front_rows(M);
     const int* status = reinterpret_cast<const int*>(static_cast<const float*>(workspace) + ws_rows * N) + N / 16;
     int host = 0;
     EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));

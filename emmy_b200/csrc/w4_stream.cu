@@ -11,7 +11,7 @@
 
 namespace eq {
 
-constexpr int kStreamWarps = 32;        // one fat CTA per SM
+constexpr int kStreamWarps = 32;        // one fat CTA per SM (single-row calls; multi-row calls use half as many warps for twice the registers)
 #ifndef EQ_EXP_DEPTH
 #define EQ_EXP_DEPTH 4
 #endif
@@ -25,10 +25,10 @@ constexpr int kSlot = 1024 + 256;      // ring slot: 32 x 16 B + 32 x 16 B of ni
 __device__ unsigned long long g_w4_trace[4096 * 8];
 #define EQ_TRACE(slot)                                                                                            \
     do {                                                                                                          \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x * kStreamWarps + (threadIdx.x >> 5) < 4096) {                   \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x * 32 + (threadIdx.x >> 5) < 4096) {                             \
             unsigned long long t_;                                                                                \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                \
-            g_w4_trace[(blockIdx.x * kStreamWarps + (threadIdx.x >> 5)) * 8 + (slot)] = t_;                       \
+            g_w4_trace[(blockIdx.x * 32 + (threadIdx.x >> 5)) * 8 + (slot)] = t_;                                 \
         }                                                                                                         \
     } while (0)
 #else
@@ -133,8 +133,9 @@ __device__ __forceinline__ void stream_flush(const W4Params& p, float* acc_slot,
     }
 }
 
-template <typename ActT, int MT, bool ONE>
-__global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(const W4Params p) {
+template <typename ActT, int MT, bool ONE, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Params p) {
+    constexpr int kStreamWarps = WARPS;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     EQ_TRACE(0);
     constexpr int kRows = ONE ? 1 : MT * 8;
@@ -274,27 +275,28 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
 }
 
 // Shared memory the stream kernel needs for `tiles` column tiles on `ctas` CTAs, or 0 when it does not fit.
-static size_t stream_smem(long long tiles, long long ctas, int rows, int K) {
+static size_t stream_smem(long long tiles, long long ctas, int rows, int K, int warps) {
     const long long per_cta = ceil_div(tiles, ctas);
-    size_t bytes = static_cast<size_t>(kStreamWarps) * kStreamDepth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float);
+    size_t bytes = static_cast<size_t>(warps) * kStreamDepth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float);
     if (rows == 1) bytes += static_cast<size_t>(K) * 2 + static_cast<size_t>(K / 128) * sizeof(float2);  // staged x and its item sums
     return bytes <= 220 * 1024 ? bytes : 0;
 }
 
 template <typename ActT, int MT, bool ONE>
 static int launch_stream(W4Params p, cudaStream_t stream) {
+    constexpr int kWarps = ONE ? kStreamWarps : kStreamWarps / 2;
     const long long tiles = p.N / 16;
     long long ctas = sm_count();
     if (ctas > tiles) ctas = tiles;
     p.span_base = static_cast<int>(tiles / ctas);
     p.span_rem = static_cast<int>(tiles % ctas);
-    const size_t smem = stream_smem(tiles, ctas, ONE ? 1 : MT * 8, p.K);
+    const size_t smem = stream_smem(tiles, ctas, ONE ? 1 : MT * 8, p.K, kWarps);
     EQ_REQUIRE(smem > 0, EQ_ERR_UNSUPPORTED, "w4a16 stream kernel: accumulators do not fit shared memory");
-    auto kernel = w4a16_stream_kernel<ActT, MT, ONE>;
+    auto kernel = w4a16_stream_kernel<ActT, MT, ONE, kWarps>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
-    cfg.blockDim = dim3(kStreamWarps * 32);
+    cfg.blockDim = dim3(kWarps * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

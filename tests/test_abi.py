@@ -51,7 +51,7 @@ def test_bad_arguments_return_codes_not_crashes(eq):
     assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 128, one, 1, 2, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ARG
     assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 64, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_UNSUPPORTED
     assert eq.eq_w4a16_workspace_bytes(1, 4096, 4096) == 4096 * 4 + 257 * 4
-    front = 64 * 4096 * 4 + 257 * 4
+    front = 100 * 4096 * 4 + 257 * 4
     assert eq.eq_w4a16_workspace_bytes(100, 4096, 256) == (front + 255) // 256 * 256 + 100 * 256 * 2
 
 
