@@ -135,19 +135,29 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
 // A CTA computes a 256 x 256 output tile as two 128-row MMAs that share one B tile in shared memory: per byte
 // brought in from L2 that is 256 flop, against 170 for a 128 x 256 tile, and L2 -> SM bandwidth is what bounds
 // this kernel (a 128 x 256 tile needs ~19 TB/s of it at the tensor peak).  The two f32 accumulators fill TMEM.
-constexpr int kBM = 256, kBN = 256, kBK = 128;  // tile; kBK in bytes = e4m3 elements
-constexpr int kStages = 3;
-constexpr int kTileA = kBM * kBK, kTileB = kBN * kBK;
+// Calls with at most 128 rows (one row tile) run 128 x 128 tiles instead: twice as many CTAs stream the weight, deeper
+// stages, and two such CTAs fit an SM.
+constexpr int kBK = 128;  // K step in bytes = e4m3 elements
 constexpr int kEpilogueWarps = 8;
 constexpr int kGemmThreads = (2 + kEpilogueWarps) * 32;
-constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr uint32_t kTmemCols = 512;
 
-template <typename OutT>
+template <int HALVES, int BN>
+struct Fp8Cfg {
+    static constexpr int kBM = 128 * HALVES;
+    static constexpr int kTileA = kBM * kBK, kTileB = BN * kBK;
+    static constexpr int kStages = HALVES == 2 ? 3 : 6;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr uint32_t kTmemCols = HALVES * BN;
+};
+
+template <typename OutT, int HALVES, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     fp8_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const float* __restrict__ sx, const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K,
                        int* __restrict__ status) {
+    using Cfg = Fp8Cfg<HALVES, BN>;
+    constexpr int kBM = Cfg::kBM, kBN = BN, kTileA = Cfg::kTileA, kTileB = Cfg::kTileB, kStages = Cfg::kStages;
+    constexpr uint32_t kTmemCols = Cfg::kTmemCols;
     extern __shared__ unsigned char smem_raw[];
     // the swizzled tiles need 1024-byte alignment
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -162,7 +172,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
     const int k_blocks = K / kBK;
-    const bool two_halves = M - m0 > 128;  // the second 128 rows hold real rows
+    const bool two_halves = HALVES == 2 && M - m0 > 128;  // the second 128 rows hold real rows
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -220,9 +230,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too, so that the epilogue does not sit out its wait
         }
     } else {
-        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31; warps 2..5 take rows 0..127, 6..9 rows 128..255
+        // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31.  Two row halves: warps 2..5 take rows 0..127,
+        //      6..9 rows 128..255; one row half: the two quartets take half of the columns each.
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int quartet = (warp - 2) >> 2;
+        const int half = HALVES == 2 ? quartet : 0;
+        const int c_begin = HALVES == 2 ? 0 : quartet * (kBN / 2);
+        const int c_end = HALVES == 2 ? kBN : c_begin + kBN / 2;
         const int m = m0 + half * 128 + quarter * 32 + lane;
         const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
         if (!ok && lane == 0) atomicExch(status, 3);
@@ -230,7 +244,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (ok && (half == 0 || two_halves)) {
             const float row_scale = m < M ? sx[m] : 0.f;
 #pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
+            for (int c = c_begin; c < c_end; c += 32) {
                 uint32_t r[32];
                 tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kBN + c, r);
                 tc::tmem_ld_wait();
@@ -294,10 +308,28 @@ extern "C" size_t eq_fp8_workspace_bytes(int64_t M, int64_t K) {
     return align_up(static_cast<size_t>(M) * K, 256) + align_up(static_cast<size_t>(M) * sizeof(float), 256) + 256;
 }
 
+template <typename OutT, int HALVES, int BN>
+static int fp8_tc_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, OutT* y,
+                         int* status, cudaStream_t stream) {
+    using Cfg = Fp8Cfg<HALVES, BN>;
+    CUtensorMap map_a, map_b;
+    int st = make_tensor_map_2d(&map_a, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, Cfg::kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    auto kernel = fp8_gemm_tc_kernel<OutT, HALVES, BN>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, Cfg::kBM)));
+    kernel<<<grid, kGemmThreads, Cfg::kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                                                       status);
+    EQ_LAUNCH_OK("fp8_gemm_tc_kernel");
+    return EQ_OK;
+}
+
 template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
-    if (M <= 64) {
+    if (M <= 16) {
         const unsigned grid = static_cast<unsigned>(N / 16);
         const int mt = static_cast<int>((M + 7) / 8);
         const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
@@ -308,18 +340,8 @@ static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64
         EQ_LAUNCH_OK("fp8_smallm_kernel");
         return EQ_OK;
     }
-    CUtensorMap map_a, map_b;
-    int st = make_tensor_map_2d(&map_a, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st != EQ_OK) return st;
-    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kBN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st != EQ_OK) return st;
-    auto kernel = fp8_gemm_tc_kernel<OutT>;
-    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
-    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
-    kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N),
-                                                     static_cast<int>(K), status);
-    EQ_LAUNCH_OK("fp8_gemm_tc_kernel");
-    return EQ_OK;
+    if (M <= 128) return fp8_tc_launch<OutT, 1, 128>(w, sw, N, K, qx, sx, M, y, status, stream);
+    return fp8_tc_launch<OutT, 2, 256>(w, sw, N, K, qx, sx, M, y, status, stream);
 }
 
 extern "C" int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,

@@ -96,15 +96,22 @@ __global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int
 }
 
 // ------------------------------------------------------------------------------------------------ tensor path
-constexpr int kBM = 128, kBN = 256;
+constexpr int kBM = 128;
 constexpr int kBKBytes = 128;                 // 256 e2m1 elements of K per stage row
-constexpr int kStages = 4;
-constexpr int kTileA = kBM * kBKBytes, kTileB = kBN * kBKBytes;
-constexpr int kSfA = 4 * 512, kSfB = 2 * 4 * 512;  // four k64 atoms per stage, one / two row blocks
-constexpr int kStageBytes = kTileA + kTileB + kSfA + kSfB;
+constexpr int kTileA = kBM * kBKBytes;
+constexpr int kSfA = 4 * 512;                 // four k64 atoms per stage, one row block
 constexpr int kGemmThreads = 192;
-constexpr size_t kGemmSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
-constexpr uint32_t kTmemCols = 512;           // 256 accumulator columns + 16 (SFA) + 32 (SFB), rounded to a power of two
+
+// BN = 256 for prefill-shaped calls; BN = 128 when there is a single row tile, so that twice as many CTAs stream the weight.
+template <int BN>
+struct Fp4Cfg {
+    static constexpr int kTileB = BN * kBKBytes;
+    static constexpr int kSfB = (BN / 128) * 4 * 512;  // one or two row blocks
+    static constexpr int kStageBytes = kTileA + kTileB + kSfA + kSfB;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
+    static constexpr uint32_t kTmemCols = BN == 256 ? 512 : 256;  // accumulator columns + 16 (SFA) + 16 or 32 (SFB), as a power of two
+};
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -112,11 +119,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  : "memory");
 }
 
-template <typename OutT>
+template <typename OutT, int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     nvfp4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ gx,
                          const float* __restrict__ gw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    using Cfg = Fp4Cfg<BN>;
+    constexpr int kBN = BN, kTileB = Cfg::kTileB, kSfB = Cfg::kSfB, kStages = Cfg::kStages;
+    constexpr uint32_t kTmemCols = Cfg::kTmemCols;
+    constexpr bool kTwoBlocks = BN == 256;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* tiles_a = smem;
@@ -164,15 +175,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 }
                 const uint32_t bar = tc::smem_u32(full + s);
                 // the second row block of B may lie beyond N (N not a multiple of 256): it is then not copied
-                const bool second = rb_b + 1 < n_rb;
-                tc::mbar_expect_tx(bar, kTileA + kTileB + kSfA + (second ? kSfB : kSfB / 2));
+                const bool second = kTwoBlocks && rb_b + 1 < n_rb;
+                constexpr int kSfBlock = 4 * 512;
+                tc::mbar_expect_tx(bar, kTileA + kTileB + kSfA + (second ? 2 * kSfBlock : kSfBlock));
                 tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBKBytes, m0, bar);
                 tc::tma_load_2d(tc::smem_u32(tiles_b + s * kTileB), &map_b, kb * kBKBytes, n0, bar);
                 bulk_g2s(tc::smem_u32(sfs_a + s * kSfA), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfA, bar);
-                bulk_g2s(tc::smem_u32(sfs_b + s * kSfB), sfb + (static_cast<size_t>(rb_b) * k64_blocks + kb * 4) * 512, kSfB / 2, bar);
+                bulk_g2s(tc::smem_u32(sfs_b + s * kSfB), sfb + (static_cast<size_t>(rb_b) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
                 if (second)
-                    bulk_g2s(tc::smem_u32(sfs_b + s * kSfB + kSfB / 2),
-                             sfb + (static_cast<size_t>(rb_b + 1) * k64_blocks + kb * 4) * 512, kSfB / 2, bar);
+                    bulk_g2s(tc::smem_u32(sfs_b + s * kSfB + kSfBlock),
+                             sfb + (static_cast<size_t>(rb_b + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
             }
         }
     } else if (warp == 1) {
@@ -193,7 +205,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 for (int ks = 0; ks < 4; ++ks) {
                     tc::tmem_cp_32x128b_warpx4(tmem_sfa + ks * 4, tc::smem_desc_sf(sfa_addr + ks * 512));
                     tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8, tc::smem_desc_sf(sfb_addr + ks * 512));
-                    tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8 + 4, tc::smem_desc_sf(sfb_addr + kSfB / 2 + ks * 512));
+                    if constexpr (kTwoBlocks) tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8 + 4, tc::smem_desc_sf(sfb_addr + 4 * 512 + ks * 512));
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
@@ -336,22 +348,22 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
     st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, kBN, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    const int bn = M <= 128 ? 128 : 256;
+    st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, bn, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
-    if (act_dtype == EQ_F16) {
-        auto kernel = nvfp4_gemm_tc_kernel<__half>;
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
-        kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2,
-                                                         static_cast<__half*>(y), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
-    } else {
-        auto kernel = nvfp4_gemm_tc_kernel<__nv_bfloat16>;
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)));
-        kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2,
-                                                         static_cast<__nv_bfloat16*>(y), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
-    }
-    EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
-    return EQ_OK;
+    dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
+    auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt, static_cast<int>(M),
+                                                    static_cast<int>(N), static_cast<int>(K), status);
+        EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
+        return EQ_OK;
+    };
+    if (act_dtype == EQ_F16)
+        return bn == 128 ? run(nvfp4_gemm_tc_kernel<__half, 128>, Fp4Cfg<128>::kSmem, static_cast<__half*>(y))
+                         : run(nvfp4_gemm_tc_kernel<__half, 256>, Fp4Cfg<256>::kSmem, static_cast<__half*>(y));
+    return bn == 128 ? run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 128>, Fp4Cfg<128>::kSmem, static_cast<__nv_bfloat16*>(y))
+                     : run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 256>, Fp4Cfg<256>::kSmem, static_cast<__nv_bfloat16*>(y));
 }
 
 extern "C" int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream_) {

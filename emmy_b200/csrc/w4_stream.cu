@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Par
     const unsigned char* rec = p.wq + first + lane * 16;
     const unsigned char* met = p.wq + first + 1024 + g * 8;  // lanes of one g share it
     const ActT* x = static_cast<const ActT*>(p.x);
+    EQ_TRACE(7);
 
     // ---- a per-warp ring of kStreamDepth items in shared memory, filled by per-lane asynchronous copies: lane L
     //      copies exactly the bytes lane L reads later (its 2 x 16 weight bytes and its 8-byte scale / zero entry), so
