@@ -420,7 +420,7 @@ def _wl_moe(device, rank, world, t, exchange="peer"):
         status = ep.status
     return dict(
         step=step, flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), calls=1, kernels_per_call=8, x=x, x_host=x_host,
-        y=y, graph=world == 1, metric="moe_w4a16_tflops", dtype="int4 expert weights, bf16 activations, f32 accumulate and combine",
+        y=y, graph=world == 1 or exchange == "peer", metric="moe_w4a16_tflops", dtype="int4 expert weights, bf16 activations, f32 accumulate and combine",
         peak_mult=1.0, kernel="moe_expert_gemm_kernel", status=status,
         workload=f"moe: routed W4A16 expert layer, Qwen3-30B-A3B shapes (128 experts, top-8, hidden 2048, intermediate 768, AWQ group 128), T={t} tokens per rank"
         + (f", experts sharded {local_e} per rank, " + ("all-to-all dispatch and return over NCCL" if exchange == "nccl" else
@@ -515,9 +515,12 @@ def run_other(args, rank, world, local_rank):
             end.record(stream)
             end.synchronize()
             dev_ms = start.elapsed_time(end)
+            # keep the clock sampler fed on short runs: the same number of extra steps on every rank (the steps may be collective)
+            feed = torch.tensor([dev_ms / args.steps], dtype=torch.float64, device=device)
+            if world > 1:
+                torch.distributed.all_reduce(feed, op=torch.distributed.ReduceOp.MAX)
             if dev_ms < 400:
-                t_end = time.time() + 0.4
-                while time.time() < t_end:
+                for _ in range(min(5000, int(400.0 / max(feed.item(), 1e-3)) + 1)):
                     run()
                 stream.synchronize()
         barrier()

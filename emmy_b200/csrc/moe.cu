@@ -473,8 +473,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 // return slot).  The last CTA to finish publishes the row counts and raises this rank's flag at every destination.
 __global__ void ep_dispatch_kernel(const eq_ep_peers pe, const uint4* __restrict__ x, const int32_t* __restrict__ ids, int picks, int topk,
                                    int per_rank, int row_vec, int32_t* __restrict__ send_cursor, int32_t* __restrict__ cta_done,
-                                   uint32_t epoch, int32_t* __restrict__ status) {
+                                   uint32_t epoch, const uint32_t* __restrict__ epoch_dev, int32_t* __restrict__ status) {
     __shared__ int s_last;
+    if (epoch == 0) epoch = *epoch_dev;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp < picks) {
         const int id = ids[warp];
@@ -513,8 +514,10 @@ __global__ void ep_dispatch_kernel(const eq_ep_peers pe, const uint4* __restrict
 }
 
 // which = 0: wait for every source's dispatch; 1: for every destination's results.
-__global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int world, int which, uint32_t epoch, int32_t* __restrict__ status) {
+__global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int world, int which, uint32_t epoch, const uint32_t* __restrict__ epoch_dev,
+                               int32_t* __restrict__ status) {
     if (static_cast<int>(threadIdx.x) >= world) return;
+    if (epoch == 0) epoch = *epoch_dev;
     const uint32_t* f = flags + which * world + threadIdx.x;
     const long long start = clock64();
     while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
@@ -549,8 +552,13 @@ __global__ void ep_build_rows_kernel(const eq_ep_peers pe, const int32_t* __rest
     row_ptr[r] = ptr;
 }
 
-__global__ void ep_signal_done_kernel(const eq_ep_peers pe, uint32_t epoch) {
+// The call counter kept on the device (epoch argument 0): every call bumps it once, in lockstep on all ranks, so a
+// captured graph of the layer can be replayed.
+__global__ void ep_next_epoch_kernel(uint32_t* epoch_dev) { *epoch_dev += 1; }
+
+__global__ void ep_signal_done_kernel(const eq_ep_peers pe, uint32_t epoch, const uint32_t* __restrict__ epoch_dev) {
     if (static_cast<int>(threadIdx.x) >= pe.world) return;
+    if (epoch == 0) epoch = *epoch_dev;
     __threadfence_system();
     st_release_sys(pe.flags[threadIdx.x] + pe.world + pe.rank, epoch);
 }
@@ -558,6 +566,7 @@ __global__ void ep_signal_done_kernel(const eq_ep_peers pe, uint32_t epoch) {
 struct EpWorkspace {
     MoeWorkspace moe;
     int32_t *send_cursor, *cta_done, *eid, *src_row;
+    uint32_t* epoch;
     uint64_t* row_ptr;
     size_t bytes;
 };
@@ -575,6 +584,7 @@ static EpWorkspace carve_ep(void* base, int64_t world, int64_t cap, int64_t e_lo
     };
     w.send_cursor = reinterpret_cast<int32_t*>(take(EQ_EP_MAX_RANKS * 4));
     w.cta_done = reinterpret_cast<int32_t*>(take(4));
+    w.epoch = reinterpret_cast<uint32_t*>(take(4));
     w.eid = reinterpret_cast<int32_t*>(take(R * 4));
     w.src_row = reinterpret_cast<int32_t*>(take(R * 4));
     w.row_ptr = reinterpret_cast<uint64_t*>(take(R * 8));
@@ -695,7 +705,7 @@ extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int 
     const int64_t world = peers->world, cap = peers->cap;
     int st = check_moe_shapes("eq_ep_moe_w4a16", E_local * world, topk, H, I, G);
     if (st != EQ_OK) return st;
-    EQ_REQUIRE(T >= 0 && epoch != 0, EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: negative token count or epoch 0");
+    EQ_REQUIRE(T >= 0, EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: negative token count");
     EQ_REQUIRE(wq_gate_up && wq_down && (T == 0 || (x && ids && scores && y)), EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: null pointer");
     EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_ep_moe_w4a16: activations must be f16 or bf16");
     EQ_REQUIRE(T == 0 || aligned(x, 16), EQ_ERR_BAD_ALIGN, "eq_ep_moe_w4a16: x must be 16-byte aligned");
@@ -711,12 +721,16 @@ extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int 
     const int64_t picks = T * topk, R = world * cap;
     const int row_vec = static_cast<int>(H * 2 / 16);
     EQ_CUDA_OK(cudaMemsetAsync(w.moe.status, 0, 4, stream));
+    if (epoch == 0) {
+        ep_next_epoch_kernel<<<1, 1, 0, stream>>>(w.epoch);
+        EQ_LAUNCH_OK("ep_next_epoch_kernel");
+    }
     // every rank launches the dispatch, with or without tokens of its own: its flag is what the others wait for
     const unsigned dgrid = static_cast<unsigned>(picks > 0 ? ceil_div(picks * 32, 256) : 1);
     ep_dispatch_kernel<<<dgrid, 256, 0, stream>>>(*peers, static_cast<const uint4*>(x), ids, static_cast<int>(picks), static_cast<int>(topk),
-                                                  static_cast<int>(E_local), row_vec, w.send_cursor, w.cta_done, epoch, w.moe.status);
+                                                  static_cast<int>(E_local), row_vec, w.send_cursor, w.cta_done, epoch, w.epoch, w.moe.status);
     EQ_LAUNCH_OK("ep_dispatch_kernel");
-    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 0, epoch, w.moe.status);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 0, epoch, w.epoch, w.moe.status);
     EQ_LAUNCH_OK("ep_wait_kernel");
     ep_build_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(*peers, peers->recv_meta[me], peers->recv_count[me],
                                                                                       static_cast<int>(E_local), static_cast<size_t>(H) * 2, w.eid,
@@ -729,9 +743,9 @@ extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int 
         st = experts_forward<__nv_bfloat16>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, 0, w.eid, R,
                                             w.moe.out, w.row_ptr, stream);
     if (st != EQ_OK) return st;
-    ep_signal_done_kernel<<<1, 32, 0, stream>>>(*peers, epoch);
+    ep_signal_done_kernel<<<1, 32, 0, stream>>>(*peers, epoch, w.epoch);
     EQ_LAUNCH_OK("ep_signal_done_kernel");
-    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 1, epoch, w.moe.status);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 1, epoch, w.epoch, w.moe.status);
     EQ_LAUNCH_OK("ep_wait_kernel");
     if (T == 0) return EQ_OK;
     return eq_moe_combine(peers->back[me], scores, T, topk, H, act_dtype, y, stream_);

@@ -193,7 +193,8 @@ class EpMoe:
     Owns one symmetric buffer per rank (receive rows, their metadata and counts, returned rows, epoch flags), mapped
     into every rank of `group` through torch symmetric memory, and a local workspace.  `t_max` bounds the tokens of a
     call on any rank; `cap` (rows one source may send to one destination) defaults to twice the balanced share plus
-    slack, or all picks when the group is small; rows beyond it are dropped and reported by `status()`."""
+    slack, or all picks when the group is small; rows beyond it are dropped and reported by `status()`.  The call
+    counter lives on the device, so `forward` has no host read and can be captured in a CUDA graph."""
 
     def __init__(self, group, t_max: int, topk: int, hidden: int, inter: int, experts_local: int, dtype, device, cap: int | None = None):
         import os
@@ -232,8 +233,7 @@ class EpMoe:
         self.peers = peers
         self.lib = L
         need = L.load().eq_ep_moe_workspace_bytes(self.world, cap, experts_local, hidden, inter)
-        self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)
-        self.epoch = 0
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)  # holds the device-side call counter
 
     def forward(self, x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, w, out: torch.Tensor | None = None) -> torch.Tensor:
         """x [T, H] this rank's tokens; ids int32 [T, k] / scores f32 [T, k] over all experts; w: the local experts."""
@@ -245,12 +245,11 @@ class EpMoe:
         if t > self.t_max:
             raise ValueError(f"{t} tokens exceed the t_max={self.t_max} the buffers were sized for")
         y = out if out is not None else torch.empty((t, self.hidden), dtype=x.dtype, device=x.device)
-        self.epoch += 1
         L = self.lib
         L.check(
             L.load().eq_ep_moe_w4a16(
                 _ptr(w.gate_up), _ptr(w.down), _DTYPE[w.scale_dtype], self.experts_local, self.topk, self.hidden, self.inter, w.group,
-                _ptr(x), _ptr(ids), _ptr(scores), t, _DTYPE[x.dtype], _ptr(y), C.byref(self.peers), self.epoch, _ptr(self.workspace),
+                _ptr(x), _ptr(ids), _ptr(scores), t, _DTYPE[x.dtype], _ptr(y), C.byref(self.peers), 0, _ptr(self.workspace),
                 self.workspace.numel(), _stream(),
             )
         )

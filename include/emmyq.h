@@ -248,8 +248,11 @@ typedef struct eq_ep_peers {
 
 size_t eq_ep_moe_workspace_bytes(int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I);
 /* One routed layer on this rank's T tokens (ids / scores as eq_moe_route returns them, over all E_local * world
- * experts).  Collective: every rank of the group calls it with the same epoch, which must grow by one per call and
- * start at 1.  The workspace is local, zero on first use.  Waits on peers are bounded (about one second). */
+ * experts).  Collective: every rank of the group calls it the same number of times.  epoch = 0 keeps the call counter
+ * in the workspace on the device (one increment per call on every rank), which makes the whole layer replayable from
+ * a captured CUDA graph; a non-zero epoch is taken as given and must grow by one per call, starting at 1, the same on
+ * all ranks (do not mix the two forms on one set of buffers).  The workspace is local, zero on first use.  Waits on
+ * peers are bounded (about one second). */
 int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E_local, int64_t topk, int64_t H,
                     int64_t I, int64_t G, const void* x, const int32_t* ids, const float* scores, int64_t T, int act_dtype,
                     void* y, const eq_ep_peers* peers, uint32_t epoch, void* workspace, size_t workspace_bytes, void* stream);
