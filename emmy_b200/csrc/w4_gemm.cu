@@ -34,8 +34,8 @@ template <int HALVES, int BN, int DW, int AHEAD>
 struct GemmCfg {
     static constexpr int kDequantWarps = DW;
     static constexpr int kAhead = AHEAD;
-    static constexpr int kEpiGroups = DW / 4 / HALVES;       // warp quartets per accumulator
-    static constexpr int kEpiCols = BN / kEpiGroups;          // accumulator columns per quartet
+    static constexpr int kQuartets = DW / 4;                  // epilogue warp quartets (one warp per TMEM lane quarter)
+    static constexpr int kBoxHalves = HALVES == 2 ? 2 : 1;    // 128-row halves per TMA copy of the activation tile
     static constexpr int kTilesPerWarp = BN / 16 / kDequantWarps;
     static constexpr int kThreads = 64 + 32 * kDequantWarps;
     static constexpr int kTileA = HALVES * 128 * kRowBytes;
@@ -43,10 +43,11 @@ struct GemmCfg {
     static constexpr int kStageBytes = kTileA + kTileB;
     static constexpr int kStages = (196608 / kStageBytes) < 4 ? (196608 / kStageBytes) : 4;
     static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
-    static constexpr uint32_t kTmemCols = HALVES * BN < 32 ? 32 : HALVES * BN;
+    static constexpr uint32_t kAccCols = HALVES * BN;
+    static constexpr uint32_t kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
     static_assert(kTilesPerWarp >= 1 && kTilesPerWarp * 16 * kDequantWarps == BN, "every dequant warp needs whole weight tiles");
-    static_assert(kEpiGroups >= 1 && kEpiCols % 32 == 0, "the epilogue reads 32 accumulator columns at a time");
-    static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns: a power of two up to 512");
+    static_assert(DW % 4 == 0 && BN % 64 == 0, "the epilogue works in warp quartets on 32-column chunks");
+    static_assert(kAccCols <= 512, "the accumulators must fit TMEM");
 };
 
 #ifdef EQ_W4G_TRACE
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     }
     const int kb_lo = 2 * item_lo;
     const int k_blocks = 2 * (item_hi - item_lo);
-    const bool two_halves = HALVES == 2 && m_end - m0 > 128;
+    const int live_halves = min(HALVES, (m_end - m0 + 127) / 128);  // 128-row blocks of this tile that hold rows
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -217,8 +218,12 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 }
                 TR_END(tma_wait);
                 const uint32_t bar = full_a_addr + 8 * stage;
-                tc::mbar_expect_tx(bar, Cfg::kTileA);
-                tc::tma_load_2d(a_base + stage * Cfg::kTileA, &map_x, (kb_lo + kb) * kGK, m0, bar);
+                // one copy per TMA box (Cfg::kBoxHalves 128-row halves); halves without rows are not fetched
+                constexpr int kBoxBytes = Cfg::kBoxHalves * 128 * kRowBytes;
+                const int boxes = (live_halves + Cfg::kBoxHalves - 1) / Cfg::kBoxHalves;
+                tc::mbar_expect_tx(bar, boxes * kBoxBytes);
+                for (int bx = 0; bx < boxes; ++bx)
+                    tc::tma_load_2d(a_base + stage * Cfg::kTileA + bx * kBoxBytes, &map_x, (kb_lo + kb) * kGK, m0 + 128 * Cfg::kBoxHalves * bx, bar);
                 if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1;
@@ -253,9 +258,10 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
 #pragma unroll
                 for (int ks = 0; ks < kGK / 16; ++ks) {
                     const uint64_t db = tc::smem_desc_k_sw128(b_addr + ks * 32);
-                    tc::mma_f16(tmem_base, tc::smem_desc_k_sw128(a_addr + ks * 32), db, idesc, kb > 0 || ks > 0);
-                    if (two_halves)
-                        tc::mma_f16(tmem_base + BN, tc::smem_desc_k_sw128(a_addr + 128 * kRowBytes + ks * 32), db, idesc, kb > 0 || ks > 0);
+#pragma unroll
+                    for (int hh = 0; hh < HALVES; ++hh)
+                        if (hh < live_halves)
+                            tc::mma_f16(tmem_base + hh * BN, tc::smem_desc_k_sw128(a_addr + hh * 128 * kRowBytes + ks * 32), db, idesc, kb > 0 || ks > 0);
                 }
                 tc::mma_commit(empty_addr + 8 * stage);
                 if (++stage == kStages) {
@@ -399,15 +405,19 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31
         const int quarter = warp & 3;
         const int quartet = dw >> 2;
-        const int half = quartet / Cfg::kEpiGroups;
-        const int c_begin = (quartet % Cfg::kEpiGroups) * Cfg::kEpiCols;
-        const int m = m0 + half * 128 + quarter * 32 + lane;
-        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        const bool ok = __all_sync(0xFFFFFFFFu, tc::mbar_wait(tc::smem_u32(acc_ready), 0));
         TR_END(epi_wait);
         TR_BEGIN(epi_work);
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
-        if (ok && (half == 0 || two_halves)) {  // warp-uniform: the TMEM loads below are warp-wide instructions
+        // Work units: (128-row half, 32-column chunk of the output), dealt round-robin to the warp quartets.  Everything
+        // that decides whether a unit runs is warp-uniform: the TMEM loads are warp-wide instructions.
+        constexpr int kChunks = (MODE == kGroupedSwiGLU ? BN / 2 : BN) / 32;
+#pragma unroll 1
+        for (int unit = quartet; ok && unit < HALVES * kChunks; unit += Cfg::kQuartets) {
+            const int half = unit / kChunks, c = (unit - half * kChunks) * 32;
+            if (half >= live_halves) break;
+            const int m = m0 + half * 128 + quarter * 32 + lane;
             bool row_ok = m < m_end;
             size_t out_row = static_cast<size_t>(m);
             ActT* out_base = y;
@@ -425,10 +435,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
             if constexpr (MODE == kGroupedSwiGLU) {
                 // gate columns [0, BN/2) and up columns [BN/2, BN) of the accumulator -> BN/2 columns of the output
                 const int out_n = N / 2, out0 = n0 / 2;
-                constexpr int kCols = BN / 2 / Cfg::kEpiGroups;
-                const int cb = (quartet % Cfg::kEpiGroups) * kCols;
-#pragma unroll 1
-                for (int c = cb; c < cb + kCols; c += 32) {
+                {
                     uint32_t rg[32], ru[32];
                     tc::tmem_ld_32x32(t_row + c, rg);
                     tc::tmem_ld_32x32(t_row + BN / 2 + c, ru);
@@ -460,8 +467,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     }
                 }
             } else if constexpr (SPLIT) {
-#pragma unroll 1
-                for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
+                {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(t_row + c, r);
                     tc::tmem_ld_wait();
@@ -480,8 +486,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     }
                 }
             } else {
-#pragma unroll 1
-                for (int c = c_begin; c < c_begin + Cfg::kEpiCols; c += 32) {
+                {
                     uint32_t r[32];
                     tc::tmem_ld_32x32(t_row + c, r);
                     tc::tmem_ld_wait();
@@ -556,7 +561,7 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     CUtensorMap map_x;
     const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * HALVES, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * Cfg::kBoxHalves, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const bool cvt = scale_dtype != (ScaleMul<ActT>::kFmt == 0 ? EQ_F16 : EQ_BF16);
     auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true, MODE> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false, MODE>;

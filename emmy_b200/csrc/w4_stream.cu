@@ -7,8 +7,6 @@
 // sums into the CTA's shared accumulators.  One __syncthreads at the end, then the CTA converts and stores the tiles
 // it owns.  No global atomics, no fences, no workspace: measured on B200, the f32 workspace hand-over of an earlier
 // form of this kernel (atomic adds, fence, arrival counter) cost 4.6 us of a 10.4 us launch, the stream itself 5.8.
-#include <stdlib.h>
-
 #include "w4_tile.cuh"
 
 namespace eq {
@@ -306,7 +304,7 @@ static int launch_stream(W4Params p, cudaStream_t stream) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = getenv("EQ_NO_PDL") ? 0 : 1;
+    cfg.numAttrs = 1;
     EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, p));
     return EQ_OK;
 }

@@ -134,3 +134,42 @@ def test_moe_layer_tensor_path_ragged_shapes(dtype):
     got = y.float().cpu()
     assert torch.isfinite(got).all()
     assert float((got - ref).abs().max()) <= TOL * float(ref.abs().max())
+
+
+def test_expert_parallel_wait_runs_out_and_reports():
+    """One rank of a two-rank exchange calls alone: the peer's flag is never raised, the bounded waits run out (about
+    a second each), the call returns, and the status word says so.  Both ranks' buffers are local allocations here."""
+    import ctypes as C
+
+    from emmy_b200 import lib as L
+    from emmy_b200 import ops_moe as om
+    from emmy_b200.ops import _DTYPE, _ptr, _stream
+
+    e_local, h, inter, k, t, world = 4, 128, 128, 2, 8, 2
+    ex = make_experts(e_local, h, inter, seed=11)
+    w = om.moe_repack(tuple(dev(a) for a in ex["gate_up"]), tuple(dev(a) for a in ex["down"]))
+    cap = t * k
+    bufs = []
+    peers = L.EpPeers()
+    peers.world, peers.rank, peers.cap = world, 0, cap
+    for r in range(world):
+        recv_x = torch.zeros(world * cap * h, dtype=torch.bfloat16, device="cuda")
+        meta = torch.zeros(world * cap * 2, dtype=torch.int32, device="cuda")
+        count = torch.zeros(world, dtype=torch.int32, device="cuda")
+        back = torch.zeros(t * k * h, dtype=torch.bfloat16, device="cuda")
+        flags = torch.zeros(2 * world, dtype=torch.int32, device="cuda")
+        bufs.append((recv_x, meta, count, back, flags))
+        peers.recv_x[r], peers.recv_meta[r], peers.recv_count[r] = recv_x.data_ptr(), meta.data_ptr(), count.data_ptr()
+        peers.back[r], peers.flags[r] = back.data_ptr(), flags.data_ptr()
+    lib = L.load()
+    ws = torch.zeros(lib.eq_ep_moe_workspace_bytes(world, cap, e_local, h, inter), dtype=torch.uint8, device="cuda")
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    ids, scores = om.moe_route(torch.randn(t, e_local * world, device="cuda"), k)
+    y = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
+    L.check(lib.eq_ep_moe_w4a16(_ptr(w.gate_up), _ptr(w.down), _DTYPE[w.scale_dtype], e_local, k, h, inter, w.group, _ptr(x), _ptr(ids),
+                                _ptr(scores), t, _DTYPE[x.dtype], _ptr(y), C.byref(peers), 0, _ptr(ws), ws.numel(), _stream()))
+    with pytest.raises(L.EmmyqError) as err:
+        L.check(lib.eq_ep_moe_status(_ptr(ws), world, cap, e_local, h, inter, _stream()))
+    assert err.value.status_name == "EQ_ERR_TIMEOUT"
+    # the context is still usable
+    assert torch.isfinite(om.moe_forward(x, torch.randn(t, e_local, device="cuda"), w, k).float()).all()
