@@ -146,7 +146,7 @@ struct Fp8Cfg {
     static constexpr int kBM = 128 * HALVES;
     static constexpr int kTileA = kBM * kBK, kTileB = BN * kBK;
     static constexpr int kStages = HALVES == 2 ? 3 : 6;
-    static constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 /*alignment*/ + 256 /*barriers*/ + BN * sizeof(float) /*weight scales of the tile*/;
     static constexpr uint32_t kTmemCols = HALVES * BN;
 };
 
@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint64_t* empty = bars + kStages;      // [kStages] MMA -> TMA
     uint64_t* acc_ready = bars + 2 * kStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    float* sw_tile = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256);  // the tile's BN weight scales
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tc::mbar_fence_init();
     }
     if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kTmemCols);
+    for (int i = threadIdx.x; i < kBN; i += kGemmThreads) sw_tile[i] = blockIdx.x * kBN + i < N ? sw[blockIdx.x * kBN + i] : 0.f;
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -254,8 +256,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                         uint32_t packed[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float v0 = __uint_as_float(r[2 * i]) * row_scale * sw[n0 + c + 2 * i];
-                            const float v1 = __uint_as_float(r[2 * i + 1]) * row_scale * sw[n0 + c + 2 * i + 1];
+                            const float2 wsc = *reinterpret_cast<const float2*>(sw_tile + c + 2 * i);  // same address in every lane: a broadcast
+                            const float v0 = __uint_as_float(r[2 * i]) * row_scale * wsc.x;
+                            const float v1 = __uint_as_float(r[2 * i + 1]) * row_scale * wsc.y;
                             const OutT o0 = from_float<OutT>(v0), o1 = from_float<OutT>(v1);
                             packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
                                         (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
@@ -266,7 +269,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (n0 + c + i < N) dst[i] = from_float<OutT>(__uint_as_float(r[i]) * row_scale * sw[n0 + c + i]);
+                            if (n0 + c + i < N) dst[i] = from_float<OutT>(__uint_as_float(r[i]) * row_scale * sw_tile[c + i]);
                     }
                 }
             }

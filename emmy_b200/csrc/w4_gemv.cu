@@ -1,24 +1,21 @@
-// W4A16 linear for decode-shaped calls (and, in 64-row blocks, for any M): y[M,N] = x[M,K] @ W, W int4 group-wise.
+// W4A16 linear: the entry points and their dispatch.
 //
-// A bandwidth kernel, kept deliberately plain: many small CTAs, no staging phase, nothing between a warp and its
-// bytes.  The repacked weight (w4_repack.cu) is a run of 1088-byte ITEM records, [n-tile][item]: 16 output columns x
-// 128 input rows of nibbles plus that group's scales and zero points.  A CTA of four warps owns one 16-column tile
-// and one K split; its warps take equal runs of items.  Per item a lane
+//   M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles.
+//   M > 16    w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
+//   M > 16 with an output that is not 16-byte aligned: w4a16_tile_kernel below, in 64-row blocks.
+//
+// w4a16_tile_kernel is the plain form the other two grew out of, and the body the small-row MoE GEMMs still use
+// (w4_tile.cuh): many small CTAs of four warps, one 16-column tile and one K split each, nothing between a warp and
+// its bytes.  Per item (128 input rows x 16 columns, 1088 bytes) a lane
 //   - streams its 2 x 16 weight bytes and its 8-byte scale/zero entry (loads are issued kDepth items ahead),
-//   - reads the 64 contiguous bytes of x it needs straight from global memory (x is a few KB and lives in L1/L2; the
-//     repack deals input rows to lanes so that this is four 16-byte loads),
+//   - reads the 64 contiguous bytes of x it needs straight from global memory (the repack deals input rows to lanes so
+//     that this is four 16-byte loads),
 //   - turns each word into one m16n8k16 A fragment: four lop3 + one shift isolate the nibbles as f16 1024+q (or
 //     1024+16q), one f16x2 subtract / fma per pair removes 1024 and the zero point exactly, so the tensor core sees
 //     the integers q - z and the f32 accumulator holds sum_k x_k (q_k - z) exactly up to f32 rounding,
 //   - folds the item with its scale: y += s * acc.
 // Warps of a CTA meet in shared memory.  K splits of one tile meet in an f32 workspace with atomic adds; the CTA
 // whose arrival completes the tile converts, stores y and leaves workspace and counter zero.  Nobody waits.
-//
-// The grid is sized for granularity, not residency: splits are chosen so that there are many more CTAs than CTA
-// slots and every CTA streams 8-32 KB, which lets the hardware scheduler even out the SMs.
-//
-// tcgen05 is not used here: at M <= 16 the contraction fills 1/8 of an MMA tile and the kernel is bound by bytes and
-// by integer issue (the nibble isolation), not by tensor throughput; the warp-level MMA keeps operands in registers.
 #include "w4_tile.cuh"
 
 namespace eq {
