@@ -322,7 +322,7 @@ def _wl_nvfp4(device, rank, m):
     for _ in range(copies):
         w = torch.randint(0, 256, (GEMM_N, GEMM_K // 2), dtype=torch.uint8, device=device, generator=gen)
         sf = torch.randint(0x28, 0x40, (GEMM_N, GEMM_K // 16), dtype=torch.uint8, device=device, generator=gen)
-        ws.append((w, o4.nvfp4_tile_scales(sf, GEMM_K), torch.tensor([2.0e-5], device=device)))
+        ws.append((w, o4.nvfp4_tile_weight_scales(sf, GEMM_K), torch.tensor([2.0e-5], device=device)))
     x_host = torch.randn(m, GEMM_K, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
     x = x_host.to(device)
     s2 = o4.nvfp4_global_scale(x)

@@ -7,7 +7,8 @@
 //                            codes = e2m1(blk / max(fused, 1e-12)), all round-to-nearest f32.  Bit-exact.
 //   nvfp4_tile_scales_kernel re-tiles a plain [rows, K/16] scale matrix into the 512-byte atoms the tensor core's
 //                            scale-factor copy reads (load time for weights, inside the quantize for activations)
-//   nvfp4_gemm_tc_kernel     tcgen05.mma kind::mxf4nvf4.block_scale.scale_vec::4X: codes come by TMA (128-byte
+//   nvfp4_gemm_tc_kernel / nvfp4_gemm_tc_wide_kernel (128 x 128 tiles for M <= 128, 256 x 224 tiles above)
+//                            tcgen05.mma kind::mxf4nvf4.block_scale.scale_vec::4X: codes come by TMA (128-byte
 //                            swizzle, 256 elements of K per row), scale atoms by bulk copy and then tcgen05.cp into
 //                            TMEM, f32 accumulators in TMEM; the epilogue multiplies by the two global scales.
 // The hardware applies the raw e4m3 block scale and the global scales are factored out into the epilogue, whereas
@@ -47,6 +48,22 @@ __global__ void nvfp4_tile_scales_kernel(const uint8_t* __restrict__ plain, int6
     if (idx >= padded_rows * blocks16) return;
     const int64_t row = idx / blocks16, b = idx % blocks16;
     tiled[sf_tiled_offset(row, b, k64)] = row < rows ? plain[row * blocks16 + b] : 0;
+}
+
+// The same atoms grouped for 224-row column tiles (the prefill kernel's B tile): [tile of 224 rows][two row blocks: rows
+// 0..127 and 128..223 of the tile, the rest zero][k block of 64][512 B].
+constexpr int kWideBN = 224;
+__global__ void nvfp4_tile_scales_wide_kernel(const uint8_t* __restrict__ plain, int64_t rows, int64_t K, uint8_t* __restrict__ tiled) {
+    const int64_t blocks16 = K / 16, k64 = K / 64;
+    const int64_t tiles = (rows + kWideBN - 1) / kWideBN;
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= tiles * 256 * blocks16) return;
+    const int64_t t = idx / (256 * blocks16), rem = idx - t * (256 * blocks16);
+    const int64_t r256 = rem / blocks16, b = rem - r256 * blocks16;
+    const int64_t src = t * kWideBN + r256;
+    const int64_t blk = r256 >> 7, r = r256 & 127;
+    const size_t off = static_cast<size_t>(((t * 2 + blk) * k64 + (b >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (b & 3));
+    tiled[off] = (r256 < kWideBN && src < rows) ? plain[src * blocks16 + b] : 0;
 }
 
 // ------------------------------------------------------------------------------------------------ activation quantize
@@ -259,8 +276,159 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
+// ------------------------------------------------------------------------------------------------ prefill tile 256 x 224
+// Two 128-row accumulators share one 224-column B tile: 448 accumulator columns + 32 (A scales) + 32 (B scales) fill
+// TMEM exactly, and a K step moves 68 KB for 256 x 224 x 256 products where the 128 x 256 tile moved 54 KB for 128 x 256
+// x 256: 1.4 times fewer bytes per flop through L2, which is what bounded the 128-row form.
+constexpr int kWTileA = 256 * kBKBytes, kWTileB = kWideBN * kBKBytes;
+constexpr int kWSf = 2 * 4 * 512;  // two row blocks x four k64 atoms, for A and for B
+constexpr int kWStages = 3;
+constexpr int kWThreads = 320;
+constexpr size_t kWSmem = static_cast<size_t>(kWStages) * (kWTileA + kWTileB + 2 * kWSf) + 1024 + 256;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kWThreads, 1)
+    nvfp4_gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                              const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, const float* __restrict__ gx,
+                              const float* __restrict__ gw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_a = smem;
+    unsigned char* tiles_b = tiles_a + kWStages * kWTileA;
+    unsigned char* sfs_a = tiles_b + kWStages * kWTileB;
+    unsigned char* sfs_b = sfs_a + kWStages * kWSf;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sfs_b + kWStages * kWSf);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kWStages;
+    uint64_t* acc_ready = bars + 2 * kWStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kWStages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kWideBN, m0 = blockIdx.y * 256;
+    const int k_blocks = K / 256;
+    const int k64_blocks = K / 64;
+    const bool two_halves = M - m0 > 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), 512);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_sfa = tmem_base + 2 * kWideBN;       // half h, k64 step ks: + 16 h + 4 ks
+    const uint32_t tmem_sfb = tmem_base + 2 * kWideBN + 32;  // k64 step ks, row block b: + 8 ks + 4 b
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_a);
+            tc::tma_prefetch_desc(&map_b);
+            const int rb_a = m0 / 128;
+            constexpr int kSfBlock = 4 * 512;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kWStages;
+                if (kb >= kWStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kWStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                tc::mbar_expect_tx(bar, kWTileA + kWTileB + (two_halves ? 2 : 1) * kSfBlock + 2 * kSfBlock);
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kWTileA), &map_a, kb * kBKBytes, m0, bar);
+                tc::tma_load_2d(tc::smem_u32(tiles_b + s * kWTileB), &map_b, kb * kBKBytes, n0, bar);
+                bulk_g2s(tc::smem_u32(sfs_a + s * kWSf), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
+                if (two_halves)
+                    bulk_g2s(tc::smem_u32(sfs_a + s * kWSf + kSfBlock), sfa + (static_cast<size_t>(rb_a + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
+                const size_t tile_blocks = static_cast<size_t>(blockIdx.x) * 2;
+                bulk_g2s(tc::smem_u32(sfs_b + s * kWSf), sfb + (tile_blocks * k64_blocks + kb * 4) * 512, kSfBlock, bar);
+                bulk_g2s(tc::smem_u32(sfs_b + s * kWSf + kSfBlock), sfb + ((tile_blocks + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc_nvfp4(128, kWideBN, 0, 0);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kWStages;
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kWStages) & 1)) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles_a + s * kWTileA), b_addr = tc::smem_u32(tiles_b + s * kWTileB);
+                const uint32_t sfa_addr = tc::smem_u32(sfs_a + s * kWSf), sfb_addr = tc::smem_u32(sfs_b + s * kWSf);
+                // all scale copies of the stage are queued before its first MMA
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfa + ks * 4, tc::smem_desc_sf(sfa_addr + ks * 512));
+                    if (two_halves) tc::tmem_cp_32x128b_warpx4(tmem_sfa + 16 + ks * 4, tc::smem_desc_sf(sfa_addr + 4 * 512 + ks * 512));
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8, tc::smem_desc_sf(sfb_addr + ks * 512));
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfb + ks * 8 + 4, tc::smem_desc_sf(sfb_addr + 4 * 512 + ks * 512));
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t db = tc::smem_desc_k_sw128(b_addr + ks * 32);
+                    tc::mma_mxf4nvf4(tmem_base, tc::smem_desc_k_sw128(a_addr + ks * 32), db, idesc, tmem_sfa + ks * 4, tmem_sfb + ks * 8, kb > 0 || ks > 0);
+                    if (two_halves)
+                        tc::mma_mxf4nvf4(tmem_base + kWideBN, tc::smem_desc_k_sw128(a_addr + 128 * kBKBytes + ks * 32), db, idesc, tmem_sfa + 16 + ks * 4,
+                                         tmem_sfb + ks * 8, kb > 0 || ks > 0);
+                }
+                tc::mma_commit(tc::smem_u32(empty + s));
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));
+        }
+    } else {
+        // epilogue: warps 2..5 rows 0..127, warps 6..9 rows 128..255; warp w touches TMEM lanes 32 (w % 4) .. +31
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int m = m0 + half * 128 + quarter * 32 + lane;
+        const bool ok = __all_sync(0xFFFFFFFFu, tc::mbar_wait(tc::smem_u32(acc_ready), 0));
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok && (half == 0 || two_halves)) {
+            const float g = gx[0] * gw[0];
+#pragma unroll 1
+            for (int c = 0; c < kWideBN; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * kWideBN + c, r);
+                tc::tmem_ld_wait();
+                if (m < M && n0 + c < N) {
+                    OutT* dst = y + static_cast<size_t>(m) * N + n0 + c;
+                    if (n0 + c + 32 <= N) {
+                        uint32_t packed[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const OutT o0 = from_float<OutT>(__uint_as_float(r[2 * i]) * g), o1 = from_float<OutT>(__uint_as_float(r[2 * i + 1]) * g);
+                            packed[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                        (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        }
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<uint4*>(dst)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (n0 + c + i < N) dst[i] = from_float<OutT>(__uint_as_float(r[i]) * g);
+                    }
+                }
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, 512);
+    }
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t sf_tiled_bytes(int64_t rows, int64_t K) { return static_cast<size_t>((rows + 127) / 128) * (K / 64) * 512; }
+static size_t sf_wide_bytes(int64_t rows, int64_t K) { return static_cast<size_t>((rows + kWideBN - 1) / kWideBN) * 2 * (K / 64) * 512; }
 
 }  // namespace eq
 
@@ -277,6 +445,24 @@ extern "C" int eq_nvfp4_tile_scales(const uint8_t* scale_bits, int64_t rows, int
     const int64_t total = (rows + 127) / 128 * 128 * (K / 16);
     nvfp4_tile_scales_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(scale_bits, rows, K, tiled);
     EQ_LAUNCH_OK("nvfp4_tile_scales_kernel");
+    return EQ_OK;
+}
+
+extern "C" size_t eq_nvfp4_weight_scale_bytes(int64_t N, int64_t K) {
+    if (N <= 0 || K <= 0 || K % 64) return 0;
+    return align_up(sf_tiled_bytes(N, K), 256) + sf_wide_bytes(N, K);
+}
+
+extern "C" int eq_nvfp4_tile_weight_scales(const uint8_t* scale_bits, int64_t N, int64_t K, uint8_t* tiled, void* stream) {
+    EQ_REQUIRE(scale_bits && tiled, EQ_ERR_BAD_ARG, "eq_nvfp4_tile_weight_scales: null pointer");
+    EQ_REQUIRE(N > 0 && K > 0 && K % 64 == 0, EQ_ERR_UNSUPPORTED, "eq_nvfp4_tile_weight_scales: needs K %% 64 == 0 (K=%lld)", (long long)K);
+    EQ_REQUIRE(aligned(tiled, 256), EQ_ERR_BAD_ALIGN, "eq_nvfp4_tile_weight_scales: the output must be 256-byte aligned");
+    int st = eq_nvfp4_tile_scales(scale_bits, N, K, tiled, stream);
+    if (st != EQ_OK) return st;
+    const int64_t total = (N + kWideBN - 1) / kWideBN * 256 * (K / 16);
+    nvfp4_tile_scales_wide_kernel<<<static_cast<unsigned>(ceil_div(total, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        scale_bits, N, K, tiled + align_up(sf_tiled_bytes(N, K), 256));
+    EQ_LAUNCH_OK("nvfp4_tile_scales_wide_kernel");
     return EQ_OK;
 }
 
@@ -334,7 +520,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     EQ_REQUIRE(weight && weight_scale_tiled && weight_scale_2 && x && input_scale && y, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: null pointer");
     EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: activations must be f16 or bf16");
     EQ_REQUIRE(K % 256 == 0 && N % 8 == 0, EQ_ERR_UNSUPPORTED, "eq_nvfp4_linear: needs K %% 256 == 0 and N %% 8 == 0 (K=%lld N=%lld)", (long long)K, (long long)N);
-    EQ_REQUIRE(aligned(weight, 16) && aligned(weight_scale_tiled, 16) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: weight and scales must be 16-byte aligned");
+    EQ_REQUIRE(aligned(weight, 16) && aligned(weight_scale_tiled, 256) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: weight and scales must be 16-byte aligned");
     EQ_REQUIRE(workspace && workspace_bytes >= eq_nvfp4_workspace_bytes(M, K), EQ_ERR_WORKSPACE, "eq_nvfp4_linear: workspace of %zu bytes needed, %zu given",
                eq_nvfp4_workspace_bytes(M, K), workspace_bytes);
     EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "eq_nvfp4_linear: workspace must be 256-byte aligned");
@@ -348,22 +534,37 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
     st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    const int bn = M <= 128 ? 128 : 256;
-    st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, bn, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (M <= 128) {
+        // one row tile: 128-column tiles, the 128-row-block scale layout at the front of the blob
+        st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != EQ_OK) return st;
+        dim3 grid(static_cast<unsigned>(ceil_div(N, 128)), 1);
+        auto run = [&](auto kernel, auto* yt) -> int {
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Fp4Cfg<128>::kSmem)));
+            kernel<<<grid, kGemmThreads, Fp4Cfg<128>::kSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt,
+                                                                      static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+            EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
+            return EQ_OK;
+        };
+        return act_dtype == EQ_F16 ? run(nvfp4_gemm_tc_kernel<__half, 128>, static_cast<__half*>(y))
+                                   : run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 128>, static_cast<__nv_bfloat16*>(y));
+    }
+    // prefill-shaped: 256 x 224 tiles, the 224-row-tile scale layout behind the first one
+    st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, 256, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
-    auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt, static_cast<int>(M),
-                                                    static_cast<int>(N), static_cast<int>(K), status);
-        EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
+    st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, kWideBN, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    const uint8_t* sfb_wide = weight_scale_tiled + align_up(sf_tiled_bytes(N, K), 256);
+    dim3 grid(static_cast<unsigned>(ceil_div(N, kWideBN)), static_cast<unsigned>(ceil_div(M, 256)));
+    auto run = [&](auto kernel, auto* yt) -> int {
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kWSmem)));
+        kernel<<<grid, kWThreads, kWSmem, stream>>>(map_a, map_b, sfa, sfb_wide, input_scale, weight_scale_2, yt, static_cast<int>(M),
+                                                   static_cast<int>(N), static_cast<int>(K), status);
+        EQ_LAUNCH_OK("nvfp4_gemm_tc_wide_kernel");
         return EQ_OK;
     };
-    if (act_dtype == EQ_F16)
-        return bn == 128 ? run(nvfp4_gemm_tc_kernel<__half, 128>, Fp4Cfg<128>::kSmem, static_cast<__half*>(y))
-                         : run(nvfp4_gemm_tc_kernel<__half, 256>, Fp4Cfg<256>::kSmem, static_cast<__half*>(y));
-    return bn == 128 ? run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 128>, Fp4Cfg<128>::kSmem, static_cast<__nv_bfloat16*>(y))
-                     : run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 256>, Fp4Cfg<256>::kSmem, static_cast<__nv_bfloat16*>(y));
+    return act_dtype == EQ_F16 ? run(nvfp4_gemm_tc_wide_kernel<__half>, static_cast<__half*>(y))
+                               : run(nvfp4_gemm_tc_wide_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16*>(y));
 }
 
 extern "C" int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream_) {

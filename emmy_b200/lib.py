@@ -92,6 +92,8 @@ def load() -> C.CDLL:
         "eq_quant_nvfp4_act": (i, [p, i64, i64, i, p, p, p, p, p]),
         "eq_nvfp4_tiled_scale_bytes": (sz, [i64, i64]),
         "eq_nvfp4_tile_scales": (i, [p, i64, i64, p, p]),
+        "eq_nvfp4_weight_scale_bytes": (sz, [i64, i64]),
+        "eq_nvfp4_tile_weight_scales": (i, [p, i64, i64, p, p]),
         "eq_nvfp4_workspace_bytes": (sz, [i64, i64]),
         "eq_nvfp4_linear": (i, [p, p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
         "eq_nvfp4_status": (i, [p, i64, i64, p]),

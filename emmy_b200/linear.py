@@ -145,7 +145,7 @@ class NVFP4Linear(nn.Module):
         self._tiled = None
 
     def finalize(self) -> "NVFP4Linear":
-        self._tiled = ops_nvfp4.nvfp4_tile_scales(self.weight_scale, self.in_features)
+        self._tiled = ops_nvfp4.nvfp4_tile_weight_scales(self.weight_scale, self.in_features)
         return self
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

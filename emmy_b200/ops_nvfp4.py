@@ -42,6 +42,15 @@ def nvfp4_tile_scales(scale_bits: torch.Tensor, k: int) -> torch.Tensor:
     return out
 
 
+def nvfp4_tile_weight_scales(scale_bits: torch.Tensor, k: int) -> torch.Tensor:
+    """weight_scale [N, K/16] -> the scale blob eq_nvfp4_linear reads (both tile groupings; load time)."""
+    _need_cuda(scale_bits)
+    rows = scale_bits.shape[0]
+    out = torch.empty(L.load().eq_nvfp4_weight_scale_bytes(rows, k), dtype=torch.uint8, device=scale_bits.device)
+    L.check(L.load().eq_nvfp4_tile_weight_scales(_ptr(scale_bits), rows, k, _ptr(out), _stream()))
+    return out
+
+
 def nvfp4_workspace(m: int, k: int, device) -> torch.Tensor:
     return torch.zeros(max(L.load().eq_nvfp4_workspace_bytes(m, k), 256), dtype=torch.uint8, device=device)
 

@@ -183,9 +183,14 @@ int eq_quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const 
  * copy into tensor memory wants this order.)  Needs K % 64 == 0. */
 size_t eq_nvfp4_tiled_scale_bytes(int64_t rows, int64_t K);
 int eq_nvfp4_tile_scales(const uint8_t* scale_bits, int64_t rows, int64_t K, uint8_t* tiled, void* stream);
+/* The weight's scales for eq_nvfp4_linear: the layout above, followed (256-byte aligned) by the same atoms grouped for
+ * the prefill kernel's 224-row column tiles ([tile of 224 rows][two row blocks][64 elements of K][512 B], rows past the
+ * tile zero).  `tiled` must be 256-byte aligned. */
+size_t eq_nvfp4_weight_scale_bytes(int64_t N, int64_t K);
+int eq_nvfp4_tile_weight_scales(const uint8_t* scale_bits, int64_t N, int64_t K, uint8_t* tiled, void* stream);
 /* y[M, N] = input_scale * weight_scale_2 * sum_blocks s_x s_w sum_k c_x c_w in act_dtype: the native block-scaled
  * product (tcgen05.mma kind::mxf4nvf4).  weight: packed e2m1 [N, K/2] as stored; weight_scale_tiled: from
- * eq_nvfp4_tile_scales; weight_scale_2, input_scale: device f32 [1].  The activation is quantized inside the call.
+ * eq_nvfp4_tile_weight_scales; weight_scale_2, input_scale: device f32 [1].  The activation is quantized inside the call.
  * The operator the reference spells as NVFP4 decode + static activation quantize in front of a LinearOp
  * (emmy/compiler/loader/quant.py:2142-2209, 1968-2139).  Needs K % 256 == 0, N % 8 == 0. */
 size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K);

@@ -96,7 +96,7 @@ def _check(m, n, k, seed=0, dtype="bf16"):
     s2x = oact.nvfp4_global_scale(x)
     t = dev(x).bfloat16() if dtype == "bf16" else dev(x).half()
     ws = o4.nvfp4_workspace(m, k, t.device)
-    y = o4.nvfp4_linear(t, dev(packed), o4.nvfp4_tile_scales(dev(sbits), k), dev(s2w), dev(np.array([s2x], np.float32)), workspace=ws)
+    y = o4.nvfp4_linear(t, dev(packed), o4.nvfp4_tile_weight_scales(dev(sbits), k), dev(s2w), dev(np.array([s2x], np.float32)), workspace=ws)
     o4.nvfp4_status(ws, m, k)
     got = y.float().cpu().numpy()
     ref = ol.nvfp4_linear(x, packed, sbits, s2w, s2x)
@@ -106,7 +106,7 @@ def _check(m, n, k, seed=0, dtype="bf16"):
     return err
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 256, 1024), (64, 512, 512), (1, 256, 512), (200, 264, 768), (128, 128, 256)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 256, 1024), (64, 512, 512), (1, 256, 512), (200, 264, 768), (128, 128, 256), (129, 224, 256), (300, 504, 512), (700, 1000, 1024)])
 def test_nvfp4_linear_tensor_path(m, n, k):
     _check(m, n, k, seed=m + n)
 
@@ -128,12 +128,12 @@ def test_nvfp4_linear_known_answer():
     xsf = rng.choice(np.array([0.5, 1.0, 2.0], np.float32), (m, k // 16))
     xval = (fm.E2M1_VALUES[xc] * np.repeat(xsf, 16, axis=1)).astype(np.float32)
     s2x = np.float32(1.0)
-    y = o4.nvfp4_linear(dev(xval).bfloat16(), dev(wpacked), o4.nvfp4_tile_scales(dev(wsf), k), dev(np.array([1.0], np.float32)),
+    y = o4.nvfp4_linear(dev(xval).bfloat16(), dev(wpacked), o4.nvfp4_tile_weight_scales(dev(wsf), k), dev(np.array([1.0], np.float32)),
                         dev(np.array([s2x], np.float32))).float().cpu().numpy()
     ref = fm.round_bf16(xval @ wval.T)
     np.testing.assert_array_equal(y, ref)
 
 
-@pytest.mark.parametrize("m", [1, 128])
+@pytest.mark.parametrize("m", [1, 128, 300])
 def test_nvfp4_linear_full_width(m):
     _check(m, 17408, 5120, seed=3)
