@@ -12,14 +12,7 @@
 namespace eq {
 
 constexpr int kStreamWarps = 32;        // one fat CTA per SM (single-row calls; multi-row calls use half as many warps for twice the registers)
-#ifndef EQ_EXP_DEPTH
-#define EQ_EXP_DEPTH 4
-#endif
-#ifndef EQ_EXP_CTAS
-#define EQ_EXP_CTAS 8
-#endif
-constexpr int kStreamDepth = EQ_EXP_DEPTH;        // items in flight per warp (power of two)
-constexpr int kSlot = 1024 + 256;      // ring slot: 32 x 16 B + 32 x 16 B of nibbles, 32 x 8 B scale / zero entries
+constexpr int kSlot = kItemBytes;       // ring slot: one item record as it lies in global memory
 
 #ifdef EQ_W4_TRACE
 __device__ unsigned long long g_w4_trace[4096 * 8];
@@ -133,9 +126,12 @@ __device__ __forceinline__ void stream_flush(const W4Params& p, float* acc_slot,
     }
 }
 
-template <typename ActT, int MT, bool ONE, int WARPS>
+// DEPTH: items in flight per warp.  A warp of the benchmark's shapes owns six items, so DEPTH = 6 requests its whole
+// span before the first item is consumed.
+template <typename ActT, int MT, bool ONE, int WARPS, int DEPTH>
 __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Params p) {
     constexpr int kStreamWarps = WARPS;
+    constexpr int kStreamDepth = DEPTH;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     EQ_TRACE(0);
     constexpr int kRows = ONE ? 1 : MT * 8;
@@ -162,18 +158,18 @@ __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Par
     EQ_TRACE(7);
 
     // ---- a per-warp ring of kStreamDepth items in shared memory, filled by per-lane asynchronous copies: lane L
-    //      copies exactly the bytes lane L reads later (its 2 x 16 weight bytes and its 8-byte scale / zero entry), so
-    //      cp.async.wait_group alone orders producer and consumer and no warp-level synchronization is needed.
+    //      copies the 2 x 16 weight bytes it reads later; the eight lanes with j == 0 also copy the 8-byte scale / zero
+    //      entry of their column pair, which the other lanes of the pair read too, hence the __syncwarp after the wait.
     //      One commit group per item; iteration i waits until at most kStreamDepth - 1 groups are pending.
     unsigned char* ring = smem_all + warp * (kStreamDepth * kSlot);
     const uint32_t ring_lo = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + lane * 16;
-    const uint32_t ring_meta = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + 1024 + lane * 8;
+    const uint32_t ring_meta = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + 1024 + g * 8;
     auto issue = [&](int d, int i) {
         if (i < n) {
             const size_t off = static_cast<size_t>(i) * kItemBytes;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_lo + d * kSlot), "l"(rec + off) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_lo + d * kSlot + 512), "l"(rec + off + 512) : "memory");
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(ring_meta + d * kSlot), "l"(met + off) : "memory");
+            if (j == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(ring_meta + d * kSlot), "l"(met + off) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -240,12 +236,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Par
     bool dirty = false;
 
     for (int i = 0; i < n; ++i) {
-        const int d = i & (kStreamDepth - 1);
+        const int d = i % kStreamDepth;
         asm volatile("cp.async.wait_group %0;" ::"n"(kStreamDepth - 1) : "memory");
+        __syncwarp();  // the scale / zero entry was copied by another lane of the column pair
         const unsigned char* slot = ring + d * kSlot;
         const uint4 wl = *reinterpret_cast<const uint4*>(slot + lane * 16);
         const uint4 wh = *reinterpret_cast<const uint4*>(slot + 512 + lane * 16);
-        const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + lane * 8);
+        const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
+        __syncwarp();  // every lane has read the slot before any lane refills it
         if constexpr (ONE)
             w4_item_one<ActT>(p.scale_dtype, xs + it * 16 + 4 * j, xsum[it], wl, wh, mt_, yacc);
         else
@@ -276,24 +274,17 @@ __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Par
 }
 
 // Shared memory the stream kernel needs for `tiles` column tiles on `ctas` CTAs, or 0 when it does not fit.
-static size_t stream_smem(long long tiles, long long ctas, int rows, int K, int warps) {
+static size_t stream_smem(long long tiles, long long ctas, int rows, int K, int warps, int depth) {
     const long long per_cta = ceil_div(tiles, ctas);
-    size_t bytes = static_cast<size_t>(warps) * kStreamDepth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float);
+    size_t bytes = static_cast<size_t>(warps) * depth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float);
     if (rows == 1) bytes += static_cast<size_t>(K) * 2 + static_cast<size_t>(K / 128) * sizeof(float2);  // staged x and its item sums
     return bytes <= 220 * 1024 ? bytes : 0;
 }
 
-template <typename ActT, int MT, bool ONE>
-static int launch_stream(W4Params p, cudaStream_t stream) {
+template <typename ActT, int MT, bool ONE, int DEPTH>
+static int launch_stream_depth(W4Params p, size_t smem, long long ctas, cudaStream_t stream) {
     constexpr int kWarps = ONE ? kStreamWarps : kStreamWarps / 2;
-    const long long tiles = p.N / 16;
-    long long ctas = sm_count();
-    if (ctas > tiles) ctas = tiles;
-    p.span_base = static_cast<int>(tiles / ctas);
-    p.span_rem = static_cast<int>(tiles % ctas);
-    const size_t smem = stream_smem(tiles, ctas, ONE ? 1 : MT * 8, p.K, kWarps);
-    EQ_REQUIRE(smem > 0, EQ_ERR_UNSUPPORTED, "w4a16 stream kernel: accumulators do not fit shared memory");
-    auto kernel = w4a16_stream_kernel<ActT, MT, ONE, kWarps>;
+    auto kernel = w4a16_stream_kernel<ActT, MT, ONE, kWarps, DEPTH>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
@@ -307,6 +298,23 @@ static int launch_stream(W4Params p, cudaStream_t stream) {
     cfg.numAttrs = 1;
     EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, p));
     return EQ_OK;
+}
+
+template <typename ActT, int MT, bool ONE>
+static int launch_stream(W4Params p, cudaStream_t stream) {
+    constexpr int kWarps = ONE ? kStreamWarps : kStreamWarps / 2;
+    const long long tiles = p.N / 16;
+    long long ctas = sm_count();
+    if (ctas > tiles) ctas = tiles;
+    p.span_base = static_cast<int>(tiles / ctas);
+    p.span_rem = static_cast<int>(tiles % ctas);
+    const int rows = ONE ? 1 : MT * 8;
+    // the deepest ring that fits: six items cover a warp's whole span at the Llama MLP shapes
+    if (const size_t smem = stream_smem(tiles, ctas, rows, p.K, kWarps, 6)) return launch_stream_depth<ActT, MT, ONE, 6>(p, smem, ctas, stream);
+    if (const size_t smem = stream_smem(tiles, ctas, rows, p.K, kWarps, 5)) return launch_stream_depth<ActT, MT, ONE, 5>(p, smem, ctas, stream);
+    const size_t smem = stream_smem(tiles, ctas, rows, p.K, kWarps, 4);
+    EQ_REQUIRE(smem > 0, EQ_ERR_UNSUPPORTED, "w4a16 stream kernel: accumulators do not fit shared memory");
+    return launch_stream_depth<ActT, MT, ONE, 4>(p, smem, ctas, stream);
 }
 
 template <typename ActT>
