@@ -534,20 +534,27 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
     st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    if (M <= 128) {
-        // one row tile: 128-column tiles, the 128-row-block scale layout at the front of the blob
-        st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+    // 256 x 224 tiles pay off once there are enough row tiles to fill whole waves; below that the 128-row tiles
+    // (128 columns for a single row tile, 256 otherwise) spread the work over more CTAs.
+    const bool wide = ceil_div(N, kWideBN) * ceil_div(M, 256) >= 4 * static_cast<int64_t>(sm_count());
+    if (!wide) {
+        // the 128-row-block scale layout at the front of the blob
+        const int bn = M <= 128 ? 128 : 256;
+        st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, bn, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EQ_OK) return st;
-        dim3 grid(static_cast<unsigned>(ceil_div(N, 128)), 1);
-        auto run = [&](auto kernel, auto* yt) -> int {
-            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Fp4Cfg<128>::kSmem)));
-            kernel<<<grid, kGemmThreads, Fp4Cfg<128>::kSmem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt,
-                                                                      static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+        dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
+        auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt, static_cast<int>(M),
+                                                        static_cast<int>(N), static_cast<int>(K), status);
             EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
             return EQ_OK;
         };
-        return act_dtype == EQ_F16 ? run(nvfp4_gemm_tc_kernel<__half, 128>, static_cast<__half*>(y))
-                                   : run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 128>, static_cast<__nv_bfloat16*>(y));
+        if (act_dtype == EQ_F16)
+            return bn == 128 ? run(nvfp4_gemm_tc_kernel<__half, 128>, Fp4Cfg<128>::kSmem, static_cast<__half*>(y))
+                             : run(nvfp4_gemm_tc_kernel<__half, 256>, Fp4Cfg<256>::kSmem, static_cast<__half*>(y));
+        return bn == 128 ? run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 128>, Fp4Cfg<128>::kSmem, static_cast<__nv_bfloat16*>(y))
+                         : run(nvfp4_gemm_tc_kernel<__nv_bfloat16, 256>, Fp4Cfg<256>::kSmem, static_cast<__nv_bfloat16*>(y));
     }
     // prefill-shaped: 256 x 224 tiles, the 224-row-tile scale layout behind the first one
     st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, 256, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
