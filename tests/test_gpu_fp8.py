@@ -128,3 +128,19 @@ def test_fp8_linear_small_integer_known_answer():
 def test_fp8_linear_full_size_m1(n):
     bits, sw = synth.fp8_weight(n, 5120, seed=0)
     _check(synth.activations(1, 5120, "bf16", seed=1), bits, sw)
+
+
+@pytest.mark.parametrize("m,n,k", [(17, 144, 128), (100, 400, 256), (129, 144, 128), (257, 528, 640), (600, 784, 384)])
+def test_fp8_linear_tile_edges(m, n, k):
+    """Row counts on either side of the 16 / 128 / 256 boundaries where the kernel or the tiling changes, and widths
+    that leave a partial 128- or 256-column tile."""
+    bits, sw = synth.fp8_weight(n, k, seed=m)
+    _check(synth.activations(m, k, "bf16", seed=n), bits, sw)
+
+
+def test_fp8_linear_empty_batch():
+    from emmy_b200 import ops
+
+    bits, sw = synth.fp8_weight(64, 128, seed=0)
+    y = ops.fp8_linear(torch.empty(0, 128, dtype=torch.bfloat16, device="cuda"), dev(bits), dev(sw.reshape(-1)))
+    assert y.shape == (0, 64)

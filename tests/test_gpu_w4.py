@@ -319,3 +319,29 @@ def test_prefill_matches_dequantised_matmul_at_full_size(m):
     ref = x.float() @ wd.float()
     err = float((y.float() - ref).abs().max())
     assert err <= 4e-3 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("group", [-1, 256])
+def test_prefill_wide_groups(group):
+    """Groups wider than one 128-row item (their scale record repeats per item) on the tensor path."""
+    from emmy_b200 import ops
+
+    k, n = 512, 208
+    qw, qz, sc = synth.awq_linear(k, n, group=k if group == -1 else group, seed=21)
+    w = ops.w4_repack(dev(qw), dev(qz), dev(sc), group, "awq")
+    for m in (40, 150):
+        x = synth.activations(m, k, "f16", seed=m)
+        check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, group, "awq", "f16"))
+
+
+def test_prefill_bf16_scales_with_f16_activations():
+    """Scales stored in the other 16-bit type are converted once per item on the tensor path."""
+    from emmy_b200 import ops
+
+    k, n = 384, 160
+    qw, qz, sc = synth.awq_linear(k, n, seed=5, scale_dtype=np.float32)  # bf16-rounded values held as f32
+    sc_dev = torch.from_numpy(sc).cuda().bfloat16()
+    w = ops.w4_repack(dev(qw), dev(qz), sc_dev, 128, "awq")
+    for m in (3, 64):
+        x = synth.activations(m, k, "f16", seed=m)
+        check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, 128, "awq", "f16"))
