@@ -79,10 +79,18 @@ struct Raw<__nv_bfloat16> {
 
 // xs_lane: the lane column's 64 staged bytes of the item; sums: {offset S1, S2} of the item.
 template <typename ActT>
-__device__ __forceinline__ void w4_item_one(int scale_dtype, const uint4* xs_lane, float2 sums, const uint4& wl, const uint4& wh,
-                                            const uint2& mt_, float (&yacc)[1][4]) {
-    // staged as {low slot, high slot} word pairs per k16 step: a 16-byte read is the B fragment of two steps
-    const uint4 x0 = xs_lane[0], x1 = xs_lane[1], x2 = xs_lane[2], x3 = xs_lane[3];
+__device__ __forceinline__ void w4_item_one(int scale_dtype, const uint4* xs_lane, bool feeds_column0, float2 sums, const uint4& wl,
+                                            const uint4& wh, const uint2& mt_, float (&yacc)[1][4]) {
+    // staged as {low slot, high slot} word pairs per k16 step: a 16-byte read is the B fragment of two steps.  Only
+    // column 0 of the product is ever looked at, and its B values sit in lanes 0..3 (g = 0): the other lanes pass
+    // zeros and their shared-memory reads are predicated off, a quarter of the wavefronts.
+    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
+    if (feeds_column0) {
+        x0 = xs_lane[0];
+        x1 = xs_lane[1];
+        x2 = xs_lane[2];
+        x3 = xs_lane[3];
+    }
     const uint32_t lo[8] = {x0.x, x0.z, x1.x, x1.z, x2.x, x2.z, x3.x, x3.z};
     const uint32_t hi[8] = {x0.y, x0.w, x1.y, x1.w, x2.y, x2.w, x3.y, x3.w};
     const uint32_t words[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
@@ -245,7 +253,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) w4a16_stream_kernel(const W4Par
         const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
         __syncwarp();  // every lane has read the slot before any lane refills it
         if constexpr (ONE)
-            w4_item_one<ActT>(p.scale_dtype, xs + it * 16 + 4 * j, xsum[it], wl, wh, mt_, yacc);
+            w4_item_one<ActT>(p.scale_dtype, xs + it * 16 + 4 * j, g == 0, xsum[it], wl, wh, mt_, yacc);
         else
             w4_item<ActT, MT, ONE>(p, x, it, wl, wh, mt_, g, j, yacc);
         issue(d, i + kStreamDepth);  // the slot's bytes are in registers: refill it
