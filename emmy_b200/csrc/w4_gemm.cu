@@ -36,7 +36,11 @@ struct GemmCfg {
     static constexpr int kAhead = AHEAD;
     static constexpr int kQuartets = DW / 4;                  // epilogue warp quartets (one warp per TMEM lane quarter)
     static constexpr int kBoxHalves = HALVES == 2 ? 2 : 1;    // 128-row halves per TMA copy of the activation tile
-    static constexpr int kTilesPerWarp = BN / 16 / kDequantWarps;
+    // With more dequant warps than 16-column tiles the warps also split K: group r of them takes K step r of every item.
+    static constexpr int kTiles = BN / 16;
+    static constexpr int kKSplit = DW > kTiles ? DW / kTiles : 1;
+    static constexpr int kWarpsPerStep = DW / kKSplit;          // warps that fill (and arrive on) one stage
+    static constexpr int kTilesPerWarp = kTiles / kWarpsPerStep;
     static constexpr int kThreads = 64 + 32 * kDequantWarps;
     static constexpr int kTileA = HALVES * 128 * kRowBytes;
     static constexpr int kTileB = BN * kRowBytes;
@@ -45,7 +49,8 @@ struct GemmCfg {
     static constexpr size_t kSmem = static_cast<size_t>(kStages) * kStageBytes + 1024 + 256;
     static constexpr uint32_t kAccCols = HALVES * BN;
     static constexpr uint32_t kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
-    static_assert(kTilesPerWarp >= 1 && kTilesPerWarp * 16 * kDequantWarps == BN, "every dequant warp needs whole weight tiles");
+    static_assert(kTilesPerWarp >= 1 && kTilesPerWarp * kWarpsPerStep == kTiles && (kKSplit == 1 || kKSplit == 2),
+                  "every dequant warp needs whole weight tiles, and an item has two K steps to split");
     static_assert(DW % 4 == 0 && BN % 64 == 0, "the epilogue works in warp quartets on 32-column chunks");
     static_assert(kAccCols <= 512, "the accumulators must fit TMEM");
 };
@@ -118,6 +123,9 @@ __global__ void gather_cols_kernel(const ActT* __restrict__ x, const int32_t* __
     xg[idx] = x[m * K + perm[k]];
 }
 
+// Rows of the TMA box of the activation tile for single-half plain tiles: the row count rounded up to a swizzle atom.
+__host__ __device__ inline int a_box_rows(int M) { return M >= 121 ? 128 : (M + 7) / 8 * 8; }
+
 // MODE: kPlain: one weight, CTA row tile = blockIdx.y.  kGrouped: blockIdx.y walks a device-side list of row blocks, each
 // a run of rows of ONE expert in an expert-ordered activation matrix; the weight is that expert's slice of a stacked
 // tensor and output rows may be scattered through y_rows.  kGroupedSwiGLU: the same, with the first 128 columns of the
@@ -187,7 +195,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             tc::mbar_init(tc::smem_u32(full_a + s), 1);
-            tc::mbar_init(tc::smem_u32(full_b + s), Cfg::kDequantWarps);
+            tc::mbar_init(tc::smem_u32(full_b + s), Cfg::kWarpsPerStep);
             tc::mbar_init(tc::smem_u32(empty + s), 1);
         }
         tc::mbar_init(tc::smem_u32(acc_ready), 1);
@@ -221,7 +229,10 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 // one copy per TMA box (Cfg::kBoxHalves 128-row halves); halves without rows are not fetched
                 constexpr int kBoxBytes = Cfg::kBoxHalves * 128 * kRowBytes;
                 const int boxes = (live_halves + Cfg::kBoxHalves - 1) / Cfg::kBoxHalves;
-                tc::mbar_expect_tx(bar, boxes * kBoxBytes);
+                // single-half plain tiles of fewer than 128 rows use a shorter box (see a_box_rows): rows past it keep
+                // whatever the stage held, and the accumulator rows they feed are never stored
+                const int box_bytes = (HALVES == 1 && MODE == kPlain) ? a_box_rows(M) * kRowBytes : kBoxBytes;
+                tc::mbar_expect_tx(bar, boxes * box_bytes);
                 for (int bx = 0; bx < boxes; ++bx)
                     tc::tma_load_2d(a_base + stage * Cfg::kTileA + bx * kBoxBytes, &map_x, (kb_lo + kb) * kGK, m0 + 128 * Cfg::kBoxHalves * bx, bar);
                 if (++stage == kStages) {
@@ -278,6 +289,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     } else {
         // ---- dequant producers
         const int dw = warp - 2;
+        const int kgrp = dw / Cfg::kWarpsPerStep;  // which K step of an item this warp fills when the warps split K
         const int g = lane & 7, h = (lane >> 3) & 1, jj = lane >> 4;
         // Shared-memory byte offsets of the lane's four 16-byte chunks inside a B tile: row r = 16 tile + g (+8) is an
         // output column, chunk q = 4 jj + 2 high + h of its 128 bytes is swizzled with r & 7 = g.
@@ -287,7 +299,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         bool live[Cfg::kTilesPerWarp];
 #pragma unroll
         for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
-            const int tile_in_cta = dw * Cfg::kTilesPerWarp + nt;
+            const int tile_in_cta = (dw % Cfg::kWarpsPerStep) * Cfg::kTilesPerWarp + nt;
             int tile = n0 / 16 + tile_in_cta;
             if constexpr (MODE == kGroupedSwiGLU) {
                 constexpr int kHalfTiles = BN / 32;  // gate tiles of this CTA, then as many up tiles
@@ -309,8 +321,8 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
             if (d < my_items) {
 #pragma unroll
                 for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
-                    w0[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes);
-                    w1[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes + 32);
+                    if (Cfg::kKSplit == 1 || kgrp == 0) w0[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes);
+                    if (Cfg::kKSplit == 1 || kgrp == 1) w1[d][nt] = ld_stream_v4(wp[nt] + static_cast<size_t>(d) * kItemBytes + 32);
                     meta[d][nt] = ld_pinned_v2(mp[nt] + static_cast<size_t>(d) * kItemBytes);
                 }
             }
@@ -346,6 +358,14 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (broken) continue;
+                    if (Cfg::kKSplit == 2 && t != kgrp) {  // the other warp group's K step
+                        if (++stage == kStages) {
+                            stage = 0;
+                            phase ^= 1;
+                            first = false;
+                        }
+                        continue;
+                    }
                     TR_BEGIN(dq_wait);
                     if (!first && !tc::mbar_wait(empty_addr + 8 * stage, phase ^ 1)) {
                         if (lane == 0) atomicExch(status, 4);
@@ -390,8 +410,8 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
 #pragma unroll
                     for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
                         const size_t off = static_cast<size_t>(it + kAhead) * kItemBytes;
-                        w0[d][nt] = ld_stream_v4(wp[nt] + off);
-                        w1[d][nt] = ld_stream_v4(wp[nt] + off + 32);
+                        if (Cfg::kKSplit == 1 || kgrp == 0) w0[d][nt] = ld_stream_v4(wp[nt] + off);
+                        if (Cfg::kKSplit == 1 || kgrp == 1) w1[d][nt] = ld_stream_v4(wp[nt] + off + 32);
                         meta[d][nt] = ld_pinned_v2(mp[nt] + off);
                     }
                 }
@@ -561,7 +581,8 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
     using Cfg = GemmCfg<HALVES, BN, DW, AHEAD>;
     CUtensorMap map_x;
     const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128 * Cfg::kBoxHalves, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    const int box_rows = (HALVES == 1 && MODE == kPlain) ? a_box_rows(static_cast<int>(M)) : 128 * Cfg::kBoxHalves;
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, box_rows, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const bool cvt = scale_dtype != (ScaleMul<ActT>::kFmt == 0 ? EQ_F16 : EQ_BF16);
     auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true, MODE> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false, MODE>;
@@ -580,7 +601,7 @@ int launch_split(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* 
     using Cfg = GemmCfg<1, 256, 16, 2>;
     CUtensorMap map_x;
     const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, 128, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, a_box_rows(static_cast<int>(M)), kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const int64_t tiles = ceil_div(N, 256), items = K / 128;
     int64_t splits = sm_count() / tiles;
@@ -617,7 +638,7 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
     if (M <= 128) {
         // wide matrices fill the SMs with 64-column tiles; narrow ones split K over 256-column tiles instead
         if (ceil_div(N, 64) >= sm_count())
-            return launch_cfg<ActT, 1, 64, 4, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, 1, stream);
+            return launch_cfg<ActT, 1, 64, 8, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, 1, stream);
         return launch_split<ActT>(wq, scale_dtype, x, y, M, N, K, status, partial, counters, stream);
     }
     if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
