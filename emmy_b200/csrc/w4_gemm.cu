@@ -643,7 +643,7 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
     }
     if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
         return launch_cfg<ActT, 2, 256, 16, 2, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
-    return launch_cfg<ActT, 2, 128, 8, 3, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
+    return launch_cfg<ActT, 2, 128, 16, 3, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
 }
 
 }  // namespace
