@@ -55,18 +55,6 @@ struct GemmCfg {
     static_assert(kAccCols <= 512, "the accumulators must fit TMEM");
 };
 
-#ifdef EQ_W4G_TRACE
-__device__ unsigned long long g_w4g_trace[16];
-#define TR_DECL(n) long long tr_##n = 0
-#define TR_BEGIN(n) const long long tb_##n = clock64()
-#define TR_END(n) tr_##n += clock64() - tb_##n
-#define TR_FLUSH(slot, n) atomicAdd(&g_w4g_trace[slot], static_cast<unsigned long long>(tr_##n))
-#else
-#define TR_DECL(n)
-#define TR_BEGIN(n)
-#define TR_END(n)
-#define TR_FLUSH(slot, n)
-#endif
 
 // 8-byte read-only load that stays where it is written (issued kAhead steps before its use).
 __device__ __forceinline__ uint2 ld_pinned_v2(const void* p) {
@@ -214,17 +202,14 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         // ---- TMA producer of the activation tiles
         if (tc::elect_one()) {
             tc::tma_prefetch_desc(&map_x);
-            TR_DECL(tma_wait);
             int stage = 0;
             uint32_t phase = 0;
             bool first = true;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                TR_BEGIN(tma_wait);
                 if (!first && !tc::mbar_wait(empty_addr + 8 * stage, phase ^ 1)) {
                     atomicExch(status, 1);
                     break;
                 }
-                TR_END(tma_wait);
                 const uint32_t bar = full_a_addr + 8 * stage;
                 // one copy per TMA box (Cfg::kBoxHalves 128-row halves); halves without rows are not fetched
                 constexpr int kBoxBytes = Cfg::kBoxHalves * 128 * kRowBytes;
@@ -241,25 +226,16 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     first = false;
                 }
             }
-            TR_FLUSH(0, tma_wait);
         }
     } else if (warp == 1) {
         // ---- MMA issuer
         if (tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc(ScaleMul<ActT>::kFmt, ScaleMul<ActT>::kFmt, 128, BN);
-            TR_DECL(mma_wa);
-            TR_DECL(mma_wb);
-            TR_DECL(mma_total);
-            TR_BEGIN(mma_total);
             int stage = 0;
             uint32_t phase = 0;
             for (int kb = 0; kb < k_blocks; ++kb) {
-                TR_BEGIN(mma_wa);
                 const bool got_a = tc::mbar_wait(full_a_addr + 8 * stage, phase);
-                TR_END(mma_wa);
-                TR_BEGIN(mma_wb);
                 const bool got_b = got_a && tc::mbar_wait(full_b_addr + 8 * stage, phase);
-                TR_END(mma_wb);
                 if (!got_b) {
                     atomicExch(status, 2);
                     break;
@@ -281,10 +257,6 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 }
             }
             tc::mma_commit(tc::smem_u32(acc_ready));  // on a broken pipeline too: the epilogue must not sit out its wait
-            TR_END(mma_total);
-            TR_FLUSH(1, mma_wa);
-            TR_FLUSH(2, mma_wb);
-            TR_FLUSH(3, mma_total);
         }
     } else {
         // ---- dequant producers
@@ -330,17 +302,12 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         bool broken = false, first = true;
         int stage = 0;
         uint32_t phase = 0;
-        TR_DECL(dq_wait);
-        TR_DECL(dq_work);
-        TR_DECL(dq_const);
-        TR_DECL(dq_refill);
         for (int it0 = 0; it0 < my_items && !broken; it0 += kAhead) {
 #pragma unroll
             for (int d = 0; d < kAhead; ++d) {
                 const int it = it0 + d;
                 if (it >= my_items || broken) continue;
                 // the item's constants: exact-dequant zero terms and the scale pair of columns g and g + 8
-                TR_BEGIN(dq_const);
                 typename Frag<ActT>::Zero z_lo[Cfg::kTilesPerWarp], z_hi[Cfg::kTilesPerWarp];
                 uint32_t s_lo[Cfg::kTilesPerWarp], s_hi[Cfg::kTilesPerWarp];
 #pragma unroll
@@ -351,10 +318,6 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                     s_lo[nt] = ScaleMul<ActT>::template pair<CVT>(mt.x & 0xFFFFu);
                     s_hi[nt] = ScaleMul<ActT>::template pair<CVT>(mt.x >> 16);
                 }
-#ifdef EQ_W4G_TRACE
-                asm volatile("" ::"r"(s_hi[0]), "r"(z_hi[0].sub) : "memory");
-#endif
-                TR_END(dq_const);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     if (broken) continue;
@@ -366,14 +329,11 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         }
                         continue;
                     }
-                    TR_BEGIN(dq_wait);
                     if (!first && !tc::mbar_wait(empty_addr + 8 * stage, phase ^ 1)) {
                         if (lane == 0) atomicExch(status, 4);
                         broken = true;
                         continue;
                     }
-                    TR_END(dq_wait);
-                    TR_BEGIN(dq_work);
                     const uint32_t tile_addr = b_base + stage * Cfg::kTileB;
 #pragma unroll
                     for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
@@ -403,9 +363,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         phase ^= 1;
                         first = false;
                     }
-                    TR_END(dq_work);
                 }
-                TR_BEGIN(dq_refill);
                 if (it + kAhead < my_items) {  // refill this ring slot
 #pragma unroll
                     for (int nt = 0; nt < Cfg::kTilesPerWarp; ++nt) {
@@ -415,19 +373,13 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                         meta[d][nt] = ld_pinned_v2(mp[nt] + off);
                     }
                 }
-                TR_END(dq_refill);
             }
         }
-        TR_DECL(epi_wait);
-        TR_DECL(epi_work);
-        TR_BEGIN(epi_wait);
 
         // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. +31
         const int quarter = warp & 3;
         const int quartet = dw >> 2;
         const bool ok = __all_sync(0xFFFFFFFFu, tc::mbar_wait(tc::smem_u32(acc_ready), 0));
-        TR_END(epi_wait);
-        TR_BEGIN(epi_work);
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
         // Work units: (128-row half, 32-column chunk of the output), dealt round-robin to the warp quartets.  Everything
@@ -557,14 +509,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 if (dw == 0 && lane == 0) split.counters[blockIdx.x] = 0;
             }
         }
-        TR_END(epi_work);
         if (lane == 0 && dw == 0) {
-            TR_FLUSH(4, dq_wait);
-            TR_FLUSH(5, dq_work);
-            TR_FLUSH(6, epi_wait);
-            TR_FLUSH(7, epi_work);
-            TR_FLUSH(8, dq_const);
-            TR_FLUSH(9, dq_refill);
         }
     }
     tc::fence_before_sync();
@@ -680,14 +625,3 @@ int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int
 }
 
 }  // namespace eq
-
-#ifdef EQ_W4G_TRACE
-extern "C" int eq_debug_w4g_trace(unsigned long long* out, int reset) {
-    if (cudaMemcpyFromSymbol(out, eq::g_w4g_trace, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
-    if (reset) {
-        unsigned long long zero[16] = {0};
-        if (cudaMemcpyToSymbol(eq::g_w4g_trace, zero, sizeof(zero)) != cudaSuccess) return -1;
-    }
-    return 0;
-}
-#endif

@@ -1,8 +1,10 @@
 // W4A16 linear: the entry points and their dispatch.
 //
-//   M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles.
-//   M > 16    w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
-//   M > 16 with an output that is not 16-byte aligned: w4a16_tile_kernel below, in 64-row blocks.
+//   M == 1         w4a16_gemv1_kernel (w4_gemv1.cu): half-SM CTAs, equal item spans, launches overlap in pairs.
+//   2 <= M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles.
+//   M > 16         w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
+//   w4a16_tile_kernel below: M > 16 with an output that is not 16-byte aligned (in 64-row blocks), and decode
+//   shapes whose activations do not fit shared memory (K beyond about 100 k at M == 1).
 //
 // w4a16_tile_kernel is the plain form the other two grew out of, and the body the small-row MoE GEMMs still use
 // (w4_tile.cuh): many small CTAs of four warps, one 16-column tile and one K split each, nothing between a warp and
@@ -20,7 +22,9 @@
 
 namespace eq {
 
-int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream);  // w4_stream.cu
+int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream, bool* fits);  // w4_stream.cu
+int w4_gemv1_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t N, int64_t K,
+                    int act_dtype, uint32_t* xchg, int* status, cudaStream_t stream, bool* fits);  // w4_gemv1.cu
 int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
                       int64_t K, int act_dtype, void* gathered, int* status, float* partial, int* counters, cudaStream_t stream);  // w4_gemm.cu
 
@@ -77,12 +81,14 @@ static int launch_w4(const W4Params& p, cudaStream_t stream) {
 
 using namespace eq;
 
-// Front part: f32 partial sums of up to 128 rows, one arrival counter per 16-column tile, one status word.  Calls with
-// M > 16 add room for the column-gathered copy of x that act-order weights need on the tensor path.
+// Workspace layout: a 256-byte header whose first word is the status word (fixed place, whatever M and N are), then
+// f32 partial sums of up to 128 rows and one arrival counter per 16-column tile.  Calls with M > 16 add room for the
+// column-gathered copy of x that act-order weights need on the tensor path.
+static constexpr size_t kW4Header = 256;
 static int64_t w4_front_rows(int64_t M) { return M < 128 ? M : 128; }
 static size_t w4_front_bytes(int64_t M, int64_t N) {
     const int64_t rows = w4_front_rows(M);
-    return static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16 + 1) * sizeof(int);
+    return kW4Header + static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16) * sizeof(int);
 }
 static size_t w4_gather_offset(int64_t M, int64_t N) { return (w4_front_bytes(M, N) + 255) / 256 * 256; }
 
@@ -92,38 +98,51 @@ extern "C" size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     return w4_gather_offset(M, N) + static_cast<size_t>(M) * K * 2;
 }
 
+static int w4a16_check(const char* who, const void* wq, int scale_dtype, int64_t K, int64_t N, int64_t* G, const void* x, int64_t M,
+                       int act_dtype, const void* y) {
+    EQ_REQUIRE(wq && (M == 0 || (x && y)), EQ_ERR_BAD_ARG, "%s: null pointer", who);
+    EQ_REQUIRE(K > 0 && N > 0 && M >= 0, EQ_ERR_BAD_ARG, "%s: bad extents M=%lld K=%lld N=%lld", who, (long long)M, (long long)K,
+               (long long)N);
+    if (*G == -1) *G = K;
+    EQ_REQUIRE(*G > 0 && K % *G == 0, EQ_ERR_BAD_ARG, "%s: group size %lld does not cover K=%lld", who, (long long)*G, (long long)K);
+    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0 && *G % 128 == 0, EQ_ERR_UNSUPPORTED,
+               "%s: needs K %% 128 == 0, N %% 16 == 0, G %% 128 == 0 (K=%lld N=%lld G=%lld)", who, (long long)K, (long long)N,
+               (long long)*G);
+    EQ_REQUIRE(K < (1 << 24) && N < (1 << 24), EQ_ERR_UNSUPPORTED, "%s: extent too large", who);
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "%s: activations must be f16 or bf16", who);
+    EQ_REQUIRE(scale_dtype == EQ_F16 || scale_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "%s: scales must be f16 or bf16", who);
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(aligned(wq, 16) && aligned(x, 16) && aligned(y, 2), EQ_ERR_BAD_ALIGN, "%s: wq and x need 16-byte alignment", who);
+    return EQ_OK;
+}
+
 extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                                const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
                                void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    EQ_REQUIRE(wq && (M == 0 || (x && y)), EQ_ERR_BAD_ARG, "eq_w4a16_linear: null pointer");
-    EQ_REQUIRE(K > 0 && N > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_w4a16_linear: bad extents M=%lld K=%lld N=%lld", (long long)M,
-               (long long)K, (long long)N);
-    if (G == -1) G = K;
-    EQ_REQUIRE(G > 0 && K % G == 0, EQ_ERR_BAD_ARG, "eq_w4a16_linear: group size %lld does not cover K=%lld", (long long)G,
-               (long long)K);
-    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0 && G % 128 == 0, EQ_ERR_UNSUPPORTED,
-               "eq_w4a16_linear: needs K %% 128 == 0, N %% 16 == 0, G %% 128 == 0 (K=%lld N=%lld G=%lld)", (long long)K,
-               (long long)N, (long long)G);
-    EQ_REQUIRE(K < (1 << 24) && N < (1 << 24), EQ_ERR_UNSUPPORTED, "eq_w4a16_linear: extent too large");
-    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_w4a16_linear: activations must be f16 or bf16");
-    EQ_REQUIRE(scale_dtype == EQ_F16 || scale_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_w4a16_linear: scales must be f16 or bf16");
-    if (M == 0) return EQ_OK;
-    EQ_REQUIRE(aligned(wq, 16) && aligned(x, 16) && aligned(y, 2), EQ_ERR_BAD_ALIGN,
-               "eq_w4a16_linear: wq and x need 16-byte alignment");
+    const int checked = w4a16_check("eq_w4a16_linear", wq, scale_dtype, K, N, &G, x, M, act_dtype, y);
+    if (checked != EQ_OK || M == 0) return checked;
     EQ_REQUIRE(workspace && workspace_bytes >= eq_w4a16_workspace_bytes(M, N, K), EQ_ERR_WORKSPACE,
                "eq_w4a16_linear: workspace of %zu bytes needed, %zu given", eq_w4a16_workspace_bytes(M, N, K), workspace_bytes);
     EQ_REQUIRE(aligned(workspace, 16), EQ_ERR_BAD_ALIGN, "eq_w4a16_linear: workspace must be 16-byte aligned");
 
+    int* status = static_cast<int*>(workspace);
+    float* partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kW4Header);
+    int* counters = reinterpret_cast<int*>(partial + w4_front_rows(M) * N);
+
     if (M > 16 && aligned(y, 16)) {
-        // prefill-shaped: the tcgen05 kernel; its bounded waits report through the workspace's status word
-        const int64_t ws_rows = w4_front_rows(M);
-        float* partial = static_cast<float*>(workspace);
-        int* counters = reinterpret_cast<int*>(partial + ws_rows * N);
-        int* status = counters + N / 16;
+        // prefill-shaped: the tcgen05 kernel; its bounded waits report through the status word, cleared per call
+        EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
         void* gathered = static_cast<unsigned char*>(workspace) + w4_gather_offset(M, N);
         return w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
                                  partial, counters, stream);
+    }
+    if (M == 1) {
+        // the decode step's GEMV; the workspace carries its sixteen-word hand-overs between neighbouring CTAs
+        bool fits = false;
+        const int st = w4_gemv1_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, N, K, act_dtype,
+                                       reinterpret_cast<uint32_t*>(partial), status, stream, &fits);
+        if (st != EQ_OK || fits) return st;
     }
 
     const size_t esz = 2;
@@ -134,9 +153,8 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         p.perm = perm;
         p.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * K * esz;
         p.y = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
-        p.wsp = static_cast<float*>(workspace);
-        const int64_t ws_rows = w4_front_rows(M);
-        p.counters = reinterpret_cast<int*>(static_cast<float*>(workspace) + ws_rows * N);
+        p.wsp = partial;
+        p.counters = counters;
         p.K = static_cast<int>(K);
         p.N = static_cast<int>(N);
         p.M = mb;
@@ -146,74 +164,98 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         p.x_rows = nullptr;
         p.y_rows = nullptr;
         p.y_ptrs = nullptr;
-        int st;
-        if (mb <= 16 && static_cast<long long>(N / 16) * (K / 128) < (1LL << 30))
-            st = w4_stream_launch(p, act_dtype, stream);  // decode-shaped: one wave of equal spans
-        else
+        int st = EQ_OK;
+        bool fits = false;
+        if (mb > 1 && mb <= 16 && static_cast<long long>(N / 16) * (K / 128) < (1LL << 30))
+            st = w4_stream_launch(p, act_dtype, stream, &fits);  // decode-shaped: one wave of equal spans
+        if (st != EQ_OK) return st;
+        if (!fits)  // shapes whose staging does not fit shared memory, and row blocks of an unaligned output: K splits
+                    // of small CTAs that meet in the workspace
             st = act_dtype == EQ_F16 ? launch_w4<__half>(p, stream) : launch_w4<__nv_bfloat16>(p, stream);
         if (st != EQ_OK) return st;
     }
     return EQ_OK;
 }
 
-// The decode kernels have no device-side wait; the tensor-path kernel sets the status word when one of its bounded
-// pipeline waits ran out.
+// The tensor-path kernel and the GEMV's hand-over wait are bounded; one that runs out sets the status word.
 extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     EQ_REQUIRE(workspace && M > 0 && N > 0, EQ_ERR_BAD_ARG, "eq_w4a16_status: bad arguments");
-    const int64_t ws_rows = w4_front_rows(M);
-    const int* status = reinterpret_cast<const int*>(static_cast<const float*>(workspace) + ws_rows * N) + N / 16;
     int host = 0;
-    EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
     EQ_CUDA_OK(cudaStreamSynchronize(stream));
     EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_w4a16_status: the workspace status word is set (%d)", host);
     return EQ_OK;
 }
 
 // ---- entry point for callers that cannot allocate ------------------------------------------------------------
-// The scratch of eq_w4a16_linear (partial sums, arrival counters, status word) for up to kNoAllocMaxM rows and
-// kNoAllocMaxN columns, resident in every device that loads this library until the process exits.
+// The scratch of eq_w4a16_linear (status word, hand-over words / partial sums, arrival counters) for up to kNoAllocMaxM
+// rows and kNoAllocMaxN columns, resident in every device that loads this library until the process exits.
 namespace {
 constexpr int64_t kNoAllocMaxM = 16;
 constexpr int64_t kNoAllocMaxN = 32768;
-constexpr size_t kNoAllocBytes = static_cast<size_t>(kNoAllocMaxM) * kNoAllocMaxN * sizeof(float) +
-                                 (static_cast<size_t>(kNoAllocMaxN) / 16 + 1) * sizeof(int) + 252;
-static __device__ __align__(256) unsigned char g_w4_noalloc_scratch[kNoAllocBytes];
+constexpr size_t kNoAllocBytes = kW4Header + static_cast<size_t>(kNoAllocMaxM) * kNoAllocMaxN * sizeof(float) +
+                                 (static_cast<size_t>(kNoAllocMaxN) / 16) * sizeof(int) + 256;
+static __device__ __align__(256) unsigned char g_w4_noalloc_scratch[kNoAllocBytes];  // zero when the module loads
+
+struct NoAllocState {
+    void* ptr;   // device address of the array on this device
+    int dirty;   // a call failed after it may have launched: clear the array before the next use
+};
 
 // Device address of the array above on the current device.  The array's name is only a host-side handle; the
 // address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
-int noalloc_scratch(void** out) {
-    static void* cached[64] = {nullptr};
+int noalloc_state(NoAllocState** out) {
+    static NoAllocState state[64] = {};
     int dev = -1;
     EQ_CUDA_OK(cudaGetDevice(&dev));
     EQ_REQUIRE(dev >= 0 && dev < 64, EQ_ERR_UNSUPPORTED, "eq_w4a16_linear_noalloc: device index %d out of range", dev);
-    void* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    void* ptr = __atomic_load_n(&state[dev].ptr, __ATOMIC_ACQUIRE);
     if (!ptr) {
         EQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_w4_noalloc_scratch));
         EQ_REQUIRE(ptr != nullptr, EQ_ERR_CUDA, "eq_w4a16_linear_noalloc: no device address for the static scratch");
-        __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
+        __atomic_store_n(&state[dev].ptr, ptr, __ATOMIC_RELEASE);
     }
-    *out = ptr;
+    *out = &state[dev];
     return EQ_OK;
 }
 }  // namespace
 
 extern "C" int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N,
                                        int64_t G, const void* x, int64_t M, int act_dtype, void* y, void* stream_) {
-    EQ_REQUIRE(M >= 0 && M <= kNoAllocMaxM, EQ_ERR_UNSUPPORTED,
+    const int checked = w4a16_check("eq_w4a16_linear_noalloc", wq, scale_dtype, K, N, &G, x, M, act_dtype, y);
+    if (checked != EQ_OK) return checked;
+    EQ_REQUIRE(M <= kNoAllocMaxM, EQ_ERR_UNSUPPORTED,
                "eq_w4a16_linear_noalloc: M=%lld exceeds the built-in scratch (at most %lld rows); use eq_w4a16_linear with "
                "a caller workspace",
                (long long)M, (long long)kNoAllocMaxM);
-    EQ_REQUIRE(N > 0 && N <= kNoAllocMaxN, EQ_ERR_UNSUPPORTED,
+    EQ_REQUIRE(N <= kNoAllocMaxN, EQ_ERR_UNSUPPORTED,
                "eq_w4a16_linear_noalloc: N=%lld exceeds the built-in scratch (at most %lld columns); use eq_w4a16_linear "
                "with a caller workspace",
                (long long)N, (long long)kNoAllocMaxN);
     if (M == 0) return EQ_OK;
-    void* scratch = nullptr;
-    int st = noalloc_scratch(&scratch);
+    NoAllocState* state = nullptr;
+    int st = noalloc_state(&state);
     if (st != EQ_OK) return st;
     const size_t used = eq_w4a16_workspace_bytes(M, N, K);
-    // all calls share the one array: whatever an earlier (possibly failed) call left there is cleared first
-    EQ_CUDA_OK(cudaMemsetAsync(scratch, 0, used, static_cast<cudaStream_t>(stream_)));
-    return eq_w4a16_linear(wq, scale_dtype, perm, K, N, G, x, M, act_dtype, y, scratch, used, stream_);
+    // The array starts out zero and every kernel leaves the words it used zero again, so nothing is cleared on the
+    // way in; only after a call that failed part-way is the whole array cleared before the next one.
+    if (__atomic_load_n(&state->dirty, __ATOMIC_ACQUIRE)) {
+        EQ_CUDA_OK(cudaMemsetAsync(state->ptr, 0, kNoAllocBytes, static_cast<cudaStream_t>(stream_)));
+        __atomic_store_n(&state->dirty, 0, __ATOMIC_RELEASE);
+    }
+    st = eq_w4a16_linear(wq, scale_dtype, perm, K, N, G, x, M, act_dtype, y, state->ptr, used, stream_);
+    if (st != EQ_OK) __atomic_store_n(&state->dirty, 1, __ATOMIC_RELEASE);
+    return st;
+}
+
+// Reads the built-in array's status word (synchronizes the stream): EQ_ERR_TIMEOUT if a bounded wait of an earlier
+// eq_w4a16_linear_noalloc call on this device ran out; the array is then cleared before its next use.
+extern "C" int eq_w4a16_noalloc_status(void* stream_) {
+    NoAllocState* state = nullptr;
+    int st = noalloc_state(&state);
+    if (st != EQ_OK) return st;
+    st = eq_w4a16_status(state->ptr, 1, 16, stream_);
+    if (st != EQ_OK) __atomic_store_n(&state->dirty, 1, __ATOMIC_RELEASE);
+    return st;
 }

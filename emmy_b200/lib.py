@@ -104,6 +104,7 @@ def load() -> C.CDLL:
         "eq_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, i64, i, p, p, sz, p]),
         "eq_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),
         "eq_w4a16_linear_noalloc": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p]),
+        "eq_w4a16_noalloc_status": (i, [p]),
         "eq_ep_moe_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),
         "eq_ep_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, p, i64, i, p, C.POINTER(EpPeers), C.c_uint32, p, sz, p]),
         "eq_ep_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),

@@ -15,23 +15,26 @@ from torch import nn
 
 from . import ops, ops_moe, ops_nvfp4
 
-_REGISTRY: dict[int, object] = {}
+# The custom ops take the repacked weights as TENSORS (plus plain ints), never as process-local handles: the packed
+# blobs are module buffers, so they follow module.to(), are freed with the module, and a traced graph holds nothing
+# but tensors and shapes.
 
 
-def _register(obj) -> int:
-    key = id(obj)
-    _REGISTRY[key] = obj
-    return key
+def _w4_weight(wq, perm, k, n, group, scale_bf16) -> ops.W4Weight:
+    w = ops.W4Weight()
+    w.wq, w.perm, w.k, w.n, w.group = wq, (perm if perm is not None and perm.numel() else None), k, n, group
+    w.scale_dtype, w.fmt = (torch.bfloat16 if scale_bf16 else torch.float16), "packed"
+    return w
 
 
 @torch.library.custom_op("emmyq::w4a16_linear", mutates_args=(), device_types="cuda")
-def _w4a16_op(x: torch.Tensor, handle: int) -> torch.Tensor:
-    return ops.w4a16_linear(x.contiguous(), _REGISTRY[handle])
+def _w4a16_op(x: torch.Tensor, wq: torch.Tensor, perm: torch.Tensor, k: int, n: int, group: int, scale_bf16: bool) -> torch.Tensor:
+    return ops.w4a16_linear(x.contiguous(), _w4_weight(wq, perm, k, n, group, scale_bf16))
 
 
 @_w4a16_op.register_fake
-def _(x, handle):
-    return x.new_empty((x.shape[0], _REGISTRY[handle].n))
+def _(x, wq, perm, k, n, group, scale_bf16):
+    return x.new_empty((x.shape[0], n))
 
 
 @torch.library.custom_op("emmyq::fp8_linear", mutates_args=(), device_types="cuda")
@@ -55,12 +58,16 @@ def _(x, weight, scale_tiled, scale_2, input_scale):
 
 
 @torch.library.custom_op("emmyq::moe_w4a16", mutates_args=(), device_types="cuda")
-def _moe_op(x: torch.Tensor, router_logits: torch.Tensor, handle: int, topk: int) -> torch.Tensor:
-    return ops_moe.moe_forward(x.contiguous(), router_logits.float().contiguous(), _REGISTRY[handle], topk)
+def _moe_op(x: torch.Tensor, router_logits: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, experts: int, hidden: int,
+            inter: int, group: int, scale_bf16: bool, topk: int) -> torch.Tensor:
+    w = ops_moe.MoEWeights()
+    w.gate_up, w.down, w.experts, w.hidden, w.inter, w.group = gate_up, down, experts, hidden, inter, group
+    w.scale_dtype = torch.bfloat16 if scale_bf16 else torch.float16
+    return ops_moe.moe_forward(x.contiguous(), router_logits.float().contiguous(), w, topk)
 
 
 @_moe_op.register_fake
-def _(x, router_logits, handle, topk):
+def _(x, router_logits, gate_up, down, experts, hidden, inter, group, scale_bf16, topk):
     return torch.empty_like(x)
 
 
@@ -89,14 +96,23 @@ class W4A16Linear(nn.Module):
             self.register_buffer("g_idx", torch.arange(in_features, dtype=torch.int32) // g)
         else:
             self.g_idx = None
-        self._packed = None
-        self._handle = None
+        # the repacked stream (and the row order of scattered act-order groups): derived data, not part of the state dict
+        self.register_buffer("packed_wq", None, persistent=False)
+        self.register_buffer("packed_perm", None, persistent=False)
+        self._scale_bf16 = scale_dtype == torch.bfloat16
 
     def finalize(self, keep_checkpoint: bool = False) -> "W4A16Linear":
-        self._packed = ops.w4_repack(self.qweight, self.qzeros, self.scales, self.group_size, self.fmt, g_idx=self.g_idx)
-        self._handle = _register(self._packed)
+        """Repack on the device (the checkpoint buffers must already be there)."""
+        if self.qweight is None:
+            raise RuntimeError("W4A16Linear.finalize: the checkpoint tensors were already released")
+        if not self.qweight.is_cuda:
+            raise RuntimeError("W4A16Linear.finalize: move the module to a CUDA device first; there is no CPU path")
+        packed = ops.w4_repack(self.qweight, self.qzeros, self.scales, self.group_size, self.fmt, g_idx=self.g_idx)
+        self.packed_wq = packed.wq
+        self.packed_perm = packed.perm if packed.perm is not None else torch.empty(0, dtype=torch.int32, device=packed.wq.device)
+        self._scale_bf16 = packed.scale_dtype == torch.bfloat16
         if not keep_checkpoint:
-            self.qweight = self.qzeros = self.scales = None
+            self.qweight = self.qzeros = self.scales = self.g_idx = None
         return self
 
     def dequantized_weight(self, dtype=torch.float16) -> torch.Tensor:
@@ -105,10 +121,12 @@ class W4A16Linear(nn.Module):
                               transpose=True)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self._packed is None:
+        if self.packed_wq is None:
             self.finalize(keep_checkpoint=True)
         x2, lead = _flat(x)
-        return _w4a16_op(x2, self._handle).reshape(*lead, self.out_features)
+        g = self.in_features if self.group_size == -1 else self.group_size
+        y = _w4a16_op(x2, self.packed_wq, self.packed_perm, self.in_features, self.out_features, g, self._scale_bf16)
+        return y.reshape(*lead, self.out_features)
 
 
 class FP8Linear(nn.Module):
@@ -142,17 +160,19 @@ class NVFP4Linear(nn.Module):
         self.register_buffer("weight_scale", torch.zeros((out_features, in_features // 16), dtype=torch.uint8))
         self.register_buffer("weight_scale_2", torch.ones(1, dtype=torch.float32))
         self.register_buffer("input_scale", torch.ones(1, dtype=torch.float32))
-        self._tiled = None
+        self.register_buffer("scale_tiled", None, persistent=False)  # weight_scale in the tensor core's atom order
 
     def finalize(self) -> "NVFP4Linear":
-        self._tiled = ops_nvfp4.nvfp4_tile_weight_scales(self.weight_scale, self.in_features)
+        if not self.weight_scale.is_cuda:
+            raise RuntimeError("NVFP4Linear.finalize: move the module to a CUDA device first; there is no CPU path")
+        self.scale_tiled = ops_nvfp4.nvfp4_tile_weight_scales(self.weight_scale, self.in_features)
         return self
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self._tiled is None:
+        if self.scale_tiled is None:
             self.finalize()
         x2, lead = _flat(x)
-        y = _nvfp4_op(x2, self.weight, self._tiled, self.weight_scale_2.reshape(1), self.input_scale.reshape(1))
+        y = _nvfp4_op(x2, self.weight, self.scale_tiled, self.weight_scale_2.reshape(1), self.input_scale.reshape(1))
         return y.reshape(*lead, self.out_features)
 
 
@@ -164,14 +184,19 @@ class QuantMoE(nn.Module):
     def __init__(self, top_k: int):
         super().__init__()
         self.top_k = top_k
-        self._weights = None
-        self._handle = None
+        self.register_buffer("packed_gate_up", None, persistent=False)
+        self.register_buffer("packed_down", None, persistent=False)
+        self._geometry = None
 
     def load_experts(self, w_gate_up, w_down, group_size: int = 128, fmt: str = "awq") -> "QuantMoE":
-        self._weights = ops_moe.moe_repack(w_gate_up, w_down, group_size, fmt)
-        self._handle = _register(self._weights)
+        w = ops_moe.moe_repack(w_gate_up, w_down, group_size, fmt)
+        self.packed_gate_up, self.packed_down = w.gate_up, w.down
+        self._geometry = (w.experts, w.hidden, w.inter, w.group, w.scale_dtype == torch.bfloat16)
         return self
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
+        if self._geometry is None:
+            raise RuntimeError("QuantMoE.forward: load_experts() has not been called")
         x2, lead = _flat(x)
-        return _moe_op(x2, router_logits.reshape(-1, router_logits.shape[-1]), self._handle, self.top_k).reshape(*lead, x.shape[-1])
+        y = _moe_op(x2, router_logits.reshape(-1, router_logits.shape[-1]), self.packed_gate_up, self.packed_down, *self._geometry, self.top_k)
+        return y.reshape(*lead, x.shape[-1])

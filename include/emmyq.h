@@ -105,40 +105,46 @@ int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, vo
 
 /* ------------------------------------------------------------------ W4A16 linear */
 
-/* Scratch for eq_w4a16_linear: f32 partial sums, per-tile arrival counters and a status word, plus, for M > 16,
- * room for a column-gathered copy of x (used when the weight carries a row permutation).  The buffer must be zero
- * the first time it is used; every call leaves its counters and sums zero again, so it can be reused by calls on one
- * stream. */
+/* Scratch for eq_w4a16_linear: a 256-byte header whose first word is the status word, then f32 words (the partial
+ * sums of the split-K kernels; at M = 1 the sixteen-word hand-overs between neighbouring CTAs of the GEMV) and one
+ * arrival counter per 16-column tile, plus, for M > 16, room for a column-gathered copy of x (used when the weight
+ * carries a row permutation).  The buffer must be zero the first time it is used; every call leaves the words it used
+ * zero again, so it can be reused by calls on one stream (calls on different streams need different buffers). */
 size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /* y[M, N] = x[M, K] @ W on repacked weights; x and y are act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * The operator the reference spells as int4 decode algebra in front of a LinearOp
  * (emmy/compiler/loader/quant.py:1235-1435) and evaluates eagerly as dequantize + F.linear
  * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it.
  * Needs K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1); x and wq 16-byte aligned.
- * M <= 16 runs the bandwidth kernels; M > 16 runs the tcgen05 kernel, which dequantises into shared memory. */
+ * M <= 16 runs the bandwidth kernels (any K: shapes whose activations do not fit shared memory run a split-K form
+ * through the workspace); M > 16 runs the tcgen05 kernel, which dequantises into shared memory. */
 int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                     const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
                     void* stream);
-/* The only device-side waits are the tensor-path kernel's pipeline barriers and they are bounded; one that runs out
- * sets a status word in the workspace and the affected outputs are undefined.  This call synchronizes the stream, reads the
- * word and returns EQ_ERR_TIMEOUT if it is set (the reference's counterpart is the host-side hung-launch deadline,
- * crates/emmy-runtime/src/cuda.rs:1401-1451).  M and N as given to eq_w4a16_linear. */
+/* The device-side waits (the tensor-path kernel's pipeline barriers, the GEMV's wait for a neighbour's sixteen words)
+ * are bounded; one that runs out sets the status word at the start of the workspace and the affected outputs are
+ * undefined.  This call synchronizes the stream, reads the word and returns EQ_ERR_TIMEOUT if it is set (the
+ * reference's counterpart is the host-side hung-launch deadline, crates/emmy-runtime/src/cuda.rs:1401-1451). */
 int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 
 /* eq_w4a16_linear for hosts that cannot hand over scratch memory.  (No counterpart in the reference: its runtime
  * owns all device memory itself.)  Some callers of this library run where device allocation is off limits: a
  * serving engine that has already given every byte to its KV-cache pool and forbids cudaMalloc afterwards, code on
  * a latency-critical decode path where an allocation would synchronize the device, or a plug-in loaded into a
- * process whose allocator it may not touch.  This variant takes inputs and outputs only.  Its partial sums and
- * counters live in one array built into the library (about 2 MiB, present on every GPU that loads the library
- * until the process exits), which limits it to M <= 16 rows and N <= 32768 columns; larger calls are refused with
- * EQ_ERR_UNSUPPORTED and should use eq_w4a16_linear.  It calls no allocating routine.
+ * process whose allocator it may not touch.  This variant takes inputs and outputs only.  The workspace of
+ * eq_w4a16_linear (status word, hand-over words of the M = 1 kernel, partial sums and arrival counters of the split-K
+ * kernel that serves very large K) is one array built into the library (about 2 MiB, present on every GPU that loads
+ * the library until the process exits), which limits it to M <= 16 rows and N <= 32768 columns; larger calls are
+ * refused with EQ_ERR_UNSUPPORTED and should use eq_w4a16_linear.  It calls no allocating routine.
  * The first call on each device looks up the array's device address (the device must be current); make that call
- * before starting a stream capture.  Every call clears the part of the array it uses and all calls share it, so
- * two calls that overlap on the GPU (different streams, or different threads without ordering) race: keep calls on
- * one device ordered. */
+ * before starting a stream capture.  The array starts out zero, every kernel leaves the words it used zero again,
+ * and all calls share it, so two calls that overlap on the GPU (different streams, or different threads without
+ * ordering) race: keep calls on one device ordered.  After a call that failed the array is cleared before its next
+ * use. */
 int eq_w4a16_linear_noalloc(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                             const void* x, int64_t M, int act_dtype, void* y, void* stream);
+/* eq_w4a16_status for the built-in array of the current device (no counterpart in the reference). */
+int eq_w4a16_noalloc_status(void* stream);
 
 /* ------------------------------------------------------------------ FP8-E4M3 W8A8 linear */
 
@@ -235,8 +241,10 @@ int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_t topk, int
 /* ------------------------------------------------------------------ expert-parallel MoE over peer memory */
 
 /* Experts sharded E_local per rank over `world` GPUs of one node.  The token exchange of the reference's expert
- * sharding (tests/serving/test_expert_sharding.py:49-165 pin its host-side split; the dispatch itself is an NCCL
- * all-to-all in the reference's stack) is done here by the kernels: rows are stored into the owner's receive buffer
+ * sharding is different: every rank keeps a slice of EVERY expert's intermediate axis and the partial outputs meet in
+ * one all-reduce (emmy/compiler/trace/huggingface.py:1071-1124, emmy/serving/vllm_model_gen.py:986-991; the host-side
+ * split is pinned by tests/serving/test_expert_sharding.py:49-165); it has no token exchange.  Here whole experts are
+ * sharded and the kernels move the tokens: rows are stored into the owner's receive buffer
  * and results stored back into the token's rank over NVLink peer mappings, ordered by epoch flags.  Every pointer
  * below is a device address valid ON THE CALLING RANK (its own buffer, or a peer's buffer mapped into this
  * process, e.g. through CUDA IPC or torch symmetric memory); entry r describes rank r's buffers. */

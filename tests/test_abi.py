@@ -50,8 +50,13 @@ def test_bad_arguments_return_codes_not_crashes(eq):
     assert eq.eq_w4a16_linear(C.c_void_p(8), 0, null, 4096, 4096, 128, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ALIGN
     assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 128, one, 1, 2, one, one, 1 << 20, null) == L.EQ_ERR_BAD_ARG
     assert eq.eq_w4a16_linear(one, 0, null, 4096, 4096, 64, one, 1, 0, one, one, 1 << 20, null) == L.EQ_ERR_UNSUPPORTED
-    assert eq.eq_w4a16_workspace_bytes(1, 4096, 4096) == 4096 * 4 + 257 * 4
-    front = 100 * 4096 * 4 + 257 * 4
+    # the allocation-free variant validates before anything else, also for an empty call
+    assert eq.eq_w4a16_linear_noalloc(one, 0, null, 4096, 4096, 64, one, 0, 0, one, null) == L.EQ_ERR_UNSUPPORTED
+    assert eq.eq_w4a16_linear_noalloc(one, 0, null, 4096, 4096, 128, one, 0, 5, one, null) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_w4a16_linear_noalloc(one, 0, null, 4096, 65536, 128, one, 1, 0, one, null) == L.EQ_ERR_UNSUPPORTED
+    # a 256-byte header (status word first), f32 words, one counter per 16-column tile
+    assert eq.eq_w4a16_workspace_bytes(1, 4096, 4096) == 256 + 4096 * 4 + 256 * 4
+    front = 256 + 100 * 4096 * 4 + 256 * 4
     assert eq.eq_w4a16_workspace_bytes(100, 4096, 256) == (front + 255) // 256 * 256 + 100 * 256 * 2
 
 
