@@ -14,10 +14,9 @@ Three partitions, as the path shards naturally:
   the data path.
 
 The reference shards differently -- every rank holds a 1/W slice of EVERY expert's intermediate axis and the
-partials are all-reduced (expert_intermediate_slice / slice_routed_experts,
-emmy/compiler/trace/huggingface.py:1071-1124; emmy/serving/vllm_model_gen.py:986-991).  `expert_intermediate_slice`
-below restates that slicing too: its partial sums must equal the expert-parallel result up to f32 summation order,
-which the tests use as a cross-check.
+partials are all-reduced (emmy/compiler/trace/huggingface.py:1071-1124; emmy/serving/vllm_model_gen.py:986-991).
+That slicing is restated with the test oracle, whose partial sums must equal the expert-parallel result up to f32
+summation order: the tests use it as a cross-check.
 
 The compute steps are passed in as callables, so the partition and exchange logic runs unchanged on CPU tensors
 with the gloo backend (that is how it is tested without GPUs); on GPUs the callables are the C-ABI operators.
@@ -78,22 +77,6 @@ def column_slice_nvfp4(weight, weight_scale, weight_scale_2, rank: int, world: i
     """Rows of the packed [N, K/2] weight and of its [N, K/16] block scales; the global scale is shared."""
     c = _cols(weight.shape[0], rank, world, 8)
     return weight[c].contiguous(), weight_scale[c].contiguous(), weight_scale_2
-
-
-def expert_intermediate_slice(name: str, tensor, rank: int, world: int, *, stacked: bool = False):
-    """The reference's tensor-parallel slice of one expert tensor along the intermediate axis
-    (emmy/compiler/trace/huggingface.py:1071-1089): gate and up keep rows, down keeps columns, a concatenated
-    w_gate_up keeps the same rows of each half, an extent-1 scale stays whole."""
-    axis = (1 if name.startswith("w_down") else 0) + int(stacked)
-    halves = 2 if name.startswith("w_gate_up") else 1
-    extent = tensor.shape[axis] // halves
-    if extent == 1:
-        return tensor
-    if extent % world:
-        raise ValueError(f"expert input {name!r} has {extent} intermediate entries on axis {axis}, not divisible by {world} ranks")
-    width = extent // world
-    parts = [tensor.narrow(axis, half * extent + rank * width, width) for half in range(halves)]
-    return torch.cat(parts, dim=axis).contiguous()
 
 
 def expert_owner(expert_ids: torch.Tensor, num_experts: int, world: int) -> torch.Tensor:
@@ -192,9 +175,20 @@ class EpMoe:
 
     Owns one symmetric buffer per rank (receive rows, their metadata and counts, returned rows, epoch flags), mapped
     into every rank of `group` through torch symmetric memory, and a local workspace.  `t_max` bounds the tokens of a
-    call on any rank; `cap` (rows one source may send to one destination) defaults to twice the balanced share plus
-    slack, or all picks when the group is small; rows beyond it are dropped and reported by `status()`.  The call
-    counter lives on the device, so `forward` has no host read and can be captured in a CUDA graph."""
+    call on any rank.  `cap` is the number of rows one source may send to one destination in one call; the default,
+    all of a rank's picks, can never overflow.  A smaller cap saves receive memory (`default_cap` gives twice the
+    balanced share plus slack) but is a bet on the routing: rows beyond it are DROPPED, which only the status word
+    reports.  Results of a call are defined only if `status()` (or `forward(..., check=True)`) comes back clean: an
+    overflow or a peer that did not arrive within the kernels' bounded wait leaves y undefined.  The call counter lives
+    on the device, so `forward` has no host read and can be captured in a CUDA graph.  Construction is collective: it
+    ends with a host barrier, so that no rank's first exchange waits on a peer that is still setting up."""
+
+    @staticmethod
+    def default_cap(t_max: int, topk: int, world: int) -> int:
+        """The opt-in smaller receive capacity: twice the balanced share of a rank's picks plus 256 rows."""
+        picks = t_max * topk
+        return min(picks, 2 * picks // world + 256)
+
 
     def __init__(self, group, t_max: int, topk: int, hidden: int, inter: int, experts_local: int, dtype, device, cap: int | None = None):
         import os
@@ -210,7 +204,9 @@ class EpMoe:
             raise ValueError(f"at most {L.EQ_EP_MAX_RANKS} ranks")
         picks = t_max * topk
         if cap is None:
-            cap = picks if self.world <= 2 else min(picks, 2 * picks // self.world + 256)
+            cap = picks
+        if not 0 < cap <= picks:
+            raise ValueError(f"cap must be in 1..{picks}")
         self.cap, self.t_max, self.topk, self.hidden, self.inter, self.experts_local = cap, t_max, topk, hidden, inter, experts_local
         self.dtype, self.device = dtype, device
         esz = 2
@@ -234,9 +230,13 @@ class EpMoe:
         self.lib = L
         need = L.load().eq_ep_moe_workspace_bytes(self.world, cap, experts_local, hidden, inter)
         self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)  # holds the device-side call counter
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's buffers and flags exist before anybody's first exchange
 
-    def forward(self, x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, w, out: torch.Tensor | None = None) -> torch.Tensor:
-        """x [T, H] this rank's tokens; ids int32 [T, k] / scores f32 [T, k] over all experts; w: the local experts."""
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, w, out: torch.Tensor | None = None,
+                check: bool = False) -> torch.Tensor:
+        """x [T, H] this rank's tokens; ids int32 [T, k] / scores f32 [T, k] over all experts; w: the local experts.
+        check=True synchronizes the stream and raises if the call overflowed `cap` or timed out on a peer."""
         import ctypes as C
 
         from .ops import _DTYPE, _ptr, _stream
@@ -253,6 +253,8 @@ class EpMoe:
                 self.workspace.numel(), _stream(),
             )
         )
+        if check:
+            self.status()
         return y
 
     def status(self) -> None:

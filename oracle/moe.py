@@ -86,3 +86,21 @@ def moe_layer(x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_
     """Whole routed layer on dense expert weights."""
     scores, ids = route_softmax_topk(logits, k)
     return combine_routed(x, scores, ids, lambda e, rows: expert_ffn(x[rows], w_gate_up[e], w_down[e]))
+
+
+def tp_expert_slice(name: str, tensor: torch.Tensor, rank: int, world: int, stacked: bool = False) -> torch.Tensor:
+    """The reference's own sharding of ONE expert tensor, used here as a cross-check of expert parallelism: every rank
+    keeps 1/world of the intermediate axis of every expert (emmy/compiler/trace/huggingface.py:1071-1089).  The
+    intermediate axis is the rows of w_gate / w_up / w_gate_up and the columns of w_down (one further in for
+    expert-stacked tensors); w_gate_up holds gate rows then up rows and keeps the same row range of both; a tensor
+    whose intermediate extent is 1 (a broadcast scale) is returned as it is."""
+    dim = int(stacked) + (1 if name.startswith("w_down") else 0)
+    blocks = 2 if name.startswith("w_gate_up") else 1
+    per_block = tensor.shape[dim] // blocks
+    if per_block == 1:
+        return tensor
+    if per_block % world:
+        raise ValueError(f"{name}: {per_block} intermediate entries do not split over {world} ranks")
+    share = per_block // world
+    index = torch.cat([torch.arange(b * per_block + rank * share, b * per_block + (rank + 1) * share) for b in range(blocks)])
+    return tensor.index_select(dim, index)

@@ -88,13 +88,39 @@ def test_reference_intermediate_slices_sum_to_the_whole_expert():
     x = torch.randn(5, h, generator=g, dtype=torch.float64)
     whole = omoe.expert_ffn(x, w_gate_up, w_down)
     parts = sum(
-        omoe.expert_ffn(x, shard.expert_intermediate_slice("w_gate_up", w_gate_up, r, world),
-                        shard.expert_intermediate_slice("w_down", w_down, r, world))
+        omoe.expert_ffn(x, omoe.tp_expert_slice("w_gate_up", w_gate_up, r, world),
+                        omoe.tp_expert_slice("w_down", w_down, r, world))
         for r in range(world)
     )
     torch.testing.assert_close(parts, whole, rtol=1e-5, atol=1e-5)
     scale = torch.ones(h, 1)  # a scale broadcast along the intermediate axis stays whole on every rank
-    assert shard.expert_intermediate_slice("w_down_scale", scale, 1, world) is scale
+    assert omoe.tp_expert_slice("w_down_scale", scale, 1, world) is scale
+
+
+def test_single_row_path_equals_batch_path():
+    """tests/serving/test_expert_sharding.py:101-165: routing a batch row by row gives bit for bit what routing the
+    batch at once gives (the combine adds each row's picks in ascending expert order whatever else is in the batch)."""
+    g = torch.Generator().manual_seed(3)
+    e, h, inter, k, t = 8, 32, 16, 3, 7
+    w_gu = (torch.randn(e, 2 * inter, h, generator=g) * 0.2).bfloat16()
+    w_dn = (torch.randn(e, h, inter, generator=g) * 0.2).bfloat16()
+    x = torch.randn(t, h, generator=g).bfloat16()
+    logits = torch.randn(t, e, generator=g)
+    whole = omoe.moe_layer(x, logits, w_gu, w_dn, k)
+    rows = torch.cat([omoe.moe_layer(x[r : r + 1], logits[r : r + 1], w_gu, w_dn, k) for r in range(t)])
+    assert torch.equal(whole, rows)
+    # and the stacked form of the reference's slicing agrees with slicing expert by expert
+    stacked = omoe.tp_expert_slice("w_gate_up", w_gu, 1, 2, stacked=True)
+    assert torch.equal(stacked[3], omoe.tp_expert_slice("w_gate_up", w_gu[3], 1, 2))
+
+
+def test_ep_default_cap_arithmetic():
+    """The opt-in smaller receive capacity: twice the balanced share plus slack, never more than all picks."""
+    assert shard.EpMoe.default_cap(4096, 8, 8) == 2 * 4096 * 8 // 8 + 256
+    assert shard.EpMoe.default_cap(4, 8, 2) == 32  # small calls: all picks
+    # a skewed routing that sends everything to one rank exceeds it; the default cap (all picks) cannot be exceeded
+    picks = 4096 * 8
+    assert picks > shard.EpMoe.default_cap(4096, 8, 8)
 
 
 def _ep_worker(rank, world, port, e, h, inter, k, t, ret):
