@@ -112,6 +112,40 @@ __global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int
     if (sf_tiled) sf_tiled[sf_tiled_offset(row, b, K / 64)] = sbits;
 }
 
+// ------------------------------------------------------------------------------------------------ weight quantize
+// The two-level weight quantizer (emmy/compiler/loader/quant.py:206-237), one thread per 16-element block:
+// block scale = amax_blk / 6 stored as e4m3 relative to scale_2; the divisor is the FUSED scale f16(dec(bits) * scale_2);
+// codes = e2m1(blk / fused) with zero where the fused scale is zero.  Every step an f32 round-to-nearest operation, as
+// numpy does them: bit-exact with the reference's output.
+template <typename InT>
+__global__ void quant_nvfp4_weight_kernel(const InT* __restrict__ w, int64_t N, int64_t K, const float* __restrict__ scale2,
+                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain) {
+    const int64_t blocks16 = K / 16;
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= N * blocks16) return;
+    const InT* src = w + idx * 16;
+    float v[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        v[i] = to_float(src[i]);
+        amax = fmaxf(amax, fabsf(v[i]));
+    }
+    const float s2 = scale2[0];
+    const uint8_t sbits = e4m3_satfinite(__fdiv_rn(__fdiv_rn(amax, 6.0f), s2));
+    const float fused = __half2float(__float2half_rn(__fmul_rn(e4m3_to_float(sbits), s2)));
+    uint32_t out[2] = {0, 0};
+    if (fused != 0.f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint8_t byte = e2m1x2_satfinite(__fdiv_rn(v[2 * i], fused), __fdiv_rn(v[2 * i + 1], fused));
+            out[i >> 2] |= static_cast<uint32_t>(byte) << (8 * (i & 3));
+        }
+    }
+    *reinterpret_cast<uint2*>(codes + idx * 8) = make_uint2(out[0], out[1]);
+    sf_plain[idx] = sbits;
+}
+
 // ------------------------------------------------------------------------------------------------ tensor path
 constexpr int kBM = 128;
 constexpr int kBKBytes = 128;                 // 256 e2m1 elements of K per stage row
@@ -482,6 +516,27 @@ extern "C" int eq_nvfp4_global_scale(const void* x, int64_t M, int64_t K, int in
     EQ_LAUNCH_OK("nvfp4_amax_kernel");
     nvfp4_scale2_kernel<<<1, 1, 0, stream>>>(scratch_u32, scale2);
     EQ_LAUNCH_OK("nvfp4_scale2_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_quant_nvfp4_weight(const void* values, int64_t N, int64_t K, int in_dtype, uint8_t* packed, uint8_t* scale_bits,
+                                     float* scale_2, unsigned int* scratch_u32, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(values && packed && scale_bits && scale_2 && scratch_u32, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_weight: null pointer");
+    EQ_REQUIRE(N > 0 && K > 0, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_weight: bad extents");
+    EQ_REQUIRE(K % 16 == 0, EQ_ERR_UNSUPPORTED, "eq_quant_nvfp4_weight: K must be a multiple of 16");
+    EQ_REQUIRE(aligned(packed, 8), EQ_ERR_BAD_ALIGN, "eq_quant_nvfp4_weight: packed must be 8-byte aligned");
+    int st = eq_nvfp4_global_scale(values, N, K, in_dtype, scale_2, scratch_u32, stream_);  // the same max(amax, 1e-12) / (6 * 448)
+    if (st != EQ_OK) return st;
+    const int64_t total = N * (K / 16);
+    const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
+    switch (in_dtype) {
+        case EQ_F16: quant_nvfp4_weight_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(values), N, K, scale_2, packed, scale_bits); break;
+        case EQ_BF16: quant_nvfp4_weight_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(values), N, K, scale_2, packed, scale_bits); break;
+        case EQ_F32: quant_nvfp4_weight_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(values), N, K, scale_2, packed, scale_bits); break;
+        default: return fail(EQ_ERR_BAD_ARG, "eq_quant_nvfp4_weight: unknown dtype %d", in_dtype);
+    }
+    EQ_LAUNCH_OK("quant_nvfp4_weight_kernel");
     return EQ_OK;
 }
 

@@ -90,6 +90,7 @@ def load() -> C.CDLL:
         "eq_fp8_status": (i, [p, i64, i64, p]),
         "eq_nvfp4_global_scale": (i, [p, i64, i64, i, p, p, p]),
         "eq_quant_nvfp4_act": (i, [p, i64, i64, i, p, p, p, p, p]),
+        "eq_quant_nvfp4_weight": (i, [p, i64, i64, i, p, p, p, p, p]),
         "eq_nvfp4_tiled_scale_bytes": (sz, [i64, i64]),
         "eq_nvfp4_tile_scales": (i, [p, i64, i64, p, p]),
         "eq_nvfp4_weight_scale_bytes": (sz, [i64, i64]),

@@ -18,6 +18,19 @@ def nvfp4_global_scale(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def quant_nvfp4_weight(values: torch.Tensor):
+    """values [N, K] (f32 / f16 / bf16) -> (packed uint8 [N, K/2], scale_bits uint8 [N, K/16], scale_2 f32 [1]): the
+    reference's weight quantizer, on the device."""
+    _need_cuda(values)
+    n, k = values.shape
+    packed = torch.empty((n, k // 2), dtype=torch.uint8, device=values.device)
+    sf = torch.empty((n, k // 16), dtype=torch.uint8, device=values.device)
+    s2 = torch.empty(1, dtype=torch.float32, device=values.device)
+    scratch = torch.empty(1, dtype=torch.int32, device=values.device)
+    L.check(L.load().eq_quant_nvfp4_weight(_ptr(values), n, k, _DTYPE[values.dtype], _ptr(packed), _ptr(sf), _ptr(s2), _ptr(scratch), _stream()))
+    return packed, sf, s2
+
+
 def quant_nvfp4_act(x: torch.Tensor, input_scale: torch.Tensor, tiled: bool = False):
     """x [M, K] -> (codes uint8 [M, K/2], scale_bits uint8 [M, K/16][, tiled scales])."""
     _need_cuda(x, input_scale)

@@ -176,6 +176,14 @@ int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream);
  * emmy/compiler/loader/quant.py:221-226).  scale2: device f32 [1]; scratch_u32: device uint32 [1]. */
 int eq_nvfp4_global_scale(const void* x, int64_t M, int64_t K, int in_dtype, float* scale2, unsigned int* scratch_u32,
                           void* stream);
+/* The NVFP4 weight quantizer, bit-exact with quantize_nvfp4 (emmy/compiler/loader/quant.py:206-237): scale_2 =
+ * max(amax, 1e-12) / (6 * 448) for the whole tensor, one e4m3 scale per 16 elements along K stored relative to it
+ * (block amax / 6 / scale_2), codes = e2m1 (round to nearest even code, saturating at 6) of value / f16(scale *
+ * scale_2), zero where that fused scale is zero.  values: [N, K] of in_dtype (EQ_F32, EQ_F16 or EQ_BF16); packed:
+ * [N, K/2] bytes (low nibble = even k); scale_bits: [N, K/16]; scale_2: device f32 [1]; scratch_u32: device uint32 [1].
+ * Needs K % 16 == 0.  (The reference's limit |values| <= 6 * 65504 for an f16 fused scale is the caller's to keep.) */
+int eq_quant_nvfp4_weight(const void* values, int64_t N, int64_t K, int in_dtype, uint8_t* packed, uint8_t* scale_bits,
+                          float* scale_2, unsigned int* scratch_u32, void* stream);
 /* Static-scale NVFP4 activation quantize, bit-exact with the algebra the reference spells
  * (_spell_static_fp4_quantize, emmy/compiler/loader/quant.py:1968-2139; pinned by _static_quantize_ref,
  * tests/compiler/loader/test_quant.py:1776-1784).  codes: [M, K/2] bytes (low nibble = even k); scale_bits: optional

@@ -138,3 +138,26 @@ def test_nvfp4_linear_known_answer():
 @pytest.mark.parametrize("m", [1, 128, 300])
 def test_nvfp4_linear_full_width(m):
     _check(m, 17408, 5120, seed=3)
+
+
+def test_weight_quantizer_bit_exact():
+    """eq_quant_nvfp4_weight against the oracle port of quantize_nvfp4 (itself pinned to the reference's output):
+    N(0, 0.02) weights, a zero block, a block far below the tensor's range and one value at the tensor's maximum."""
+    from emmy_b200 import ops_nvfp4 as o4
+    from oracle import formats as fm
+
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((96, 512)) * 0.02).astype(np.float32)
+    w[3, 32:48] = 0.0
+    w[5, 64:80] *= 1e-6
+    w[7, 100] = 0.25
+    packed, sbits, s2 = fm.quant_nvfp4(w)
+    got = o4.quant_nvfp4_weight(torch.from_numpy(w).cuda())
+    np.testing.assert_array_equal(got[2].cpu().numpy(), s2)
+    np.testing.assert_array_equal(got[1].cpu().numpy(), sbits)
+    np.testing.assert_array_equal(got[0].cpu().numpy(), packed)
+    # an all-zero tensor: scale_2 floors at 1e-12 / (6 * 448), every code and scale is zero
+    z = o4.quant_nvfp4_weight(torch.zeros(8, 64, device="cuda"))
+    pz, sz, s2z = fm.quant_nvfp4(np.zeros((8, 64), np.float32))
+    np.testing.assert_array_equal(z[2].cpu().numpy(), s2z)
+    assert int(z[0].count_nonzero()) == 0 and int(z[1].count_nonzero()) == 0 and not pz.any() and not sz.any()
