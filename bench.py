@@ -1,15 +1,23 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME [--rows ROWS]]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+                    [--workload NAME [--rows ROWS]]
 
-Default workload (`gptq_llama8b_mlp_m1`): the W4A16 M=1 GEMV on GPTQ act-order weights with the
-Llama-3.1-8B MLP shapes (gate/up K=4096 N=14336, down K=14336 N=4096, group 128) -- one step is one pass
-over a 32-layer stack of gate, up and down projections (96 GEMVs, 2.9 GB of packed weights, far larger
-than L2, so every step streams its weights from HBM).  Metric: algorithmic HBM bytes per second.
+Headline (`gptq_llama8b_mlp_m1`): the W4A16 M=1 GEMV on GPTQ act-order weights with the Llama-3.1-8B MLP shapes
+(gate/up K=4096 N=14336, down K=14336 N=4096, group 128) -- one step is one pass over a 32-layer stack of gate, up
+and down projections (96 GEMVs, 2.9 GB of packed weights, far larger than L2, so every step streams its weights from
+HBM).  Metric: algorithmic HBM bytes per second.
 
-Prints ONE JSON line on rank 0.  Launched by torchrun for N > 1 (one rank per GPU); every rank then owns its
-own 32-layer stack (weak scaling: independent layers, no data-path collective).
+The same JSON line carries `extra`: one record per other call of the path at the benchmark shapes (AWQ and GPTQ at
+their row counts, FP8 and NVFP4 linears, the MoE layer; with N > 1 also the sharded layers), each timed the same way:
+one CUDA graph per step over weight copies that exceed L2, ten samples of the replay region, median / min / max, the
+roofline floor that binds (the higher of bytes / HBM bandwidth and flops / tensor peak), and the end-to-end figure
+with pinned host buffers.  `--workload NAME` runs one of them alone under the headline's contract (these are the
+commands the profiles were made with).
+
+Prints ONE JSON line on rank 0.  Launched by torchrun for N > 1 (one rank per GPU); every rank then owns its own
+32-layer stack (weak scaling: independent layers, no data-path collective).
 """
 
 from __future__ import annotations
@@ -33,36 +41,35 @@ sys.path.insert(0, str(ROOT))
 LAYERS = 32
 SHAPES = {"gate": (4096, 14336), "up": (4096, 14336), "down": (14336, 4096)}
 GROUP = 128
+GEMM_K, GEMM_N = 5120, 17408
+SAMPLES = 10  # repeats of the timed region behind median / min / max
 
 
-def algorithmic_bytes(k: int, n: int, m: int = 1) -> int:
-    """Bytes one GEMV must move, exactly as the checkpoint stores them: packed weight, packed zeros,
-    fp16 scales, g_idx, x and y."""
-    return k * n // 2 + (k // GROUP) * n // 2 + (k // GROUP) * n * 2 + k * 4 + m * k * 2 + m * n * 2
+def algorithmic_bytes(k: int, n: int, m: int = 1, g_idx: bool = True) -> int:
+    """Bytes one W4A16 call must move, exactly as the checkpoint stores them: packed weight, packed zeros,
+    16-bit scales, g_idx, x and y."""
+    return k * n // 2 + (k // GROUP) * n // 2 + (k // GROUP) * n * 2 + (k * 4 if g_idx else 0) + m * k * 2 + m * n * 2
 
 
 STEP_BYTES = LAYERS * sum(algorithmic_bytes(k, n) for k, n in SHAPES.values())
 
+# dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of the captured launches of
+# this workload) from the ncu capture summarised in profiles/w4a16_gemv1_kernel_gptq_m1.md
+GEMV_KERNEL = "w4a16_gemv1_kernel<__half, true, DEPTH>"
+TRAFFIC_PER_LAUNCH = 31224000
+
 
 def peaks():
+    """(HBM GB/s, bf16 burst TFLOP/s, bf16 sustained TFLOP/s, kind)."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
-
-
-def tensor_peaks():
-    """(burst, sustained) dense bf16 TFLOP/s; FP8 runs at twice and NVFP4 at four times these."""
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        d = json.loads(p.read_text())
-        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
-    return 1590.0, 1400.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while timed regions run; summary(t0, t1) covers a window."""
 
     FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
@@ -83,7 +90,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -91,10 +98,12 @@ class ClockSampler:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
-    def summary(self):
+    def summary(self, t0: float = 0.0, t1: float = float("inf")):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for stamp, r in self.rows:
+            if not (t0 - 0.05 <= stamp <= t1 + 0.15):
+                continue
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -108,45 +117,149 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# --------------------------------------------------------------------------------------------- our arm
+def stats(xs):
+    return {"median": round(statistics.median(xs), 5), "min": round(min(xs), 5), "max": round(max(xs), 5), "samples": len(xs)}
 
 
-def build_stack(device, seed: int):
-    """32 layers of GPTQ act-order weights, generated on the device and repacked at load time."""
+class Timer:
+    """One workload's step captured in a CUDA graph (or run eagerly) and timed with CUDA events on its stream."""
+
+    def __init__(self, step, stream, device, world, capture=True, warmup=3):
+        self.stream, self.device, self.world = stream, device, world
+        with torch.cuda.stream(stream):
+            for _ in range(max(warmup, 3)):
+                step()
+            stream.synchronize()
+            self.run = step
+            if capture:
+                self.graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self.graph, stream=stream):
+                    step()
+                self.run = self.graph.replay
+            for _ in range(2):
+                self.run()
+            stream.synchronize()
+
+    def barrier(self):
+        torch.cuda.synchronize()
+        if self.world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def region(self, steps: int) -> float:
+        """ms for `steps` steps, barrier + synchronize on both sides, max over ranks."""
+        with torch.cuda.stream(self.stream):
+            self.barrier()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(self.stream)
+            for _ in range(steps):
+                self.run()
+            end.record(self.stream)
+            end.synchronize()
+            ms = start.elapsed_time(end)
+            self.barrier()
+        if self.world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def e2e(self, steps: int, h2d, d2h) -> float:
+        """ms per step with the step's inputs copied from pinned host memory and its result copied back, wall clock."""
+        with torch.cuda.stream(self.stream):
+            self.barrier()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                for dst, src in h2d:
+                    dst.copy_(src, non_blocking=True)
+                self.run()
+                for dst, src in d2h:
+                    dst.copy_(src, non_blocking=True)
+                self.stream.synchronize()
+            ms = (time.perf_counter() - t0) * 1e3 / steps
+            self.barrier()
+        if self.world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=self.device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+
+def roofline(alg_bytes, flops, peak_mult, seconds, kernel, traffic=None):
+    """The floor that binds: the higher of bytes / HBM bandwidth and flops / tensor peak (the reference's rule for mid
+    row counts, emmy/serving/roofline.py:137-148), against the measured time of one call."""
+    hbm, burst, sustained, kind = peaks()
+    t_hbm = (alg_bytes or 0) / (hbm * 1e9)
+    t_tc = (flops or 0) / (sustained * peak_mult * 1e12) if peak_mult else 0.0
+    if t_hbm >= t_tc:
+        out = {"bound": "hbm", "achieved": round(alg_bytes / seconds / 1e9, 1), "peak": hbm, "unit": "GB/s"}
+    else:
+        out = {"bound": "tensor", "achieved": round(flops / seconds / 1e12, 1), "peak": round(sustained * peak_mult, 1), "unit": "TFLOP/s",
+               "frac_of_burst": round(flops / seconds / 1e12 / (burst * peak_mult), 4)}
+    out.update({"frac": round(max(t_hbm, t_tc) / seconds, 4), "peak_kind": kind, "traffic": traffic, "kernel": kernel,
+                "floor_us": {"hbm": round(t_hbm * 1e6, 2), "tensor": round(t_tc * 1e6, 2)}})
+    return out
+
+
+# --------------------------------------------------------------------------------------------- synthetic weights
+
+
+def gptq_weight(device, gen, k, n):
     from emmy_b200 import ops
 
-    gen = torch.Generator(device=device).manual_seed(seed)
-    stack = []
-    for _ in range(LAYERS):
-        layer = {}
-        for name, (k, n) in SHAPES.items():
-            qweight = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, device=device, generator=gen)
-            qzeros = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32, device=device)  # stored 7 = zero 8
-            scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
-            perm = torch.randperm(k // GROUP, device=device, generator=gen)
-            g_idx = perm[torch.arange(k, device=device) // GROUP].int()
-            layer[name] = ops.w4_repack(qweight, qzeros, scales, GROUP, "gptq", g_idx=g_idx)
-        stack.append(layer)
-    torch.cuda.synchronize()
-    return stack
+    qweight = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, device=device, generator=gen)
+    qzeros = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32, device=device)  # stored 7 = zero 8
+    scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+    perm = torch.randperm(k // GROUP, device=device, generator=gen)
+    g_idx = perm[torch.arange(k, device=device) // GROUP].int()
+    return ops.w4_repack(qweight, qzeros, scales, GROUP, "gptq", g_idx=g_idx)
 
 
-def run_ours(args, rank, world, local_rank):
+def awq_weight(device, gen, k, n):
     from emmy_b200 import ops
-    from emmy_b200.build import build
 
-    if not (ROOT / "emmy_b200" / "libemmyq.so").exists():
-        build()
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    stack = build_stack(device, seed=1234 + rank)
-    gen = torch.Generator().manual_seed(7 + rank)
-    x_host = torch.randn(1, 4096, generator=gen).half().pin_memory()
-    h_host = torch.randn(1, 14336, generator=gen).half().pin_memory()
+    qweight = torch.randint(-(2**31), 2**31 - 1, (k, n // 8), dtype=torch.int32, device=device, generator=gen)
+    qzeros = torch.randint(-(2**31), 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=device, generator=gen)
+    scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+    return ops.w4_repack(qweight, qzeros, scales, GROUP, "awq")
+
+
+def fp8_weight(device, gen, n, k):
+    """W ~ N(0, 0.02) quantized per output channel (the dynamic rule applied to the weight's rows)."""
+    from emmy_b200 import ops
+
+    w = torch.randn(n, k, device=device, generator=gen) * 0.02
+    bits, scale = ops.quant_fp8_per_token(w)
+    return bits, scale.reshape(-1).contiguous()
+
+
+def nvfp4_weight(device, gen, n, k):
+    """W ~ N(0, 0.02) through the reference's weight quantizer (on the device), scales tiled for the tensor path."""
+    from emmy_b200 import ops_nvfp4 as o4
+
+    w = torch.randn(n, k, device=device, generator=gen) * 0.02
+    packed, sf, s2 = o4.quant_nvfp4_weight(w)
+    return packed, o4.nvfp4_tile_weight_scales(sf, k), s2
+
+
+# --------------------------------------------------------------------------------------------- workloads
+#
+# Each returns a dict: step (callable), calls per step, algorithmic bytes and flops PER CALL, the tensor peak multiple
+# of the operand type, host/device buffers of one step for the end-to-end leg, a status check, and labels.
+
+
+def wl_gemv_stack(device, rank):
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+    stack = [{name: gptq_weight(device, gen, k, n) for name, (k, n) in SHAPES.items()} for _ in range(LAYERS)]
+    hg = torch.Generator().manual_seed(7 + rank)
+    x_host = torch.randn(1, 4096, generator=hg).half().pin_memory()
+    h_host = torch.randn(1, 14336, generator=hg).half().pin_memory()
     x, h = x_host.to(device), h_host.to(device)
     ys = {name: torch.empty(1, n, dtype=torch.float16, device=device) for name, (_, n) in SHAPES.items()}
-    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
     out_host = {name: torch.empty(1, n, dtype=torch.float16).pin_memory() for name, (_, n) in SHAPES.items()}
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device=device)
 
     def step():
         for layer in stack:
@@ -154,76 +267,332 @@ def run_ours(args, rank, world, local_rank):
             ops.w4a16_linear(x, layer["up"], workspace=ws, out=ys["up"])
             ops.w4a16_linear(h, layer["down"], workspace=ws, out=ys["down"])
 
+    def hot_step():  # one layer's three weights over and over: 92 MB, resident in L2
+        for _ in range(LAYERS):
+            ops.w4a16_linear(x, stack[0]["gate"], workspace=ws, out=ys["gate"])
+            ops.w4a16_linear(x, stack[0]["up"], workspace=ws, out=ys["up"])
+            ops.w4a16_linear(h, stack[0]["down"], workspace=ws, out=ys["down"])
+
+    return dict(step=step, hot_step=hot_step, calls=3 * LAYERS, kernels_per_call=1, alg_bytes=STEP_BYTES / (3 * LAYERS), flops=0.0, peak_mult=0.0,
+                h2d=[(x, x_host), (h, h_host)], d2h=[(out_host[n_], ys[n_]) for n_ in ys], status=lambda: ops.w4a16_status(ws, 1, 4096),
+                kernel=GEMV_KERNEL, traffic=TRAFFIC_PER_LAUNCH)
+
+
+def wl_w4(device, rank, fmt, k, n, m):
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(300 + rank)
+    copies = max(3, int(2.2 * 126e6 // (k * n // 2)) + 1)
+    ws = [(gptq_weight if fmt == "gptq" else awq_weight)(device, gen, k, n) for _ in range(copies)]
+    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).half().pin_memory()
+    y_host = torch.empty(m, n, dtype=torch.float16).pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, n, dtype=torch.float16, device=device)
+    wsp = torch.zeros(ops.L.load().eq_w4a16_workspace_bytes(m, n, k) + 256, dtype=torch.uint8, device=device)
+
+    def step():
+        for w in ws:
+            ops.w4a16_linear(x, w, workspace=wsp, out=y)
+
+    kernel = GEMV_KERNEL if m == 1 else ("w4a16_stream_kernel" if m <= 16 else "w4a16_gemm_tc_kernel<__half>")
+    return dict(step=step, calls=copies, kernels_per_call=1, alg_bytes=algorithmic_bytes(k, n, m, fmt == "gptq"), flops=2.0 * m * k * n, peak_mult=1.0,
+                h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.w4a16_status(wsp, m, n), kernel=kernel,
+                dtype="int4 weights, f16 activations, f32 accumulate")
+
+
+def wl_fp8(device, rank, m, n=GEMM_N, k=GEMM_K):
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(100 + rank)
+    copies = max(2, int(2.2 * 126e6 // (n * k)) + 1)
+    ws = [fp8_weight(device, gen, n, k) for _ in range(copies)]
+    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
+    y_host = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    wsp = ops.fp8_workspace(m, k, device)
+
+    def step():
+        for w, s in ws:
+            ops.fp8_linear(x, w, s, workspace=wsp, out=y)
+
+    return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + n * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n, peak_mult=2.0,
+                h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.fp8_status(wsp, m, k),
+                kernel="fp8_gemm_tc_kernel<__nv_bfloat16>" if m > 16 else "fp8_decode_kernel",
+                dtype="e4m3 weights and activations, f32 accumulate, bf16 out")
+
+
+def wl_nvfp4(device, rank, m, n=GEMM_N, k=GEMM_K):
+    from emmy_b200 import ops_nvfp4 as o4
+
+    gen = torch.Generator(device=device).manual_seed(200 + rank)
+    copies = 3
+    ws = [nvfp4_weight(device, gen, n, k) for _ in range(copies)]
+    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
+    y_host = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(device)
+    s2 = o4.nvfp4_global_scale(x)  # input_scale calibrated on the sample (emmy/compiler/loader/synthesize.py:181-183)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    wsp = o4.nvfp4_workspace(m, k, device)
+
+    def step():
+        for w, sf, g in ws:
+            o4.nvfp4_linear(x, w, sf, g, s2, workspace=wsp, out=y)
+
+    return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k // 2 + n * k // 16 + 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n,
+                peak_mult=4.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: o4.nvfp4_status(wsp, m, k),
+                kernel="nvfp4_gemm_tc_kernel<__nv_bfloat16>", dtype="e2m1 weights and activations with e4m3 block scales, f32 accumulate, bf16 out")
+
+
+MOE = dict(e=128, topk=8, hidden=2048, inter=768)
+MOE_EXPERT_BYTES = 2_451_456  # one expert's packed gate_up + down, zeros and scales (AWQ group 128)
+
+
+def moe_experts_weights(device, seed, first, count):
+    """`count` experts starting at expert `first` of the 128 (seeded per expert, so that every rank draws the same)."""
+    from emmy_b200 import ops_moe as om
+
+    h, i = MOE["hidden"], MOE["inter"]
+
+    def stack(k, n, salt):
+        qw, qz, sc = [], [], []
+        for e in range(first, first + count):
+            gen = torch.Generator(device=device).manual_seed(seed + 7919 * e + salt)
+            qw.append(torch.randint(-(2**31), 2**31 - 1, (k, n // 8), dtype=torch.int32, device=device, generator=gen))
+            qz.append(torch.randint(-(2**31), 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=device, generator=gen))
+            sc.append((torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half())
+        return torch.stack(qw), torch.stack(qz), torch.stack(sc)
+
+    return om.moe_repack(stack(h, 2 * i, 0), stack(i, h, 1))
+
+
+def wl_moe(device, rank, world, t, exchange="peer"):
+    """Qwen3-30B-A3B expert shapes; with N > 1 ranks the experts are sharded E/N per rank and the tokens travel."""
+    from emmy_b200 import ops_moe as om
+    from emmy_b200 import shard
+
+    e, topk, hidden, inter = MOE["e"], MOE["topk"], MOE["hidden"], MOE["inter"]
+    local_e = e // world
+    w = moe_experts_weights(device, 400, rank * local_e, local_e)
+    hg = torch.Generator().manual_seed(rank)
+    x_host = torch.randn(t, hidden, generator=hg).bfloat16().pin_memory()
+    y_host = torch.empty(t, hidden, dtype=torch.bfloat16).pin_memory()
+    logits = torch.randn(t, e, generator=hg).to(device)
+    x = x_host.to(device)
+    y = torch.empty(t, hidden, dtype=torch.bfloat16, device=device)
+    if world == 1:
+        wsp = om.moe_workspace(t, w, topk, device)
+
+        def step():
+            om.moe_forward(x, logits, w, topk, workspace=wsp, out=y)
+
+        status = lambda: om.moe_status(wsp, t, w, topk)
+        capture = True
+    elif exchange == "nccl":
+        def step():
+            ids, scores = om.moe_route(logits, topk)
+            out = shard.ep_moe_forward(x, ids, scores, e, lambda rows, eid: om.moe_experts(rows, eid, w),
+                                       lambda rows, sc: om.moe_combine(rows, sc, topk))
+            y.copy_(out)
+
+        status = lambda: None
+        capture = False
+    else:
+        ep = shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device)
+
+        def step():
+            ids, scores = om.moe_route(logits, topk)
+            ep.forward(x, ids, scores, w, out=y)
+
+        status = ep.status
+        capture = True
+
+    def parity():
+        """Sampled rows of this rank's output against the single-GPU layer on all 128 experts."""
+        rows = torch.from_numpy(np.sort(np.random.default_rng(rank).choice(t, size=min(t, 48), replace=False))).to(device)
+        full = w if world == 1 else moe_experts_weights(device, 400, 0, e)
+        ref = om.moe_forward(x[rows].contiguous(), logits[rows].contiguous(), full, topk).float()
+        return float((y[rows].float() - ref).abs().max() / ref.abs().max())
+
+    if world == 1:
+        hit = int(torch.unique(om.moe_route(logits, topk)[0]).numel())  # distinct experts this batch touches
+    else:
+        hit = local_e  # every local expert is hit by the ranks' tokens at these sizes
+    return dict(step=step, calls=1, kernels_per_call=8, alg_bytes=hit * MOE_EXPERT_BYTES + t * (2 * hidden * 2 + e * 4),
+                flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), peak_mult=1.0,
+                h2d=[(x, x_host)], d2h=[(y_host, y)], status=status, capture=capture, parity=parity if world > 1 else None,
+                kernel="w4a16_gemm_tc_kernel (grouped)" if t * topk >= 2 * e else "moe grouped GEMV",
+                dtype="int4 expert weights, bf16 activations, f32 accumulate and combine")
+
+
+def wl_tp_mlp(device, rank, world, m):
+    """A Llama-3.1-8B MLP split over the ranks: gate and up column-parallel (no collective), down row-parallel with one
+    f32 all-reduce; GPTQ act-order weights, every rank draws the same full weights and keeps its shard."""
+    from emmy_b200 import ops, shard
+
+    h, inter = 4096, 14336
+    gen = torch.Generator().manual_seed(500)
+
+    def raw(k, n):
+        qw = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, generator=gen)
+        qz = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32)
+        sc = (torch.rand((k // GROUP, n), generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
+        perm = torch.randperm(k // GROUP, generator=gen)
+        return qw, qz, sc, perm[torch.arange(k) // GROUP].int()
+
+    full, local = {}, {}
+    for name, (k, n) in (("gate", (h, inter)), ("up", (h, inter)), ("down", (inter, h))):
+        t4 = raw(k, n)
+        full[name] = ops.w4_repack(*(a.to(device) for a in t4[:3]), GROUP, "gptq", g_idx=t4[3].to(device))
+        if name == "down":
+            a, b, c, g, rows = shard.row_slice_w4("gptq", *t4, GROUP, rank, world)
+        else:
+            a, b, c, g = shard.column_slice_w4("gptq", *t4, rank, world)
+        local[name] = ops.w4_repack(a.to(device), b.to(device), c.to(device), GROUP, "gptq", g_idx=g.to(device))
+    x_host = (torch.randn(m, h, generator=torch.Generator().manual_seed(9)) * 0.25).half().pin_memory()  # the same tokens on every rank
+    y_host = torch.empty(m, h, dtype=torch.float16).pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, h, dtype=torch.float16, device=device)
+    down = shard.RowParallelLinear(lambda v: ops.w4a16_linear(v, local["down"]), slice(0, inter // world))
+
+    def mlp(weights, xx):
+        return torch.nn.functional.silu(ops.w4a16_linear(xx, weights["gate"])) * ops.w4a16_linear(xx, weights["up"])
+
+    def step():
+        hidden = mlp(local, x)  # [M, inter / world]: this rank's columns
+        y.copy_(down(hidden) if world > 1 else ops.w4a16_linear(hidden, local["down"]))
+
+    def parity():
+        rows = torch.arange(0, m, max(1, m // 32), device=device)
+        ref = ops.w4a16_linear(mlp(full, x[rows].contiguous()), full["down"]).float()
+        return float((y[rows].float() - ref).abs().max() / ref.abs().max())
+
+    return dict(step=step, calls=1, kernels_per_call=5, alg_bytes=sum(algorithmic_bytes(k, n, m) for k, n in SHAPES.values()) // world,
+                flops=2.0 * m * 3 * h * inter / world, peak_mult=1.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, capture=False,
+                parity=parity, kernel="w4a16 linears + NCCL all-reduce", dtype="int4 weights, f16 activations, f32 accumulate and all-reduce")
+
+
+# --------------------------------------------------------------------------------------------- records
+
+
+def measure(wl, device, world, steps, clocks, name, metric, unit, workload):
+    """Times one workload and returns its `extra` record."""
     stream = torch.cuda.Stream(device)
+    timer = Timer(wl["step"], stream, device, world, capture=wl.get("capture", True))
     with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
-            step()
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step()
-        for _ in range(2):
-            graph.replay()
-        stream.synchronize()
+        wl["status"]()
+    t0 = time.time()
+    per_step = [timer.region(steps) / steps for _ in range(SAMPLES)]
+    t1 = time.time()
+    with torch.cuda.stream(stream):
+        wl["status"]()  # after the timed replays too
+        e2e_ms = timer.e2e(max(1, min(steps, 5)), wl["h2d"], wl["d2h"])
+        parity = wl["parity"]() if wl.get("parity") else None
+    med = statistics.median(per_step)
+    call_s = med * 1e-3 / wl["calls"]
+    units = wl["alg_bytes"] if unit == "GB/s" else wl["flops"]
+    scale = 1e9 if unit == "GB/s" else 1e12
+    rec = {
+        "name": name, "metric": metric, "unit": unit, "value": round(units * world / call_s / scale, 1), "n_gpus": world,
+        "ms_per_step": stats(per_step), "us_per_call": round(call_s * 1e6, 2), "calls_per_step": wl["calls"], "steps_per_sample": steps,
+        "config": {"workload": workload, "l2": "weights rotate over copies that exceed L2", "launch": "one CUDA graph per step" if wl.get("capture", True) else "eager calls"},
+        "dtype": wl["dtype"], "roofline": roofline(wl["alg_bytes"], wl["flops"], wl["peak_mult"], call_s, wl["kernel"]),
+        "e2e": {"value": round(units * world / (e2e_ms * 1e-3 / wl["calls"]) / scale, 2), "unit": unit,
+                "h2d_bytes_per_step": int(sum(s.numel() * s.element_size() for _, s in wl["h2d"])),
+                "d2h_bytes_per_step": int(sum(d.numel() * d.element_size() for d, _ in wl["d2h"]))},
+        "clocks": clocks.summary(t0, t1),
+    }
+    if parity is not None:
+        rec["parity_max_rel_err"] = round(parity, 6)
+    return rec
 
-        def barrier():
-            torch.cuda.synchronize()
-            if world > 1:
-                torch.distributed.barrier()
-            torch.cuda.synchronize()
 
-        # ---- device-timed region: weights resident, K steps
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            start.record(stream)
-            for _ in range(args.steps):
-                graph.replay()
-            end.record(stream)
-            end.synchronize()
-            dev_ms = start.elapsed_time(end)
-            # keep the sampler fed for short runs
-            if dev_ms < 400:
-                t_end = time.time() + 0.4
-                while time.time() < t_end:
-                    graph.replay()
-                stream.synchronize()
-        barrier()
+def extra_records(device, rank, world, clocks, quick_steps=3):
+    """The other calls of the path at the benchmark shapes.  N = 1: every rank-local call.  N > 1: the sharded layers."""
+    recs = []
 
-        # ---- end to end through the operator API with host buffers
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            x.copy_(x_host, non_blocking=True)
-            h.copy_(h_host, non_blocking=True)
-            graph.replay()
-            for name in ys:
-                out_host[name].copy_(ys[name], non_blocking=True)
+    def add(builder, *a, **kw):
+        try:
+            wl = builder()
+            recs.append(measure(wl, device, world, *a, **kw))
+            del wl
+        except Exception as exc:  # one record must not take the headline down
+            recs.append({"name": kw.get("name") or a[1], "error": f"{type(exc).__name__}: {exc}"[:300]})
+        torch.cuda.empty_cache()
+
+    if world == 1:
+        for m in (1, 16):
+            add(lambda: wl_w4(device, rank, "awq", 4096, 4096, m), quick_steps, clocks, f"awq_4096_m{m}", "w4a16_gemv_hbm_gbs", "GB/s",
+                f"AWQ W4A16, K=N=4096, group 128, M={m}")
+        for proj, (k, n) in (("gate_up", SHAPES["gate"]), ("down", SHAPES["down"])):
+            for m in (4, 16, 64, 256):
+                unit = "GB/s" if m <= 16 else "TFLOP/s"
+                add(lambda: wl_w4(device, rank, "gptq", k, n, m), quick_steps, clocks, f"gptq_{proj}_m{m}",
+                    "w4a16_gemv_hbm_gbs" if m <= 16 else "w4a16_gemm_tflops", unit, f"GPTQ act-order W4A16, Llama-3.1-8B {proj} K={k} N={n}, M={m}")
+        for m in (1, 32, 512, 8192):
+            unit = "GB/s" if m <= 32 else "TFLOP/s"
+            add(lambda: wl_fp8(device, rank, m), quick_steps, clocks, f"fp8_m{m}", "fp8_w8a8_hbm_gbs" if m <= 32 else "fp8_w8a8_gemm_tflops", unit,
+                f"FP8-E4M3 W8A8, per-channel weight scale, dynamic per-token activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}")
+        for m in (1, 128, 4096):
+            unit = "GB/s" if m == 1 else "TFLOP/s"
+            add(lambda: wl_nvfp4(device, rank, m), quick_steps, clocks, f"nvfp4_m{m}", "nvfp4_hbm_gbs" if m == 1 else "nvfp4_gemm_tflops", unit,
+                f"NVFP4 W4A4, weights N(0,0.02) through the two-level weight quantizer, static activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}")
+        for t in (1, 64, 4096):
+            unit = "GB/s" if t <= 64 else "TFLOP/s"
+            add(lambda: wl_moe(device, rank, 1, t), quick_steps, clocks, f"moe_t{t}", "moe_hbm_gbs" if t <= 64 else "moe_w4a16_tflops", unit,
+                f"routed W4A16 MoE layer, Qwen3-30B-A3B shapes (128 experts, top-8, hidden 2048, intermediate 768, AWQ group 128), T={t}")
+    else:
+        add(lambda: wl_moe(device, rank, world, 4096, "peer"), quick_steps, clocks, "moe_ep_t4096", "moe_w4a16_tflops", "TFLOP/s",
+            f"expert-parallel MoE, {128 // world} experts per rank, T=4096 tokens per rank, rows stored into the owner's receive buffer and results "
+            "stored back from the second GEMM's epilogue over NVLink peer memory")
+        for m in (16, 2048):
+            add(lambda: wl_tp_mlp(device, rank, world, m), quick_steps, clocks, f"tp_mlp_m{m}", "w4a16_mlp_tflops", "TFLOP/s",
+                f"tensor-parallel Llama-3.1-8B MLP over {world} ranks: gate/up column-parallel, down row-parallel + f32 all-reduce (NCCL), M={m}")
+    return recs
+
+
+# --------------------------------------------------------------------------------------------- our arm
+
+
+def run_ours(args, rank, world, local_rank):
+    from emmy_b200.build import build
+
+    if not (ROOT / "emmy_b200" / "libemmyq.so").exists():
+        build()
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    warmup = max(args.warmup, 3)
+    with ClockSampler(local_rank) as clocks:
+        wl = wl_gemv_stack(device, rank)
+        stream = torch.cuda.Stream(device)
+        timer = Timer(wl["step"], stream, device, world, warmup=warmup)
+        # ---- the timed region of the contract: K steps, weights resident, device time, max over ranks
+        t0 = time.time()
+        dev_ms = timer.region(args.steps)
+        t1 = time.time()
+        if dev_ms < 400:  # keep the clock sampler fed on short runs
+            end = time.time() + 0.4
+            while time.time() < end:
+                timer.run()
             stream.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3
-        barrier()
-        # the same with one operator call per projection instead of the captured graph (reported, not the headline)
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            x.copy_(x_host, non_blocking=True)
-            h.copy_(h_host, non_blocking=True)
-            step()
-            for name in ys:
-                out_host[name].copy_(ys[name], non_blocking=True)
-            stream.synchronize()
-        eager_ms = (time.perf_counter() - t0) * 1e3
-        barrier()
-
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    dev_ms, e2e_ms = times.tolist()
+            t1 = time.time()
+        samples = [timer.region(args.steps) / args.steps for _ in range(SAMPLES)]
+        e2e_ms = timer.e2e(args.steps, wl["h2d"], wl["d2h"]) * args.steps
+        eager = Timer(wl["step"], stream, device, world, capture=False)
+        eager_ms = eager.e2e(max(1, min(args.steps, 5)), wl["h2d"], wl["d2h"])
+        hot = Timer(wl["hot_step"], stream, device, world)
+        hot_ms = statistics.median(hot.region(args.steps) / args.steps for _ in range(3))
+        with torch.cuda.stream(stream):
+            wl["status"]()
+        headline_clocks = clocks.summary(t0, t1)
+        del timer, eager, hot, wl
+        torch.cuda.empty_cache()
+        extras = [] if args.no_extra else extra_records(device, rank, world, clocks)
     if rank != 0:
         return
-    peak, peak_kind = peaks()
+    hbm, _, _, peak_kind = peaks()
     total_bytes = STEP_BYTES * world
     value = total_bytes * args.steps / (dev_ms * 1e-3) / 1e9
-    e2e_value = total_bytes * args.steps / (e2e_ms * 1e-3) / 1e9
     launches = 3 * LAYERS
     per_launch_us = dev_ms * 1e3 / (args.steps * launches)
     achieved = (STEP_BYTES / launches) / (per_launch_us * 1e-6) / 1e9
@@ -233,7 +602,7 @@ def run_ours(args, rank, world, local_rank):
         "unit": "GB/s",
         "n_gpus": world,
         "steps": args.steps,
-        "warmup": max(args.warmup, 3),
+        "warmup": warmup,
         "ms_per_step": round(dev_ms / args.steps, 4),
         "higher_is_better": True,
         "scaling": "weak",
@@ -247,191 +616,39 @@ def run_ours(args, rank, world, local_rank):
             "launch": "one CUDA graph of 96 GEMV launches per step",
         },
         "e2e": {
-            "value": round(e2e_value, 1),
+            "value": round(total_bytes * args.steps / (e2e_ms * 1e-3) / 1e9, 1),
             "unit": "GB/s",
-            "h2d_bytes_per_step": int(x_host.numel() * 2 + h_host.numel() * 2),
-            "d2h_bytes_per_step": int(sum(t.numel() * 2 for t in out_host.values())),
-            "eager_calls_value": round(STEP_BYTES * args.steps / (eager_ms * 1e-3) / 1e9, 1),
+            "h2d_bytes_per_step": 2 * (4096 + 14336),
+            "d2h_bytes_per_step": 2 * (14336 + 14336 + 4096),
+            "eager_calls_value": round(total_bytes / (eager_ms * 1e-3) / 1e9, 1),
         },
         "gpu_launches": launches * args.steps,
         "roofline": {
             "bound": "hbm",
             "achieved": round(achieved, 1),
-            "peak": peak,
+            "peak": hbm,
             "unit": "GB/s",
-            "frac": round(achieved / peak, 4),
+            "frac": round(achieved / hbm, 4),
             "peak_kind": peak_kind,
             "traffic": TRAFFIC_PER_LAUNCH,
-            "kernel": "w4a16_stream_kernel<__half,1,true>",
+            "kernel": GEMV_KERNEL,
             "avg_launch_us": round(per_launch_us, 3),
         },
-        "clocks": clocks.summary(),
+        "samples": {"ms_per_step": stats(samples), "gbs_median": round(total_bytes / (statistics.median(samples) * 1e-3) / 1e9, 1),
+                    "hot_l2_gbs": round(total_bytes / (hot_ms * 1e-3) / 1e9, 1),
+                    "note": f"{SAMPLES} repeats of the {args.steps}-step region after the contract's region; hot_l2: one layer's weights (92 MB) replayed, resident in L2"},
+        "clocks": headline_clocks,
         "cpu_baseline": cpu_baseline(sample_layers=1),
+        "extra": extras,
     }
     print(json.dumps(line), flush=True)
 
 
-# dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of three launches of this
-# workload) from the ncu capture summarised in profiles/w4a16_stream_kernel_gptq_m1.md
-TRAFFIC_PER_LAUNCH = 31224000
-
-
-# --------------------------------------------------------------------------------------------- other workloads
-#
-# The same contract for the other calls of the path; `--workload NAME [--rows ROWS]`.  One step = `copies` calls on distinct
-# weight copies (so that weights come from HBM, not L2), captured in one CUDA graph where the call has no host read.
-
-GEMM_K, GEMM_N = 5120, 17408
-
-
-def _wl_fp8(device, rank, m):
-    from emmy_b200 import ops
-
-    gen = torch.Generator(device=device).manual_seed(100 + rank)
-    copies = 2
-    ws = []
-    for _ in range(copies):
-        w = (torch.randn(GEMM_N, GEMM_K, device=device, generator=gen) * 0.02)
-        s = w.abs().amax(dim=1).clamp_min(1e-12) / 448.0
-        ws.append(((w / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s.float().contiguous()))
-    x_host = torch.randn(m, GEMM_K, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
-    x = x_host.to(device)
-    y = torch.empty(m, GEMM_N, dtype=torch.bfloat16, device=device)
-    wsp = ops.fp8_workspace(m, GEMM_K, device)
-
-    def step():
-        for w, s in ws:
-            ops.fp8_linear(x, w, s, workspace=wsp, out=y)
-
-    return dict(
-        step=step, flops=2.0 * m * GEMM_K * GEMM_N * copies, calls=copies, kernels_per_call=2, x=x, x_host=x_host, y=y, graph=True,
-        metric="fp8_w8a8_gemm_tflops", dtype="e4m3 weights and activations, f32 accumulate, bf16 out", peak_mult=2.0,
-        kernel="fp8_gemm_tc_kernel<__nv_bfloat16>" if m > 64 else "fp8_smallm_kernel",
-        status=lambda: ops.fp8_status(wsp, m, GEMM_K),
-        workload=f"fp8_gemm: FP8-E4M3 W8A8, per-channel weight scale, dynamic per-token activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}, bf16 out",
-        alg_bytes=GEMM_N * GEMM_K + GEMM_N * 4 + m * GEMM_K * 2 + m * GEMM_N * 2,
-    )
-
-
-def _wl_nvfp4(device, rank, m):
-    from emmy_b200 import ops_nvfp4 as o4
-
-    gen = torch.Generator(device=device).manual_seed(200 + rank)
-    copies = 3
-    ws = []
-    for _ in range(copies):
-        w = torch.randint(0, 256, (GEMM_N, GEMM_K // 2), dtype=torch.uint8, device=device, generator=gen)
-        sf = torch.randint(0x28, 0x40, (GEMM_N, GEMM_K // 16), dtype=torch.uint8, device=device, generator=gen)
-        ws.append((w, o4.nvfp4_tile_weight_scales(sf, GEMM_K), torch.tensor([2.0e-5], device=device)))
-    x_host = torch.randn(m, GEMM_K, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
-    x = x_host.to(device)
-    s2 = o4.nvfp4_global_scale(x)
-    y = torch.empty(m, GEMM_N, dtype=torch.bfloat16, device=device)
-    wsp = o4.nvfp4_workspace(m, GEMM_K, device)
-
-    def step():
-        for w, sf, g in ws:
-            o4.nvfp4_linear(x, w, sf, g, s2, workspace=wsp, out=y)
-
-    return dict(
-        step=step, flops=2.0 * m * GEMM_K * GEMM_N * copies, calls=copies, kernels_per_call=2, x=x, x_host=x_host, y=y, graph=True,
-        metric="nvfp4_gemm_tflops", dtype="e2m1 weights and activations with e4m3 block scales, f32 accumulate, bf16 out", peak_mult=4.0,
-        kernel="nvfp4_gemm_tc_kernel<__nv_bfloat16>", status=lambda: o4.nvfp4_status(wsp, m, GEMM_K),
-        workload=f"nvfp4_gemm: NVFP4 block-scaled W4A4 (codes uniform, block scales uniform 0x28..0x3F: synthetic codes stand in for quantized N(0,0.02) weights), static activation scale (quantize timed), K={GEMM_K} N={GEMM_N} M={m}, bf16 out",
-        alg_bytes=GEMM_N * GEMM_K // 2 + GEMM_N * GEMM_K // 16 + 4 + m * GEMM_K * 2 + m * GEMM_N * 2,
-    )
-
-
-def _wl_w4_prefill(device, rank, m):
-    from emmy_b200 import ops
-
-    gen = torch.Generator(device=device).manual_seed(300 + rank)
-    k, n = SHAPES["gate"]
-    copies = 4
-    ws = []
-    for _ in range(copies):
-        qweight = torch.randint(-(2**31), 2**31 - 1, (k // 8, n), dtype=torch.int32, device=device, generator=gen)
-        qzeros = torch.full((k // GROUP, n // 8), 0x77777777, dtype=torch.int32, device=device)
-        scales = (torch.rand((k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
-        perm = torch.randperm(k // GROUP, device=device, generator=gen)
-        g_idx = perm[torch.arange(k, device=device) // GROUP].int()
-        ws.append(ops.w4_repack(qweight, qzeros, scales, GROUP, "gptq", g_idx=g_idx))
-    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).half().pin_memory()
-    x = x_host.to(device)
-    y = torch.empty(m, n, dtype=torch.float16, device=device)
-    wsp = torch.zeros(ops.L.load().eq_w4a16_workspace_bytes(m, n, k) + 256, dtype=torch.uint8, device=device)
-
-    def step():
-        for w in ws:
-            ops.w4a16_linear(x, w, workspace=wsp, out=y)
-
-    return dict(
-        step=step, flops=2.0 * m * k * n * copies, calls=copies, kernels_per_call=1, x=x, x_host=x_host, y=y, graph=True,
-        metric="w4a16_gemm_tflops", dtype="int4 weights dequantised to f16 in shared memory, f16 activations, f32 accumulate", peak_mult=1.0,
-        kernel="w4a16_gemm_tc_kernel<__half>", status=lambda: ops.w4a16_status(wsp, m, n),
-        workload=f"w4a16_prefill: GPTQ-Int4 act-order W4A16, Llama-3.1-8B gate/up shape K={k} N={n} group 128, M={m}",
-        alg_bytes=algorithmic_bytes(k, n, m),
-    )
-
-
-def _wl_moe(device, rank, world, t, exchange="peer"):
-    """Qwen3-30B-A3B expert shapes; with N > 1 ranks the experts are sharded E/N per rank and tokens travel by all-to-all."""
-    from emmy_b200 import ops_moe as om
-    from emmy_b200 import shard
-
-    e, topk, hidden, inter = 128, 8, 2048, 768
-    local_e = e // world
-    gen = torch.Generator(device=device).manual_seed(400 + rank)
-
-    def stack(k, n):
-        qw = torch.randint(-(2**31), 2**31 - 1, (local_e, k, n // 8), dtype=torch.int32, device=device, generator=gen)
-        qz = torch.randint(-(2**31), 2**31 - 1, (local_e, k // GROUP, n // 8), dtype=torch.int32, device=device, generator=gen)
-        sc = (torch.rand((local_e, k // GROUP, n), device=device, generator=gen) * (2e-2 - 1e-3) + 1e-3).half()
-        return qw, qz, sc
-
-    w = om.moe_repack(stack(hidden, 2 * inter), stack(inter, hidden))
-    hg = torch.Generator().manual_seed(rank)
-    x_host = torch.randn(t, hidden, generator=hg).bfloat16().pin_memory()
-    logits = torch.randn(t, e, generator=hg).to(device)
-    x = x_host.to(device)
-    y = torch.empty(t, hidden, dtype=torch.bfloat16, device=device)
-    if world == 1:
-        wsp = om.moe_workspace(t, w, topk, device)
-
-        def step():
-            om.moe_forward(x, logits, w, topk, workspace=wsp, out=y)
-
-        status = lambda: om.moe_status(wsp, t, w, topk)
-    elif exchange == "nccl":
-        def step():
-            ids, scores = om.moe_route(logits, topk)
-            out = shard.ep_moe_forward(x, ids, scores, e, lambda rows, eid: om.moe_experts(rows, eid, w),
-                                       lambda rows, sc: om.moe_combine(rows, sc, topk))
-            y.copy_(out)
-
-        status = lambda: None
-    else:
-        ep = shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device)
-
-        def step():
-            ids, scores = om.moe_route(logits, topk)
-            ep.forward(x, ids, scores, w, out=y)
-
-        status = ep.status
-    return dict(
-        step=step, flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), calls=1, kernels_per_call=8, x=x, x_host=x_host,
-        y=y, graph=world == 1 or exchange == "peer", metric="moe_w4a16_tflops", dtype="int4 expert weights, bf16 activations, f32 accumulate and combine",
-        peak_mult=1.0, kernel="moe_expert_gemm_kernel", status=status,
-        workload=f"moe: routed W4A16 expert layer, Qwen3-30B-A3B shapes (128 experts, top-8, hidden 2048, intermediate 768, AWQ group 128), T={t} tokens per rank"
-        + (f", experts sharded {local_e} per rank, " + ("all-to-all dispatch and return over NCCL" if exchange == "nccl" else
-            "rows stored into the owner's receive buffer and results stored back from the second GEMM's epilogue over NVLink peer memory")
-           if world > 1 else ""),
-        alg_bytes=None,
-    )
+# --------------------------------------------------------------------------------------------- one workload alone
 
 
 def cpu_sample(name, m):
-    """The oracle port on a bounded sample of the workload's rows; (units, seconds, description)."""
+    """The oracle port on a bounded sample of a secondary workload's rows; (units, seconds, description)."""
     from oracle import linear as ol
     from oracle import moe as omoe
     from oracle import synth
@@ -481,95 +698,49 @@ def run_other(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     name = args.workload
-    default_m = {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
-    m = args.rows or default_m
-    wl = _wl_moe(device, rank, world, m, args.exchange) if name == "moe" else {"fp8_gemm": _wl_fp8, "nvfp4_gemm": _wl_nvfp4, "w4a16_prefill": _wl_w4_prefill}[name](device, rank, m)
-    step = wl["step"]
+    m = args.rows or {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
+    if name == "moe":
+        wl, metric = wl_moe(device, rank, world, m, args.exchange), "moe_w4a16_tflops"
+    elif name == "fp8_gemm":
+        wl, metric = wl_fp8(device, rank, m), "fp8_w8a8_gemm_tflops"
+    elif name == "nvfp4_gemm":
+        wl, metric = wl_nvfp4(device, rank, m), "nvfp4_gemm_tflops"
+    else:
+        wl, metric = wl_w4(device, rank, "gptq", *SHAPES["gate"], m), "w4a16_gemm_tflops"
     stream = torch.cuda.Stream(device)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
+    warmup = max(args.warmup, 3)
+    timer = Timer(wl["step"], stream, device, world, capture=wl.get("capture", True), warmup=warmup)
     with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
-            step()
-        stream.synchronize()
         wl["status"]()
-        run = step
-        if wl["graph"]:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-            graph.replay()
+    with ClockSampler(local_rank) as clocks:
+        dev_ms = timer.region(args.steps)
+        if dev_ms < 400:
+            for _ in range(min(5000, int(400.0 / max(dev_ms / args.steps, 1e-3)) + 1)):
+                timer.run()
             stream.synchronize()
-            run = graph.replay
-        barrier()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            start.record(stream)
-            for _ in range(args.steps):
-                run()
-            end.record(stream)
-            end.synchronize()
-            dev_ms = start.elapsed_time(end)
-            # keep the clock sampler fed on short runs: the same number of extra steps on every rank (the steps may be collective)
-            feed = torch.tensor([dev_ms / args.steps], dtype=torch.float64, device=device)
-            if world > 1:
-                torch.distributed.all_reduce(feed, op=torch.distributed.ReduceOp.MAX)
-            if dev_ms < 400:
-                for _ in range(min(5000, int(400.0 / max(feed.item(), 1e-3)) + 1)):
-                    run()
-                stream.synchronize()
-        barrier()
-        # end to end: the step's activations come from pinned host memory, its result goes back
-        y_host = torch.empty(wl["y"].shape, dtype=wl["y"].dtype).pin_memory()
-        e2e_steps = max(1, min(args.steps, 5))
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            wl["x"].copy_(wl["x_host"], non_blocking=True)
-            run()
-            y_host.copy_(wl["y"], non_blocking=True)
-            stream.synchronize()
-        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        barrier()
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    dev_ms, e2e_ms = times.tolist()
+    with torch.cuda.stream(stream):
+        wl["status"]()
+    e2e_ms = timer.e2e(max(1, min(args.steps, 5)), wl["h2d"], wl["d2h"])
     if rank != 0:
         return
-    burst, sustained, kind = tensor_peaks()
     step_ms = dev_ms / args.steps
-    value = wl["flops"] * world / (step_ms * 1e-3) / 1e12
-    per_call_us = step_ms * 1e3 / wl["calls"]
-    achieved = wl["flops"] / wl["calls"] / (per_call_us * 1e-6) / 1e12
-    peak = sustained * wl["peak_mult"]
+    call_s = step_ms * 1e-3 / wl["calls"]
     units, secs, what = cpu_sample(name, m)
     line = {
-        "metric": wl["metric"], "value": round(value, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
+        "metric": metric, "value": round(wl["flops"] * wl["calls"] * world / (step_ms * 1e-3) / 1e12, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["workload"], "flops_per_step": wl["flops"], "calls_per_step": wl["calls"],
-                   "l2": "weights rotate over distinct copies and activations plus outputs exceed L2",
-                   "launch": "one CUDA graph per step" if wl["graph"] else "eager calls"},
-        "e2e": {"value": round(wl["flops"] * world / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                "h2d_bytes_per_step": int(wl["x_host"].numel() * wl["x_host"].element_size()),
-                "d2h_bytes_per_step": int(y_host.numel() * y_host.element_size())},
+        "config": {"workload": f"{name} rows={m}", "flops_per_call": wl["flops"], "calls_per_step": wl["calls"],
+                   "algorithmic_bytes_per_call": wl["alg_bytes"], "l2": "weights rotate over distinct copies that exceed L2",
+                   "launch": "one CUDA graph per step" if wl.get("capture", True) else "eager calls"},
+        "e2e": {"value": round(wl["flops"] * wl["calls"] * world / (e2e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(sum(s.numel() * s.element_size() for _, s in wl["h2d"])),
+                "d2h_bytes_per_step": int(sum(d.numel() * d.element_size() for d, _ in wl["d2h"]))},
         "gpu_launches": wl["calls"] * wl["kernels_per_call"] * args.steps,
-        "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
-                     "frac": round(achieved / peak, 4), "peak_kind": f"{kind}: {wl['peak_mult']:g} x sustained bf16 {sustained} (burst {burst})",
-                     "frac_of_burst": round(achieved / (burst * wl["peak_mult"]), 4), "traffic": None, "kernel": wl["kernel"],
-                     "avg_call_us": round(per_call_us, 2), "includes": "activation quantize and the GEMM of each call"},
+        "roofline": roofline(wl["alg_bytes"], wl["flops"], wl["peak_mult"], call_s, wl["kernel"]),
         "clocks": clocks.summary(),
         "cpu_baseline": {"value": round(units / secs / 1e12, 6), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": f"{what}, {secs:.1f} s"},
     }
-    if wl["alg_bytes"]:
-        line["config"]["algorithmic_bytes_per_call"] = wl["alg_bytes"]
-        line["roofline"]["hbm_gbs"] = round(wl["alg_bytes"] / (per_call_us * 1e-6) / 1e9, 1)
     print(json.dumps(line), flush=True)
 
 
@@ -580,22 +751,30 @@ def cpu_threads() -> int:
     return max(1, min(os.cpu_count() or 1, 64))
 
 
-def cpu_layer_seconds(seed: int = 0):
-    """The reference's CPU path for one layer's three projections at M=1: numpy dequantize (with the g_idx
-    gather; column chunks on all host threads), one rounding to fp16, torch CPU linear.  Returns (seconds,
-    algorithmic bytes)."""
+def cpu_layer_inputs(seed: int = 0):
+    """One layer's three GPTQ projections and their activations (synthetic; generated outside any timed region)."""
+    from oracle import synth
+
+    out = []
+    for k, n in SHAPES.values():
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=seed)
+        x = torch.from_numpy(synth.activations(1, k, "f16", seed=seed + 1)).half()
+        out.append((k, n, qw, qz, sc, gi, x))
+    return out
+
+
+def cpu_layer_seconds(inputs):
+    """The reference's CPU path for one layer's three projections at M=1: numpy dequantize (with the g_idx gather;
+    column chunks on all host threads), one rounding to fp16, torch CPU linear.  Returns (seconds, algorithmic bytes)."""
     from concurrent.futures import ThreadPoolExecutor
 
     from oracle import formats as fm
-    from oracle import synth
 
     threads = cpu_threads()
     torch.set_num_threads(threads)
     total_s, total_b = 0.0, 0
     with ThreadPoolExecutor(max_workers=threads) as pool:
-        for k, n in SHAPES.values():
-            qw, qz, sc, gi = synth.gptq_linear(k, n, seed=seed)
-            x = torch.from_numpy(synth.activations(1, k, "f16", seed=seed + 1)).half()
+        for k, n, qw, qz, sc, gi, x in inputs:
             step = max(8, (n // threads + 7) // 8 * 8)
             chunks = [(c, min(c + step, n)) for c in range(0, n, step)]
             t0 = time.perf_counter()
@@ -611,7 +790,7 @@ def cpu_layer_seconds(seed: int = 0):
 def cpu_baseline(sample_layers: int = 1):
     secs, nbytes = 0.0, 0
     for i in range(sample_layers):
-        s, b = cpu_layer_seconds(seed=i)
+        s, b = cpu_layer_seconds(cpu_layer_inputs(seed=i))
         secs += s
         nbytes += b
     return {
@@ -624,16 +803,19 @@ def cpu_baseline(sample_layers: int = 1):
 
 
 def run_reference(args, rank):
+    """The reference's CPU implementation of the path (the oracle port: the reference itself is Python plus a Rust runtime
+    that does not build here), one layer of the stack per step, inputs generated outside the timed region."""
     if rank != 0:
         return
-    for _ in range(min(args.warmup, 1)):
-        cpu_layer_seconds(seed=99)
-    t0 = time.perf_counter()
-    nbytes = 0
+    warmup = max(args.warmup, 0)
+    inputs = [cpu_layer_inputs(seed=i) for i in range(min(args.steps, 4))]  # steps cycle over a few distinct layers
+    for i in range(warmup):
+        cpu_layer_seconds(inputs[i % len(inputs)])
+    secs, nbytes = 0.0, 0
     for i in range(args.steps):
-        _, b = cpu_layer_seconds(seed=i)
+        s, b = cpu_layer_seconds(inputs[i % len(inputs)])
+        secs += s
         nbytes += b
-    secs = time.perf_counter() - t0
     value = nbytes / secs / 1e9
     line = {
         "impl": "reference",
@@ -642,7 +824,7 @@ def run_reference(args, rank):
         "unit": "GB/s",
         "n_gpus": args.gpus,
         "steps": args.steps,
-        "warmup": min(args.warmup, 1),
+        "warmup": warmup,
         "ms_per_step": round(secs * 1e3 / args.steps, 2),
         "higher_is_better": True,
         "scaling": "weak",
@@ -650,7 +832,8 @@ def run_reference(args, rank):
         "dtype": "int4 weights, f16 activations, f32 accumulate",
         "data": "synthetic",
         "config": {
-            "workload": "gptq_llama8b_mlp_m1: GPTQ-Int4 act-order W4A16 GEMV, Llama-3.1-8B MLP shapes, M=1; each step is ONE layer (gate, up, down) of the 32-layer stack on the host cores",
+            "workload": "gptq_llama8b_mlp_m1: GPTQ-Int4 act-order W4A16 GEMV, Llama-3.1-8B MLP shapes (gate/up 4096x14336, down 14336x4096, group 128), M=1, 32-layer stack per GPU",
+            "sample": "each step is ONE layer (gate, up, down) of the 32-layer stack on the host cores; inputs are generated before the timed region",
         },
         "cpu_baseline": {
             "value": round(value, 4),
@@ -674,6 +857,7 @@ def main():
                     choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "nvfp4_gemm", "moe"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="moe workload at N > 1: who moves the tokens")
     ap.add_argument("--rows", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
+    ap.add_argument("--no-extra", action="store_true", help="headline only: skip the extra records")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -684,6 +868,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operators have no CPU path")
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
         if args.workload == "gptq_llama8b_mlp_m1":

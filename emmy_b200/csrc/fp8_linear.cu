@@ -3,10 +3,16 @@
 //   quant_fp8_rows_kernel   x[M,K] f16/bf16/f32 -> e4m3 bits + one f32 scale per row.  s = max(amax, 1e-12) / 448
 //                           and q = e4m3_rne_satfinite(x / s), both with round-to-nearest f32 division: bit-exact
 //                           against the numpy rule the reference spells (emmy/compiler/loader/quant.py:1655-1735).
-//   fp8_smallm_kernel       M <= 64 (decode-shaped): a bandwidth kernel.  Weights [N,K] are read as stored, 16 bytes
+//   quant_fp8_rows_vec_kernel  the same for few rows (decode): one 1024-thread CTA per row, the row held in registers
+//                           between the maximum and the encode, 16-byte loads; also clears the status word.
+//   fp8_decode_kernel       M <= 16 (decode-shaped): a bandwidth kernel.  Weights [N,K] are read as stored, 16 bytes
 //                           per lane, straight into m16n8k32 e4m3 A fragments (no dequant instruction at all);
-//                           eight warps of a CTA split K for one 16-column tile and meet in shared memory.
-//   fp8_gemm_tc_kernel      M > 64 (prefill-shaped): tcgen05.mma kind::f8f6f4, 256x256 output tile per CTA, K-major
+//                           four warps of a CTA split K for one 16-column tile and meet in shared memory; all CTAs
+//                           of a launch are resident at once.  Narrow weights split K over the CTAs of a cluster,
+//                           whose partial sums meet through distributed shared memory.  Launched as a programmatic
+//                           dependent of the quantize: its first weight bytes are in flight before the activation
+//                           codes exist.
+//   fp8_gemm_tc_kernel      M > 16 (prefill-shaped): tcgen05.mma kind::f8f6f4, 256x256 output tile per CTA, K-major
 //                           operands brought by TMA with the 128-byte swizzle through a 3-stage mbarrier ring,
 //                           f32 accumulators in TMEM, one producer warp, one MMA warp, eight epilogue warps that read
 //                           TMEM with tcgen05.ld, apply both scales and store bf16/f16.
@@ -66,21 +72,25 @@ __device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int kSmallWarps = 8;
+constexpr int kDecWarps = 4;
 
-// One CTA per 16 output columns; warp w takes the w-th eighth of K.  A lane's 16 weight bytes of row g (and g+8)
-// feed two k32 MMAs; which actual k a fragment slot means is irrelevant as long as the activation fragment uses the
-// same bytes, so both are simply the lane's 16 consecutive bytes.
+// One CTA per (16 output columns, K split); warp w takes the w-th quarter of the CTA's K range.  A lane's 16 weight
+// bytes of row g (and g+8) feed two k32 MMAs; which actual k a fragment slot means is irrelevant as long as the
+// activation fragment uses the same bytes, so both are simply the lane's 16 consecutive bytes.  SPLIT > 1: the CTAs of a
+// cluster share a tile; CTA 0 of the cluster adds the others' partial sums out of their shared memory.
 template <typename OutT, int MT>
-__global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
-                                                                       const uint8_t* __restrict__ qx, const float* __restrict__ sx,
-                                                                       OutT* __restrict__ y, int M, int N, int K) {
-    __shared__ float red[kSmallWarps][MT][16][8];
+__global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
+                                                                     const uint8_t* __restrict__ qx, const float* __restrict__ sx,
+                                                                     OutT* __restrict__ y, int M, int N, int K, int split) {
+    __shared__ float red[kDecWarps][MT][16][8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, j = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int tile = blockIdx.x / split, part = blockIdx.x - tile * split;
+    const int n0 = tile * 16;
     const int steps = K / 64;
-    const int s0 = steps * warp / kSmallWarps, s1 = steps * (warp + 1) / kSmallWarps;
+    const int c0 = steps * part / split, c1 = steps * (part + 1) / split;
+    const int s0 = c0 + (c1 - c0) * warp / kDecWarps, s1 = c0 + (c1 - c0) * (warp + 1) / kDecWarps;
     const uint8_t* wr_lo = w + static_cast<size_t>(n0 + g) * K + 16 * j;
     const uint8_t* wr_hi = wr_lo + static_cast<size_t>(8) * K;
     float acc[MT][4];
@@ -88,8 +98,8 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
     for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
 
     constexpr int U = 4;  // steps in flight per warp
-    for (int sb = s0; sb < s1; sb += U) {
-        uint4 a_lo[U], a_hi[U];
+    uint4 a_lo[U], a_hi[U];
+    auto fetch = [&](int sb) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (sb + u < s1) {
@@ -97,6 +107,11 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
                 a_hi[u] = ld_stream_v4(wr_hi + static_cast<size_t>(sb + u) * 64);
             }
         }
+    };
+    fetch(s0);
+    // the weights never depend on the kernel before; the activation codes do (they come from the quantize)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int sb = s0; sb < s1; sb += U) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (sb + u < s1) {
@@ -110,6 +125,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
                 }
             }
         }
+        fetch(sb + U);  // the other warps of the SM keep the memory system busy while this batch is on its way
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -118,17 +134,35 @@ __global__ void __launch_bounds__(kSmallWarps * 32) fp8_smallm_kernel(const uint
         red[warp][mt][g + 8][2 * j] = acc[mt][2];
         red[warp][mt][g + 8][2 * j + 1] = acc[mt][3];
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < MT * 128; idx += kSmallWarps * 32) {
-        const int mt = idx >> 7, n = (idx >> 3) & 15, mm = idx & 7;
-        const int m = mt * 8 + mm;
-        if (m < M) {
-            float s = 0.f;
+    if (split == 1) {
+        __syncthreads();
+    } else {
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    if (part == 0) {
+        for (int idx = threadIdx.x; idx < MT * 128; idx += kDecWarps * 32) {
+            const int mt = idx >> 7, n = (idx >> 3) & 15, mm = idx & 7;
+            const int m = mt * 8 + mm;
+            if (m < M) {
+                float s = 0.f;
 #pragma unroll
-            for (int wv = 0; wv < kSmallWarps; ++wv) s += red[wv][mt][n][mm];
-            y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
+                for (int wv = 0; wv < kDecWarps; ++wv) s += red[wv][mt][n][mm];
+                for (int peer = 1; peer < split; ++peer) {
+#pragma unroll
+                    for (int wv = 0; wv < kDecWarps; ++wv) {
+                        uint32_t remote;
+                        float v;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(&red[wv][mt][n][mm]))), "r"(peer));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+                        s += v;
+                    }
+                }
+                y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
+            }
         }
     }
+    if (split > 1)  // the peers' shared memory must outlive the reads above
+        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------------------------------ prefill-shaped
@@ -283,11 +317,96 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
+// Few rows (decode): one CTA of 1024 threads per row; the row stays in registers between the two passes.
+// kVecs 16-byte vectors per thread cover K <= 1024 * kVecs * (16 / sizeof(InT)) elements.
+template <typename InT, int kVecs>
+__global__ void __launch_bounds__(1024) quant_fp8_rows_vec_kernel(const InT* __restrict__ x, int64_t K, uint8_t* __restrict__ q,
+                                                                  float* __restrict__ scale, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the linear behind this may start fetching weights
+    constexpr int kPer = 16 / sizeof(InT);  // elements per 16-byte vector
+    __shared__ float warp_max[32];
+    __shared__ float row_scale;
+    const int64_t row = blockIdx.x;
+    if (status && row == 0 && threadIdx.x == 0) *status = 0;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * K);
+    const int n_vec = static_cast<int>(K / kPer);
+    uint4 v[kVecs];
+    float amax = 0.f;
+#pragma unroll
+    for (int u = 0; u < kVecs; ++u) {
+        const int idx = threadIdx.x + u * 1024;
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (idx < n_vec) v[u] = __ldg(xr + idx);
+        const InT* e = reinterpret_cast<const InT*>(&v[u]);
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) amax = fmaxf(amax, fabsf(to_float(e[i])));
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float m = warp_max[threadIdx.x];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+        if (threadIdx.x == 0) {
+            const float s = __fdiv_rn(fmaxf(m, 1e-12f), 448.0f);
+            row_scale = s;
+            scale[row] = s;
+        }
+    }
+    __syncthreads();
+    const float s = row_scale;
+    uint8_t* qr = q + row * K;
+#pragma unroll
+    for (int u = 0; u < kVecs; ++u) {
+        const int idx = threadIdx.x + u * 1024;
+        if (idx < n_vec) {
+            const InT* e = reinterpret_cast<const InT*>(&v[u]);
+            uint16_t out[kPer / 2];
+#pragma unroll
+            for (int i = 0; i < kPer / 2; ++i) out[i] = e4m3x2_satfinite(__fdiv_rn(to_float(e[2 * i]), s), __fdiv_rn(to_float(e[2 * i + 1]), s));
+            if constexpr (kPer == 8)
+                *reinterpret_cast<uint2*>(qr + static_cast<size_t>(idx) * kPer) = *reinterpret_cast<const uint2*>(out);
+            else
+                *reinterpret_cast<uint32_t*>(qr + static_cast<size_t>(idx) * kPer) = *reinterpret_cast<const uint32_t*>(out);
+        }
+    }
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace eq
 
 using namespace eq;
+
+template <typename InT>
+static int quant_rows_launch(const InT* x, int64_t M, int64_t K, uint8_t* q, float* scale, int* status, cudaStream_t stream) {
+    constexpr int kPer = 16 / sizeof(InT);
+    const bool vec = M <= 64 && K % kPer == 0 && aligned(x, 16) && aligned(q, 8) && K / kPer <= 4 * 1024;
+    if (vec) {
+        const unsigned grid = static_cast<unsigned>(M);
+        if (K / kPer <= 1024) quant_fp8_rows_vec_kernel<InT, 1><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
+        else if (K / kPer <= 2048) quant_fp8_rows_vec_kernel<InT, 2><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
+        else quant_fp8_rows_vec_kernel<InT, 4><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
+        EQ_LAUNCH_OK("quant_fp8_rows_vec_kernel");
+        return EQ_OK;
+    }
+    if (status) EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+    quant_fp8_rows_kernel<InT><<<static_cast<unsigned>(M), 256, 0, stream>>>(x, K, q, scale);
+    EQ_LAUNCH_OK("quant_fp8_rows_kernel");
+    return EQ_OK;
+}
+
+// Quantizes the rows and, when `status` is given, clears that word on the way (the linear's status word).
+static int quant_fp8_rows(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, int* status, cudaStream_t stream) {
+    switch (in_dtype) {
+        case EQ_F16: return quant_rows_launch(static_cast<const __half*>(x), M, K, q, scale, status, stream);
+        case EQ_BF16: return quant_rows_launch(static_cast<const __nv_bfloat16*>(x), M, K, q, scale, status, stream);
+        case EQ_F32: return quant_rows_launch(static_cast<const float*>(x), M, K, q, scale, status, stream);
+        default: return fail(EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: unknown dtype %d", in_dtype);
+    }
+}
 
 extern "C" int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -295,15 +414,7 @@ extern "C" int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int i
     if (M == 0) return EQ_OK;
     EQ_REQUIRE(x && q && scale, EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: null pointer");
     EQ_REQUIRE(K % 2 == 0 && aligned(q, 2), EQ_ERR_BAD_ALIGN, "eq_quant_fp8_per_token: K must be even and q 2-byte aligned");
-    const unsigned grid = static_cast<unsigned>(M);
-    switch (in_dtype) {
-        case EQ_F16: quant_fp8_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), K, q, scale); break;
-        case EQ_BF16: quant_fp8_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), K, q, scale); break;
-        case EQ_F32: quant_fp8_rows_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), K, q, scale); break;
-        default: return fail(EQ_ERR_BAD_ARG, "eq_quant_fp8_per_token: unknown dtype %d", in_dtype);
-    }
-    EQ_LAUNCH_OK("quant_fp8_rows_kernel");
-    return EQ_OK;
+    return quant_fp8_rows(x, M, K, in_dtype, q, scale, nullptr, stream);
 }
 
 extern "C" size_t eq_fp8_workspace_bytes(int64_t M, int64_t K) {
@@ -333,14 +444,26 @@ template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
     if (M <= 16) {
-        const unsigned grid = static_cast<unsigned>(N / 16);
-        const int mt = static_cast<int>((M + 7) / 8);
+        // all CTAs resident at once (eight per SM); narrow weights split K over clusters until there are enough CTAs
+        const long long tiles = N / 16, want = 6LL * sm_count();
+        int split = 1;
+        while (split < 8 && tiles * split < want && K / 64 / (2 * split) >= kDecWarps) split *= 2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
+        cfg.blockDim = dim3(kDecWarps * 32);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = static_cast<unsigned>(split);
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = split > 1 ? 2 : 1;
         const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
-        if (mt <= 1) fp8_smallm_kernel<OutT, 1><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
-        else if (mt <= 2) fp8_smallm_kernel<OutT, 2><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
-        else if (mt <= 4) fp8_smallm_kernel<OutT, 4><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
-        else fp8_smallm_kernel<OutT, 8><<<grid, kSmallWarps * 32, 0, stream>>>(w, sw, qx, sx, y, Mi, Ni, Ki);
-        EQ_LAUNCH_OK("fp8_smallm_kernel");
+        if (M <= 8) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 1>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
+        else EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 2>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
         return EQ_OK;
     }
     if (M <= 128) return fp8_tc_launch<OutT, 1, 128>(w, sw, N, K, qx, sx, M, y, status, stream);
@@ -364,8 +487,7 @@ extern "C" int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, i
     uint8_t* qx = static_cast<uint8_t*>(workspace);
     float* sx = reinterpret_cast<float*>(qx + align_up(static_cast<size_t>(M) * K, 256));
     int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + align_up(static_cast<size_t>(M) * sizeof(float), 256));
-    EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    int st = eq_quant_fp8_per_token(x, M, K, act_dtype, qx, sx, stream_);
+    int st = quant_fp8_rows(x, M, K, act_dtype, qx, sx, status, stream);  // also clears the status word
     if (st != EQ_OK) return st;
     if (act_dtype == EQ_F16) return fp8_linear_launch<__half>(weight, weight_scale, N, K, qx, sx, M, static_cast<__half*>(y), status, stream);
     return fp8_linear_launch<__nv_bfloat16>(weight, weight_scale, N, K, qx, sx, M, static_cast<__nv_bfloat16*>(y), status, stream);

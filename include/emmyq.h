@@ -159,7 +159,7 @@ int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int in_dtype, ui
 size_t eq_fp8_workspace_bytes(int64_t M, int64_t K);
 /* y[M, N] = (sum_k q_x[m,k] q_w[n,k]) * s_x[m] * s_w[n] in act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * weight: e4m3 bits [N, K] as the checkpoint stores them, weight_scale: f32 [N] multiplier.  The activation is
- * quantized per token inside the call.  M <= 64 runs a weight-streaming kernel, larger M the tcgen05 tensor path.
+ * quantized per token inside the call.  M <= 16 runs a weight-streaming kernel, larger M the tcgen05 tensor path.
  * The operator the reference spells as FP8 decode + dynamic activation round trip in front of a LinearOp
  * (emmy/compiler/loader/quant.py:1581-1768) and runs natively with both scales hoisted
  * (tests/compiler/passes/test_fp8_mma.py:111-120).  Needs K % 128 == 0, N % 16 == 0; workspace 256-byte aligned. */
