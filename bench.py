@@ -373,7 +373,10 @@ def wl_moe(device, rank, world, t, exchange="peer"):
 
     e, topk, hidden, inter = MOE["e"], MOE["topk"], MOE["hidden"], MOE["inter"]
     local_e = e // world
-    w = moe_experts_weights(device, 400, rank * local_e, local_e)
+    # decode-sized steps run several layers (distinct weights) per graph, as a decode step does; the figures are per layer
+    layers = 4 if (world == 1 and t <= 64) else 1
+    ws = [moe_experts_weights(device, 400 + 31 * layer, rank * local_e, local_e) for layer in range(layers)]
+    w = ws[0]
     hg = torch.Generator().manual_seed(rank)
     x_host = torch.randn(t, hidden, generator=hg).bfloat16().pin_memory()
     y_host = torch.empty(t, hidden, dtype=torch.bfloat16).pin_memory()
@@ -384,7 +387,8 @@ def wl_moe(device, rank, world, t, exchange="peer"):
         wsp = om.moe_workspace(t, w, topk, device)
 
         def step():
-            om.moe_forward(x, logits, w, topk, workspace=wsp, out=y)
+            for wl_ in ws:
+                om.moe_forward(x, logits, wl_, topk, workspace=wsp, out=y)
 
         status = lambda: om.moe_status(wsp, t, w, topk)
         capture = True
@@ -418,7 +422,7 @@ def wl_moe(device, rank, world, t, exchange="peer"):
         hit = int(torch.unique(om.moe_route(logits, topk)[0]).numel())  # distinct experts this batch touches
     else:
         hit = local_e  # every local expert is hit by the ranks' tokens at these sizes
-    return dict(step=step, calls=1, kernels_per_call=8, alg_bytes=hit * MOE_EXPERT_BYTES + t * (2 * hidden * 2 + e * 4),
+    return dict(step=step, calls=layers, kernels_per_call=2 if t <= 16 else 8, alg_bytes=hit * MOE_EXPERT_BYTES + t * (2 * hidden * 2 + e * 4),
                 flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), peak_mult=1.0,
                 h2d=[(x, x_host)], d2h=[(y_host, y)], status=status, capture=capture, parity=parity if world > 1 else None,
                 kernel="w4a16_gemm_tc_kernel (grouped)" if t * topk >= 2 * e else "moe grouped GEMV",

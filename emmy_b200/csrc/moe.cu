@@ -27,6 +27,10 @@
 
 namespace eq {
 
+bool moe_decode_fits(int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I);  // moe_decode.cu
+int moe_decode_launch(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t topk, int64_t H, int64_t I,
+                      const void* x, const float* logits, int64_t T, int act_dtype, void* y, int32_t* ids, float* scores, void* gu, void* rows,
+                      int* tile_count, int* status, cudaStream_t stream);
 int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
                               int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
                               const int32_t* y_rows, const uint64_t* y_ptrs, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
@@ -698,6 +702,10 @@ extern "C" int eq_moe_w4a16(const void* wq_gate_up, const void* wq_down, int sca
                "eq_moe_w4a16: workspace of %zu bytes (256-byte aligned) needed, %zu given", eq_moe_workspace_bytes(T, E, topk, H, I), workspace_bytes);
     MoeWorkspace w = carve(workspace, T, E, topk, H, I);
     const int64_t R = T * topk;
+    if (moe_decode_fits(T, E, topk, H, I) && aligned(x, 16))
+        // a handful of tokens: router + [gate | up] in one launch, SwiGLU + down + combine in a second one
+        return moe_decode_launch(wq_gate_up, wq_down, scale_dtype, E, topk, H, I, x, router_logits, T, act_dtype, y, w.ids, w.scores, w.h1, w.out,
+                                 reinterpret_cast<int*>(w.h), w.status, stream);
     EQ_CUDA_OK(cudaMemsetAsync(w.status, 0, 4, stream));
     st = eq_moe_route(router_logits, T, E, topk, 1, w.ids, w.scores, stream_);
     if (st != EQ_OK) return st;

@@ -586,6 +586,16 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
             return launch_cfg<ActT, 1, 64, 8, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, 1, stream);
         return launch_split<ActT>(wq, scale_dtype, x, y, M, N, K, status, partial, counters, stream);
     }
+    if (M <= 512 && ceil_div(N, 128) * ceil_div(M, 256) * 2 <= sm_count()) {
+        // a few hundred rows of a narrow matrix would leave most SMs idle on 256-row tiles: run 128-row blocks through the
+        // split-K form instead (each block streams the weight once more, which is still far cheaper)
+        for (int64_t m0 = 0; m0 < M; m0 += 128) {
+            const int64_t mb = M - m0 < 128 ? M - m0 : 128;
+            const int st = launch_split<ActT>(wq, scale_dtype, x + m0 * K, y + m0 * N, mb, N, K, status, partial, counters, stream);
+            if (st != EQ_OK) return st;
+        }
+        return EQ_OK;
+    }
     if (ceil_div(N, 256) * ceil_div(M, 256) >= sm_count())
         return launch_cfg<ActT, 2, 256, 16, 2, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);
     return launch_cfg<ActT, 2, 128, 16, 3, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, static_cast<unsigned>(ceil_div(M, 256)), stream);

@@ -29,13 +29,10 @@
 // bf16: 128 + q is exact, nothing is pre-divided and S1 = S2.  Five integer instructions per eight nibbles.
 // (tcgen05 is not used: at one row the contraction is 1/16 of an MMA tile and the kernel is bound by instruction issue;
 // the warp-level MMA keeps the operands in registers.)
-#include "w4_tile.cuh"
+#include "w4_gemv1.cuh"
 
 namespace eq {
 
-constexpr int kG1Warps = 16;
-constexpr int kG1Threads = kG1Warps * 32;
-constexpr int kG1Slot = 1024 + 256;        // ring slot: the item's nibbles, then one private 8-byte scale / zero entry per lane
 constexpr int kG1SmemPair = 112 * 1024;    // dynamic shared memory that still lets two CTAs share an SM
 constexpr int kG1SmemSolo = 226 * 1024;
 constexpr unsigned kG1SpinLimit = 1u << 22;  // polls of the hand-over words before the owner gives up (about a second)
@@ -53,66 +50,6 @@ struct G1Params {
     int by_items;             // spans are counted in items (1) or in whole tiles (0)
     int acc_tiles;            // accumulator slots per CTA
 };
-
-template <typename ActT>
-struct Raw;
-template <>
-struct Raw<__half> {
-    static constexpr float kOffset = 1024.f;
-    static constexpr bool kPrescaleHi = true;
-    static __device__ __forceinline__ void expand(uint32_t w, uint32_t (&a)[4]) {
-        constexpr uint32_t kMagic = 0x64006400u;
-        a[0] = lop3<0xEA>(w, 0x000F000Fu, kMagic);
-        a[2] = lop3<0xEA>(w, 0x00F000F0u, kMagic);
-        const uint32_t w8 = w >> 8;
-        a[1] = lop3<0xEA>(w8, 0x000F000Fu, kMagic);
-        a[3] = lop3<0xEA>(w8, 0x00F000F0u, kMagic);
-    }
-    static __device__ __forceinline__ uint32_t sixteenth(uint32_t pair) {
-        uint32_t r;
-        asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(pair), "r"(0x2C002C00u));
-        return r;
-    }
-    static __device__ __forceinline__ float pair_sum(uint32_t pair) {
-        const __half2 h = *reinterpret_cast<const __half2*>(&pair);
-        return __low2float(h) + __high2float(h);
-    }
-};
-template <>
-struct Raw<__nv_bfloat16> {
-    static constexpr float kOffset = 128.f;
-    static constexpr bool kPrescaleHi = false;
-    static __device__ __forceinline__ void expand(uint32_t w, uint32_t (&a)[4]) {
-        constexpr uint32_t kMagic = 0x43004300u;
-        a[0] = lop3<0xEA>(w, 0x000F000Fu, kMagic);
-        a[2] = lop3<0xEA>(w >> 4, 0x000F000Fu, kMagic);
-        a[1] = lop3<0xEA>(w >> 8, 0x000F000Fu, kMagic);
-        a[3] = lop3<0xEA>(w >> 12, 0x000F000Fu, kMagic);
-    }
-    static __device__ __forceinline__ uint32_t sixteenth(uint32_t pair) { return pair; }
-    static __device__ __forceinline__ float pair_sum(uint32_t pair) {
-        return __uint_as_float(pair << 16) + __uint_as_float(pair & 0xFFFF0000u);
-    }
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_relaxed_gpu(uint32_t* p, uint32_t v) {
-    asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-
-// n / d for 0 <= n < 2^30 by one multiply: inv = floor(2^32 / d) + 1 overestimates the quotient by at most one.
-__device__ __forceinline__ int quotient(int n, int d, uint32_t inv) {
-    if (inv == 0) return n;  // d == 1
-    int q = static_cast<int>(__umulhi(static_cast<uint32_t>(n), inv));
-    if (q * d > n) --q;
-    return q;
-}
 
 template <typename ActT, bool SCALE_F16, int DEPTH>
 __global__ void __launch_bounds__(kG1Threads, 2) w4a16_gemv1_kernel(const G1Params p) {
@@ -221,34 +158,7 @@ __global__ void __launch_bounds__(kG1Threads, 2) w4a16_gemv1_kernel(const G1Para
             for (int u = 0; u < kBatch; ++u) {
                 const int v = v0 + u * kG1Threads;
                 if (v >= ((n_vec + 31) & ~31)) break;  // warp-uniform
-                uint4 val = vals[u];
-                // rows 16..31 of every 32-row lane block are the high k-slots: vectors 2, 3 of every four
-                float s2 = Raw<ActT>::pair_sum(val.x) + Raw<ActT>::pair_sum(val.y) + Raw<ActT>::pair_sum(val.z) + Raw<ActT>::pair_sum(val.w);
-                float s1 = s2;
-                if (Raw<ActT>::kPrescaleHi && (v & 2)) {
-                    val.x = Raw<ActT>::sixteenth(val.x);
-                    val.y = Raw<ActT>::sixteenth(val.y);
-                    val.z = Raw<ActT>::sixteenth(val.z);
-                    val.w = Raw<ActT>::sixteenth(val.w);
-                    s1 = Raw<ActT>::pair_sum(val.x) + Raw<ActT>::pair_sum(val.y) + Raw<ActT>::pair_sum(val.z) + Raw<ActT>::pair_sum(val.w);
-                }
-                if (v < n_vec) {
-                    // vector v = 16 item + 4 j + q: q & 1 picks steps 0..3 / 4..7, q >> 1 the low / high slots; its word i
-                    // is step s = 4 (q & 1) + i: chunk s / 2, word 2 (s & 1) + (q >> 1) of the chunk
-                    const int q = v & 3, jj = (v >> 2) & 3, item = v >> 4;
-                    uint32_t* dst = reinterpret_cast<uint32_t*>(xs) + item * 64 + (2 * (q & 1)) * 16 + jj * 4 + (q >> 1);
-                    dst[0] = val.x;   // step 4 (q & 1)
-                    dst[2] = val.y;   // step 4 (q & 1) + 1: same chunk, next pair
-                    dst[16] = val.z;  // next chunk
-                    dst[18] = val.w;
-                }
-                // an item is 16 consecutive vectors = 16 consecutive lanes of this warp
-#pragma unroll
-                for (int off = 1; off < 16; off <<= 1) {
-                    s1 += __shfl_xor_sync(0xFFFFFFFFu, s1, off);
-                    s2 += __shfl_xor_sync(0xFFFFFFFFu, s2, off);
-                }
-                if (v < n_vec && (v & 15) == 0) xsum[v >> 4] = make_float2(Raw<ActT>::kOffset * s1, s2);
+                stage_vector<ActT>(vals[u], v, v < n_vec, xs, xsum);
             }
         }
     }
@@ -268,43 +178,8 @@ __global__ void __launch_bounds__(kG1Threads, 2) w4a16_gemv1_kernel(const G1Para
         uint32_t sum_addr = smem_u32(xsum) + it * 8;
         for (int c = stretch; c > 0; --c) {
             asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
-            uint32_t w[8], m0, m1, xv[16];
-            float sum1, sum2;
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(ring_w + slot) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+512];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(ring_w + slot) : "memory");
-            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(m0), "=r"(m1) : "r"(ring_m + slot) : "memory");
-            // the B fragments of the eight k16 steps.  Only column 0 of the 16 x 8 product is ever looked at (its B values
-            // sit in lanes 0..3); every lane of a column j reads the same 64 bytes, so all eight columns are copies.
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xv[0]), "=r"(xv[1]), "=r"(xv[2]), "=r"(xv[3]) : "r"(x_addr) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+64];" : "=r"(xv[4]), "=r"(xv[5]), "=r"(xv[6]), "=r"(xv[7]) : "r"(x_addr) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+128];" : "=r"(xv[8]), "=r"(xv[9]), "=r"(xv[10]), "=r"(xv[11]) : "r"(x_addr) : "memory");
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+192];" : "=r"(xv[12]), "=r"(xv[13]), "=r"(xv[14]), "=r"(xv[15]) : "r"(x_addr) : "memory");
-            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(sum1), "=f"(sum2) : "r"(sum_addr) : "memory");
-            float acc[2][4];
-#pragma unroll
-            for (int st = 0; st < 8; ++st) {
-                uint32_t a[4];
-                Raw<ActT>::expand(w[st], a);
-                // staged as {low slot, high slot} word pairs per k16 step
-                if (st < 2)
-                    Frag<ActT>::mma0(acc[st & 1], a, xv[2 * st], xv[2 * st + 1]);
-                else
-                    Frag<ActT>::mma(acc[st & 1], a, xv[2 * st], xv[2 * st + 1]);
-            }
+            gemv1_item<ActT, SCALE_F16>(ring_w + slot, ring_m + slot, x_addr, sum_addr, y_lo, y_hi);
             issue(slot);  // the slot's bytes have been consumed: refill it
-            float s_lo, s_hi;
-            if (SCALE_F16) {
-                const __half2 sc = *reinterpret_cast<const __half2*>(&m0);
-                s_lo = __low2float(sc);
-                s_hi = __high2float(sc);
-            } else {
-                s_lo = __uint_as_float(m0 << 16);
-                s_hi = __uint_as_float(m0 & 0xFFFF0000u);
-            }
-            const __half2 z = *reinterpret_cast<const __half2*>(&m1);
-            // c0: column g, c2: column g + 8 of row 0 of the product, both in lanes j == 0
-            y_lo = fmaf(s_lo, (acc[0][0] + acc[1][0]) - fmaf(__low2float(z), sum2, sum1), y_lo);
-            y_hi = fmaf(s_hi, (acc[0][2] + acc[1][2]) - fmaf(__high2float(z), sum2, sum1), y_hi);
             slot += kG1Slot;
             if (slot == DEPTH * kG1Slot) slot = 0;
             x_addr += 256;
