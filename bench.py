@@ -472,7 +472,7 @@ def wl_tp_mlp(device, rank, world, m):
         return float((y[rows].float() - ref).abs().max() / ref.abs().max())
 
     return dict(step=step, calls=1, kernels_per_call=5, alg_bytes=sum(algorithmic_bytes(k, n, m) for k, n in SHAPES.values()) // world,
-                flops=2.0 * m * 3 * h * inter / world, peak_mult=1.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, capture=False,
+                flops=2.0 * m * 3 * h * inter / world, peak_mult=1.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, capture=True,
                 parity=parity, kernel="w4a16 linears + NCCL all-reduce", dtype="int4 weights, f16 activations, f32 accumulate and all-reduce")
 
 

@@ -121,7 +121,7 @@ using namespace eq;
 
 extern "C" int eq_unpack_int4(int fmt, int along_rows, const int32_t* words, int64_t rows, int64_t cols, uint8_t* out,
                               void* stream) {
-    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ, EQ_ERR_BAD_ARG, "eq_unpack_int4: unknown format %d", fmt);
+    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ || fmt == EQ_W4_CT, EQ_ERR_BAD_ARG, "eq_unpack_int4: unknown format %d", fmt);
     EQ_REQUIRE(words && out, EQ_ERR_BAD_ARG, "eq_unpack_int4: null pointer");
     EQ_REQUIRE(rows >= 0 && cols >= 0, EQ_ERR_BAD_ARG, "eq_unpack_int4: negative extent");
     EQ_REQUIRE(aligned(out, 8), EQ_ERR_BAD_ALIGN, "eq_unpack_int4: out must be 8-byte aligned");
@@ -137,7 +137,7 @@ extern "C" int eq_unpack_int4(int fmt, int along_rows, const int32_t* words, int
 extern "C" int eq_dequant_w4(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales,
                              int scale_dtype, const int32_t* g_idx, int64_t K, int64_t N, int64_t G, int out_dtype,
                              int transpose, void* out, void* stream) {
-    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ, EQ_ERR_BAD_ARG, "eq_dequant_w4: unknown format %d", fmt);
+    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ || fmt == EQ_W4_CT, EQ_ERR_BAD_ARG, "eq_dequant_w4: unknown format %d", fmt);
     EQ_REQUIRE(qweight && qzeros && scales && out, EQ_ERR_BAD_ARG, "eq_dequant_w4: null pointer");
     EQ_REQUIRE(scale_dtype == EQ_F16 || scale_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_dequant_w4: scales must be f16 or bf16");
     EQ_REQUIRE(K > 0 && N > 0, EQ_ERR_BAD_ARG, "eq_dequant_w4: K and N must be positive");

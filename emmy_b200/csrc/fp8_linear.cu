@@ -374,6 +374,19 @@ __global__ void __launch_bounds__(1024) quant_fp8_rows_vec_kernel(const InT* __r
     }
 }
 
+// Static activation scale: every row divides by the same calibrated scale.
+template <typename InT>
+__global__ void __launch_bounds__(256) quant_fp8_static_kernel(const InT* __restrict__ x, int64_t total, const float* __restrict__ input_scale,
+                                                               int64_t M, uint8_t* __restrict__ q, float* __restrict__ scale, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const float s = input_scale[0];
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx < M) scale[idx] = s;
+    if (status && idx == 0) *status = 0;
+    const int64_t k = 2 * idx;
+    if (k < total) *reinterpret_cast<uint16_t*>(q + k) = e4m3x2_satfinite(__fdiv_rn(to_float(x[k]), s), __fdiv_rn(to_float(x[k + 1]), s));
+}
+
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace eq
@@ -470,27 +483,48 @@ static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64
     return fp8_tc_launch<OutT, 2, 256>(w, sw, N, K, qx, sx, M, y, status, stream);
 }
 
-extern "C" int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
-                             int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_fp8_linear: bad extents M=%lld K=%lld N=%lld", (long long)M,
-               (long long)K, (long long)N);
+static int fp8_linear_any(const char* who, const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x,
+                          const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "%s: bad extents M=%lld K=%lld N=%lld", who, (long long)M, (long long)K, (long long)N);
     if (M == 0) return EQ_OK;
-    EQ_REQUIRE(weight && weight_scale && x && y, EQ_ERR_BAD_ARG, "eq_fp8_linear: null pointer");
-    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "eq_fp8_linear: activations must be f16 or bf16");
-    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED, "eq_fp8_linear: needs K %% 128 == 0 and N %% 16 == 0 (K=%lld N=%lld)",
-               (long long)K, (long long)N);
-    EQ_REQUIRE(aligned(weight, 16) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "eq_fp8_linear: weight and y must be 16-byte aligned");
-    EQ_REQUIRE(workspace && workspace_bytes >= eq_fp8_workspace_bytes(M, K), EQ_ERR_WORKSPACE,
-               "eq_fp8_linear: workspace of %zu bytes needed, %zu given", eq_fp8_workspace_bytes(M, K), workspace_bytes);
-    EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "eq_fp8_linear: workspace must be 256-byte aligned");
+    EQ_REQUIRE(weight && weight_scale && x && y, EQ_ERR_BAD_ARG, "%s: null pointer", who);
+    EQ_REQUIRE(act_dtype == EQ_F16 || act_dtype == EQ_BF16, EQ_ERR_BAD_ARG, "%s: activations must be f16 or bf16", who);
+    EQ_REQUIRE(K % 128 == 0 && N % 16 == 0, EQ_ERR_UNSUPPORTED, "%s: needs K %% 128 == 0 and N %% 16 == 0 (K=%lld N=%lld)", who, (long long)K,
+               (long long)N);
+    EQ_REQUIRE(aligned(weight, 16) && aligned(y, 16), EQ_ERR_BAD_ALIGN, "%s: weight and y must be 16-byte aligned", who);
+    EQ_REQUIRE(workspace && workspace_bytes >= eq_fp8_workspace_bytes(M, K), EQ_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", who,
+               eq_fp8_workspace_bytes(M, K), workspace_bytes);
+    EQ_REQUIRE(aligned(workspace, 256), EQ_ERR_BAD_ALIGN, "%s: workspace must be 256-byte aligned", who);
     uint8_t* qx = static_cast<uint8_t*>(workspace);
     float* sx = reinterpret_cast<float*>(qx + align_up(static_cast<size_t>(M) * K, 256));
     int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + align_up(static_cast<size_t>(M) * sizeof(float), 256));
-    int st = quant_fp8_rows(x, M, K, act_dtype, qx, sx, status, stream);  // also clears the status word
+    int st = EQ_OK;
+    if (input_scale) {
+        const int64_t total = M * K;
+        const unsigned grid = static_cast<unsigned>(ceil_div(total / 2 > M ? total / 2 : M, 256));
+        if (act_dtype == EQ_F16) quant_fp8_static_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), total, input_scale, M, qx, sx, status);
+        else quant_fp8_static_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), total, input_scale, M, qx, sx, status);
+        EQ_LAUNCH_OK("quant_fp8_static_kernel");
+    } else {
+        st = quant_fp8_rows(x, M, K, act_dtype, qx, sx, status, stream);  // also clears the status word
+    }
     if (st != EQ_OK) return st;
     if (act_dtype == EQ_F16) return fp8_linear_launch<__half>(weight, weight_scale, N, K, qx, sx, M, static_cast<__half*>(y), status, stream);
     return fp8_linear_launch<__nv_bfloat16>(weight, weight_scale, N, K, qx, sx, M, static_cast<__nv_bfloat16*>(y), status, stream);
+}
+
+extern "C" int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
+                             int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream_) {
+    return fp8_linear_any("eq_fp8_linear", weight, weight_scale, N, K, x, nullptr, M, act_dtype, y, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int eq_fp8_linear_static(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x,
+                                    const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                                    void* stream_) {
+    EQ_REQUIRE(input_scale, EQ_ERR_BAD_ARG, "eq_fp8_linear_static: null input_scale");
+    return fp8_linear_any("eq_fp8_linear_static", weight, weight_scale, N, K, x, input_scale, M, act_dtype, y, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream_) {

@@ -179,7 +179,7 @@ extern "C" int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzer
                             const int32_t* g_idx, int64_t K, int64_t N, int64_t G, void* wq, int32_t* perm, int* uses_perm,
                             void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ, EQ_ERR_BAD_ARG, "eq_w4_repack: unknown format %d", fmt);
+    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ || fmt == EQ_W4_CT, EQ_ERR_BAD_ARG, "eq_w4_repack: unknown format %d", fmt);
     EQ_REQUIRE(qweight && qzeros && scales && wq, EQ_ERR_BAD_ARG, "eq_w4_repack: null pointer");
     int st = check_geometry("eq_w4_repack", K, N, G);
     if (st != EQ_OK) return st;

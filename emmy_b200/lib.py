@@ -18,7 +18,7 @@ HEADER = PKG.parent / "include" / "emmyq.h"
 EQ_OK = 0
 EQ_ERR_BAD_ARG, EQ_ERR_BAD_ALIGN, EQ_ERR_UNSUPPORTED, EQ_ERR_CUDA = -1, -2, -3, -4
 EQ_ERR_NCCL, EQ_ERR_TIMEOUT, EQ_ERR_WORKSPACE = -5, -6, -7
-EQ_W4_AWQ, EQ_W4_GPTQ = 0, 1
+EQ_W4_AWQ, EQ_W4_GPTQ, EQ_W4_CT = 0, 1, 2
 EQ_F16, EQ_BF16, EQ_F32 = 0, 1, 2
 
 
@@ -87,7 +87,11 @@ def load() -> C.CDLL:
         "eq_quant_fp8_per_token": (i, [p, i64, i64, i, p, p, p]),
         "eq_fp8_workspace_bytes": (sz, [i64, i64]),
         "eq_fp8_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),
+        "eq_fp8_linear_static": (i, [p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
         "eq_fp8_status": (i, [p, i64, i64, p]),
+        "eq_quant_fp8_per_group": (i, [p, i64, i64, i, p, p, p]),
+        "eq_fp8_block_workspace_bytes": (sz, [i64, i64]),
+        "eq_fp8_block_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_nvfp4_global_scale": (i, [p, i64, i64, i, p, p, p]),
         "eq_quant_nvfp4_act": (i, [p, i64, i64, i, p, p, p, p, p]),
         "eq_quant_nvfp4_weight": (i, [p, i64, i64, i, p, p, p, p, p]),

@@ -47,6 +47,26 @@ def _(x, weight, weight_scale):
     return x.new_empty((x.shape[0], weight.shape[0]))
 
 
+@torch.library.custom_op("emmyq::fp8_linear_static", mutates_args=(), device_types="cuda")
+def _fp8_static_op(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, input_scale: torch.Tensor) -> torch.Tensor:
+    return ops.fp8_linear(x.contiguous(), weight, weight_scale, input_scale=input_scale)
+
+
+@_fp8_static_op.register_fake
+def _(x, weight, weight_scale, input_scale):
+    return x.new_empty((x.shape[0], weight.shape[0]))
+
+
+@torch.library.custom_op("emmyq::fp8_block_linear", mutates_args=(), device_types="cuda")
+def _fp8_block_op(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor) -> torch.Tensor:
+    return ops.fp8_block_linear(x.contiguous(), weight, weight_scale)
+
+
+@_fp8_block_op.register_fake
+def _(x, weight, weight_scale):
+    return x.new_empty((x.shape[0], weight.shape[0]))
+
+
 @torch.library.custom_op("emmyq::nvfp4_linear", mutates_args=(), device_types="cuda")
 def _nvfp4_op(x: torch.Tensor, weight: torch.Tensor, scale_tiled: torch.Tensor, scale_2: torch.Tensor, input_scale: torch.Tensor) -> torch.Tensor:
     return ops_nvfp4.nvfp4_linear(x.contiguous(), weight, scale_tiled, scale_2, input_scale)
@@ -76,7 +96,8 @@ def _flat(x):
 
 
 class W4A16Linear(nn.Module):
-    """AWQ (`fmt="awq"`) or GPTQ (`fmt="gptq"`, optional act-order `g_idx`) int4 linear.
+    """AWQ (`fmt="awq"`), GPTQ (`fmt="gptq"`, optional act-order `g_idx`) or compressed-tensors (`fmt="ct"`: its three
+    tensors already transposed into GPTQ's orientation) int4 linear.
 
     Buffers keep the checkpoint names and layouts; `finalize()` repacks them once on the device (load time) and
     frees the originals unless `keep_checkpoint=True`."""
@@ -84,7 +105,7 @@ class W4A16Linear(nn.Module):
     def __init__(self, in_features: int, out_features: int, group_size: int = 128, fmt: str = "awq", act_order: bool = False,
                  scale_dtype=torch.float16):
         super().__init__()
-        if fmt not in ("awq", "gptq"):
+        if fmt not in ("awq", "gptq", "ct"):
             raise ValueError(f"unknown packed-int4 family {fmt!r}")
         g = in_features if group_size == -1 else group_size
         self.in_features, self.out_features, self.group_size, self.fmt = in_features, out_features, group_size, fmt
@@ -144,9 +165,40 @@ class FP8Linear(nn.Module):
         self.weight_scale = weight_scale.reshape(-1).float().contiguous()
         return self
 
+    def set_static_input_scale(self, input_scale: torch.Tensor) -> "FP8Linear":
+        """A checkpoint's calibrated `input_scale` / `activation_scale` (one f32): activations are then encoded as
+        x / scale instead of with a per-token scale (emmy/compiler/loader/quant.py:1818-1905)."""
+        self.register_buffer("input_scale", input_scale.float().reshape(1).to(self.weight.device))
+        return self
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         x2, lead = _flat(x)
+        if getattr(self, "input_scale", None) is not None:
+            return _fp8_static_op(x2, self.weight, self.weight_scale, self.input_scale).reshape(*lead, self.out_features)
         return _fp8_op(x2, self.weight, self.weight_scale).reshape(*lead, self.out_features)
+
+
+class FP8BlockLinear(nn.Module):
+    """Block-scaled FP8 W8A8 linear (the official 128 x 128 `weight_block_size` form): `weight` e4m3 bits [N, K],
+    `weight_scale_inv` f32 [N / 128, K / 128] used as a multiplier, activations quantized per token and per 128
+    elements of K inside the call."""
+
+    def __init__(self, in_features: int, out_features: int, block=(128, 128)):
+        super().__init__()
+        if tuple(block) != (128, 128):
+            raise ValueError(f"block-scaled FP8 kernels take 128 x 128 weight blocks, got {tuple(block)}")
+        self.in_features, self.out_features = in_features, out_features
+        self.register_buffer("weight", torch.zeros((out_features, in_features), dtype=torch.uint8))
+        self.register_buffer("weight_scale_inv", torch.ones((out_features // 128, in_features // 128), dtype=torch.float32))
+
+    def load_float8(self, weight_f8: torch.Tensor, weight_scale: torch.Tensor) -> "FP8BlockLinear":
+        self.weight = weight_f8.view(torch.uint8).contiguous()
+        self.weight_scale_inv = weight_scale.float().contiguous()
+        return self
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x2, lead = _flat(x)
+        return _fp8_block_op(x2, self.weight, self.weight_scale_inv).reshape(*lead, self.out_features)
 
 
 class NVFP4Linear(nn.Module):

@@ -15,7 +15,7 @@ import torch
 from . import lib as L
 
 _DTYPE = {torch.float16: L.EQ_F16, torch.bfloat16: L.EQ_BF16, torch.float32: L.EQ_F32}
-_FMT = {"awq": L.EQ_W4_AWQ, "gptq": L.EQ_W4_GPTQ}
+_FMT = {"awq": L.EQ_W4_AWQ, "gptq": L.EQ_W4_GPTQ, "ct": L.EQ_W4_CT}
 
 
 def _ptr(t):
@@ -47,7 +47,7 @@ def dequant_w4(qweight, qzeros, scales, group_size, fmt, g_idx=None, out_dtype=t
     _need_cuda(qweight, qzeros, scales, g_idx)
     if fmt == "awq":
         k, n = qweight.shape[0], qweight.shape[1] * 8
-    else:
+    else:  # "gptq", and "ct" (compressed-tensors int4 already transposed into GPTQ's orientation)
         k, n = qweight.shape[0] * 8, qweight.shape[1]
     out = torch.empty((n, k) if transpose else (k, n), dtype=out_dtype, device=qweight.device)
     L.check(
@@ -188,15 +188,23 @@ def fp8_workspace(m: int, k: int, device) -> torch.Tensor:
     return torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
 
 
-def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None):
-    """y[M, N] = x @ (weight * scale).T with x quantized per token; weight uint8 e4m3 bits [N, K], scale f32 [N]."""
-    _need_cuda(x, weight, weight_scale)
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None, input_scale=None):
+    """y[M, N] = x @ (weight * scale).T with x quantized per token (or with the static `input_scale`, f32 [1]);
+    weight uint8 e4m3 bits [N, K], scale f32 [N]."""
+    _need_cuda(x, weight, weight_scale, input_scale)
     m, k = x.shape
     n = weight.shape[0]
     if weight.shape[1] != k:
         raise ValueError(f"x has {k} features, the weight takes {weight.shape[1]}")
     y = out if out is not None else torch.empty((m, n), dtype=x.dtype, device=x.device)
     ws = workspace if workspace is not None else fp8_workspace(m, k, x.device)
+    if input_scale is not None:
+        L.check(
+            L.load().eq_fp8_linear_static(
+                _ptr(weight), _ptr(weight_scale), n, k, _ptr(x), _ptr(input_scale), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()
+            )
+        )
+        return y
     L.check(
         L.load().eq_fp8_linear(
             _ptr(weight), _ptr(weight_scale), n, k, _ptr(x), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()
@@ -207,3 +215,27 @@ def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor
 
 def fp8_status(workspace: torch.Tensor, m: int, k: int) -> None:
     L.check(L.load().eq_fp8_status(_ptr(workspace), m, k, _stream()))
+
+
+def quant_fp8_per_group(x: torch.Tensor):
+    """x [M, K] -> (bits uint8 [M, K], scale f32 [M, K / 128]): the dynamic rule per token and per 128 elements of K."""
+    _need_cuda(x)
+    m, k = x.shape
+    q = torch.empty((m, k), dtype=torch.uint8, device=x.device)
+    s = torch.empty((m, k // 128), dtype=torch.float32, device=x.device)
+    L.check(L.load().eq_quant_fp8_per_group(_ptr(x), m, k, _DTYPE[x.dtype], _ptr(q), _ptr(s), _stream()))
+    return q, s
+
+
+def fp8_block_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None):
+    """Block-scaled W8A8: weight uint8 e4m3 bits [N, K], weight_scale f32 [N / 128, K / 128] (a multiplier)."""
+    _need_cuda(x, weight, weight_scale)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or tuple(weight_scale.shape) != (n // 128, k // 128):
+        raise ValueError(f"block-scaled FP8: x {tuple(x.shape)}, weight {tuple(weight.shape)}, scale {tuple(weight_scale.shape)} do not fit")
+    y = out if out is not None else torch.empty((m, n), dtype=x.dtype, device=x.device)
+    need = L.load().eq_fp8_block_workspace_bytes(m, k)
+    ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+    L.check(L.load().eq_fp8_block_linear(_ptr(weight), _ptr(weight_scale), n, k, _ptr(x), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()))
+    return y

@@ -21,6 +21,7 @@
  *   AWQ   qweight int32 [K, N/8] (nibble order 0,2,4,6,1,3,5,7), qzeros int32 [K/G, N/8], scales f16 [K/G, N]
  *   GPTQ  qweight int32 [K/8, N] (sequential down K), qzeros int32 [K/G, N/8] (zero = stored + 1),
  *         scales f16 [K/G, N], g_idx int32 [K] (optional)
+ *   CT    compressed-tensors int4: GPTQ's layout once transposed (see EQ_W4_CT), zero = stored, scales usually bf16
  *   FP8   weight u8 e4m3fn [N, K], weight_scale f32 [N] (multiplier)
  *   NVFP4 weight u8 [N, K/2] (low nibble = even k), weight_scale u8 e4m3 [N, K/16], weight_scale_2 f32 [1]
  * K = in features, N = out features, G = group size, y[M,N] = x[M,K] @ W[K,N].
@@ -46,7 +47,10 @@ enum {
     EQ_ERR_WORKSPACE = -7    /* workspace missing or too small */
 };
 
-enum { EQ_W4_AWQ = 0, EQ_W4_GPTQ = 1 };           /* packed-int4 family */
+/* Packed-int4 family (emmy/compiler/loader/quant.py:86-133).  EQ_W4_CT is compressed-tensors' pack-quantized int4 AFTER its
+ * three tensors have been transposed into GPTQ's orientation (weight_packed [N, K/8] -> [K/8, N], weight_zero_point
+ * [N/8, K/G] -> [K/G, N/8], weight_scale [N, K/G] -> [K/G, N]): GPTQ's sequential nibble order, zero point as stored. */
+enum { EQ_W4_AWQ = 0, EQ_W4_GPTQ = 1, EQ_W4_CT = 2 };
 enum { EQ_F16 = 0, EQ_BF16 = 1, EQ_F32 = 2 };     /* element types of activations / outputs / scales */
 
 /* Library version (major*10000 + minor*100 + patch) and message of the calling thread's last failure. */
@@ -165,9 +169,23 @@ size_t eq_fp8_workspace_bytes(int64_t M, int64_t K);
  * (tests/compiler/passes/test_fp8_mma.py:111-120).  Needs K % 128 == 0, N % 16 == 0; workspace 256-byte aligned. */
 int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
                   int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* The same with a STATIC activation scale: q = e4m3(x / input_scale) for every token (input_scale: device f32 [1], the
+ * checkpoint's `input_scale` / `activation_scale`), y = (sum q_x q_w) * input_scale * s_w[n].  The static FP8 activation
+ * the reference spells for `activation_scheme: static` checkpoints (emmy/compiler/loader/quant.py:1818-1905). */
+int eq_fp8_linear_static(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, const float* input_scale,
+                         int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
 /* Synchronizes the stream and returns EQ_ERR_TIMEOUT if a bounded pipeline wait of the last eq_fp8_linear call on
  * this workspace ran out (same role as eq_w4a16_status). */
 int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream);
+
+/* Block-scaled FP8 (the official 128 x 128 weight-block form): weight e4m3 [N, K], weight_scale f32 [N/128, K/128]
+ * (the checkpoint's `weight_scale_inv`, a multiplier: emmy/compiler/loader/quant.py:136-144), activations quantized per
+ * token and per 128 elements of K (emmy/compiler/loader/quant.py:1581-1593, 1655-1717):
+ * y[m, n] = sum_kb (sum_{k in kb} q_x q_w) * s_x[m, kb] * s_w[n / 128, kb].  Needs K % 128 == 0, N % 128 == 0. */
+int eq_quant_fp8_per_group(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream);
+size_t eq_fp8_block_workspace_bytes(int64_t M, int64_t K);
+int eq_fp8_block_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
+                        int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ NVFP4 W4A4 linear */
 

@@ -29,6 +29,15 @@ def fp8_dynamic_round_trip(x) -> np.ndarray:
     return e4m3_decode(bits) * s
 
 
+def fp8_dynamic_per_group(x, group: int = 128) -> tuple[np.ndarray, np.ndarray]:
+    """The dynamic rule per token AND per `group` elements of K: x [M, K] -> (bits u8 [M, K], scale f32 [M, K / group]);
+    what a `weight_block_size` declaration selects (emmy/compiler/loader/quant.py:1581-1593, 1655-1717)."""
+    xf = np.asarray(x, dtype=np.float32)
+    m, k = xf.shape
+    bits, s = quant_fp8_rows(xf.reshape(m * (k // group), group))
+    return bits.reshape(m, k), s.reshape(m, k // group)
+
+
 def nvfp4_global_scale(x) -> np.float32:
     """The calibrated-on-the-sample input scale: max(amax, 1e-12) / (6 * 448)
     (emmy/compiler/loader/synthesize.py:181-183)."""

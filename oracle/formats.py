@@ -150,6 +150,9 @@ FORMATS = {
     # name: (shifts, qweight packed along K rows?, zero bias)
     "awq": (AWQ_SHIFTS, False, 0),
     "gptq": (GPTQ_SHIFTS, True, 1),
+    # compressed-tensors pack-quantized int4 once its three tensors are transposed into GPTQ's orientation:
+    # sequential nibbles down K, zero point as stored (emmy/compiler/loader/quant.py:119-133)
+    "ct": (GPTQ_SHIFTS, True, 0),
 }
 
 

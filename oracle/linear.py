@@ -43,6 +43,17 @@ def fp8_linear_native(x, w_bits, w_scale) -> np.ndarray:
     return acc * sx * np.asarray(w_scale, dtype=np.float32).reshape(1, -1)
 
 
+def fp8_block_linear(x, w_bits, w_scale_blocks, dtype="bf16") -> np.ndarray:
+    """Block-scaled W8A8 value path: activations round-tripped per token and per 128 elements of K, weight
+    dequantized by its 2-D block scales, both rounded to the model dtype, ordinary linear
+    (emmy/compiler/loader/quant.py:147-170, 1655-1717)."""
+    rnd = fm.round_bf16 if dtype == "bf16" else fm.round_f16
+    bits, s = act.fp8_dynamic_per_group(x)
+    xh = rnd(fm.e4m3_decode(bits) * np.repeat(s, 128, axis=1))
+    wh = rnd(fm.dequant_fp8(w_bits, w_scale_blocks))
+    return _matmul_f32(xh, wh.T)
+
+
 def nvfp4_linear(x, w_packed, w_scale_bits, w_scale_2, input_scale) -> np.ndarray:
     """W4A4: static-quantized activation round trip times the dequantized
     weight (tests/compiler/loader/test_quant.py:1809-1812)."""
