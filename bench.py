@@ -300,6 +300,58 @@ def wl_w4(device, rank, fmt, k, n, m):
                 dtype="int4 weights, f16 activations, f32 accumulate")
 
 
+def wl_gate_up_fused(device, rank):
+    """gate and up of the Llama MLP as ONE linear ([gate | up] concatenated along N, as the reference stores expert
+    weights): one launch streams both projections behind one prologue."""
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(350 + rank)
+    k, n = SHAPES["gate"]
+    copies = 5
+    ws = [ops.w4_concat([gptq_weight(device, gen, k, n), gptq_weight(device, gen, k, n)]) for _ in range(copies)]
+    x_host = torch.randn(1, k, generator=torch.Generator().manual_seed(rank)).half().pin_memory()
+    y_host = torch.empty(1, 2 * n, dtype=torch.float16).pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(1, 2 * n, dtype=torch.float16, device=device)
+    wsp = torch.zeros(ops.L.load().eq_w4a16_workspace_bytes(1, 2 * n, k) + 256, dtype=torch.uint8, device=device)
+
+    def step():
+        for w in ws:
+            ops.w4a16_linear(x, w, workspace=wsp, out=y)
+
+    return dict(step=step, calls=copies, kernels_per_call=1, alg_bytes=2 * algorithmic_bytes(k, n) - 2 * k, flops=4.0 * k * n, peak_mult=1.0,
+                h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.w4a16_status(wsp, 1, 2 * n), kernel=GEMV_KERNEL,
+                dtype="int4 weights, f16 activations, f32 accumulate")
+
+
+def wl_fp8_block(device, rank, m, n=GEMM_N, k=GEMM_K):
+    """The official block-scaled FP8 form: 128 x 128 weight blocks, activations per token and per 128 elements of K."""
+    from emmy_b200 import ops
+
+    gen = torch.Generator(device=device).manual_seed(150 + rank)
+    copies = 2
+    ws = []
+    for _ in range(copies):
+        w = torch.randn(n, k, device=device, generator=gen) * 0.02
+        blocks = w.reshape(n // 128, 128, k // 128, 128)
+        s = (blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / 448.0).float()
+        bits = (blocks / s[:, None, :, None]).reshape(n, k).to(torch.float8_e4m3fn).view(torch.uint8)
+        ws.append((bits.contiguous(), s.contiguous()))
+    x_host = torch.randn(m, k, generator=torch.Generator().manual_seed(rank)).bfloat16().pin_memory()
+    y_host = torch.empty(m, n, dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(device)
+    y = torch.empty(m, n, dtype=torch.bfloat16, device=device)
+    wsp = torch.empty(ops.L.load().eq_fp8_block_workspace_bytes(m, k) + 256, dtype=torch.uint8, device=device)
+
+    def step():
+        for w, s in ws:
+            ops.fp8_block_linear(x, w, s, workspace=wsp, out=y)
+
+    return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + (n // 128) * (k // 128) * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n,
+                peak_mult=2.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, kernel="fp8_block_gemm_kernel<__nv_bfloat16>",
+                dtype="e4m3 weights (128 x 128 block scales) and activations (per token, per 128 of K), f32 accumulate, bf16 out")
+
+
 def wl_fp8(device, rank, m, n=GEMM_N, k=GEMM_K):
     from emmy_b200 import ops
 
@@ -533,6 +585,11 @@ def extra_records(device, rank, world, clocks, quick_steps=3):
                 unit = "GB/s" if m <= 16 else "TFLOP/s"
                 add(lambda: wl_w4(device, rank, "gptq", k, n, m), quick_steps, clocks, f"gptq_{proj}_m{m}",
                     "w4a16_gemv_hbm_gbs" if m <= 16 else "w4a16_gemm_tflops", unit, f"GPTQ act-order W4A16, Llama-3.1-8B {proj} K={k} N={n}, M={m}")
+        add(lambda: wl_gate_up_fused(device, rank), quick_steps, clocks, "gptq_gate_up_fused_m1", "w4a16_gemv_hbm_gbs", "GB/s",
+            "GPTQ act-order W4A16, Llama-3.1-8B gate and up as one [gate | up] linear K=4096 N=28672, M=1: one launch for both projections")
+        for m in (16, 2048):
+            add(lambda: wl_fp8_block(device, rank, m), quick_steps, clocks, f"fp8_block_m{m}", "fp8_block_hbm_gbs" if m <= 16 else "fp8_block_gemm_tflops",
+                "GB/s" if m <= 16 else "TFLOP/s", f"block-scaled FP8 W8A8 (128 x 128 weight blocks, per-token per-128 activation scales, quantize timed), K={GEMM_K} N={GEMM_N} M={m}")
         for m in (1, 32, 512, 8192):
             unit = "GB/s" if m <= 32 else "TFLOP/s"
             add(lambda: wl_fp8(device, rank, m), quick_steps, clocks, f"fp8_m{m}", "fp8_w8a8_hbm_gbs" if m <= 32 else "fp8_w8a8_gemm_tflops", unit,

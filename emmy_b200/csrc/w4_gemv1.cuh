@@ -122,16 +122,17 @@ __device__ __forceinline__ void gemv1_item(uint32_t w_addr, uint32_t m_addr, uin
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+128];" : "=r"(xv[8]), "=r"(xv[9]), "=r"(xv[10]), "=r"(xv[11]) : "r"(x_addr) : "memory");
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+192];" : "=r"(xv[12]), "=r"(xv[13]), "=r"(xv[14]), "=r"(xv[15]) : "r"(x_addr) : "memory");
     asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(sum1), "=f"(sum2) : "r"(sum_addr) : "memory");
-    float acc[2][4];
+    constexpr int kChains = 2;  // independent accumulator chains (four were slower: registers)
+    float acc[kChains][4];
 #pragma unroll
     for (int st = 0; st < 8; ++st) {
         uint32_t a[4];
         Raw<ActT>::expand(w[st], a);
         // staged as {low slot, high slot} word pairs per k16 step
-        if (st < 2)
-            Frag<ActT>::mma0(acc[st & 1], a, xv[2 * st], xv[2 * st + 1]);
+        if (st < kChains)
+            Frag<ActT>::mma0(acc[st % kChains], a, xv[2 * st], xv[2 * st + 1]);
         else
-            Frag<ActT>::mma(acc[st & 1], a, xv[2 * st], xv[2 * st + 1]);
+            Frag<ActT>::mma(acc[st % kChains], a, xv[2 * st], xv[2 * st + 1]);
     }
     float s_lo, s_hi;
     if (SCALE_F16) {

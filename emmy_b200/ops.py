@@ -112,6 +112,22 @@ def w4_repack(qweight, qzeros, scales, group_size, fmt, g_idx=None) -> W4Weight:
     return w
 
 
+def w4_concat(weights: list[W4Weight]) -> W4Weight:
+    """Several repacked linears that read the same activations (gate and up, or q / k / v) as ONE linear whose output
+    is their outputs side by side: the repacked stream is [column tile][K run], so concatenating along N is concatenating
+    the blobs.  One launch then streams all of them behind one prologue -- the reference stores `[gate | up]` as one
+    tensor for the same reason (emmy/compiler/trace/huggingface.py:2110-2141).  The parts must agree in K, group size
+    and scale dtype, and none may carry a row permutation (scattered act-order groups differ per linear)."""
+    first = weights[0]
+    for w in weights:
+        if (w.k, w.group, w.scale_dtype) != (first.k, first.group, first.scale_dtype) or w.perm is not None:
+            raise ValueError("w4_concat: the parts must share K, group size and scale dtype and carry no row permutation")
+    out = W4Weight()
+    out.wq = torch.cat([w.wq for w in weights])
+    out.perm, out.k, out.n, out.group, out.scale_dtype, out.fmt = None, first.k, sum(w.n for w in weights), first.group, first.scale_dtype, first.fmt
+    return out
+
+
 def w4_unpack_repacked(w: W4Weight) -> torch.Tensor:
     out = torch.empty((w.k, w.n), dtype=torch.uint8, device=w.wq.device)
     L.check(L.load().eq_w4_unpack_repacked(_ptr(w.wq), w.k, w.n, _ptr(out), _stream()))

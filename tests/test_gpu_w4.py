@@ -345,3 +345,26 @@ def test_prefill_bf16_scales_with_f16_activations():
     for m in (3, 64):
         x = synth.activations(m, k, "f16", seed=m)
         check_close(ops.w4a16_linear(act(x, "f16"), w), ol.w4a16_linear(x, qw, qz, sc, 128, "awq", "f16"))
+
+
+def test_concatenated_linears_share_one_launch():
+    """[gate | up] as one linear: the outputs of the parts side by side, bit for bit (same kernel, same tiles)."""
+    from emmy_b200 import ops
+
+    k = 1024
+    parts, refs = [], []
+    x = synth.activations(1, k, "f16", seed=3)
+    for i, n in enumerate((2400, 2384)):
+        qw, qz, sc, gi = synth.gptq_linear(k, n, seed=30 + i)
+        w = ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi))
+        parts.append(w)
+        refs.append(ol.w4a16_linear(x, qw, qz, sc, 128, "gptq", "f16", gi))
+    both = ops.w4_concat(parts)
+    assert both.n == 4784
+    y = ops.w4a16_linear(act(x, "f16"), both)
+    check_close(y, np.concatenate(refs, axis=1))
+    for m in (5, 40):
+        xm = synth.activations(m, k, "f16", seed=m)
+        ym = ops.w4a16_linear(act(xm, "f16"), both)
+        sep = torch.cat([ops.w4a16_linear(act(xm, "f16"), w) for w in parts], dim=1)
+        assert float((ym.float() - sep.float()).abs().max()) <= 2e-3 * float(sep.float().abs().max())
