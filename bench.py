@@ -56,7 +56,7 @@ STEP_BYTES = LAYERS * sum(algorithmic_bytes(k, n) for k, n in SHAPES.values())
 # dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of the captured launches of
 # this workload) from the ncu capture summarised in profiles/w4a16_gemv1_kernel_gptq_m1.md
 GEMV_KERNEL = "w4a16_gemv1_kernel<__half, true, DEPTH>"
-TRAFFIC_PER_LAUNCH = 31224000
+TRAFFIC_PER_LAUNCH = 31242000
 
 
 def peaks():

@@ -80,22 +80,32 @@ __device__ __forceinline__ uint8_t e2m1x2_satfinite(float lo, float hi) {
 }
 
 // One thread per 16-element block.  Writes the packed codes [M, K/2], the plain scales [M, K/16] (optional) and the
-// tiled scales (optional).
+// tiled scales (optional).  `status`, when given, is cleared for the linear that follows in the stream; that linear
+// may be launched as a programmatic dependent and fetch its weights while this kernel runs.
 template <typename InT>
 __global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int64_t K, const float* __restrict__ scale2,
-                                       uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_tiled) {
+                                       uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_tiled,
+                                       int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t blocks16 = K / 16;
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (status && idx == 0) *status = 0;
     if (idx >= M * blocks16) return;
     const int64_t row = idx / blocks16, b = idx % blocks16;
     const InT* src = x + row * K + b * 16;
     float v[16];
+    if (sizeof(InT) == 2 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        uint4 raw[2] = {reinterpret_cast<const uint4*>(src)[0], reinterpret_cast<const uint4*>(src)[1]};
+        const InT* e = reinterpret_cast<const InT*>(raw);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = to_float(e[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = to_float(src[i]);
+    }
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        v[i] = to_float(src[i]);
-        amax = fmaxf(amax, fabsf(v[i]));
-    }
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
     const float s2 = scale2[0];
     const float ratio = __fmul_rn(__fmul_rn(amax, __fdiv_rn(1.0f, 6.0f)), __fdiv_rn(1.0f, s2));
     const uint8_t sbits = e4m3_satfinite(ratio);
@@ -195,6 +205,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
     const int k_blocks = K / 256;   // stages of 256 elements
     const int k64_blocks = K / 64;  // scale atoms along K
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -212,33 +223,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const uint32_t tmem_sfa = tmem_base + kBN;        // 4 columns per k64 step
     const uint32_t tmem_sfb = tmem_base + kBN + 16;   // 8 columns per k64 step
 
+    // The kernel may have been launched as a programmatic dependent of the activation quantize: the weights and their
+    // scales never depend on it, so the first ring of weight stages is requested before the dependency is awaited;
+    // every other role waits first, so that its bounded waits count from the moment the codes exist.
     if (warp == 0) {
         if (tc::elect_one()) {
             tc::tma_prefetch_desc(&map_a);
             tc::tma_prefetch_desc(&map_b);
             const int rb_a = m0 / 128, rb_b = n0 / 128;
             const int n_rb = (N + 127) / 128;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % kStages;
-                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
-                    atomicExch(status, 1);
-                    break;
-                }
-                const uint32_t bar = tc::smem_u32(full + s);
-                // the second row block of B may lie beyond N (N not a multiple of 256): it is then not copied
-                const bool second = kTwoBlocks && rb_b + 1 < n_rb;
-                constexpr int kSfBlock = 4 * 512;
+            // the second row block of B may lie beyond N (N not a multiple of 256): it is then not copied
+            const bool second = kTwoBlocks && rb_b + 1 < n_rb;
+            constexpr int kSfBlock = 4 * 512;
+            auto weights = [&](int kb, int s, uint32_t bar) {
                 tc::mbar_expect_tx(bar, kTileA + kTileB + kSfA + (second ? 2 * kSfBlock : kSfBlock));
-                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBKBytes, m0, bar);
                 tc::tma_load_2d(tc::smem_u32(tiles_b + s * kTileB), &map_b, kb * kBKBytes, n0, bar);
-                bulk_g2s(tc::smem_u32(sfs_a + s * kSfA), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfA, bar);
                 bulk_g2s(tc::smem_u32(sfs_b + s * kSfB), sfb + (static_cast<size_t>(rb_b) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
                 if (second)
                     bulk_g2s(tc::smem_u32(sfs_b + s * kSfB + kSfBlock),
                              sfb + (static_cast<size_t>(rb_b + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
+            };
+            auto codes = [&](int kb, int s, uint32_t bar) {
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBKBytes, m0, bar);
+                bulk_g2s(tc::smem_u32(sfs_a + s * kSfA), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfA, bar);
+            };
+            const int ahead = k_blocks < kStages ? k_blocks : kStages;
+            for (int kb = 0; kb < ahead; ++kb) weights(kb, kb, tc::smem_u32(full + kb));
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int kb = 0; kb < ahead; ++kb) codes(kb, kb, tc::smem_u32(full + kb));
+            for (int kb = ahead; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                if (!tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                weights(kb, s, bar);
+                codes(kb, s, bar);
             }
         }
     } else if (warp == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         if (tc::elect_one()) {
             constexpr uint32_t idesc = tc::instr_desc_nvfp4(kBM, kBN, 0, 0);
             for (int kb = 0; kb < k_blocks; ++kb) {
@@ -268,6 +293,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc::mma_commit(tc::smem_u32(acc_ready));
         }
     } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int quarter = warp & 3;
         const int m = m0 + quarter * 32 + lane;
         const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
@@ -540,25 +566,32 @@ extern "C" int eq_quant_nvfp4_weight(const void* values, int64_t N, int64_t K, i
     return EQ_OK;
 }
 
-extern "C" int eq_quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const float* input_scale, uint8_t* codes,
-                                  uint8_t* scale_bits, uint8_t* scale_tiled, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+// `pad_rows`: zero the tiled scales of the rows between M and the end of its 128-row block (what a caller that reads the
+// tiled layout expects).  The linear passes false: those rows of A arrive as zeros from the tensor map and the output
+// rows they produce are never stored.  `status`: cleared by the kernel for the linear behind it.
+static int quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const float* input_scale, uint8_t* codes, uint8_t* scale_bits,
+                           uint8_t* scale_tiled, bool pad_rows, int* status, cudaStream_t stream) {
     EQ_REQUIRE(M >= 0 && K > 0, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: bad extents");
     if (M == 0) return EQ_OK;
     EQ_REQUIRE(x && input_scale && codes, EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: null pointer");
     EQ_REQUIRE(K % 16 == 0 && (!scale_tiled || K % 64 == 0), EQ_ERR_UNSUPPORTED, "eq_quant_nvfp4_act: K must be a multiple of 16 (64 with tiled scales)");
     EQ_REQUIRE(aligned(codes, 8), EQ_ERR_BAD_ALIGN, "eq_quant_nvfp4_act: codes must be 8-byte aligned");
-    if (scale_tiled) EQ_CUDA_OK(cudaMemsetAsync(scale_tiled, 0, sf_tiled_bytes(M, K), stream));  // rows beyond M
+    if (scale_tiled && pad_rows) EQ_CUDA_OK(cudaMemsetAsync(scale_tiled, 0, sf_tiled_bytes(M, K), stream));
     const int64_t total = M * (K / 16);
     const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
     switch (in_dtype) {
-        case EQ_F16: quant_nvfp4_act_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
-        case EQ_BF16: quant_nvfp4_act_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
-        case EQ_F32: quant_nvfp4_act_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), M, K, input_scale, codes, scale_bits, scale_tiled); break;
+        case EQ_F16: quant_nvfp4_act_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
+        case EQ_BF16: quant_nvfp4_act_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
+        case EQ_F32: quant_nvfp4_act_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
         default: return fail(EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: unknown dtype %d", in_dtype);
     }
     EQ_LAUNCH_OK("quant_nvfp4_act_kernel");
     return EQ_OK;
+}
+
+extern "C" int eq_quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, const float* input_scale, uint8_t* codes,
+                                  uint8_t* scale_bits, uint8_t* scale_tiled, void* stream_) {
+    return quant_nvfp4_act(x, M, K, in_dtype, input_scale, codes, scale_bits, scale_tiled, true, nullptr, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K) {
@@ -582,8 +615,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     uint8_t* codes = static_cast<uint8_t*>(workspace);
     uint8_t* sfa = codes + align_up(static_cast<size_t>(M) * K / 2, 256);
     int* status = reinterpret_cast<int*>(sfa + align_up(sf_tiled_bytes(M, K), 256));
-    EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
-    int st = eq_quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, stream_);
+    int st = quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, false, status, stream);
     if (st != EQ_OK) return st;
     CUtensorMap map_a, map_b;
     // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
@@ -600,9 +632,19 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
         dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
         auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
             EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            kernel<<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, sfa, weight_scale_tiled, input_scale, weight_scale_2, yt, static_cast<int>(M),
-                                                        static_cast<int>(N), static_cast<int>(K), status);
-            EQ_LAUNCH_OK("nvfp4_gemm_tc_kernel");
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start (and fetch weights) while the quantize runs
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            const uint8_t* sfa_c = sfa;
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, sfa_c, weight_scale_tiled, input_scale, weight_scale_2, yt, static_cast<int>(M),
+                                          static_cast<int>(N), static_cast<int>(K), status));
             return EQ_OK;
         };
         if (act_dtype == EQ_F16)

@@ -134,8 +134,12 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         // prefill-shaped: the tcgen05 kernel; its bounded waits report through the status word, cleared per call
         EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
         void* gathered = static_cast<unsigned char*>(workspace) + w4_gather_offset(M, N);
-        return w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
-                                 partial, counters, stream);
+        const int st = w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
+                                         partial, counters, stream);
+        // Everything behind the header is zero between calls, whatever their shapes: a later call of another shape keeps its
+        // partial sums or hand-over words where this one kept the gathered copy of x, so that copy is wiped again.
+        if (st == EQ_OK && perm) EQ_CUDA_OK(cudaMemsetAsync(gathered, 0, static_cast<size_t>(M) * K * 2, stream));
+        return st;
     }
     if (M == 1) {
         // the decode step's GEMV; the workspace carries its sixteen-word hand-overs between neighbouring CTAs

@@ -83,6 +83,10 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) yacc[mt][0] = yacc[mt][1] = yacc[mt][2] = yacc[mt][3] = 0.f;
     bool dirty = false;
+    // the rows of x run one item ahead of the weights in registers: they come from L1 / L2, and with four warps per
+    // scheduler nothing else would cover that latency
+    uint4 xv[MT][4];
+    if (n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
 
     for (int i = 0; i < n; ++i) {
         const int d = i % kStreamDepth;
@@ -93,8 +97,15 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
         const uint4 wh = *reinterpret_cast<const uint4*>(slot + 512 + lane * 16);
         const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
         __syncwarp();  // every lane has read the slot before any lane refills it
-        w4_item<ActT, MT, false>(p, x, it, wl, wh, mt_, g, j, yacc);
         issue(d, i + kStreamDepth);  // the slot's bytes are in registers: refill it
+        uint4 xn[MT][4];
+        const int it_next = it + 1 == p.items ? 0 : it + 1;
+        if (i + 1 < n) w4_item_x<ActT, MT, false>(p, x, it_next, g, j, xn);
+        w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) xv[mt][v] = xn[mt][v];
         dirty = true;
         if (++it == p.items) {  // the span leaves this tile
             stream_flush<ActT, MT>(p, acc_s + slot_t * kRows * 16, yacc, g, j);

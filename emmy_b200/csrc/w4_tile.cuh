@@ -133,11 +133,29 @@ __device__ __forceinline__ void load_x(const ActT* xrow, const int32_t* perm, in
     }
 }
 
-// One item (128 input rows x 16 columns) of a tile against the rows of x: yacc += s * sum_k x_k (q_k - z).
-// wl / wh: the lane's 16 bytes of the item's two nibble tiles; meta: its scale / zero entry (columns g, g+8).
+// The rows of x an item multiplies, as the lane's MMA operands: rows mt * 8 + g, the 32 input positions from
+// it * 128 + 32 * j on.  Rows beyond M read as zeros.
 template <typename ActT, int MT, bool ONE>
-__device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it, const uint4& wl, const uint4& wh, const uint2& mt_,
-                                        int g, int j, float (&yacc)[MT][4]) {
+__device__ __forceinline__ void w4_item_x(const W4Params& p, const ActT* x, int it, int g, int j, uint4 (&xv)[MT][4]) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int m = ONE ? 0 : mt * 8 + g;
+        if (ONE || m < p.M) {
+            const size_t xr = p.x_rows ? static_cast<size_t>(p.x_rows[m]) : static_cast<size_t>(m);
+            load_x<ActT>(x + xr * p.K, p.perm, it * 128 + 32 * j, xv[mt]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[mt][i] = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// One item (128 input rows x 16 columns) of a tile against the rows of x: yacc += s * sum_k x_k (q_k - z).
+// wl / wh: the lane's 16 bytes of the item's two nibble tiles; meta: its scale / zero entry (columns g, g+8);
+// xv: the lane's operands from w4_item_x.
+template <typename ActT, int MT>
+__device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv)[MT][4], const uint4& wl, const uint4& wh, const uint2& mt_,
+                                             float (&yacc)[MT][4]) {
     float s_lo, s_hi;
     if (p.scale_dtype == EQ_F16) {
         const __half2 s = *reinterpret_cast<const __half2*>(&mt_.x);
@@ -150,18 +168,6 @@ __device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it
     const typename Frag<ActT>::Zero z_lo = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x1010));
     const typename Frag<ActT>::Zero z_hi = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x3232));
     const uint32_t words[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
-    uint4 xv[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        const int m = ONE ? 0 : mt * 8 + g;
-        if (ONE || m < p.M) {
-            const size_t xr = p.x_rows ? static_cast<size_t>(p.x_rows[m]) : static_cast<size_t>(m);
-            load_x<ActT>(x + xr * p.K, p.perm, it * 128 + 32 * j, xv[mt]);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) xv[mt][i] = make_uint4(0, 0, 0, 0);
-        }
-    }
     // even and odd k16 steps accumulate into separate registers: two chains of four MMAs instead of one of eight
     float acc[2][MT][4];
 #pragma unroll
@@ -185,6 +191,14 @@ __device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it
         yacc[mt][2] = fmaf(s_hi, acc[0][mt][2] + acc[1][mt][2], yacc[mt][2]);
         yacc[mt][3] = fmaf(s_hi, acc[0][mt][3] + acc[1][mt][3], yacc[mt][3]);
     }
+}
+
+template <typename ActT, int MT, bool ONE>
+__device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it, const uint4& wl, const uint4& wh, const uint2& mt_,
+                                        int g, int j, float (&yacc)[MT][4]) {
+    uint4 xv[MT][4];
+    w4_item_x<ActT, MT, ONE>(p, x, it, g, j, xv);
+    w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
 }
 
 // One output tile (16 columns) x one K split, for a problem (wq, x, y, M).  ONE: a single activation row; every lane

@@ -368,3 +368,27 @@ def test_concatenated_linears_share_one_launch():
         ym = ops.w4a16_linear(act(xm, "f16"), both)
         sep = torch.cat([ops.w4a16_linear(act(xm, "f16"), w) for w in parts], dim=1)
         assert float((ym.float() - sep.float()).abs().max()) <= 2e-3 * float(sep.float().abs().max())
+
+
+def test_workspace_is_left_zero_by_every_path():
+    """One workspace serves calls of different shapes in turn (prefill with scattered act-order groups, which keeps a
+    gathered copy of x in it, then mid-M split-K, then the one-row GEMV, whose hand-over words must start out zero):
+    every call leaves everything behind the header zero and every result matches the oracle."""
+    from emmy_b200 import ops
+
+    k, g = 1024, 128
+    cases = []
+    for n, seed in ((256, 8), (2048, 9)):
+        qw, qz, sc, _ = synth.gptq_linear(k, n, group=g, seed=seed)
+        gi = np.random.default_rng(seed).permutation(np.arange(k) // g).astype(np.int32)
+        cases.append((n, qw, qz, sc, gi, ops.w4_repack(dev(qw), dev(qz), dev(sc), g, "gptq", g_idx=dev(gi))))
+    lib = ops.L.load()
+    size = max(lib.eq_w4a16_workspace_bytes(m, n, k) for m in (1, 8, 40, 333) for n in (256, 2048))
+    ws = torch.zeros(size + 256, dtype=torch.uint8, device="cuda")
+    for m in (333, 40, 1, 8, 333, 1):
+        for n, qw, qz, sc, gi, w in cases:
+            x = synth.activations(m, k, "f16", seed=m + n)
+            y = ops.w4a16_linear(act(x, "f16"), w, workspace=ws)
+            ops.w4a16_status(ws, m, n)
+            assert int(ws[256:].count_nonzero()) == 0, f"M={m} N={n} left the workspace dirty"
+            check_close(y, ol.w4a16_linear(x, qw, qz, sc, g, "gptq", "f16", gi))
