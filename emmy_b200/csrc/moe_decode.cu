@@ -42,64 +42,58 @@ struct MoeDecParams {
     int acc_tiles;
 };
 
-// One warp routes one token: ids ascending, scores renormalised.  (The router of moe.cu; see there.)
+// f32 -> a 32-bit key whose unsigned order is the float order (so that one redux.sync finds a warp's maximum).
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k); }
+
+// One warp routes one token: ids ascending, scores renormalised.  (The router of moe.cu, see there, with the warp-wide
+// argmax done by two redux.sync: the maximum key, then the lowest expert id that holds it.)
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, int E, int topk, int32_t* ids, float* scores) {
     const int lane = threadIdx.x & 31;
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    uint32_t top = 0;
+    for (int e = lane; e < E; e += 32) top = max(top, order_key(lg[e]));
+    const float mx = key_value(__reduce_max_sync(0xFFFFFFFFu, top));
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-    int pick_id[kDecMaxTopK];
-    float pick_p[kDecMaxTopK];
     unsigned long long taken = 0;  // this lane's experts already picked (bit = (e - lane) / 32)
     float psum = 0.f;
+    int my_id = 0x7FFFFFFF;  // lane jj keeps pick jj
+    float my_p = 0.f;
     for (int jj = 0; jj < topk; ++jj) {
-        float best = -INFINITY;
+        uint32_t best = 0;  // below every real key
         int best_e = 0x7FFFFFFF;
         for (int e = lane, b = 0; e < E; e += 32, ++b) {
             if ((taken >> b) & 1ull) continue;
-            const float v = lg[e];
-            if (v > best || (v == best && e < best_e)) {
-                best = v;
+            const uint32_t k = order_key(lg[e]);
+            if (k > best) {  // ascending e: the first of equal values stays
+                best = k;
                 best_e = e;
             }
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, off);
-            const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, off);
-            if (ov > best || (ov == best && oe < best_e)) {
-                best = ov;
-                best_e = oe;
-            }
+        const uint32_t win = __reduce_max_sync(0xFFFFFFFFu, best);
+        const int win_e = static_cast<int>(__reduce_min_sync(0xFFFFFFFFu, static_cast<unsigned>(best == win ? best_e : 0x7FFFFFFF)));
+        if (win_e < E && (win_e & 31) == lane) taken |= 1ull << (win_e >> 5);
+        const float pr = win_e < E ? expf(key_value(win) - mx) / sum : 0.f;
+        if (lane == jj) {
+            my_id = win_e < E ? win_e : E - 1;
+            my_p = pr;
         }
-        if (best_e < E && (best_e & 31) == lane) taken |= 1ull << (best_e >> 5);
-        const float pr = best_e < E ? expf(best - mx) / sum : 0.f;
-        pick_id[jj] = best_e < E ? best_e : E - 1;
-        pick_p[jj] = pr;
         psum += pr;
     }
-    if (lane == 0) {
-        for (int a = 1; a < topk; ++a) {  // ascending expert id: the order the combine adds in
-            const int id = pick_id[a];
-            const float pv = pick_p[a];
-            int b = a - 1;
-            while (b >= 0 && pick_id[b] > id) {
-                pick_id[b + 1] = pick_id[b];
-                pick_p[b + 1] = pick_p[b];
-                --b;
-            }
-            pick_id[b + 1] = id;
-            pick_p[b + 1] = pv;
-        }
-        for (int jj = 0; jj < topk; ++jj) {
-            ids[jj] = pick_id[jj];
-            scores[jj] = pick_p[jj] / psum;
-        }
+    // ascending expert id (the order the combine adds in): a pick's place is the number of picks with a smaller id
+    int place = 0;
+    for (int jj = 0; jj < topk; ++jj) {
+        const int other = __shfl_sync(0xFFFFFFFFu, my_id, jj);
+        place += (other < my_id || (other == my_id && jj < lane)) ? 1 : 0;
+    }
+    if (lane < topk) {
+        ids[place] = my_id;
+        scores[place] = my_p / psum;
     }
 }
 
@@ -120,7 +114,10 @@ __device__ __forceinline__ uint32_t swiglu_pair(uint32_t gate, uint32_t up) {
 
 template <typename ActT, bool SCALE_F16, int DEPTH, int PHASE>
 __global__ void __launch_bounds__(kG1Threads, 2) moe_decode_kernel(const MoeDecParams p) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Phase 1 follows phase 0 as a programmatic dependent.  CTA 0 of phase 0 releases it only once the routing is in
+    // global memory (every other CTA at once), so phase 1 reads the picks and requests its weights while phase 0 still
+    // computes; what phase 0 computes (the gate / up rows) is read behind griddepcontrol.wait.
+    if (PHASE == 1 || blockIdx.x != 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) unsigned char smem_all[];
     __shared__ int32_t ids_s[kDecMaxTokens * kDecMaxTopK];
     __shared__ float scores_s[kDecMaxTokens * kDecMaxTopK];
@@ -129,8 +126,8 @@ __global__ void __launch_bounds__(kG1Threads, 2) moe_decode_kernel(const MoeDecP
     const int items = p.items, tpp = p.tiles_per_pick;
     const int picks = p.T * p.topk;
 
-    // everything this kernel reads but the weights comes from the kernel before it
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // phase 0: everything but the weights comes from the kernel before it (and its weights are chosen by the routing)
+    if (PHASE == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- this CTA's whole tiles [tile0, tile0 + ntiles) of the picks' tile stream
     const int cta = blockIdx.x;
     const int tile0 = cta * p.span_base + min(cta, p.span_rem);
@@ -145,51 +142,55 @@ __global__ void __launch_bounds__(kG1Threads, 2) moe_decode_kernel(const MoeDecP
     float2* xsum = reinterpret_cast<float2*>(xs + 2 * (p.K / 8));  // [2][items]
     for (int i = threadIdx.x; i < acc_words; i += kG1Threads) acc_s[i] = 0.f;
 
-    // ---- the routing (phase 0: the first T warps, one token each) and the activation row(s) of the span's picks, which
-    //      depend on the pick index only, not on the routing: the other warps stage them meanwhile
+    // The activation row(s) of the span's picks depend on the pick index only, not on the routing.
+    auto stage_rows = [&](int first_warp) {
+        const int n_vec = p.K / 8;
+        const int rows = second_from < ntiles ? 2 : 1;
+        const int stagers = (kG1Warps - first_warp) * 32;
+        if (warp < first_warp) return;
+        for (int r = 0; r < rows; ++r) {
+            const int pick = pick0 + r;
+            for (int v = threadIdx.x - first_warp * 32; v < ((n_vec + 31) & ~31); v += stagers) {  // whole warps: the sums shuffle
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (v < n_vec) {
+                    if (PHASE == 0) {
+                        val = __ldg(reinterpret_cast<const uint4*>(static_cast<const ActT*>(p.x) + static_cast<size_t>(pick / p.topk) * p.K) + v);
+                    } else {
+                        const uint4* gu = reinterpret_cast<const uint4*>(static_cast<const ActT*>(p.x) + static_cast<size_t>(pick) * 2 * p.K);
+                        const uint4 gate = __ldcg(gu + v), up = __ldcg(gu + n_vec + v);
+                        val = make_uint4(swiglu_pair<ActT>(gate.x, up.x), swiglu_pair<ActT>(gate.y, up.y), swiglu_pair<ActT>(gate.z, up.z),
+                                         swiglu_pair<ActT>(gate.w, up.w));
+                    }
+                }
+                stage_vector<ActT>(val, v, v < n_vec, xs + r * n_vec, xsum + r * items);
+            }
+        }
+    };
+
     if (PHASE == 0) {
+        // the routing (the first T warps, one token each); the other warps stage the rows meanwhile
         if (warp < p.T) route_token(p.logits + static_cast<size_t>(warp) * p.E, p.E, p.topk, ids_s + warp * p.topk, scores_s + warp * p.topk);
         // this launch also leaves the arrival counters of phase 1 and the status word zero
         for (int i = blockIdx.x * kG1Threads + threadIdx.x; i < p.T * (p.K / 16); i += gridDim.x * kG1Threads) p.tile_count[i] = 0;
         if (blockIdx.x == 0 && threadIdx.x == 0) *p.status = 0;
+        stage_rows(p.T < kG1Warps ? p.T : 0);
+        __syncthreads();
+        if (blockIdx.x == 0) {
+            for (int i = threadIdx.x; i < picks; i += kG1Threads) {
+                p.ids[i] = ids_s[i];
+                p.scores[i] = scores_s[i];
+            }
+            __threadfence();  // the routing is in global memory ...
+            __syncthreads();
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // ... before phase 1 may start
+        }
     } else {
         for (int i = threadIdx.x; i < picks; i += kG1Threads) {
-            ids_s[i] = p.ids[i];
-            scores_s[i] = p.scores[i];
+            ids_s[i] = __ldcg(p.ids + i);
+            scores_s[i] = __ldcg(p.scores + i);
         }
+        __syncthreads();
     }
-    {
-        const int n_vec = p.K / 8;
-        const int rows = second_from < ntiles ? 2 : 1;
-        // phase 0 with few tokens: the routing warps join late, so the staging is spread over the other warps only
-        const int first_warp = (PHASE == 0 && p.T < kG1Warps) ? p.T : 0;
-        const int stagers = (kG1Warps - first_warp) * 32;
-        if (warp >= first_warp) {
-            for (int r = 0; r < rows; ++r) {
-                const int pick = pick0 + r;
-                for (int v = threadIdx.x - first_warp * 32; v < ((n_vec + 31) & ~31); v += stagers) {  // whole warps: the sums shuffle
-                    uint4 val = make_uint4(0, 0, 0, 0);
-                    if (v < n_vec) {
-                        if (PHASE == 0) {
-                            val = __ldg(reinterpret_cast<const uint4*>(static_cast<const ActT*>(p.x) + static_cast<size_t>(pick / p.topk) * p.K) + v);
-                        } else {
-                            const uint4* gu = reinterpret_cast<const uint4*>(static_cast<const ActT*>(p.x) + static_cast<size_t>(pick) * 2 * p.K);
-                            const uint4 gate = __ldcg(gu + v), up = __ldcg(gu + n_vec + v);
-                            val = make_uint4(swiglu_pair<ActT>(gate.x, up.x), swiglu_pair<ActT>(gate.y, up.y), swiglu_pair<ActT>(gate.z, up.z),
-                                             swiglu_pair<ActT>(gate.w, up.w));
-                        }
-                    }
-                    stage_vector<ActT>(val, v, v < n_vec, xs + r * n_vec, xsum + r * items);
-                }
-            }
-        }
-    }
-    __syncthreads();
-    if (PHASE == 0 && blockIdx.x == 0)
-        for (int i = threadIdx.x; i < picks; i += kG1Threads) {
-            p.ids[i] = ids_s[i];
-            p.scores[i] = scores_s[i];
-        }
 
     // ---- this warp's items: an equal contiguous share of the CTA's ntiles * items
     const int cta_items = ntiles * items;
@@ -232,6 +233,15 @@ __global__ void __launch_bounds__(kG1Threads, 2) moe_decode_kernel(const MoeDecP
     };
 #pragma unroll 1
     for (int d = 0; d < DEPTH; ++d) issue(d * kG1Slot);
+
+    if (PHASE == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // the picks the weights were requested for are the picks phase 0 ended with: anything else is reported
+        for (int i = threadIdx.x; i < picks; i += kG1Threads)
+            if (__ldcg(p.ids + i) != ids_s[i]) atomicExch(p.status, 5);
+        stage_rows(0);
+        __syncthreads();
+    }
 
     float y_lo = 0.f, y_hi = 0.f;
     int i = 0;

@@ -8,6 +8,11 @@
 // sums into the CTA's shared accumulators.  One __syncthreads at the end, then the CTA converts and stores the tiles
 // it owns.  No global atomics, no fences, no workspace: measured on B200, the f32 workspace hand-over of an earlier
 // form of this kernel (atomic adds, fence, arrival counter) cost 4.6 us of a 10.4 us launch, the stream itself 5.8.
+//
+// Every item multiplies the same M rows of x, 4 KB per item at M = 16: read from global memory that is 117 MB per
+// launch through L1 / L2 against 29 MB of weights, and it bounded the launch.  Where M x K fits beside the ring
+// (STAGED) the CTA copies x once into shared memory in the order the MMA operands are read (conflict-free 16-byte
+// reads); otherwise the rows are read from global memory, one item ahead of the weights where registers allow.
 #include "w4_tile.cuh"
 
 namespace eq {
@@ -30,8 +35,11 @@ __device__ __forceinline__ void stream_flush(const W4Params& p, float* acc_slot,
     }
 }
 
-// DEPTH: items in flight per warp.
-template <typename ActT, int MT, int DEPTH>
+// Shared-memory bytes of the staged x: [item][row block of 8][16-byte chunk 0..3][lane][16 B].
+static size_t staged_x_bytes(int64_t K, int rows) { return static_cast<size_t>(K / 128) * (rows / 8) * 2048; }
+
+// DEPTH: items in flight per warp.  STAGED: x lives in shared memory.
+template <typename ActT, int MT, int DEPTH, bool STAGED>
 __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(const W4Params p) {
     constexpr int kStreamDepth = DEPTH;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -83,10 +91,30 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) yacc[mt][0] = yacc[mt][1] = yacc[mt][2] = yacc[mt][3] = 0.f;
     bool dirty = false;
-    // the rows of x run one item ahead of the weights in registers: they come from L1 / L2, and with four warps per
-    // scheduler nothing else would cover that latency
+    const unsigned char* xs = smem_all + kStreamWarps * kStreamDepth * kSlot + static_cast<size_t>(p.acc_tiles) * kRows * 16 * sizeof(float);
+    if (STAGED) {
+        // one warp per (item, row block): lane (g, j) copies the 64 bytes it will read as MMA operands, 16 at a time
+        unsigned char* xw = const_cast<unsigned char*>(xs);
+        for (int b = warp; b < p.items * MT; b += kStreamWarps) {
+            const int bi = b / MT, mt = b - bi * MT;
+            const int m = mt * 8 + g;
+            uint4 v[4];
+            if (m < p.M) {
+                load_x<ActT>(x + static_cast<size_t>(m) * p.K, p.perm, bi * 128 + 32 * j, v);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(xw + (static_cast<size_t>(b) * 4 + c) * 512 + lane * 16) = v[c];
+        }
+        __syncthreads();
+    }
+    // Unstaged with one row block: the rows of x run one item ahead of the weights in registers (they come from L1 /
+    // L2, and with four warps per scheduler nothing else would cover that latency); two row blocks would spill.
+    constexpr bool kAhead = !STAGED && MT == 1;
     uint4 xv[MT][4];
-    if (n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
+    if (kAhead && n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
 
     for (int i = 0; i < n; ++i) {
         const int d = i % kStreamDepth;
@@ -98,14 +126,26 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
         const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
         __syncwarp();  // every lane has read the slot before any lane refills it
         issue(d, i + kStreamDepth);  // the slot's bytes are in registers: refill it
-        uint4 xn[MT][4];
-        const int it_next = it + 1 == p.items ? 0 : it + 1;
-        if (i + 1 < n) w4_item_x<ActT, MT, false>(p, x, it_next, g, j, xn);
-        w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+        if (STAGED) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-            for (int v = 0; v < 4; ++v) xv[mt][v] = xn[mt][v];
+                for (int c = 0; c < 4; ++c)
+                    xv[mt][c] = *reinterpret_cast<const uint4*>(xs + (static_cast<size_t>(it * MT + mt) * 4 + c) * 512 + lane * 16);
+            w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+        } else if (kAhead) {
+            uint4 xn[MT][4];
+            const int it_next = it + 1 == p.items ? 0 : it + 1;
+            if (i + 1 < n) w4_item_x<ActT, MT, false>(p, x, it_next, g, j, xn);
+            w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) xv[mt][v] = xn[mt][v];
+        } else {
+            w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
+            w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+        }
         dirty = true;
         if (++it == p.items) {  // the span leaves this tile
             stream_flush<ActT, MT>(p, acc_s + slot_t * kRows * 16, yacc, g, j);
@@ -126,16 +166,17 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     }
 }
 
-// Shared memory the stream kernel needs for `tiles` column tiles on `ctas` CTAs, or 0 when it does not fit.
-static size_t stream_smem(long long tiles, long long ctas, int rows, int depth) {
+// Shared memory the stream kernel needs for `tiles` column tiles on `ctas` CTAs (plus the staged x when asked for), or
+// 0 when it does not fit.
+static size_t stream_smem(long long tiles, long long ctas, int rows, int depth, size_t staged) {
     const long long per_cta = ceil_div(tiles, ctas);
-    const size_t bytes = static_cast<size_t>(kStreamWarps) * depth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float);
+    const size_t bytes = static_cast<size_t>(kStreamWarps) * depth * kSlot + static_cast<size_t>(per_cta) * rows * 16 * sizeof(float) + staged;
     return bytes <= 220 * 1024 ? bytes : 0;
 }
 
-template <typename ActT, int MT, int DEPTH>
+template <typename ActT, int MT, int DEPTH, bool STAGED>
 static int launch_stream_depth(W4Params p, size_t smem, long long ctas, cudaStream_t stream) {
-    auto kernel = w4a16_stream_kernel<ActT, MT, DEPTH>;
+    auto kernel = w4a16_stream_kernel<ActT, MT, DEPTH, STAGED>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
@@ -158,11 +199,19 @@ static int launch_stream(W4Params p, cudaStream_t stream, bool* fits) {
     if (ctas > tiles) ctas = tiles;
     p.span_base = static_cast<int>(tiles / ctas);
     p.span_rem = static_cast<int>(tiles % ctas);
+    p.acc_tiles = static_cast<int>(ceil_div(tiles, ctas));
     const int rows = MT * 8;
     *fits = true;
+    // x in shared memory where it fits beside a ring of at least three items (gathered rows are read in place)
+    const size_t staged = p.x_rows ? 0 : staged_x_bytes(p.K, rows);
+    if (staged) {
+        if (const size_t smem = stream_smem(tiles, ctas, rows, 6, staged)) return launch_stream_depth<ActT, MT, 6, true>(p, smem, ctas, stream);
+        if (const size_t smem = stream_smem(tiles, ctas, rows, 4, staged)) return launch_stream_depth<ActT, MT, 4, true>(p, smem, ctas, stream);
+        if (const size_t smem = stream_smem(tiles, ctas, rows, 3, staged)) return launch_stream_depth<ActT, MT, 3, true>(p, smem, ctas, stream);
+    }
     // the deepest ring that fits
-    if (const size_t smem = stream_smem(tiles, ctas, rows, 6)) return launch_stream_depth<ActT, MT, 6>(p, smem, ctas, stream);
-    if (const size_t smem = stream_smem(tiles, ctas, rows, 4)) return launch_stream_depth<ActT, MT, 4>(p, smem, ctas, stream);
+    if (const size_t smem = stream_smem(tiles, ctas, rows, 6, 0)) return launch_stream_depth<ActT, MT, 6, false>(p, smem, ctas, stream);
+    if (const size_t smem = stream_smem(tiles, ctas, rows, 4, 0)) return launch_stream_depth<ActT, MT, 4, false>(p, smem, ctas, stream);
     *fits = false;  // the accumulators of the CTA's tiles do not fit shared memory
     return EQ_OK;
 }

@@ -22,7 +22,8 @@ struct W4Params {
     int items;                // K / 128
     int splits;               // K splits per tile
     int scale_dtype;
-    int span_base, span_rem;  // stream kernel: items per warp, plus one for the first span_rem warps
+    int span_base, span_rem;  // stream kernel: whole tiles per CTA, plus one for the first span_rem CTAs
+    int acc_tiles;            // stream kernel: accumulator slots per CTA (the largest tile count)
     const int32_t* x_rows;    // optional: activation row m of the problem is row x_rows[m] of x (gather)
     const int32_t* y_rows;    // optional: output row m of the problem is row y_rows[m] of y (scatter)
     const uint64_t* y_ptrs;   // optional (unsplit tiles only): output row m starts at address y_ptrs[m], possibly on a peer GPU
