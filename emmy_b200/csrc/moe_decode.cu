@@ -319,17 +319,9 @@ static size_t dec_smem(int depth, int acc_tiles, int K) {
            static_cast<size_t>((acc_tiles + 3) & ~3) * sizeof(int) + 2 * (static_cast<size_t>(K) * 2 + static_cast<size_t>(K / 128) * sizeof(float2));
 }
 
-template <typename ActT, bool SCALE_F16, int PHASE>
-static int launch_phase(MoeDecParams p, cudaStream_t stream) {
-    constexpr int kDepth = 4;
-    const long long tiles = static_cast<long long>(p.T) * p.topk * p.tiles_per_pick;
-    long long ctas = sm_count();
-    if (ctas > tiles) ctas = tiles;
-    p.span_base = static_cast<int>(tiles / ctas);
-    p.span_rem = static_cast<int>(tiles % ctas);
-    p.acc_tiles = p.span_base + 1;
-    const size_t smem = dec_smem(kDepth, p.acc_tiles, p.K);
-    auto kernel = moe_decode_kernel<ActT, SCALE_F16, kDepth, PHASE>;
+template <typename ActT, bool SCALE_F16, int PHASE, int DEPTH>
+static int launch_phase_depth(const MoeDecParams& p, size_t smem, long long ctas, cudaStream_t stream) {
+    auto kernel = moe_decode_kernel<ActT, SCALE_F16, DEPTH, PHASE>;
     static bool configured[64] = {};
     int dev = 0;
     EQ_CUDA_OK(cudaGetDevice(&dev));
@@ -350,6 +342,22 @@ static int launch_phase(MoeDecParams p, cudaStream_t stream) {
     cfg.numAttrs = 1;
     EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, p));
     return EQ_OK;
+}
+
+template <typename ActT, bool SCALE_F16, int PHASE>
+static int launch_phase(MoeDecParams p, cudaStream_t stream) {
+    const long long tiles = static_cast<long long>(p.T) * p.topk * p.tiles_per_pick;
+    long long ctas = sm_count();
+    if (ctas > tiles) ctas = tiles;
+    p.span_base = static_cast<int>(tiles / ctas);
+    p.span_rem = static_cast<int>(tiles % ctas);
+    p.acc_tiles = p.span_base + 1;
+    // a warp's share of the CTA's items decides the ring: five slots where that covers more of it and still leaves
+    // room for a second CTA on the SM, else four
+    const long long per_warp = ceil_div(static_cast<long long>(p.acc_tiles) * p.items, kG1Warps);
+    const size_t smem5 = dec_smem(5, p.acc_tiles, p.K);
+    if (per_warp > 4 && smem5 <= 112 * 1024) return launch_phase_depth<ActT, SCALE_F16, PHASE, 5>(p, smem5, ctas, stream);
+    return launch_phase_depth<ActT, SCALE_F16, PHASE, 4>(p, dec_smem(4, p.acc_tiles, p.K), ctas, stream);
 }
 
 // Whether the decode tier serves this layer: few tokens, every CTA's tiles inside two picks, everything in 112 KB.

@@ -87,6 +87,9 @@ __global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int
                                        uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_tiled,
                                        int* __restrict__ status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // launched as a programmatic dependent itself when it runs inside the linear: the kernel before it (usually the
+    // previous linear on this workspace) still reads the codes and the status word this one rewrites
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t blocks16 = K / 16;
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (status && idx == 0) *status = 0;
@@ -336,6 +339,149 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
 }
 
+// ------------------------------------------------------------------------------------------------ decode tile (M <= 16)
+// With a handful of rows the operands swap roles: a 128-channel tile of the WEIGHT is the MMA's A operand (M = 128) and
+// the activation rows are B (N = 16), so a K step stages 16 KB of weight codes + 2 KB of activation codes + 2 x 2 KB of
+// scale atoms instead of a 16 KB activation tile that is all zeros but its first rows.  Five stages are 110 KB: two
+// CTAs fit an SM, and they belong to consecutive launches (programmatic dependent launch: the later one requests its
+// weights while the earlier one computes; measured on B200, a launch that streams this matrix alone takes 10.4 us, of
+// which 3.5 us are the launch boundary).  The accumulator is [channel (TMEM lane)][row (column)], 16 columns.
+constexpr int kDecStages = 5;
+constexpr int kDecTileW = 128 * kBKBytes, kDecTileX = 16 * kBKBytes, kDecSf = 4 * 512;
+constexpr int kDecStageBytes = kDecTileW + kDecTileX + 2 * kDecSf;
+constexpr size_t kDecSmem = static_cast<size_t>(kDecStages) * kDecStageBytes + 1024 + 256;
+constexpr uint32_t kDecTmemCols = 64;  // 16 accumulator columns, 16 + 16 scale columns
+
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+    nvfp4_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        const uint8_t* __restrict__ sfw, const uint8_t* __restrict__ sfx, const float* __restrict__ gx,
+                        const float* __restrict__ gw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_w = smem;
+    unsigned char* tiles_x = tiles_w + kDecStages * kDecTileW;
+    unsigned char* sfs_w = tiles_x + kDecStages * kDecTileX;
+    unsigned char* sfs_x = sfs_w + kDecStages * kDecSf;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sfs_x + kDecStages * kDecSf);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kDecStages;
+    uint64_t* acc_ready = bars + 2 * kDecStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kDecStages + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 128;
+    const int k_blocks = K / 256, k64_blocks = K / 64;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDecStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kDecTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_sfw = tmem_base + 16, tmem_sfx = tmem_base + 32;  // 4 columns per k64 step each
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_w);
+            tc::tma_prefetch_desc(&map_x);
+            const int rb_w = n0 / 128;
+            auto weights = [&](int kb, int s, uint32_t bar) {
+                tc::mbar_expect_tx(bar, kDecStageBytes);
+                tc::tma_load_2d(tc::smem_u32(tiles_w + s * kDecTileW), &map_w, kb * kBKBytes, n0, bar);
+                bulk_g2s(tc::smem_u32(sfs_w + s * kDecSf), sfw + (static_cast<size_t>(rb_w) * k64_blocks + kb * 4) * 512, kDecSf, bar);
+            };
+            auto codes = [&](int kb, int s, uint32_t bar) {
+                tc::tma_load_2d(tc::smem_u32(tiles_x + s * kDecTileX), &map_x, kb * kBKBytes, 0, bar);
+                bulk_g2s(tc::smem_u32(sfs_x + s * kDecSf), sfx + static_cast<size_t>(kb) * 4 * 512, kDecSf, bar);
+            };
+            // the weights never depend on the kernel before (the activation quantize): request them ahead of the wait
+            const int ahead = k_blocks < kDecStages ? k_blocks : kDecStages;
+            for (int kb = 0; kb < ahead; ++kb) weights(kb, kb, tc::smem_u32(full + kb));
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int kb = 0; kb < ahead; ++kb) codes(kb, kb, tc::smem_u32(full + kb));
+            for (int kb = ahead; kb < k_blocks; ++kb) {
+                const int s = kb % kDecStages;
+                if (!tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kDecStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                weights(kb, s, bar);
+                codes(kb, s, bar);
+            }
+        }
+    } else if (warp == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // bounded waits count from the moment the codes exist
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc_nvfp4(128, 16, 0, 0);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kDecStages;
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kDecStages) & 1)) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t w_addr = tc::smem_u32(tiles_w + s * kDecTileW), x_addr = tc::smem_u32(tiles_x + s * kDecTileX);
+                const uint32_t sfw_addr = tc::smem_u32(sfs_w + s * kDecSf), sfx_addr = tc::smem_u32(sfs_x + s * kDecSf);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfw + ks * 4, tc::smem_desc_sf(sfw_addr + ks * 512));
+                    tc::tmem_cp_32x128b_warpx4(tmem_sfx + ks * 4, tc::smem_desc_sf(sfx_addr + ks * 512));
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t da = tc::smem_desc_k_sw128(w_addr + ks * 32), db = tc::smem_desc_k_sw128(x_addr + ks * 32);
+                    tc::mma_mxf4nvf4(tmem_base, da, db, idesc, tmem_sfw + ks * 4, tmem_sfx + ks * 4, kb > 0 || ks > 0);
+                }
+                tc::mma_commit(tc::smem_u32(empty + s));
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));
+        }
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;  // this thread's output channel
+        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok) {
+            const float g = gx[0] * gw[0];
+            uint32_t r[16];
+            tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), r);
+            tc::tmem_ld_wait();
+            if (n < N) {
+#pragma unroll
+                for (int m = 0; m < 16; ++m)
+                    if (m < M) y[static_cast<size_t>(m) * N + n] = from_float<OutT>(__uint_as_float(r[m]) * g);
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, kDecTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ prefill tile 256 x 224
 // Two 128-row accumulators share one 224-column B tile: 448 accumulator columns + 32 (A scales) + 32 (B scales) fill
 // TMEM exactly, and a K step moves 68 KB for 256 x 224 x 256 products where the 128 x 256 tile moved 54 KB for 128 x 256
@@ -578,14 +724,21 @@ static int quant_nvfp4_act(const void* x, int64_t M, int64_t K, int in_dtype, co
     EQ_REQUIRE(aligned(codes, 8), EQ_ERR_BAD_ALIGN, "eq_quant_nvfp4_act: codes must be 8-byte aligned");
     if (scale_tiled && pad_rows) EQ_CUDA_OK(cudaMemsetAsync(scale_tiled, 0, sf_tiled_bytes(M, K), stream));
     const int64_t total = M * (K / 16);
-    const unsigned grid = static_cast<unsigned>(ceil_div(total, 128));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(total, 128)));
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = status ? 1 : 0;  // inside the linear: resident, and past its launch latency, when the kernel before it ends
     switch (in_dtype) {
-        case EQ_F16: quant_nvfp4_act_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
-        case EQ_BF16: quant_nvfp4_act_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
-        case EQ_F32: quant_nvfp4_act_kernel<float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status); break;
+        case EQ_F16: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_nvfp4_act_kernel<__half>, static_cast<const __half*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status)); break;
+        case EQ_BF16: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_nvfp4_act_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status)); break;
+        case EQ_F32: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_nvfp4_act_kernel<float>, static_cast<const float*>(x), M, K, input_scale, codes, scale_bits, scale_tiled, status)); break;
         default: return fail(EQ_ERR_BAD_ARG, "eq_quant_nvfp4_act: unknown dtype %d", in_dtype);
     }
-    EQ_LAUNCH_OK("quant_nvfp4_act_kernel");
     return EQ_OK;
 }
 
@@ -618,6 +771,33 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     int st = quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, false, status, stream);
     if (st != EQ_OK) return st;
     CUtensorMap map_a, map_b;
+    if (M <= 16) {
+        // decode-shaped: weight tiles as the MMA's A operand, the rows as B
+        st = make_tensor_map_2d(&map_a, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, 128, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != EQ_OK) return st;
+        st = make_tensor_map_2d(&map_b, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, 16, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != EQ_OK) return st;
+        auto run = [&](auto kernel, auto* yt) -> int {
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDecSmem)));
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(N, 128)));
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = kDecSmem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            const uint8_t* sfx = sfa;
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, weight_scale_tiled, sfx, input_scale, weight_scale_2, yt, static_cast<int>(M),
+                                          static_cast<int>(N), static_cast<int>(K), status));
+            return EQ_OK;
+        };
+        return act_dtype == EQ_F16 ? run(nvfp4_decode_kernel<__half>, static_cast<__half*>(y))
+                                   : run(nvfp4_decode_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16*>(y));
+    }
     // codes are bytes holding two e2m1 values: the maps move bytes; 128 bytes = 256 elements of K per tile row
     st = make_tensor_map_2d(&map_a, codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K / 2, K / 2, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
@@ -632,6 +812,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
         dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
         auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
             EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = grid;
             cfg.blockDim = dim3(kGemmThreads);
