@@ -385,8 +385,61 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         // Work units: (128-row half, 32-column chunk of the output), dealt round-robin to the warp quartets.  Everything
         // that decides whether a unit runs is warp-uniform: the TMEM loads are warp-wide instructions.
         constexpr int kChunks = (MODE == kGroupedSwiGLU ? BN / 2 : BN) / 32;
+        // Rows that leave for their own addresses (possibly on a peer GPU): a thread's 64 bytes of its own row would make
+        // every warp-wide store 32 separate 16-byte pieces, which NVLink carries at a fraction of its rate (measured: the
+        // expert-parallel down projection took 480 us against 195 us with local stores).  The warp turns its 32 rows x 64
+        // columns in shared memory (the stages are idle once the accumulator is complete) and stores 128 contiguous bytes
+        // of one row with every eight lanes.
+        bool turned = false;
+        if constexpr (MODE == kGrouped) turned = N % 64 == 0;  // scattered local rows (y_rows) gain from whole lines too
+        if (turned) {
+            constexpr int kChunks64 = BN / 64;
+            unsigned char* stg = smem + dw * 4096;  // [32 rows][8 x 16 B], chunk v of row r at v ^ (r & 7)
+            const uint32_t stg_w = tc::smem_u32(stg) + lane * 128;
 #pragma unroll 1
-        for (int unit = quartet; ok && unit < HALVES * kChunks; unit += Cfg::kQuartets) {
+            for (int unit = quartet; ok && unit < HALVES * kChunks64; unit += Cfg::kQuartets) {
+                const int half = unit / kChunks64, c = (unit - half * kChunks64) * 64;
+                if (half >= live_halves) break;
+                const int row0 = m0 + half * 128 + quarter * 32;
+                const int m = row0 + lane;
+                uint64_t mine = 0ull;  // lane r holds row r's destination
+                if (m < m_end)
+                    mine = grp.y_ptrs ? grp.y_ptrs[m]
+                                      : reinterpret_cast<uint64_t>(y + (grp.y_rows ? static_cast<size_t>(grp.y_rows[m]) : static_cast<size_t>(m)) * N);
+                const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN;
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32(t_row + c + 32 * part, r);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const ActT o0 = from_float<ActT>(__uint_as_float(r[8 * v + 2 * i])), o1 = from_float<ActT>(__uint_as_float(r[8 * v + 2 * i + 1]));
+                            pk[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) |
+                                    (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                        }
+                        const uint32_t at = stg_w + (((4 * part + v) ^ (lane & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+                    }
+                }
+                __syncwarp();
+                const int v = lane & 7;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const uint64_t dst = __shfl_sync(0xFFFFFFFFu, mine, rr);
+                    const uint4 val = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((v ^ (rr & 7)) << 4));
+                    if (dst != 0ull && n0 + c + 8 * v < N)
+                        *reinterpret_cast<uint4*>(dst + static_cast<size_t>(n0 + c + 8 * v) * sizeof(ActT)) = val;
+                }
+                __syncwarp();
+            }
+        }
+#pragma unroll 1
+        for (int unit = quartet; ok && !turned && unit < HALVES * kChunks; unit += Cfg::kQuartets) {
             const int half = unit / kChunks, c = (unit - half * kChunks) * 32;
             if (half >= live_halves) break;
             const int m = m0 + half * 128 + quarter * 32 + lane;
