@@ -55,6 +55,7 @@ STEP_BYTES = LAYERS * sum(algorithmic_bytes(k, n) for k, n in SHAPES.values())
 
 # dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of the captured launches of
 # this workload) from the ncu capture summarised in profiles/w4a16_gemv1_kernel_gptq_m1.md
+EP_CHUNKS = int(os.environ.get("EQ_BENCH_EP_CHUNKS", "2"))  # slices of the expert-parallel MoE record (1 = unsliced)
 GEMV_KERNEL = "w4a16_gemv1_kernel<__half, true, DEPTH>"
 TRAFFIC_PER_LAUNCH = 31242000
 
@@ -348,7 +349,8 @@ def wl_fp8_block(device, rank, m, n=GEMM_N, k=GEMM_K):
             ops.fp8_block_linear(x, w, s, workspace=wsp, out=y)
 
     return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + (n // 128) * (k // 128) * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n,
-                peak_mult=2.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, kernel="fp8_block_gemm_kernel<__nv_bfloat16>",
+                peak_mult=2.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.fp8_block_status(wsp, m, k),
+                kernel="fp8_decode_kernel<__nv_bfloat16, MT, true>" if m <= 16 else "fp8_block_tc_kernel<__nv_bfloat16>",
                 dtype="e4m3 weights (128 x 128 block scales) and activations (per token, per 128 of K), f32 accumulate, bf16 out")
 
 
@@ -454,7 +456,9 @@ def wl_moe(device, rank, world, t, exchange="peer"):
         status = lambda: None
         capture = False
     else:
-        ep = shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device)
+        # large batches go in two slices on two streams, so that one slice's exchange runs under the other's GEMMs
+        ep = (shard.EpMoePipelined(None, t, topk, hidden, inter, local_e, torch.bfloat16, device, chunks=EP_CHUNKS) if t >= 2048 and EP_CHUNKS > 1
+              else shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device))
 
         def step():
             ids, scores = om.moe_route(logits, topk)

@@ -18,6 +18,12 @@
 
 namespace eq {
 
+int fp8_block_decode_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, int act_dtype,
+                            void* y, cudaStream_t stream);  // fp8_linear.cu
+int fp8_block_tc_launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, void* y, int64_t M, int64_t N, int64_t K,
+                        int act_dtype, int* status, cudaStream_t stream);  // fp8_block_tc.cu
+
+
 __device__ __forceinline__ uint16_t e4m3x2_sat(float lo, float hi) {
     uint16_t r;
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
@@ -27,7 +33,9 @@ __device__ __forceinline__ uint16_t e4m3x2_sat(float lo, float hi) {
 // One warp per (row, 128-element group); K % 128 == 0.
 template <typename InT>
 __global__ void __launch_bounds__(256) quant_fp8_groups_kernel(const InT* __restrict__ x, int64_t M, int64_t K, uint8_t* __restrict__ q,
-                                                               float* __restrict__ scale) {
+                                                               float* __restrict__ scale, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the linear behind this may start fetching weights
+    if (status && blockIdx.x == 0 && threadIdx.x == 0) *status = 0;  // the linear's status word, cleared on the way
     const int64_t groups = K / 128;
     const int64_t gw = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -184,8 +192,7 @@ static size_t blk_align(size_t v) { return (v + 255) / 256 * 256; }
 
 using namespace eq;
 
-extern "C" int eq_quant_fp8_per_group(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream_) {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+static int quant_fp8_groups(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, int* status, cudaStream_t stream) {
     EQ_REQUIRE(M >= 0 && K > 0, EQ_ERR_BAD_ARG, "eq_quant_fp8_per_group: bad extents M=%lld K=%lld", (long long)M, (long long)K);
     if (M == 0) return EQ_OK;
     EQ_REQUIRE(x && q && scale, EQ_ERR_BAD_ARG, "eq_quant_fp8_per_group: null pointer");
@@ -194,18 +201,22 @@ extern "C" int eq_quant_fp8_per_group(const void* x, int64_t M, int64_t K, int i
     const int64_t warps = M * (K / 128);
     const unsigned grid = static_cast<unsigned>(ceil_div(warps * 32, 256));
     switch (in_dtype) {
-        case EQ_F16: quant_fp8_groups_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), M, K, q, scale); break;
-        case EQ_BF16: quant_fp8_groups_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, q, scale); break;
-        case EQ_F32: quant_fp8_groups_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), M, K, q, scale); break;
+        case EQ_F16: quant_fp8_groups_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), M, K, q, scale, status); break;
+        case EQ_BF16: quant_fp8_groups_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, q, scale, status); break;
+        case EQ_F32: quant_fp8_groups_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), M, K, q, scale, status); break;
         default: return fail(EQ_ERR_BAD_ARG, "eq_quant_fp8_per_group: unknown dtype %d", in_dtype);
     }
     EQ_LAUNCH_OK("quant_fp8_groups_kernel");
     return EQ_OK;
 }
 
+extern "C" int eq_quant_fp8_per_group(const void* x, int64_t M, int64_t K, int in_dtype, uint8_t* q, float* scale, void* stream_) {
+    return quant_fp8_groups(x, M, K, in_dtype, q, scale, nullptr, static_cast<cudaStream_t>(stream_));
+}
+
 extern "C" size_t eq_fp8_block_workspace_bytes(int64_t M, int64_t K) {
     if (M <= 0 || K <= 0) return 0;
-    return blk_align(static_cast<size_t>(M) * K) + blk_align(static_cast<size_t>(M) * (K / 128) * sizeof(float));
+    return blk_align(static_cast<size_t>(M) * K) + blk_align(static_cast<size_t>(M) * (K / 128) * sizeof(float)) + 256;  // codes, scales, status
 }
 
 extern "C" int eq_fp8_block_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
@@ -223,8 +234,13 @@ extern "C" int eq_fp8_block_linear(const uint8_t* weight, const float* weight_sc
                "eq_fp8_block_linear: workspace of %zu bytes (256-byte aligned) needed, %zu given", eq_fp8_block_workspace_bytes(M, K), workspace_bytes);
     uint8_t* qx = static_cast<uint8_t*>(workspace);
     float* sx = reinterpret_cast<float*>(qx + blk_align(static_cast<size_t>(M) * K));
-    int st = eq_quant_fp8_per_group(x, M, K, act_dtype, qx, sx, stream_);
+    int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + blk_align(static_cast<size_t>(M) * (K / 128) * sizeof(float)));
+    int st = quant_fp8_groups(x, M, K, act_dtype, qx, sx, status, stream);
     if (st != EQ_OK) return st;
+    // decode-shaped calls stream the weight through the bandwidth kernel of the per-channel form, with per-block promotion
+    if (M <= 16) return fp8_block_decode_launch(weight, weight_scale, N, K, qx, sx, M, act_dtype, y, stream);
+    // everything else runs on the tensor cores (fp8_block_tc.cu); the mma.sync tile kernel below serves an unaligned y
+    if (aligned(y, 16)) return fp8_block_tc_launch(qx, sx, weight, weight_scale, y, M, N, K, act_dtype, status, stream);
     const dim3 grid(static_cast<unsigned>(N / kBB), static_cast<unsigned>(ceil_div(M, kBB)));
     const size_t smem = 2 * kBlkStage;
     if (act_dtype == EQ_F16) {
@@ -237,5 +253,17 @@ extern "C" int eq_fp8_block_linear(const uint8_t* weight, const float* weight_sc
                                                                                   static_cast<int>(M), static_cast<int>(N), static_cast<int>(K));
     }
     EQ_LAUNCH_OK("fp8_block_gemm_kernel");
+    return EQ_OK;
+}
+
+extern "C" int eq_fp8_block_status(const void* workspace, int64_t M, int64_t K, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(workspace && M > 0 && K > 0, EQ_ERR_BAD_ARG, "eq_fp8_block_status: bad arguments");
+    const unsigned char* base = static_cast<const unsigned char*>(workspace);
+    const int* status = reinterpret_cast<const int*>(base + blk_align(static_cast<size_t>(M) * K) + blk_align(static_cast<size_t>(M) * (K / 128) * sizeof(float)));
+    int host = 0;
+    EQ_CUDA_OK(cudaMemcpyAsync(&host, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_fp8_block_status: a bounded pipeline wait ran out (code %d)", host);
     return EQ_OK;
 }

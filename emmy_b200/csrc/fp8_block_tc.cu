@@ -1,0 +1,191 @@
+// Block-scaled FP8 W8A8 linear on the 5th-generation tensor cores (M > 16).
+//
+//     y[m, n] = sum_kb ( sum_{k in kb} q_x[m, k] q_w[n, k] ) * s_x[m, kb] * s_w[n / 128, kb]
+//
+// kind::f8f6f4 accumulates in tensor memory over as many K steps as it is told to, and its block-scaled sibling wants
+// power-of-two scales per 32 elements, so f32 scales per 128 elements have to be applied OUTSIDE the MMA.  The kernel
+// therefore never accumulates across K blocks in tensor memory: every 128-element K block is four k32 MMAs into a
+// FRESH accumulator (two accumulators of 256 columns alternate and fill TMEM), and the epilogue warps promote each
+// finished block into f32 sums they keep in registers -- sum += acc * (s_x[m, kb] * s_w[n / 128, kb]) -- while the tensor
+// core works on the next block.  (The reference spells the same arithmetic as a per-group activation round trip in front
+// of a block-dequantized weight, emmy/compiler/loader/quant.py:1655-1717.)
+//
+//   warp 0      TMA producer: A tile 128 rows x 128 bytes, B tile 256 channels x 128 bytes, four 48 KB stages
+//   warp 1      MMA issuer: per K block 4 x tcgen05.mma 128 x 256 x 32, commit -> stage free, commit -> accumulator full
+//   warps 2..9  promotion and store: quartet q owns columns [128 q, 128 q + 128) = one weight scale block; a thread owns
+//               one row and keeps its 128 sums in registers; after reading a block's accumulator it hands it back
+// Every wait is bounded and reports through the status word.
+#include "tc_common.cuh"
+
+namespace eq {
+
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 128;
+constexpr int kTileA = kBM * kBK, kTileB = kBN * kBK;
+constexpr int kStages = 4;
+constexpr int kThreads = 10 * 32;
+constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 + 256;
+constexpr uint32_t kTmemCols = 512;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+    fp8_block_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const float* __restrict__ sx, const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K,
+                        int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_a = smem;
+    unsigned char* tiles_b = smem + kStages * kTileA;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * (kTileA + kTileB));
+    uint64_t* full = bars;                    // [kStages] TMA -> MMA
+    uint64_t* empty = bars + kStages;         // [kStages] MMA -> TMA
+    uint64_t* acc_full = bars + 2 * kStages;  // [2] MMA -> promotion warps
+    uint64_t* acc_free = acc_full + 2;        // [2] promotion warps -> MMA (eight arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    const int k_blocks = K / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(tc::smem_u32(acc_full + b), 1);
+            tc::mbar_init(tc::smem_u32(acc_free + b), 8);
+        }
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_a);
+            tc::tma_prefetch_desc(&map_b);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages;
+                if (kb >= kStages && !tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                tc::mbar_expect_tx(bar, kTileA + kTileB);
+                tc::tma_load_2d(tc::smem_u32(tiles_a + s * kTileA), &map_a, kb * kBK, m0, bar);
+                tc::tma_load_2d(tc::smem_u32(tiles_b + s * kTileB), &map_b, kb * kBK, n0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc(0, 0, kBM, kBN);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kStages, buf = kb & 1, use = kb >> 1;
+                // the accumulator's previous block has been read out
+                if (use > 0 && !tc::mbar_wait(tc::smem_u32(acc_free + buf), (use - 1) & 1)) {
+                    atomicExch(status, 4);
+                    break;
+                }
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kStages) & 1)) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t a_addr = tc::smem_u32(tiles_a + s * kTileA), b_addr = tc::smem_u32(tiles_b + s * kTileB);
+#pragma unroll
+                for (int ks = 0; ks < kBK / 32; ++ks)
+                    tc::mma_f8f6f4(tmem_base + buf * kBN, tc::smem_desc_k_sw128(a_addr + ks * 32), tc::smem_desc_k_sw128(b_addr + ks * 32), idesc,
+                                   ks > 0);  // every K block starts a fresh sum
+                tc::mma_commit(tc::smem_u32(empty + s));
+                tc::mma_commit(tc::smem_u32(acc_full + buf));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;         // TMEM lanes 32 quarter .. + 31
+        const int q = (warp - 2) >> 2;        // which 128 columns = which weight scale block
+        const int m = m0 + quarter * 32 + lane;
+        const int nb = (n0 >> 7) + q;         // row of the weight scales
+        const bool cols_live = n0 + q * 128 < N;
+        const int kblocks_w = K / 128;
+        float sum[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) sum[i] = 0.f;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+            const int buf = kb & 1, use = kb >> 1;
+            ok = tc::mbar_wait(tc::smem_u32(acc_full + buf), use & 1);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) {
+                if (lane == 0) atomicExch(status, 3);
+                break;
+            }
+            tc::fence_after_sync();
+            const float f = (m < M && cols_live) ? __ldg(sx + static_cast<size_t>(m) * kblocks_w + kb) * __ldg(sw + static_cast<size_t>(nb) * kblocks_w + kb) : 0.f;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN + q * 128;
+#pragma unroll
+            for (int c = 0; c < 128; c += 32) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32(t_row + c, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum[c + i] = fmaf(__uint_as_float(r[i]), f, sum[c + i]);
+            }
+            // this warp is done with the accumulator
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(acc_free + buf));
+        }
+        if (ok && m < M && cols_live) {
+            OutT* dst = y + static_cast<size_t>(m) * N + n0 + q * 128;
+#pragma unroll
+            for (int v = 0; v < 16; ++v) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const OutT o0 = from_float<OutT>(sum[8 * v + 2 * i]), o1 = from_float<OutT>(sum[8 * v + 2 * i + 1]);
+                    pk[i] = static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o0)) | (static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(&o1)) << 16);
+                }
+                reinterpret_cast<uint4*>(dst)[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+template <typename OutT>
+int launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, OutT* y, int64_t M, int64_t N, int64_t K, int* status,
+           cudaStream_t stream) {
+    CUtensorMap map_a, map_b;
+    int st = make_tensor_map_2d(&map_a, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kBN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != EQ_OK) return st;
+    auto kernel = fp8_block_tc_kernel<OutT>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem)));
+    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
+    kernel<<<grid, kThreads, kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+    EQ_LAUNCH_OK("fp8_block_tc_kernel");
+    return EQ_OK;
+}
+
+}  // namespace
+
+// qx [M][K] e4m3 codes, sx [M][K / 128]; w [N][K], sw [N / 128][K / 128]; N and K multiples of 128, y 16-byte aligned.
+// status: one word, cleared by the caller, set when a bounded pipeline wait ran out.
+int fp8_block_tc_launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, void* y, int64_t M, int64_t N, int64_t K,
+                        int act_dtype, int* status, cudaStream_t stream) {
+    return act_dtype == EQ_F16 ? launch<__half>(qx, sx, w, sw, static_cast<__half*>(y), M, N, K, status, stream)
+                               : launch<__nv_bfloat16>(qx, sx, w, sw, static_cast<__nv_bfloat16*>(y), M, N, K, status, stream);
+}
+
+}  // namespace eq

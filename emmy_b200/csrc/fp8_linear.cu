@@ -78,7 +78,9 @@ constexpr int kDecWarps = 4;
 // bytes of row g (and g+8) feed two k32 MMAs; which actual k a fragment slot means is irrelevant as long as the
 // activation fragment uses the same bytes, so both are simply the lane's 16 consecutive bytes.  SPLIT > 1: the CTAs of a
 // cluster share a tile; CTA 0 of the cluster adds the others' partial sums out of their shared memory.
-template <typename OutT, int MT>
+// BLOCK: the block-scaled form -- sw is [N / 128][K / 128], sx is [M][K / 128], and every 128 elements of K (two steps)
+// are promoted into the sum with their own pair of scales; the K ranges of CTAs and warps are whole 128-blocks then.
+template <typename OutT, int MT, bool BLOCK>
 __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
                                                                      const uint8_t* __restrict__ qx, const float* __restrict__ sx,
                                                                      OutT* __restrict__ y, int M, int N, int K, int split) {
@@ -88,9 +90,10 @@ __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uin
     const int g = lane >> 2, j = lane & 3;
     const int tile = blockIdx.x / split, part = blockIdx.x - tile * split;
     const int n0 = tile * 16;
-    const int steps = K / 64;
+    constexpr int kUnit = BLOCK ? 2 : 1;  // steps that stay together
+    const int steps = K / 64 / kUnit;
     const int c0 = steps * part / split, c1 = steps * (part + 1) / split;
-    const int s0 = c0 + (c1 - c0) * warp / kDecWarps, s1 = c0 + (c1 - c0) * (warp + 1) / kDecWarps;
+    const int s0 = kUnit * (c0 + (c1 - c0) * warp / kDecWarps), s1 = kUnit * (c0 + (c1 - c0) * (warp + 1) / kDecWarps);
     const uint8_t* wr_lo = w + static_cast<size_t>(n0 + g) * K + 16 * j;
     const uint8_t* wr_hi = wr_lo + static_cast<size_t>(8) * K;
     float acc[MT][4];
@@ -111,6 +114,7 @@ __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uin
     fetch(s0);
     // the weights never depend on the kernel before; the activation codes do (they come from the quantize)
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int kblocks = K / 128;
     for (int sb = s0; sb < s1; sb += U) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -120,8 +124,24 @@ __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uin
                     const int m = mt * 8 + g;
                     uint4 b = make_uint4(0, 0, 0, 0);
                     if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u) * 64 + 16 * j));
-                    mma_e4m3(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
-                    mma_e4m3(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+                    if constexpr (!BLOCK) {
+                        mma_e4m3(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
+                        mma_e4m3(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+                    } else {
+                        // a step is half a 128-block (s0 is even): its products are promoted with the block's scales
+                        float part_acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_e4m3(part_acc, a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
+                        mma_e4m3(part_acc, a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
+                        const int kb = (sb + u) >> 1;
+                        const float wsc = __ldg(sw + static_cast<size_t>(n0 >> 7) * kblocks + kb);
+                        const int m0 = mt * 8 + 2 * j;
+                        const float f0 = m0 < M ? wsc * __ldg(sx + static_cast<size_t>(m0) * kblocks + kb) : 0.f;
+                        const float f1 = m0 + 1 < M ? wsc * __ldg(sx + static_cast<size_t>(m0 + 1) * kblocks + kb) : 0.f;
+                        acc[mt][0] = fmaf(part_acc[0], f0, acc[mt][0]);
+                        acc[mt][1] = fmaf(part_acc[1], f1, acc[mt][1]);
+                        acc[mt][2] = fmaf(part_acc[2], f0, acc[mt][2]);
+                        acc[mt][3] = fmaf(part_acc[3], f1, acc[mt][3]);
+                    }
                 }
             }
         }
@@ -157,7 +177,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uin
                         s += v;
                     }
                 }
-                y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
+                if constexpr (BLOCK) y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s);
+                else y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
             }
         }
     }
@@ -453,32 +474,46 @@ static int fp8_tc_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K
     return EQ_OK;
 }
 
+// M <= 16.  BLOCK: block-scaled operands (see the kernel).  Launched as a programmatic dependent of the quantize.
+template <typename OutT, bool BLOCK>
+static int fp8_decode_typed(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, OutT* y,
+                            cudaStream_t stream) {
+    // all CTAs resident at once (eight per SM); narrow weights split K over clusters until there are enough CTAs
+    const long long tiles = N / 16, want = 6LL * sm_count();
+    int split = 1;
+    while (split < 8 && tiles * split < want && K / 64 / (2 * split) >= kDecWarps * (BLOCK ? 2 : 1)) split *= 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
+    cfg.blockDim = dim3(kDecWarps * 32);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = static_cast<unsigned>(split);
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = split > 1 ? 2 : 1;
+    const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
+    if (M <= 8) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 1, BLOCK>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
+    else EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 2, BLOCK>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
+    return EQ_OK;
+}
+
+// The block-scaled linear's decode-shaped calls (fp8_block.cu): sw [N / 128][K / 128], sx [M][K / 128].
+namespace eq {
+int fp8_block_decode_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, int act_dtype,
+                            void* y, cudaStream_t stream) {
+    return act_dtype == EQ_F16 ? fp8_decode_typed<__half, true>(w, sw, N, K, qx, sx, M, static_cast<__half*>(y), stream)
+                               : fp8_decode_typed<__nv_bfloat16, true>(w, sw, N, K, qx, sx, M, static_cast<__nv_bfloat16*>(y), stream);
+}
+}  // namespace eq
+
 template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
-    if (M <= 16) {
-        // all CTAs resident at once (eight per SM); narrow weights split K over clusters until there are enough CTAs
-        const long long tiles = N / 16, want = 6LL * sm_count();
-        int split = 1;
-        while (split < 8 && tiles * split < want && K / 64 / (2 * split) >= kDecWarps) split *= 2;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
-        cfg.blockDim = dim3(kDecWarps * 32);
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = static_cast<unsigned>(split);
-        attr[1].val.clusterDim.y = 1;
-        attr[1].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = split > 1 ? 2 : 1;
-        const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
-        if (M <= 8) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 1>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
-        else EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 2>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
-        return EQ_OK;
-    }
+    if (M <= 16) return fp8_decode_typed<OutT, false>(w, sw, N, K, qx, sx, M, y, stream);
     if (M <= 128) return fp8_tc_launch<OutT, 1, 128>(w, sw, N, K, qx, sx, M, y, status, stream);
     return fp8_tc_launch<OutT, 2, 256>(w, sw, N, K, qx, sx, M, y, status, stream);
 }

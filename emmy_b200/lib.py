@@ -92,6 +92,7 @@ def load() -> C.CDLL:
         "eq_quant_fp8_per_group": (i, [p, i64, i64, i, p, p, p]),
         "eq_fp8_block_workspace_bytes": (sz, [i64, i64]),
         "eq_fp8_block_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),
+        "eq_fp8_block_status": (i, [p, i64, i64, p]),
         "eq_nvfp4_global_scale": (i, [p, i64, i64, i, p, p, p]),
         "eq_quant_nvfp4_act": (i, [p, i64, i64, i, p, p, p, p, p]),
         "eq_quant_nvfp4_weight": (i, [p, i64, i64, i, p, p, p, p, p]),

@@ -255,3 +255,7 @@ def fp8_block_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.
     ws = workspace if workspace is not None else torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
     L.check(L.load().eq_fp8_block_linear(_ptr(weight), _ptr(weight_scale), n, k, _ptr(x), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()))
     return y
+
+
+def fp8_block_status(workspace: torch.Tensor, m: int, k: int) -> None:
+    L.check(L.load().eq_fp8_block_status(_ptr(workspace), m, k, _stream()))

@@ -262,3 +262,49 @@ class EpMoe:
         from .ops import _ptr, _stream
 
         self.lib.check(self.lib.load().eq_ep_moe_status(_ptr(self.workspace), self.world, self.cap, self.experts_local, self.hidden, self.inter, _stream()))
+
+
+class EpMoePipelined:
+    """`EpMoe` over `chunks` slices of the tokens, each slice a complete exchange of its own (own buffers, flags and
+    workspace) on its own stream: while one slice's expert GEMMs run, the next slice's rows are crossing NVLink and the
+    previous slice's results are on their way back, so the exchange hides behind the math instead of adding to it.
+    The slices are row ranges of x, ids, scores and y; every rank must use the same `chunks`.  Streams are joined
+    through events, so a call still captures into one CUDA graph.  Construction is collective."""
+
+    def __init__(self, group, t_max: int, topk: int, hidden: int, inter: int, experts_local: int, dtype, device, chunks: int = 2,
+                 cap: int | None = None):
+        if chunks < 1:
+            raise ValueError("chunks must be at least 1")
+        self.chunks, self.t_max, self.hidden = chunks, t_max, hidden
+        self.per = -(-t_max // chunks)
+        self.parts = [EpMoe(group, self.per, topk, hidden, inter, experts_local, dtype, device, cap=cap) for _ in range(chunks)]
+        self.streams = [None] + [torch.cuda.Stream(device=device) for _ in range(chunks - 1)]
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, w, out: torch.Tensor | None = None,
+                check: bool = False) -> torch.Tensor:
+        t = x.shape[0]
+        if t > self.t_max:
+            raise ValueError(f"{t} tokens exceed the t_max={self.t_max} the buffers were sized for")
+        y = out if out is not None else torch.empty((t, self.hidden), dtype=x.dtype, device=x.device)
+        main = torch.cuda.current_stream(x.device)
+        # every rank runs every slice (an empty one too): its flags are what the other ranks wait for
+        bounds = [min(t, i * self.per) for i in range(self.chunks + 1)]
+        for i, part in enumerate(self.parts):
+            a, b = bounds[i], bounds[i + 1]
+            side = self.streams[i]
+            if side is None:
+                part.forward(x[a:b], ids[a:b], scores[a:b], w, out=y[a:b])
+            else:
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    part.forward(x[a:b], ids[a:b], scores[a:b], w, out=y[a:b])
+        for side in self.streams[1:]:
+            main.wait_stream(side)
+        if check:
+            self.status()
+        return y
+
+    def status(self) -> None:
+        for part in self.parts:
+            part.status()
+

@@ -186,6 +186,8 @@ int eq_quant_fp8_per_group(const void* x, int64_t M, int64_t K, int in_dtype, ui
 size_t eq_fp8_block_workspace_bytes(int64_t M, int64_t K);
 int eq_fp8_block_linear(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, int64_t M,
                         int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* Synchronizes the stream; EQ_ERR_TIMEOUT if a bounded pipeline wait of the tensor path (M > 16) ran out. */
+int eq_fp8_block_status(const void* workspace, int64_t M, int64_t K, void* stream);
 
 /* ------------------------------------------------------------------ NVFP4 W4A4 linear */
 

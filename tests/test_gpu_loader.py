@@ -89,7 +89,7 @@ def test_fp8_and_nvfp4_from_a_mixed_checkpoint(tmp_path):
     close(mods["a.k_proj"](xd), ref)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (37, 384, 256), (300, 512, 1024)])
+@pytest.mark.parametrize("m,n,k", [(1, 256, 512), (5, 384, 1536), (16, 256, 5120), (37, 384, 256), (300, 512, 1024)])
 def test_block_scaled_fp8(m, n, k, tmp_path):
     from emmy_b200 import loader, ops
 

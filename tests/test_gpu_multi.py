@@ -58,6 +58,15 @@ def _worker(rank, world, port, ret):
         ep.status()
         ret[40 + rank] = float((y2 - ref2).abs().max() / ref2.abs().max())
 
+        # the pipelined form: three slices on three streams, each a complete exchange; twice, the second time with
+        # fewer tokens than slices can be filled with (the last slice is empty on one rank)
+        pipe = shard.EpMoePipelined(None, 300, k, h, inter, per, torch.bfloat16, torch.device("cuda", rank), chunks=3)
+        y3 = pipe.forward(x2, ids2, scores2, local, check=True).float()
+        ret[50 + rank] = float((y3 - ref2).abs().max() / ref2.abs().max())
+        t3 = 150 if rank == 0 else 230
+        y4 = pipe.forward(x2[:t3], ids2[:t3], scores2[:t3], local, check=True).float()
+        ret[60 + rank] = float((y4 - ref2[:t3]).abs().max() / ref2[:t3].abs().max())
+
         kk, n = 512, 256
         qw, qz, sc, gi = synth.gptq_linear(kk, n, seed=9)
         tq = [torch.from_numpy(a) for a in (qw, qz, sc, gi)]
@@ -87,5 +96,6 @@ def test_sharded_paths_on_two_gpus():
         out = dict(ret)
     assert all(out[r] < 1e-2 for r in range(world)), out            # EP == single device up to f32 summation order
     assert all(out[30 + r] < 1e-2 and out[40 + r] < 1e-2 for r in range(world)), out  # peer-memory exchange
+    assert all(out[50 + r] < 1e-2 and out[60 + r] < 1e-2 for r in range(world)), out  # the same, sliced over streams
     assert all(out[10 + r] == 0.0 for r in range(world)), out      # column shards are the same columns
     assert all(out[20 + r] < 1e-2 for r in range(world)), out      # row partials summed in f32
