@@ -55,7 +55,7 @@ STEP_BYTES = LAYERS * sum(algorithmic_bytes(k, n) for k, n in SHAPES.values())
 
 # dram bytes per launch of the GEMV kernel (dram__bytes_read.sum + dram__bytes_write.sum, mean of the captured launches of
 # this workload) from the ncu capture summarised in profiles/w4a16_gemv1_kernel_gptq_m1.md
-EP_CHUNKS = int(os.environ.get("EQ_BENCH_EP_CHUNKS", "2"))  # slices of the expert-parallel MoE record (1 = unsliced)
+EP_CHUNKS = int(os.environ.get("EQ_BENCH_EP_CHUNKS", "1"))  # slices of the expert-parallel MoE record (1 = unsliced)
 GEMV_KERNEL = "w4a16_gemv1_kernel<__half, true, DEPTH>"
 TRAFFIC_PER_LAUNCH = 31242000
 
@@ -456,7 +456,7 @@ def wl_moe(device, rank, world, t, exchange="peer"):
         status = lambda: None
         capture = False
     else:
-        # large batches go in two slices on two streams, so that one slice's exchange runs under the other's GEMMs
+        # EQ_BENCH_EP_CHUNKS > 1 runs the token-sliced form (measured slower at two GPUs: 0.82 ms in two slices, 0.69 ms in one)
         ep = (shard.EpMoePipelined(None, t, topk, hidden, inter, local_e, torch.bfloat16, device, chunks=EP_CHUNKS) if t >= 2048 and EP_CHUNKS > 1
               else shard.EpMoe(None, t, topk, hidden, inter, local_e, torch.bfloat16, device))
 

@@ -81,7 +81,7 @@ constexpr int kDecWarps = 4;
 // BLOCK: the block-scaled form -- sw is [N / 128][K / 128], sx is [M][K / 128], and every 128 elements of K (two steps)
 // are promoted into the sum with their own pair of scales; the K ranges of CTAs and warps are whole 128-blocks then.
 template <typename OutT, int MT, bool BLOCK>
-__global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
+__global__ void __launch_bounds__(kDecWarps * 32, BLOCK ? 5 : 8) fp8_decode_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
                                                                      const uint8_t* __restrict__ qx, const float* __restrict__ sx,
                                                                      OutT* __restrict__ y, int M, int N, int K, int split) {
     __shared__ float red[kDecWarps][MT][16][8];
@@ -116,31 +116,45 @@ __global__ void __launch_bounds__(kDecWarps * 32, 8) fp8_decode_kernel(const uin
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int kblocks = K / 128;
     for (int sb = s0; sb < s1; sb += U) {
+        if constexpr (!BLOCK) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (sb + u < s1) {
+            for (int u = 0; u < U; ++u) {
+                if (sb + u < s1) {
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const int m = mt * 8 + g;
-                    uint4 b = make_uint4(0, 0, 0, 0);
-                    if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u) * 64 + 16 * j));
-                    if constexpr (!BLOCK) {
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int m = mt * 8 + g;
+                        uint4 b = make_uint4(0, 0, 0, 0);
+                        if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u) * 64 + 16 * j));
                         mma_e4m3(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
                         mma_e4m3(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
-                    } else {
-                        // a step is half a 128-block (s0 is even): its products are promoted with the block's scales
-                        float part_acc[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_e4m3(part_acc, a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
-                        mma_e4m3(part_acc, a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
-                        const int kb = (sb + u) >> 1;
-                        const float wsc = __ldg(sw + static_cast<size_t>(n0 >> 7) * kblocks + kb);
+                    }
+                }
+            }
+        } else {
+            // two steps are one 128-block (s0 and s1 are even): its products are promoted with the block's scales
+#pragma unroll
+            for (int u = 0; u < U; u += 2) {
+                if (sb + u < s1) {
+                    const int kb = (sb + u) >> 1;
+                    const float wsc = __ldg(sw + static_cast<size_t>(n0 >> 7) * kblocks + kb);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        const int m = mt * 8 + g;
+                        float blk[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint4 b = make_uint4(0, 0, 0, 0);
+                            if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u + h) * 64 + 16 * j));
+                            mma_e4m3(blk, a_lo[u + h].x, a_hi[u + h].x, a_lo[u + h].y, a_hi[u + h].y, b.x, b.y);
+                            mma_e4m3(blk, a_lo[u + h].z, a_hi[u + h].z, a_lo[u + h].w, a_hi[u + h].w, b.z, b.w);
+                        }
                         const int m0 = mt * 8 + 2 * j;
                         const float f0 = m0 < M ? wsc * __ldg(sx + static_cast<size_t>(m0) * kblocks + kb) : 0.f;
                         const float f1 = m0 + 1 < M ? wsc * __ldg(sx + static_cast<size_t>(m0 + 1) * kblocks + kb) : 0.f;
-                        acc[mt][0] = fmaf(part_acc[0], f0, acc[mt][0]);
-                        acc[mt][1] = fmaf(part_acc[1], f1, acc[mt][1]);
-                        acc[mt][2] = fmaf(part_acc[2], f0, acc[mt][2]);
-                        acc[mt][3] = fmaf(part_acc[3], f1, acc[mt][3]);
+                        acc[mt][0] = fmaf(blk[0], f0, acc[mt][0]);
+                        acc[mt][1] = fmaf(blk[1], f1, acc[mt][1]);
+                        acc[mt][2] = fmaf(blk[2], f0, acc[mt][2]);
+                        acc[mt][3] = fmaf(blk[3], f1, acc[mt][3]);
                     }
                 }
             }
