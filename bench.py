@@ -350,7 +350,7 @@ def wl_fp8_block(device, rank, m, n=GEMM_N, k=GEMM_K):
 
     return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + (n // 128) * (k // 128) * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n,
                 peak_mult=2.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.fp8_block_status(wsp, m, k),
-                kernel="fp8_decode_kernel<__nv_bfloat16, MT, true>" if m <= 16 else "fp8_block_tc_kernel<__nv_bfloat16>",
+                kernel="fp8_decode_kernel<__nv_bfloat16, 1, true>" if m <= 8 else "fp8_block_tc_kernel<__nv_bfloat16, BN>",
                 dtype="e4m3 weights (128 x 128 block scales) and activations (per token, per 128 of K), f32 accumulate, bf16 out")
 
 
@@ -591,7 +591,7 @@ def extra_records(device, rank, world, clocks, quick_steps=3):
                     "w4a16_gemv_hbm_gbs" if m <= 16 else "w4a16_gemm_tflops", unit, f"GPTQ act-order W4A16, Llama-3.1-8B {proj} K={k} N={n}, M={m}")
         add(lambda: wl_gate_up_fused(device, rank), quick_steps, clocks, "gptq_gate_up_fused_m1", "w4a16_gemv_hbm_gbs", "GB/s",
             "GPTQ act-order W4A16, Llama-3.1-8B gate and up as one [gate | up] linear K=4096 N=28672, M=1: one launch for both projections")
-        for m in (16, 2048):
+        for m in (1, 16, 2048):
             add(lambda: wl_fp8_block(device, rank, m), quick_steps, clocks, f"fp8_block_m{m}", "fp8_block_hbm_gbs" if m <= 16 else "fp8_block_gemm_tflops",
                 "GB/s" if m <= 16 else "TFLOP/s", f"block-scaled FP8 W8A8 (128 x 128 weight blocks, per-token per-128 activation scales, quantize timed), K={GEMM_K} N={GEMM_N} M={m}")
         for m in (1, 32, 512, 8192):

@@ -1,4 +1,4 @@
-// Block-scaled FP8 W8A8 linear on the 5th-generation tensor cores (M > 16).
+// Block-scaled FP8 W8A8 linear on the 5th-generation tensor cores (M > 8).
 //
 //     y[m, n] = sum_kb ( sum_{k in kb} q_x[m, k] q_w[n, k] ) * s_x[m, kb] * s_w[n / 128, kb]
 //
@@ -21,18 +21,29 @@ namespace eq {
 
 namespace {
 
-constexpr int kBM = 128, kBN = 256, kBK = 128;
-constexpr int kTileA = kBM * kBK, kTileB = kBN * kBK;
-constexpr int kStages = 4;
-constexpr int kThreads = 10 * 32;
-constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 + 256;
-constexpr uint32_t kTmemCols = 512;
+constexpr int kBM = 128, kBK = 128;
+constexpr int kTileA = kBM * kBK;
 
-template <typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+// BN = 256: two weight scale blocks per CTA, eight promotion warps, four 48 KB stages, all of TMEM.  BN = 128 (calls of
+// at most 128 rows, where the grid is one row of CTAs): twice as many CTAs stream the weight, six 32 KB stages.
+template <int BN>
+struct BlkCfg {
+    static constexpr int kTileB = BN * kBK;
+    static constexpr int kStages = BN == 256 ? 4 : 6;
+    static constexpr int kQuartets = BN / 128;
+    static constexpr int kThreads = 64 + 128 * kQuartets;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * (kTileA + kTileB) + 1024 + 256;
+    static constexpr uint32_t kTmemCols = 2 * BN;
+};
+
+template <typename OutT, int BN>
+__global__ void __launch_bounds__(BlkCfg<BN>::kThreads, 1)
     fp8_block_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const float* __restrict__ sx, const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K,
                         int* __restrict__ status) {
+    using Cfg = BlkCfg<BN>;
+    constexpr int kBN = BN, kTileB = Cfg::kTileB, kStages = Cfg::kStages;
+    constexpr uint32_t kTmemCols = Cfg::kTmemCols;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* tiles_a = smem;
@@ -41,7 +52,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint64_t* full = bars;                    // [kStages] TMA -> MMA
     uint64_t* empty = bars + kStages;         // [kStages] MMA -> TMA
     uint64_t* acc_full = bars + 2 * kStages;  // [2] MMA -> promotion warps
-    uint64_t* acc_free = acc_full + 2;        // [2] promotion warps -> MMA (eight arrivals)
+    uint64_t* acc_free = acc_full + 2;        // [2] promotion warps -> MMA (one arrival per warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -55,7 +66,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         for (int b = 0; b < 2; ++b) {
             tc::mbar_init(tc::smem_u32(acc_full + b), 1);
-            tc::mbar_init(tc::smem_u32(acc_free + b), 8);
+            tc::mbar_init(tc::smem_u32(acc_free + b), 4 * Cfg::kQuartets);
         }
         tc::mbar_fence_init();
     }
@@ -162,20 +173,27 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
-template <typename OutT>
+template <typename OutT, int BN>
 int launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, OutT* y, int64_t M, int64_t N, int64_t K, int* status,
            cudaStream_t stream) {
+    using Cfg = BlkCfg<BN>;
     CUtensorMap map_a, map_b;
     int st = make_tensor_map_2d(&map_a, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, kBN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
+    st = make_tensor_map_2d(&map_b, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BN, kBK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
-    auto kernel = fp8_block_tc_kernel<OutT>;
-    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmem)));
-    dim3 grid(static_cast<unsigned>(ceil_div(N, kBN)), static_cast<unsigned>(ceil_div(M, kBM)));
-    kernel<<<grid, kThreads, kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
+    auto kernel = fp8_block_tc_kernel<OutT, BN>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, kBM)));
+    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
     EQ_LAUNCH_OK("fp8_block_tc_kernel");
     return EQ_OK;
+}
+
+template <typename OutT>
+int launch_any(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, OutT* y, int64_t M, int64_t N, int64_t K, int* status,
+               cudaStream_t stream) {
+    return M <= 128 ? launch<OutT, 128>(qx, sx, w, sw, y, M, N, K, status, stream) : launch<OutT, 256>(qx, sx, w, sw, y, M, N, K, status, stream);
 }
 
 }  // namespace
@@ -184,8 +202,8 @@ int launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw
 // status: one word, cleared by the caller, set when a bounded pipeline wait ran out.
 int fp8_block_tc_launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, void* y, int64_t M, int64_t N, int64_t K,
                         int act_dtype, int* status, cudaStream_t stream) {
-    return act_dtype == EQ_F16 ? launch<__half>(qx, sx, w, sw, static_cast<__half*>(y), M, N, K, status, stream)
-                               : launch<__nv_bfloat16>(qx, sx, w, sw, static_cast<__nv_bfloat16*>(y), M, N, K, status, stream);
+    return act_dtype == EQ_F16 ? launch_any<__half>(qx, sx, w, sw, static_cast<__half*>(y), M, N, K, status, stream)
+                               : launch_any<__nv_bfloat16>(qx, sx, w, sw, static_cast<__nv_bfloat16*>(y), M, N, K, status, stream);
 }
 
 }  // namespace eq

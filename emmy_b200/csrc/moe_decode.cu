@@ -49,42 +49,73 @@ __device__ __forceinline__ uint32_t order_key(float v) {
 }
 __device__ __forceinline__ float key_value(uint32_t k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k); }
 
-// One warp routes one token: ids ascending, scores renormalised.  (The router of moe.cu, see there, with the warp-wide
-// argmax done by two redux.sync: the maximum key, then the lowest expert id that holds it.)
+// One warp routes one token: ids ascending, scores renormalised.  (The router of moe.cu, see there.)  The lane's logits
+// are read once and kept as order keys in registers (eight per lane cover 256 experts; beyond that they are re-read);
+// a round of the top-k is a scan of those registers and two redux.sync (the maximum key, then the lowest expert id that
+// holds it), and the exponentials of the winners are taken after the rounds, one lane per pick.
 __device__ __forceinline__ void route_token(const float* __restrict__ lg, int E, int topk, int32_t* ids, float* scores) {
+    constexpr int kKeep = 8;
     const int lane = threadIdx.x & 31;
+    uint32_t key[kKeep];
     uint32_t top = 0;
-    for (int e = lane; e < E; e += 32) top = max(top, order_key(lg[e]));
+#pragma unroll
+    for (int b = 0; b < kKeep; ++b) {
+        const int e = lane + 32 * b;
+        key[b] = e < E ? order_key(lg[e]) : 0u;  // 0 is below every real key
+        top = max(top, key[b]);
+    }
+    for (int e = lane + 32 * kKeep; e < E; e += 32) top = max(top, order_key(lg[e]));
     const float mx = key_value(__reduce_max_sync(0xFFFFFFFFu, top));
     float sum = 0.f;
-    for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+#pragma unroll
+    for (int b = 0; b < kKeep; ++b)
+        if (lane + 32 * b < E) sum += expf(key_value(key[b]) - mx);
+    for (int e = lane + 32 * kKeep; e < E; e += 32) sum += expf(lg[e] - mx);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-    unsigned long long taken = 0;  // this lane's experts already picked (bit = (e - lane) / 32)
-    float psum = 0.f;
-    int my_id = 0x7FFFFFFF;  // lane jj keeps pick jj
-    float my_p = 0.f;
+    unsigned long long taken = 0;  // this lane's experts beyond the kept ones that are already picked (bit = (e - lane) / 32)
+    int my_id = 0x7FFFFFFF;        // lane jj keeps pick jj
+    uint32_t my_key = 0;
     for (int jj = 0; jj < topk; ++jj) {
-        uint32_t best = 0;  // below every real key
-        int best_e = 0x7FFFFFFF;
-        for (int e = lane, b = 0; e < E; e += 32, ++b) {
+        uint32_t best = 0;
+        int best_b = 0;
+#pragma unroll
+        for (int b = 0; b < kKeep; ++b) {
+            if (key[b] > best) {  // ascending e: the first of equal values stays
+                best = key[b];
+                best_b = b;
+            }
+        }
+        int best_e = best ? lane + 32 * best_b : 0x7FFFFFFF;
+        for (int e = lane + 32 * kKeep, b = kKeep; e < E; e += 32, ++b) {
             if ((taken >> b) & 1ull) continue;
             const uint32_t k = order_key(lg[e]);
-            if (k > best) {  // ascending e: the first of equal values stays
+            if (k > best) {
                 best = k;
                 best_e = e;
             }
         }
         const uint32_t win = __reduce_max_sync(0xFFFFFFFFu, best);
         const int win_e = static_cast<int>(__reduce_min_sync(0xFFFFFFFFu, static_cast<unsigned>(best == win ? best_e : 0x7FFFFFFF)));
-        if (win_e < E && (win_e & 31) == lane) taken |= 1ull << (win_e >> 5);
-        const float pr = win_e < E ? expf(key_value(win) - mx) / sum : 0.f;
+        if (win_e < E && (win_e & 31) == lane) {  // this lane's expert: out of the running
+            const int b = win_e >> 5;
+            if (b < kKeep) {
+#pragma unroll
+                for (int c = 0; c < kKeep; ++c)
+                    if (c == b) key[c] = 0u;
+            } else {
+                taken |= 1ull << b;
+            }
+        }
         if (lane == jj) {
             my_id = win_e < E ? win_e : E - 1;
-            my_p = pr;
+            my_key = win_e < E ? win : 0u;
         }
-        psum += pr;
     }
+    float my_p = (lane < topk && my_key) ? expf(key_value(my_key) - mx) / sum : 0.f;
+    float psum = my_p;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) psum += __shfl_xor_sync(0xFFFFFFFFu, psum, off);
     // ascending expert id (the order the combine adds in): a pick's place is the number of picks with a smaller id
     int place = 0;
     for (int jj = 0; jj < topk; ++jj) {
