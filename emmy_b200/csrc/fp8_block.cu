@@ -7,13 +7,14 @@
 // with the inner sums exact in f32 over 128 products of e4m3 values.
 //
 //   quant_fp8_groups_kernel  s_x[m, kb] = max(amax_kb |x|, 1e-12) / 448, q = e4m3_rne_satfinite(x / s_x): the per-token
-//                            rule of fp8_linear.cu applied per 128-element group; one warp per group.
-//   fp8_block_gemm_kernel    128 x 128 output tile per CTA, K in steps of one scale block.  Operand tiles come by
-//                            cp.async into XOR-swizzled shared memory (two stages), fragments by ldmatrix, products by
-//                            mma.sync m16n8k32 e4m3 into a per-block accumulator that is folded into the running f32 sum
-//                            with the block's two scales.  The per-block scaling is why this is not a tcgen05 kernel:
-//                            kind::f8f6f4 accumulates over the whole K loop in tensor memory, and its block-scaled
-//                            sibling takes power-of-two (ue8m0) scales per 32 elements, not f32 scales per 128.
+//                            rule of fp8_linear.cu applied per 128-element group; one warp per group.  Inside the linear
+//                            it also clears the status word and lets the kernel behind it start early.
+//   M <= 8                   the decode kernel of fp8_linear.cu with per-block promotion (fp8_block_decode_launch)
+//   M > 8                    tcgen05 with a fresh accumulator per K block and promotion in registers (fp8_block_tc.cu)
+//   fp8_block_gemm_kernel    the mma.sync form, kept for an output that is not 16-byte aligned: 128 x 128 output tile per
+//                            CTA, K in steps of one scale block, operand tiles by cp.async into XOR-swizzled shared
+//                            memory (two stages), fragments by ldmatrix, products by mma.sync m16n8k32 e4m3 into a
+//                            per-block accumulator that is folded into the running f32 sum with the block's two scales.
 #include "common.cuh"
 
 namespace eq {
