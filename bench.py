@@ -478,10 +478,11 @@ def wl_moe(device, rank, world, t, exchange="peer"):
         hit = int(torch.unique(om.moe_route(logits, topk)[0]).numel())  # distinct experts this batch touches
     else:
         hit = local_e  # every local expert is hit by the ranks' tokens at these sizes
-    return dict(step=step, calls=layers, kernels_per_call=2 if t <= 16 else 8, alg_bytes=hit * MOE_EXPERT_BYTES + t * (2 * hidden * 2 + e * 4),
+    tier = "moe_decode_kernel (two phases)" if (world == 1 and t <= 16) else "moe_stream_kernel (grouped)" if t * topk <= 8 * e else "w4a16_gemm_tc_kernel (grouped)"
+    return dict(step=step, calls=layers, kernels_per_call=2 if t <= 16 else 6 if t * topk <= 8 * e else 8, alg_bytes=hit * MOE_EXPERT_BYTES + t * (2 * hidden * 2 + e * 4),
                 flops=float(t) * topk * (2.0 * hidden * 2 * inter + 2.0 * inter * hidden), peak_mult=1.0,
                 h2d=[(x, x_host)], d2h=[(y_host, y)], status=status, capture=capture, parity=parity if world > 1 else None,
-                kernel="w4a16_gemm_tc_kernel (grouped)" if t * topk >= 2 * e else "moe grouped GEMV",
+                kernel=tier,
                 dtype="int4 expert weights, bf16 activations, f32 accumulate and combine")
 
 

@@ -17,6 +17,9 @@
 //                         With many rows per expert the two GEMMs run on the tensor path instead (w4_gemm.cu): rows are
 //                         first copied into expert order (moe_gather_rows_kernel) so that TMA can read them, row
 //                         blocks are 256 rows, and SwiGLU is fused into the first GEMM's epilogue.
+//   streaming tier        up to eight rows per expert on average (and more tokens than the decode tier takes): the plan's
+//                         row blocks hold at most eight rows and both grouped linears run through moe_stream.cu, which
+//                         streams every touched expert's weights once per block; SwiGLU is a kernel of its own between.
 //   moe_swiglu_kernel     h = silu(gate) * up with the roundings of the eager form
 //                         (emmy/compiler/trace/huggingface.py:1663-1669).
 //   moe_combine_kernel    out[t] = dtype(sum_j f32(score_j) * f32(expert_j(x_t))), picks in ascending expert order,
@@ -31,6 +34,10 @@ bool moe_decode_fits(int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I); 
 int moe_decode_launch(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E, int64_t topk, int64_t H, int64_t I,
                       const void* x, const float* logits, int64_t T, int act_dtype, void* y, int32_t* ids, float* scores, void* gu, void* rows,
                       int* tile_count, int* status, cudaStream_t stream);
+bool moe_stream_fits(int max_blocks, int64_t N);  // moe_stream.cu
+int moe_stream_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, const int32_t* x_rows,
+                      const int32_t* y_rows, const uint64_t* y_ptrs, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks, int64_t K,
+                      int64_t N, int act_dtype, cudaStream_t stream);
 int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
                               int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
                               const int32_t* y_rows, const uint64_t* y_ptrs, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
@@ -358,8 +365,12 @@ struct MoeWorkspace {
 };
 
 // Rows per expert at which the grouped GEMMs move to the tensor path (256-row blocks).
-static bool tensor_path(int64_t R, int64_t E) { return R >= 2 * E; }
-static int block_rows_for(int64_t R, int64_t E) { return tensor_path(R, E) ? 256 : R <= 64 ? 8 : R <= 256 ? 16 : 64; }
+// Up to eight rows per expert on average the layer is a weight stream with a little math attached: row blocks of eight
+// rows through the streaming tier (moe_stream.cu; the tile code serves shapes it cannot hold).  Above that the tensor
+// path with 256-row blocks.
+static bool stream_rows(int64_t R, int64_t E) { return R <= 8 * E; }
+static bool tensor_path(int64_t R, int64_t E) { return !stream_rows(R, E); }
+static int block_rows_for(int64_t R, int64_t E) { return tensor_path(R, E) ? 256 : 8; }
 
 static MoeWorkspace carve(void* base, int64_t T, int64_t E, int64_t topk, int64_t H, int64_t I) {
     MoeWorkspace w;
@@ -439,6 +450,17 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
         return w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_down), static_cast<size_t>(H / 16) * (I / 128) * kItemBytes,
                                          scale_dtype, w.h, out, R, H, I, act, w.blocks, w.n_blocks, w.max_blocks, w.dst_of,
                                          row_ptr ? w.dst_ptr : nullptr, false, w.status, stream);
+    }
+    if (moe_stream_fits(w.max_blocks, 2 * I) && moe_stream_fits(w.max_blocks, H)) {
+        const int act = std::is_same<ActT, __half>::value ? EQ_F16 : EQ_BF16;
+        int st = moe_stream_launch(static_cast<const unsigned char*>(wq_gate_up), static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes, scale_dtype,
+                                   x, w.h1, w.src_of, nullptr, nullptr, w.blocks, w.n_blocks, w.max_blocks, H, 2 * I, act, stream);
+        if (st != EQ_OK) return st;
+        moe_swiglu_kernel<ActT><<<static_cast<unsigned>(ceil_div(R * I, 256)), 256, 0, stream>>>(reinterpret_cast<const ActT*>(w.h1), w.offsets + E,
+                                                                                              static_cast<int>(I), reinterpret_cast<ActT*>(w.h));
+        EQ_LAUNCH_OK("moe_swiglu_kernel");
+        return moe_stream_launch(static_cast<const unsigned char*>(wq_down), static_cast<size_t>(H / 16) * (I / 128) * kItemBytes, scale_dtype, w.h,
+                                 out, nullptr, w.dst_of, row_ptr ? w.dst_ptr : nullptr, w.blocks, w.n_blocks, w.max_blocks, I, H, act, stream);
     }
     GroupedParams g1;
     g1.wq = static_cast<const unsigned char*>(wq_gate_up);
