@@ -5,13 +5,14 @@
 //                           against the numpy rule the reference spells (emmy/compiler/loader/quant.py:1655-1735).
 //   quant_fp8_rows_vec_kernel  the same for few rows (decode): one 1024-thread CTA per row, the row held in registers
 //                           between the maximum and the encode, 16-byte loads; also clears the status word.
-//   fp8_decode_kernel       M <= 16 (decode-shaped): a bandwidth kernel.  Weights [N,K] are read as stored, 16 bytes
-//                           per lane, straight into m16n8k32 e4m3 A fragments (no dequant instruction at all);
-//                           four warps of a CTA split K for one 16-column tile and meet in shared memory; all CTAs
-//                           of a launch are resident at once.  Narrow weights split K over the CTAs of a cluster,
-//                           whose partial sums meet through distributed shared memory.  Launched as a programmatic
-//                           dependent of the quantize: its first weight bytes are in flight before the activation
-//                           codes exist.
+//   fp8_decode_tc_kernel    M <= 16 (decode-shaped): tcgen05 with the operands' roles swapped -- 128-channel weight tiles
+//                           are the MMA's A operand, the rows its B operand with N = 16 -- so one TMA thread streams the
+//                           weight, 108 KB CTAs of two consecutive launches share an SM, and the weights are requested
+//                           before griddepcontrol.wait (the quantize and the linear are both programmatic dependents).
+//   fp8_decode_kernel       the mma.sync bandwidth kernel that preceded it, now the decode path of the block-scaled form
+//                           (fp8_block.cu): weights [N,K] read as stored, 16 bytes per lane, straight into m16n8k32 e4m3
+//                           A fragments; four warps of a CTA split K for one 16-column tile and meet in shared memory;
+//                           narrow weights split K over the CTAs of a cluster (distributed shared memory).
 //   fp8_gemm_tc_kernel      M > 16 (prefill-shaped): tcgen05.mma kind::f8f6f4, 256x256 output tile per CTA, K-major
 //                           operands brought by TMA with the 128-byte swizzle through a 3-stage mbarrier ring,
 //                           f32 accumulators in TMEM, one producer warp, one MMA warp, eight epilogue warps that read
@@ -200,6 +201,121 @@ __global__ void __launch_bounds__(kDecWarps * 32, BLOCK ? 5 : 8) fp8_decode_kern
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ------------------------------------------------------------------------------------------------ decode-shaped, tensor cores
+// M <= 16 on tcgen05 with the operands' roles swapped: a 128-channel tile of the WEIGHT is the MMA's A operand (M = 128),
+// the activation rows are B (N = 16), so a K step stages 16 KB of weights and 2 KB of rows and the streaming is done by
+// one TMA thread instead of 128 lanes' loads.  Six stages are 108 KB: the CTAs of two consecutive launches share an SM,
+// the later one requesting its weights before griddepcontrol.wait while the earlier one computes.  The accumulator is
+// [channel = TMEM lane][row = column]; the epilogue applies s_x[m] * s_w[n].
+constexpr int kDtStages = 6;
+constexpr int kDtTileW = 128 * 128, kDtTileX = 16 * 128;
+constexpr size_t kDtSmem = static_cast<size_t>(kDtStages) * (kDtTileW + kDtTileX) + 1024 + 256;
+constexpr int kDtThreads = 6 * 32;
+constexpr uint32_t kDtTmemCols = 32;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kDtThreads, 2)
+    fp8_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const float* __restrict__ sx,
+                         const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* tiles_w = smem;
+    unsigned char* tiles_x = smem + kDtStages * kDtTileW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kDtStages * (kDtTileW + kDtTileX));
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kDtStages;
+    uint64_t* acc_ready = bars + 2 * kDtStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kDtStages + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 128;
+    const int k_blocks = K / 128;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDtStages; ++s) {
+            tc::mbar_init(tc::smem_u32(full + s), 1);
+            tc::mbar_init(tc::smem_u32(empty + s), 1);
+        }
+        tc::mbar_init(tc::smem_u32(acc_ready), 1);
+        tc::mbar_fence_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kDtTmemCols);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (tc::elect_one()) {
+            tc::tma_prefetch_desc(&map_w);
+            tc::tma_prefetch_desc(&map_x);
+            // the weights never depend on the kernel before (the activation quantize): request them ahead of the wait
+            const int ahead = k_blocks < kDtStages ? k_blocks : kDtStages;
+            for (int kb = 0; kb < ahead; ++kb) {
+                const uint32_t bar = tc::smem_u32(full + kb);
+                tc::mbar_expect_tx(bar, kDtTileW + kDtTileX);
+                tc::tma_load_2d(tc::smem_u32(tiles_w + kb * kDtTileW), &map_w, kb * 128, n0, bar);
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int kb = 0; kb < ahead; ++kb) tc::tma_load_2d(tc::smem_u32(tiles_x + kb * kDtTileX), &map_x, kb * 128, 0, tc::smem_u32(full + kb));
+            for (int kb = ahead; kb < k_blocks; ++kb) {
+                const int s = kb % kDtStages;
+                if (!tc::mbar_wait(tc::smem_u32(empty + s), ((kb / kDtStages) - 1) & 1)) {
+                    atomicExch(status, 1);
+                    break;
+                }
+                const uint32_t bar = tc::smem_u32(full + s);
+                tc::mbar_expect_tx(bar, kDtTileW + kDtTileX);
+                tc::tma_load_2d(tc::smem_u32(tiles_w + s * kDtTileW), &map_w, kb * 128, n0, bar);
+                tc::tma_load_2d(tc::smem_u32(tiles_x + s * kDtTileX), &map_x, kb * 128, 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // bounded waits count from the moment the codes exist
+        if (tc::elect_one()) {
+            constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, 16);
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kDtStages;
+                if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kDtStages) & 1)) {
+                    atomicExch(status, 2);
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t w_addr = tc::smem_u32(tiles_w + s * kDtTileW), x_addr = tc::smem_u32(tiles_x + s * kDtTileX);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    tc::mma_f8f6f4(tmem_base, tc::smem_desc_k_sw128(w_addr + ks * 32), tc::smem_desc_k_sw128(x_addr + ks * 32), idesc, kb > 0 || ks > 0);
+                tc::mma_commit(tc::smem_u32(empty + s));
+            }
+            tc::mma_commit(tc::smem_u32(acc_ready));
+        }
+    } else {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;  // this thread's output channel
+        const bool ok = tc::mbar_wait(tc::smem_u32(acc_ready), 0);
+        if (!ok && lane == 0) atomicExch(status, 3);
+        tc::fence_after_sync();
+        if (ok) {
+            uint32_t r[16];
+            tc::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), r);
+            tc::tmem_ld_wait();
+            if (n < N) {
+                const float wsc = sw[n];
+#pragma unroll
+                for (int m = 0; m < 16; ++m)
+                    if (m < M) y[static_cast<size_t>(m) * N + n] = from_float<OutT>(__uint_as_float(r[m]) * sx[m] * wsc);
+            }
+        }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, kDtTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ prefill-shaped
 // A CTA computes a 256 x 256 output tile as two 128-row MMAs that share one B tile in shared memory: per byte
 // brought in from L2 that is 256 flop, against 170 for a 128 x 256 tile, and L2 -> SM bandwidth is what bounds
@@ -358,6 +474,9 @@ template <typename InT, int kVecs>
 __global__ void __launch_bounds__(1024) quant_fp8_rows_vec_kernel(const InT* __restrict__ x, int64_t K, uint8_t* __restrict__ q,
                                                                   float* __restrict__ scale, int* __restrict__ status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the linear behind this may start fetching weights
+    // launched as a programmatic dependent itself: the kernel before it (usually the previous linear on this workspace)
+    // may still read the codes, scales and status word this one rewrites
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     constexpr int kPer = 16 / sizeof(InT);  // elements per 16-byte vector
     __shared__ float warp_max[32];
     __shared__ float row_scale;
@@ -433,11 +552,18 @@ static int quant_rows_launch(const InT* x, int64_t M, int64_t K, uint8_t* q, flo
     constexpr int kPer = 16 / sizeof(InT);
     const bool vec = M <= 64 && K % kPer == 0 && aligned(x, 16) && aligned(q, 8) && K / kPer <= 4 * 1024;
     if (vec) {
-        const unsigned grid = static_cast<unsigned>(M);
-        if (K / kPer <= 1024) quant_fp8_rows_vec_kernel<InT, 1><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
-        else if (K / kPer <= 2048) quant_fp8_rows_vec_kernel<InT, 2><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
-        else quant_fp8_rows_vec_kernel<InT, 4><<<grid, 1024, 0, stream>>>(x, K, q, scale, status);
-        EQ_LAUNCH_OK("quant_fp8_rows_vec_kernel");
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(M));
+        cfg.blockDim = dim3(1024);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // resident, past its launch latency, when the kernel before it ends
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (K / kPer <= 1024) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_rows_vec_kernel<InT, 1>, x, K, q, scale, status));
+        else if (K / kPer <= 2048) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_rows_vec_kernel<InT, 2>, x, K, q, scale, status));
+        else EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_rows_vec_kernel<InT, 4>, x, K, q, scale, status));
         return EQ_OK;
     }
     if (status) EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
@@ -527,7 +653,30 @@ int fp8_block_decode_launch(const uint8_t* w, const float* sw, int64_t N, int64_
 template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
-    if (M <= 16) return fp8_decode_typed<OutT, false>(w, sw, N, K, qx, sx, M, y, stream);
+    if (M <= 16) {
+        // (measured at K = 5120, N = 17408: 18.4 / 19.0 / 19.8 us at M = 1 / 8 / 16 against 21.0 / 24.4 / 32.7 us for the
+        // mma.sync decode kernel, which now serves only the block-scaled form)
+        CUtensorMap map_w, map_x;
+        int st = make_tensor_map_2d(&map_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != EQ_OK) return st;
+        st = make_tensor_map_2d(&map_x, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, 16, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != EQ_OK) return st;
+        auto kernel = fp8_decode_tc_kernel<OutT>;
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDtSmem)));
+        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(N, 128)));
+        cfg.blockDim = dim3(kDtThreads);
+        cfg.dynamicSmemBytes = kDtSmem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status));
+        return EQ_OK;
+    }
     if (M <= 128) return fp8_tc_launch<OutT, 1, 128>(w, sw, N, K, qx, sx, M, y, status, stream);
     return fp8_tc_launch<OutT, 2, 256>(w, sw, N, K, qx, sx, M, y, status, stream);
 }

@@ -352,15 +352,6 @@ constexpr int kDecStageBytes = kDecTileW + kDecTileX + 2 * kDecSf;
 constexpr size_t kDecSmem = static_cast<size_t>(kDecStages) * kDecStageBytes + 1024 + 256;
 constexpr uint32_t kDecTmemCols = 64;  // 16 accumulator columns, 16 + 16 scale columns
 
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-}
-
 template <typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 2)
     nvfp4_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -465,7 +456,7 @@ __global__ void __launch_bounds__(kGemmThreads, 2)
         if (ok) {
             const float g = gx[0] * gw[0];
             uint32_t r[16];
-            tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), r);
+            tc::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), r);
             tc::tmem_ld_wait();
             if (n < N) {
 #pragma unroll
