@@ -350,7 +350,7 @@ def wl_fp8_block(device, rank, m, n=GEMM_N, k=GEMM_K):
 
     return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + (n // 128) * (k // 128) * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n,
                 peak_mult=2.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.fp8_block_status(wsp, m, k),
-                kernel="fp8_decode_kernel<__nv_bfloat16, 1, true>" if m <= 8 else "fp8_block_tc_kernel<__nv_bfloat16, BN>",
+                kernel="fp8_block_decode_tc_kernel<__nv_bfloat16>" if m <= 16 else "fp8_block_tc_kernel<__nv_bfloat16, BN>",
                 dtype="e4m3 weights (128 x 128 block scales) and activations (per token, per 128 of K), f32 accumulate, bf16 out")
 
 
@@ -372,7 +372,7 @@ def wl_fp8(device, rank, m, n=GEMM_N, k=GEMM_K):
 
     return dict(step=step, calls=copies, kernels_per_call=2, alg_bytes=n * k + n * 4 + m * k * 2 + m * n * 2, flops=2.0 * m * k * n, peak_mult=2.0,
                 h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.fp8_status(wsp, m, k),
-                kernel="fp8_gemm_tc_kernel<__nv_bfloat16>" if m > 16 else "fp8_decode_kernel",
+                kernel="fp8_gemm_tc_kernel<__nv_bfloat16>" if m > 16 else "fp8_decode_tc_kernel<__nv_bfloat16>",
                 dtype="e4m3 weights and activations, f32 accumulate, bf16 out")
 
 

@@ -9,8 +9,8 @@
 //   quant_fp8_groups_kernel  s_x[m, kb] = max(amax_kb |x|, 1e-12) / 448, q = e4m3_rne_satfinite(x / s_x): the per-token
 //                            rule of fp8_linear.cu applied per 128-element group; one warp per group.  Inside the linear
 //                            it also clears the status word and lets the kernel behind it start early.
-//   M <= 8                   the decode kernel of fp8_linear.cu with per-block promotion (fp8_block_decode_launch)
-//   M > 8                    tcgen05 with a fresh accumulator per K block and promotion in registers (fp8_block_tc.cu)
+//   fp8_block_tc.cu          tcgen05 with a fresh accumulator per K block and promotion in registers: a swapped-operand
+//                            decode tile for M <= 16, 128 x 128 tiles up to 128 rows, 128 x 256 tiles above
 //   fp8_block_gemm_kernel    the mma.sync form, kept for an output that is not 16-byte aligned: 128 x 128 output tile per
 //                            CTA, K in steps of one scale block, operand tiles by cp.async into XOR-swizzled shared
 //                            memory (two stages), fragments by ldmatrix, products by mma.sync m16n8k32 e4m3 into a
@@ -19,8 +19,6 @@
 
 namespace eq {
 
-int fp8_block_decode_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, int act_dtype,
-                            void* y, cudaStream_t stream);  // fp8_linear.cu
 int fp8_block_tc_launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw, void* y, int64_t M, int64_t N, int64_t K,
                         int act_dtype, int* status, cudaStream_t stream);  // fp8_block_tc.cu
 
@@ -36,6 +34,9 @@ template <typename InT>
 __global__ void __launch_bounds__(256) quant_fp8_groups_kernel(const InT* __restrict__ x, int64_t M, int64_t K, uint8_t* __restrict__ q,
                                                                float* __restrict__ scale, int* __restrict__ status) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the linear behind this may start fetching weights
+    // inside the linear this kernel is a programmatic dependent itself: the kernel before it (usually the previous
+    // linear on this workspace) may still read the codes, scales and status word it rewrites
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (status && blockIdx.x == 0 && threadIdx.x == 0) *status = 0;  // the linear's status word, cleared on the way
     const int64_t groups = K / 128;
     const int64_t gw = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -200,14 +201,21 @@ static int quant_fp8_groups(const void* x, int64_t M, int64_t K, int in_dtype, u
     EQ_REQUIRE(K % 128 == 0, EQ_ERR_UNSUPPORTED, "eq_quant_fp8_per_group: K must be a multiple of 128");
     EQ_REQUIRE(aligned(q, 4), EQ_ERR_BAD_ALIGN, "eq_quant_fp8_per_group: q must be 4-byte aligned");
     const int64_t warps = M * (K / 128);
-    const unsigned grid = static_cast<unsigned>(ceil_div(warps * 32, 256));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(warps * 32, 256)));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (status && M <= 128) ? 1 : 0;  // decode-sized calls inside the linear: resident when the kernel before it ends
     switch (in_dtype) {
-        case EQ_F16: quant_fp8_groups_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), M, K, q, scale, status); break;
-        case EQ_BF16: quant_fp8_groups_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), M, K, q, scale, status); break;
-        case EQ_F32: quant_fp8_groups_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(x), M, K, q, scale, status); break;
+        case EQ_F16: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_groups_kernel<__half>, static_cast<const __half*>(x), M, K, q, scale, status)); break;
+        case EQ_BF16: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_groups_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x), M, K, q, scale, status)); break;
+        case EQ_F32: EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, quant_fp8_groups_kernel<float>, static_cast<const float*>(x), M, K, q, scale, status)); break;
         default: return fail(EQ_ERR_BAD_ARG, "eq_quant_fp8_per_group: unknown dtype %d", in_dtype);
     }
-    EQ_LAUNCH_OK("quant_fp8_groups_kernel");
     return EQ_OK;
 }
 
@@ -238,12 +246,9 @@ extern "C" int eq_fp8_block_linear(const uint8_t* weight, const float* weight_sc
     int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + blk_align(static_cast<size_t>(M) * (K / 128) * sizeof(float)));
     int st = quant_fp8_groups(x, M, K, act_dtype, qx, sx, status, stream);
     if (st != EQ_OK) return st;
-    // decode-shaped calls stream the weight through the bandwidth kernel of the per-channel form, with per-block promotion
-    // (one row block of the MMA fragments; measured: 23-25 us at M <= 8 against 30 us on the tensor path, 45 against 30 at M = 16)
-    if (M <= 8) return fp8_block_decode_launch(weight, weight_scale, N, K, qx, sx, M, act_dtype, y, stream);
-    // everything else runs on the tensor cores (fp8_block_tc.cu: 128-column tiles up to 128 rows, 256-column tiles above);
-    // the mma.sync tile kernel below serves an unaligned y
-    if (aligned(y, 16)) return fp8_block_tc_launch(qx, sx, weight, weight_scale, y, M, N, K, act_dtype, status, stream);
+    // the tensor cores (fp8_block_tc.cu: swapped-operand decode tile up to 16 rows, 128-column tiles up to 128 rows, 256-column
+    // tiles above); the mma.sync tile kernel below serves an unaligned y
+    if (M <= 16 || aligned(y, 16)) return fp8_block_tc_launch(qx, sx, weight, weight_scale, y, M, N, K, act_dtype, status, stream);
     const dim3 grid(static_cast<unsigned>(N / kBB), static_cast<unsigned>(ceil_div(M, kBB)));
     const size_t smem = 2 * kBlkStage;
     if (act_dtype == EQ_F16) {

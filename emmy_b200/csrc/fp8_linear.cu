@@ -9,10 +9,6 @@
 //                           are the MMA's A operand, the rows its B operand with N = 16 -- so one TMA thread streams the
 //                           weight, 108 KB CTAs of two consecutive launches share an SM, and the weights are requested
 //                           before griddepcontrol.wait (the quantize and the linear are both programmatic dependents).
-//   fp8_decode_kernel       the mma.sync bandwidth kernel that preceded it, now the decode path of the block-scaled form
-//                           (fp8_block.cu): weights [N,K] read as stored, 16 bytes per lane, straight into m16n8k32 e4m3
-//                           A fragments; four warps of a CTA split K for one 16-column tile and meet in shared memory;
-//                           narrow weights split K over the CTAs of a cluster (distributed shared memory).
 //   fp8_gemm_tc_kernel      M > 16 (prefill-shaped): tcgen05.mma kind::f8f6f4, 256x256 output tile per CTA, K-major
 //                           operands brought by TMA with the 128-byte swizzle through a 3-stage mbarrier ring,
 //                           f32 accumulators in TMEM, one producer warp, one MMA warp, eight epilogue warps that read
@@ -66,142 +62,6 @@ __global__ void __launch_bounds__(256) quant_fp8_rows_kernel(const InT* __restri
 }
 
 // ------------------------------------------------------------------------------------------------ decode-shaped
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-constexpr int kDecWarps = 4;
-
-// One CTA per (16 output columns, K split); warp w takes the w-th quarter of the CTA's K range.  A lane's 16 weight
-// bytes of row g (and g+8) feed two k32 MMAs; which actual k a fragment slot means is irrelevant as long as the
-// activation fragment uses the same bytes, so both are simply the lane's 16 consecutive bytes.  SPLIT > 1: the CTAs of a
-// cluster share a tile; CTA 0 of the cluster adds the others' partial sums out of their shared memory.
-// BLOCK: the block-scaled form -- sw is [N / 128][K / 128], sx is [M][K / 128], and every 128 elements of K (two steps)
-// are promoted into the sum with their own pair of scales; the K ranges of CTAs and warps are whole 128-blocks then.
-template <typename OutT, int MT, bool BLOCK>
-__global__ void __launch_bounds__(kDecWarps * 32, BLOCK ? 5 : 8) fp8_decode_kernel(const uint8_t* __restrict__ w, const float* __restrict__ sw,
-                                                                     const uint8_t* __restrict__ qx, const float* __restrict__ sx,
-                                                                     OutT* __restrict__ y, int M, int N, int K, int split) {
-    __shared__ float red[kDecWarps][MT][16][8];
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, j = lane & 3;
-    const int tile = blockIdx.x / split, part = blockIdx.x - tile * split;
-    const int n0 = tile * 16;
-    constexpr int kUnit = BLOCK ? 2 : 1;  // steps that stay together
-    const int steps = K / 64 / kUnit;
-    const int c0 = steps * part / split, c1 = steps * (part + 1) / split;
-    const int s0 = kUnit * (c0 + (c1 - c0) * warp / kDecWarps), s1 = kUnit * (c0 + (c1 - c0) * (warp + 1) / kDecWarps);
-    const uint8_t* wr_lo = w + static_cast<size_t>(n0 + g) * K + 16 * j;
-    const uint8_t* wr_hi = wr_lo + static_cast<size_t>(8) * K;
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-
-    constexpr int U = 4;  // steps in flight per warp
-    uint4 a_lo[U], a_hi[U];
-    auto fetch = [&](int sb) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (sb + u < s1) {
-                a_lo[u] = ld_stream_v4(wr_lo + static_cast<size_t>(sb + u) * 64);
-                a_hi[u] = ld_stream_v4(wr_hi + static_cast<size_t>(sb + u) * 64);
-            }
-        }
-    };
-    fetch(s0);
-    // the weights never depend on the kernel before; the activation codes do (they come from the quantize)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int kblocks = K / 128;
-    for (int sb = s0; sb < s1; sb += U) {
-        if constexpr (!BLOCK) {
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (sb + u < s1) {
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const int m = mt * 8 + g;
-                        uint4 b = make_uint4(0, 0, 0, 0);
-                        if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u) * 64 + 16 * j));
-                        mma_e4m3(acc[mt], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b.x, b.y);
-                        mma_e4m3(acc[mt], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b.z, b.w);
-                    }
-                }
-            }
-        } else {
-            // two steps are one 128-block (s0 and s1 are even): its products are promoted with the block's scales
-#pragma unroll
-            for (int u = 0; u < U; u += 2) {
-                if (sb + u < s1) {
-                    const int kb = (sb + u) >> 1;
-                    const float wsc = __ldg(sw + static_cast<size_t>(n0 >> 7) * kblocks + kb);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const int m = mt * 8 + g;
-                        float blk[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            uint4 b = make_uint4(0, 0, 0, 0);
-                            if (m < M) b = __ldg(reinterpret_cast<const uint4*>(qx + static_cast<size_t>(m) * K + (sb + u + h) * 64 + 16 * j));
-                            mma_e4m3(blk, a_lo[u + h].x, a_hi[u + h].x, a_lo[u + h].y, a_hi[u + h].y, b.x, b.y);
-                            mma_e4m3(blk, a_lo[u + h].z, a_hi[u + h].z, a_lo[u + h].w, a_hi[u + h].w, b.z, b.w);
-                        }
-                        const int m0 = mt * 8 + 2 * j;
-                        const float f0 = m0 < M ? wsc * __ldg(sx + static_cast<size_t>(m0) * kblocks + kb) : 0.f;
-                        const float f1 = m0 + 1 < M ? wsc * __ldg(sx + static_cast<size_t>(m0 + 1) * kblocks + kb) : 0.f;
-                        acc[mt][0] = fmaf(blk[0], f0, acc[mt][0]);
-                        acc[mt][1] = fmaf(blk[1], f1, acc[mt][1]);
-                        acc[mt][2] = fmaf(blk[2], f0, acc[mt][2]);
-                        acc[mt][3] = fmaf(blk[3], f1, acc[mt][3]);
-                    }
-                }
-            }
-        }
-        fetch(sb + U);  // the other warps of the SM keep the memory system busy while this batch is on its way
-    }
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        red[warp][mt][g][2 * j] = acc[mt][0];
-        red[warp][mt][g][2 * j + 1] = acc[mt][1];
-        red[warp][mt][g + 8][2 * j] = acc[mt][2];
-        red[warp][mt][g + 8][2 * j + 1] = acc[mt][3];
-    }
-    if (split == 1) {
-        __syncthreads();
-    } else {
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
-    if (part == 0) {
-        for (int idx = threadIdx.x; idx < MT * 128; idx += kDecWarps * 32) {
-            const int mt = idx >> 7, n = (idx >> 3) & 15, mm = idx & 7;
-            const int m = mt * 8 + mm;
-            if (m < M) {
-                float s = 0.f;
-#pragma unroll
-                for (int wv = 0; wv < kDecWarps; ++wv) s += red[wv][mt][n][mm];
-                for (int peer = 1; peer < split; ++peer) {
-#pragma unroll
-                    for (int wv = 0; wv < kDecWarps; ++wv) {
-                        uint32_t remote;
-                        float v;
-                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(&red[wv][mt][n][mm]))), "r"(peer));
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-                        s += v;
-                    }
-                }
-                if constexpr (BLOCK) y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s);
-                else y[static_cast<size_t>(m) * N + n0 + n] = from_float<OutT>(s * sx[m] * sw[n0 + n]);
-            }
-        }
-    }
-    if (split > 1)  // the peers' shared memory must outlive the reads above
-        asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// ------------------------------------------------------------------------------------------------ decode-shaped, tensor cores
 // M <= 16 on tcgen05 with the operands' roles swapped: a 128-channel tile of the WEIGHT is the MMA's A operand (M = 128),
 // the activation rows are B (N = 16), so a K step stages 16 KB of weights and 2 KB of rows and the streaming is done by
 // one TMA thread instead of 128 lanes' loads.  Six stages are 108 KB: the CTAs of two consecutive launches share an SM,
@@ -614,48 +474,12 @@ static int fp8_tc_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K
     return EQ_OK;
 }
 
-// M <= 16.  BLOCK: block-scaled operands (see the kernel).  Launched as a programmatic dependent of the quantize.
-template <typename OutT, bool BLOCK>
-static int fp8_decode_typed(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, OutT* y,
-                            cudaStream_t stream) {
-    // all CTAs resident at once (eight per SM); narrow weights split K over clusters until there are enough CTAs
-    const long long tiles = N / 16, want = 6LL * sm_count();
-    int split = 1;
-    while (split < 8 && tiles * split < want && K / 64 / (2 * split) >= kDecWarps * (BLOCK ? 2 : 1)) split *= 2;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(tiles * split));
-    cfg.blockDim = dim3(kDecWarps * 32);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = static_cast<unsigned>(split);
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = split > 1 ? 2 : 1;
-    const int Mi = static_cast<int>(M), Ni = static_cast<int>(N), Ki = static_cast<int>(K);
-    if (M <= 8) EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 1, BLOCK>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
-    else EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, fp8_decode_kernel<OutT, 2, BLOCK>, w, sw, qx, sx, y, Mi, Ni, Ki, split));
-    return EQ_OK;
-}
-
-// The block-scaled linear's decode-shaped calls (fp8_block.cu): sw [N / 128][K / 128], sx [M][K / 128].
-namespace eq {
-int fp8_block_decode_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M, int act_dtype,
-                            void* y, cudaStream_t stream) {
-    return act_dtype == EQ_F16 ? fp8_decode_typed<__half, true>(w, sw, N, K, qx, sx, M, static_cast<__half*>(y), stream)
-                               : fp8_decode_typed<__nv_bfloat16, true>(w, sw, N, K, qx, sx, M, static_cast<__nv_bfloat16*>(y), stream);
-}
-}  // namespace eq
-
 template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
     if (M <= 16) {
         // (measured at K = 5120, N = 17408: 18.4 / 19.0 / 19.8 us at M = 1 / 8 / 16 against 21.0 / 24.4 / 32.7 us for the
-        // mma.sync decode kernel, which now serves only the block-scaled form)
+        // mma.sync bandwidth kernel this replaced)
         CUtensorMap map_w, map_x;
         int st = make_tensor_map_2d(&map_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EQ_OK) return st;
