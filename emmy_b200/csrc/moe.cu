@@ -247,10 +247,13 @@ __global__ void moe_plan_small_kernel(const int32_t* __restrict__ eid, const int
 // xp[pos][:] = x[src_of[pos]][:], 16 bytes per thread.
 __global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int32_t* __restrict__ src_of, const int32_t* __restrict__ total_rows,
                                        int row_vec, uint4* __restrict__ xp) {
-    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    const int64_t pos = idx / row_vec, v = idx - pos * row_vec;
-    if (pos >= *total_rows) return;
-    xp[idx] = x[static_cast<int64_t>(src_of[pos]) * row_vec + v];
+    // a grid-stride loop over the rows that exist: the row list of an expert-parallel receive buffer is mostly empty
+    // slots (world x capacity), and a thread per slot would launch hundreds of thousands of CTAs that only return
+    const int64_t total = static_cast<int64_t>(*total_rows) * row_vec;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t pos = idx / row_vec, v = idx - pos * row_vec;
+        xp[idx] = x[static_cast<int64_t>(src_of[pos]) * row_vec + v];
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ grouped GEMM
@@ -440,7 +443,8 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
         const int act = sizeof(ActT) == 2 && std::is_same<ActT, __half>::value ? EQ_F16 : EQ_BF16;
         const int row_vec = static_cast<int>(H * 2 / 16);
         EQ_REQUIRE(aligned(x, 16) && aligned(out, 16), EQ_ERR_BAD_ALIGN, "grouped expert GEMM: activations and outputs must be 16-byte aligned");
-        moe_gather_rows_kernel<<<static_cast<unsigned>(ceil_div(R * row_vec, 256)), 256, 0, stream>>>(
+        const int64_t gather_ctas = ceil_div(R * row_vec, 256);
+        moe_gather_rows_kernel<<<static_cast<unsigned>(gather_ctas < 32LL * sm_count() ? gather_ctas : 32LL * sm_count()), 256, 0, stream>>>(
             static_cast<const uint4*>(x), w.src_of, w.offsets + E, row_vec, reinterpret_cast<uint4*>(w.out));
         EQ_LAUNCH_OK("moe_gather_rows_kernel");
         int st = w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq_gate_up), static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes,
