@@ -38,8 +38,11 @@ __device__ __forceinline__ void stream_flush(const W4Params& p, float* acc_slot,
 // Shared-memory bytes of the staged x: [item][row block of 8][16-byte chunk 0..3][lane][16 B].
 static size_t staged_x_bytes(int64_t K, int rows) { return static_cast<size_t>(K / 128) * (rows / 8) * 2048; }
 
-// DEPTH: items in flight per warp.  STAGED: x lives in shared memory.
-template <typename ActT, int MT, int DEPTH, bool STAGED>
+// DEPTH: items in flight per warp.  STAGED: x lives in shared memory.  SPLIT (implies STAGED): K is cut into p.splits
+// slices; CTA = (group of column tiles, K slice) stages only its slice of x, and the slices' partial sums meet in the f32
+// workspace (atomic adds; the CTA whose arrival completes a group converts it and leaves workspace and counter zero).
+// For shapes whose M x K does not fit shared memory, or whose tiles do not fill the SMs evenly.
+template <typename ActT, int MT, int DEPTH, bool STAGED, bool SPLIT = false>
 __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(const W4Params p) {
     constexpr int kStreamDepth = DEPTH;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -49,18 +52,28 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     const int g = lane >> 2, j = lane & 3;
     // whole tiles per CTA: the first span_rem CTAs take one tile more
     const int cta = blockIdx.x;
-    const int tile0 = cta * p.span_base + min(cta, p.span_rem);
-    const int ntiles = p.span_base + (cta < p.span_rem ? 1 : 0);
+    int tile0 = cta * p.span_base + min(cta, p.span_rem);
+    int ntiles = p.span_base + (cta < p.span_rem ? 1 : 0);
+    int i0 = 0, ipp = p.items;  // this CTA's run of items of every tile
+    if (SPLIT) {
+        const int grp = cta / p.splits, sp = cta - grp * p.splits;
+        tile0 = grp * p.group_tiles;
+        ntiles = min(p.group_tiles, p.N / 16 - tile0);
+        i0 = p.items * sp / p.splits;
+        ipp = p.items * (sp + 1) / p.splits - i0;
+    }
     float* acc_s = reinterpret_cast<float*>(smem_all + kStreamWarps * kStreamDepth * kSlot);  // [ntiles][kRows][16]
     for (int i = threadIdx.x; i < ntiles * kRows * 16; i += kStreamWarps * 32) acc_s[i] = 0.f;
     // equal spans of the CTA's items per warp
-    const int cta_items = ntiles * p.items;
+    const int cta_items = ntiles * ipp;
     const int q0 = static_cast<int>(static_cast<long long>(cta_items) * warp / kStreamWarps);
     const int q1 = static_cast<int>(static_cast<long long>(cta_items) * (warp + 1) / kStreamWarps);
     const int n = q1 - q0;
-    int slot_t = q0 / p.items;          // tile slot inside the CTA
-    int it = q0 - slot_t * p.items;     // item inside the tile
-    const size_t first = (static_cast<size_t>(tile0) * p.items + q0) * kItemBytes;  // records are contiguous across tiles
+    int slot_t = q0 / ipp;          // tile slot inside the CTA
+    int it = q0 - slot_t * ipp;     // item inside the CTA's run of the tile
+    // unsplit: records are contiguous across tiles; split: a tile's run starts i0 items into the tile
+    const size_t first = SPLIT ? (static_cast<size_t>(tile0 + slot_t) * p.items + i0 + it) * kItemBytes
+                               : (static_cast<size_t>(tile0) * p.items + q0) * kItemBytes;
     const unsigned char* rec = p.wq + first + lane * 16;
     const unsigned char* met = p.wq + first + 1024 + g * 8;  // lanes of one g share it
     const ActT* x = static_cast<const ActT*>(p.x);
@@ -72,12 +85,21 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     unsigned char* ring = smem_all + warp * (kStreamDepth * kSlot);
     const uint32_t ring_lo = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + lane * 16;
     const uint32_t ring_meta = static_cast<uint32_t>(__cvta_generic_to_shared(ring)) + 1024 + g * 8;
+    size_t issue_off = 0;        // split: byte offset of the next item to request, and the items left of its tile's run
+    int issue_room = ipp - it;
     auto issue = [&](int d, int i) {
         if (i < n) {
-            const size_t off = static_cast<size_t>(i) * kItemBytes;
+            const size_t off = SPLIT ? issue_off : static_cast<size_t>(i) * kItemBytes;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_lo + d * kSlot), "l"(rec + off) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ring_lo + d * kSlot + 512), "l"(rec + off + 512) : "memory");
             if (j == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(ring_meta + d * kSlot), "l"(met + off) : "memory");
+            if (SPLIT) {
+                issue_off += kItemBytes;
+                if (--issue_room == 0) {  // the next item opens the next tile's run
+                    issue_off += static_cast<size_t>(p.items - ipp) * kItemBytes;
+                    issue_room = ipp;
+                }
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -95,12 +117,12 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     if (STAGED) {
         // one warp per (item, row block): lane (g, j) copies the 64 bytes it will read as MMA operands, 16 at a time
         unsigned char* xw = const_cast<unsigned char*>(xs);
-        for (int b = warp; b < p.items * MT; b += kStreamWarps) {
+        for (int b = warp; b < ipp * MT; b += kStreamWarps) {
             const int bi = b / MT, mt = b - bi * MT;
             const int m = mt * 8 + g;
             uint4 v[4];
             if (m < p.M) {
-                load_x<ActT>(x + static_cast<size_t>(m) * p.K, p.perm, bi * 128 + 32 * j, v);
+                load_x<ActT>(x + static_cast<size_t>(m) * p.K, p.perm, (i0 + bi) * 128 + 32 * j, v);
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = make_uint4(0, 0, 0, 0);
@@ -147,7 +169,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
             w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
         }
         dirty = true;
-        if (++it == p.items) {  // the span leaves this tile
+        if (++it == ipp) {  // the span leaves this tile
             stream_flush<ActT, MT>(p, acc_s + slot_t * kRows * 16, yacc, g, j);
             dirty = false;
             it = 0;
@@ -156,8 +178,33 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     }
     if (dirty) stream_flush<ActT, MT>(p, acc_s + slot_t * kRows * 16, yacc, g, j);
     __syncthreads();
-    // ---- the CTA owns its tiles outright: convert and store
     ActT* y = static_cast<ActT*>(p.y);
+    if (SPLIT) {
+        // ---- the K slices of a tile group meet in the workspace; the last one to arrive converts and leaves zeros behind
+        __shared__ int last_s;
+        const int rows_s = p.M, grp = cta / p.splits;
+        for (int idx = threadIdx.x; idx < ntiles * rows_s * 16; idx += kStreamWarps * 32) {
+            const int t = idx / (rows_s * 16), r = idx - t * (rows_s * 16);
+            const int m = r >> 4, nn = r & 15;
+            atomicAdd(p.wsp + static_cast<size_t>(m) * p.N + (tile0 + t) * 16 + nn, acc_s[(t * kRows + m) * 16 + nn]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) last_s = atomicAdd(p.counters + grp, 1) == p.splits - 1;
+        __syncthreads();
+        if (!last_s) return;
+        __threadfence();
+        for (int idx = threadIdx.x; idx < ntiles * rows_s * 16; idx += kStreamWarps * 32) {
+            const int t = idx / (rows_s * 16), r = idx - t * (rows_s * 16);
+            const int m = r >> 4, nn = r & 15;
+            float* wv = p.wsp + static_cast<size_t>(m) * p.N + (tile0 + t) * 16 + nn;
+            y[static_cast<size_t>(m) * p.N + (tile0 + t) * 16 + nn] = from_float<ActT>(__ldcg(wv));
+            __stcg(wv, 0.f);
+        }
+        if (threadIdx.x == 0) p.counters[grp] = 0;
+        return;
+    }
+    // ---- the CTA owns its tiles outright: convert and store
     const int rows = p.M;
     for (int idx = threadIdx.x; idx < ntiles * rows * 16; idx += kStreamWarps * 32) {
         const int t = idx / (rows * 16), r = idx - t * (rows * 16);
@@ -174,9 +221,9 @@ static size_t stream_smem(long long tiles, long long ctas, int rows, int depth, 
     return bytes <= 220 * 1024 ? bytes : 0;
 }
 
-template <typename ActT, int MT, int DEPTH, bool STAGED>
+template <typename ActT, int MT, int DEPTH, bool STAGED, bool SPLIT = false>
 static int launch_stream_depth(W4Params p, size_t smem, long long ctas, cudaStream_t stream) {
-    auto kernel = w4a16_stream_kernel<ActT, MT, DEPTH, STAGED>;
+    auto kernel = w4a16_stream_kernel<ActT, MT, DEPTH, STAGED, SPLIT>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas));
@@ -200,6 +247,8 @@ static int launch_stream(W4Params p, cudaStream_t stream, bool* fits) {
     p.span_base = static_cast<int>(tiles / ctas);
     p.span_rem = static_cast<int>(tiles % ctas);
     p.acc_tiles = static_cast<int>(ceil_div(tiles, ctas));
+    p.splits = 1;
+    p.group_tiles = 0;
     const int rows = MT * 8;
     *fits = true;
     // x in shared memory where it fits beside a ring of at least three items (gathered rows are read in place)
@@ -208,6 +257,32 @@ static int launch_stream(W4Params p, cudaStream_t stream, bool* fits) {
         if (const size_t smem = stream_smem(tiles, ctas, rows, 6, staged)) return launch_stream_depth<ActT, MT, 6, true>(p, smem, ctas, stream);
         if (const size_t smem = stream_smem(tiles, ctas, rows, 4, staged)) return launch_stream_depth<ActT, MT, 4, true>(p, smem, ctas, stream);
         if (const size_t smem = stream_smem(tiles, ctas, rows, 3, staged)) return launch_stream_depth<ActT, MT, 3, true>(p, smem, ctas, stream);
+        // x does not fit: cut K into 2, 4 or 8 slices so that a slice does, groups of tiles x slices filling the SMs as
+        // evenly as whole tiles allow (needs the f32 workspace)
+        if (p.wsp && p.counters) {
+            int best_s = 0;
+            long long best_ctas = 0, best_tpg = 0;
+            for (int sp = 2; sp <= 8; sp *= 2) {
+                if (p.items < sp) break;
+                const size_t slice = staged_x_bytes(static_cast<int64_t>(ceil_div(static_cast<long long>(p.items), sp)) * 128, rows);
+                const long long groups_want = sm_count() / sp > 0 ? sm_count() / sp : 1;
+                const long long tpg = ceil_div(tiles, groups_want);
+                const long long groups = ceil_div(tiles, tpg);
+                if (!stream_smem(tpg, 1, rows, 4, slice)) continue;
+                if (groups * sp > best_ctas) {
+                    best_ctas = groups * sp;
+                    best_s = sp;
+                    best_tpg = tpg;
+                }
+            }
+            if (best_s) {
+                p.splits = best_s;
+                p.group_tiles = static_cast<int>(best_tpg);
+                p.acc_tiles = static_cast<int>(best_tpg);
+                const size_t slice = staged_x_bytes(static_cast<int64_t>(ceil_div(static_cast<long long>(p.items), best_s)) * 128, rows);
+                return launch_stream_depth<ActT, MT, 4, true, true>(p, stream_smem(best_tpg, 1, rows, 4, slice), best_ctas, stream);
+            }
+        }
     }
     // the deepest ring that fits
     if (const size_t smem = stream_smem(tiles, ctas, rows, 6, 0)) return launch_stream_depth<ActT, MT, 6, false>(p, smem, ctas, stream);

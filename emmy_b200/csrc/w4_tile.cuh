@@ -24,6 +24,7 @@ struct W4Params {
     int scale_dtype;
     int span_base, span_rem;  // stream kernel: whole tiles per CTA, plus one for the first span_rem CTAs
     int acc_tiles;            // stream kernel: accumulator slots per CTA (the largest tile count)
+    int group_tiles;          // stream kernel, K split: column tiles per CTA group (CTA = group * splits + K slice)
     const int32_t* x_rows;    // optional: activation row m of the problem is row x_rows[m] of x (gather)
     const int32_t* y_rows;    // optional: output row m of the problem is row y_rows[m] of y (scatter)
     const uint64_t* y_ptrs;   // optional (unsplit tiles only): output row m starts at address y_ptrs[m], possibly on a peer GPU
