@@ -500,16 +500,26 @@ static int experts_forward(const MoeWorkspace& w, const void* wq_gate_up, const 
 
 // ------------------------------------------------------------------------------------------------ expert parallel
 // Experts sharded E / world per rank; every rank holds T tokens.  The token exchange is done by the kernels themselves
-// over peer memory (NVLink): the dispatch stores each picked row straight into the owner's receive buffer, the second
-// expert GEMM stores each result row straight into the token's rank (per-row destination addresses), and epoch
-// flags written with release / read with acquire at system scope order the two.  No host read, no NCCL call.
-//   rank r's receive buffer: [world sources][cap rows][H]; source s fills its own region in arrival order
-//   flags of rank r: [0][s] = epoch of the last dispatch that source s completed into r's buffer
-//                    [1][d] = epoch of the last call whose results destination d has stored into r's `back`
+// over peer memory (NVLink): rows are stored straight into the owner's receive buffer IN EXPERT ORDER, so the owner's
+// grouped GEMM reads them in place (no row list, no count / scatter / gather pass), the second expert GEMM stores each
+// result row straight into the token's rank (per-row destination addresses), and epoch flags written with release /
+// read with acquire at system scope order the steps.  No host read, no NCCL call.
+//   1. every rank counts its picks per (destination, local expert) and stores that table into EVERY rank's copy of the
+//      count tables (a few hundred bytes per peer), then raises flag [0][me] everywhere;
+//   2. with all tables in hand every rank knows every destination's layout -- expert e's rows start at the sum of the
+//      experts before it, source s's segment inside it at the sum of the sources before it -- so it knows where its
+//      own rows go (no second round) and, for its own buffer, the row blocks of the grouped GEMM;
+//   3. the dispatch stores each picked row at (its segment's start + the pick's position in the segment) of the
+//      owner's buffer, with (source rank, pick index) as the return address; flag [1][me] everywhere;
+//   4. grouped FFN over the buffer; the second GEMM's epilogue stores to the sources' `back`; flag [2][me]; combine.
+//   rank r's receive buffer: [world * cap rows][H], shared by the sources
+//   count tables of rank r: [source][destination][local expert]
+//   flags of rank r: [0][s] counts of s arrived, [1][s] rows of s arrived, [2][d] results from d stored into r's `back`
 // Waits are bounded (about a second) and report through the status word.
-constexpr int kEpOverflow = 32;   // a source had more rows for one destination than `cap`
-constexpr int kEpWaitReady = 64;  // a peer's dispatch did not arrive in time
-constexpr int kEpWaitDone = 65;   // a peer's results did not arrive in time
+constexpr int kEpOverflow = 32;    // a destination was sent more rows than its receive buffer holds; the excess was dropped
+constexpr int kEpWaitReady = 64;   // a peer's rows did not arrive in time
+constexpr int kEpWaitDone = 65;    // a peer's results did not arrive in time
+constexpr int kEpWaitCounts = 66;  // a peer's count table did not arrive in time
 constexpr long long kEpWaitCycles = 2000000000LL;
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -521,51 +531,35 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
-// One warp per pick: copy the token's row into the owner's receive region of this rank and record (local expert,
-// return slot).  The last CTA to finish publishes the row counts and raises this rank's flag at every destination.
-__global__ void ep_dispatch_kernel(const eq_ep_peers pe, const uint4* __restrict__ x, const int32_t* __restrict__ ids, int picks, int topk,
-                                   int per_rank, int row_vec, int32_t* __restrict__ send_cursor, int32_t* __restrict__ cta_done,
-                                   uint32_t epoch, const uint32_t* __restrict__ epoch_dev, int32_t* __restrict__ status) {
-    __shared__ int s_last;
+// One thread per pick: its position among this rank's picks for the same (destination, local expert).
+__global__ void ep_count_kernel(const int32_t* __restrict__ ids, int picks, int per_rank, int world, int32_t* __restrict__ cnt,
+                                int32_t* __restrict__ pos, int32_t* __restrict__ status) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= picks) return;
+    const int id = ids[i];
+    if (id < 0 || id >= per_rank * world) {
+        atomicExch(status, kBadExpertId);
+        pos[i] = -1;
+        return;
+    }
+    pos[i] = atomicAdd(cnt + id, 1);  // id = destination * per_rank + local expert
+}
+
+// One CTA: this rank's table [destination][local expert] into every rank's copy, then the flag.
+__global__ void ep_publish_counts_kernel(const eq_ep_peers pe, const int32_t* __restrict__ cnt, int per_rank, uint32_t epoch,
+                                         const uint32_t* __restrict__ epoch_dev) {
     if (epoch == 0) epoch = *epoch_dev;
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp < picks) {
-        const int id = ids[warp];
-        if (id < 0 || id >= per_rank * pe.world) {
-            if (lane == 0) atomicExch(status, kBadExpertId);
-        } else {
-            const int dest = id / per_rank, le = id - dest * per_rank;
-            int slot = 0;
-            if (lane == 0) slot = atomicAdd(send_cursor + dest, 1);
-            slot = __shfl_sync(0xFFFFFFFFu, slot, 0);
-            if (slot >= pe.cap) {
-                if (lane == 0) atomicExch(status, kEpOverflow);
-            } else {
-                const size_t row = static_cast<size_t>(pe.rank) * pe.cap + slot;
-                uint4* dst = static_cast<uint4*>(pe.recv_x[dest]) + row * row_vec;
-                const uint4* src = x + static_cast<size_t>(warp / topk) * row_vec;
-                for (int v = lane; v < row_vec; v += 32) dst[v] = src[v];
-                if (lane == 0) *reinterpret_cast<int2*>(pe.recv_meta[dest] + 2 * row) = make_int2(le, warp);
-            }
-        }
+    const int entries = pe.world * per_rank;
+    for (int d = 0; d < pe.world; ++d) {
+        int32_t* dst = pe.recv_count[d] + static_cast<size_t>(pe.rank) * entries;
+        for (int i = threadIdx.x; i < entries; i += blockDim.x) dst[i] = cnt[i];
     }
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = atomicAdd(cta_done, 1) == static_cast<int>(gridDim.x) - 1;
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (static_cast<int>(threadIdx.x) < pe.world) {
-        const int d = threadIdx.x;
-        const int sent = atomicExch(send_cursor + d, 0);
-        pe.recv_count[d][pe.rank] = sent < pe.cap ? sent : static_cast<int>(pe.cap);
-        __threadfence_system();
-        st_release_sys(pe.flags[d] + pe.rank, epoch);
-    }
-    if (threadIdx.x == 0) *cta_done = 0;
+    if (static_cast<int>(threadIdx.x) < pe.world) st_release_sys(pe.flags[threadIdx.x] + pe.rank, epoch);
 }
 
-// which = 0: wait for every source's dispatch; 1: for every destination's results.
+// which = 0: every source's counts; 1: every source's rows; 2: every destination's results.
 __global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int world, int which, uint32_t epoch, const uint32_t* __restrict__ epoch_dev,
                                int32_t* __restrict__ status) {
     if (static_cast<int>(threadIdx.x) >= world) return;
@@ -574,34 +568,111 @@ __global__ void ep_wait_kernel(const uint32_t* __restrict__ flags, int world, in
     const long long start = clock64();
     while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
         if (clock64() - start > kEpWaitCycles) {
-            atomicExch(status, which == 0 ? kEpWaitReady : kEpWaitDone);
+            atomicExch(status, which == 0 ? kEpWaitCounts : which == 1 ? kEpWaitReady : kEpWaitDone);
             return;
         }
     }
 }
 
-// The received rows as a row list for the grouped FFN: row r = (source r / cap, slot r % cap).
-__global__ void ep_build_rows_kernel(const eq_ep_peers pe, const int32_t* __restrict__ meta, const int32_t* __restrict__ counts, int e_local,
-                                     size_t row_bytes, int32_t* __restrict__ eid, int32_t* __restrict__ src_row, uint64_t* __restrict__ row_ptr,
-                                     int32_t* __restrict__ status) {
-    const int64_t r = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (r >= static_cast<int64_t>(pe.world) * pe.cap) return;
-    const int s = static_cast<int>(r / pe.cap);
-    const int64_t i = r - static_cast<int64_t>(s) * pe.cap;
-    int e = -1;
-    uint64_t ptr = 0;
-    if (i < counts[s]) {
-        const int2 m = *reinterpret_cast<const int2*>(meta + 2 * r);
-        if (m.x >= 0 && m.x < e_local) {
-            e = m.x;
-            ptr = reinterpret_cast<uint64_t>(static_cast<unsigned char*>(pe.back[s]) + static_cast<size_t>(m.y) * row_bytes);
-        } else {
-            atomicExch(status, kBadExpertId);
+// One CTA.  From the count tables [source][destination][expert]: where this rank's rows start in every destination's
+// buffer (send_base[destination][expert]), and for this rank's own buffer the expert offsets and the grouped GEMM's row
+// blocks.  Counts are clamped to what can be true (a table that never arrived is zeros or an older call's), rows beyond a
+// buffer's capacity are dropped and reported.  Leaves this rank's own count table zero for the next call.
+__global__ void ep_layout_kernel(const eq_ep_peers pe, int per_rank, int block_rows, int max_blocks, int32_t* __restrict__ cnt,
+                                 int32_t* __restrict__ send_base, int32_t* __restrict__ offsets, RowBlock* __restrict__ blocks,
+                                 int32_t* __restrict__ n_blocks, int32_t* __restrict__ status) {
+    extern __shared__ int32_t sh[];  // [world][per_rank] totals per (destination, expert), then starts
+    const int world = pe.world, me = pe.rank, entries = world * per_rank;
+    const int32_t* tab = pe.recv_count[me];
+    const int64_t room = static_cast<int64_t>(world) * pe.cap;
+    auto count_of = [&](int s, int de) {
+        const int c = tab[static_cast<size_t>(s) * entries + de];
+        return c < 0 ? 0 : c > pe.cap ? static_cast<int>(pe.cap) : c;
+    };
+    for (int de = threadIdx.x; de < entries; de += blockDim.x) {
+        int total = 0, before_me = 0;
+        for (int s = 0; s < world; ++s) {
+            const int c = count_of(s, de);
+            if (s < me) before_me += c;
+            total += c;
+        }
+        sh[de] = total;
+        send_base[de] = before_me;  // + the expert's start, below
+        cnt[de] = 0;
+    }
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < world) {  // exclusive scan over the experts of one destination
+        const int d = threadIdx.x;
+        int64_t run = 0;
+        for (int e = 0; e < per_rank; ++e) {
+            const int total = sh[d * per_rank + e];
+            sh[d * per_rank + e] = static_cast<int>(run < room ? run : room);
+            run += total;
+        }
+        if (run > room) atomicExch(status, kEpOverflow);
+        if (d == me) offsets[per_rank] = static_cast<int>(run < room ? run : room);
+    }
+    __syncthreads();
+    for (int de = threadIdx.x; de < entries; de += blockDim.x) send_base[de] += sh[de];
+    if (threadIdx.x == 0) {
+        int nb = 0;
+        const int total_rows = offsets[per_rank];
+        for (int e = 0; e < per_rank; ++e) {
+            const int start = sh[me * per_rank + e];
+            const int end = e + 1 < per_rank ? sh[me * per_rank + e + 1] : total_rows;
+            offsets[e] = start;
+            for (int r0 = start; r0 < end && nb < max_blocks; r0 += block_rows) {
+                blocks[nb].expert = e;
+                blocks[nb].row0 = r0;
+                blocks[nb].rows = min(block_rows, end - r0);
+                blocks[nb].pad = 0;
+                ++nb;
+            }
+        }
+        *n_blocks = nb;
+    }
+}
+
+// One warp per pick: copy the token's row to its place in the owner's buffer and record (source rank, pick index).  The
+// last CTA to finish raises this rank's rows-arrived flag at every destination.
+__global__ void ep_dispatch_kernel(const eq_ep_peers pe, const uint4* __restrict__ x, const int32_t* __restrict__ ids,
+                                   const int32_t* __restrict__ pos, const int32_t* __restrict__ send_base, int picks, int topk, int per_rank,
+                                   int row_vec, int32_t* __restrict__ cta_done, uint32_t epoch, const uint32_t* __restrict__ epoch_dev) {
+    __shared__ int s_last;
+    if (epoch == 0) epoch = *epoch_dev;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp < picks) {
+        const int p_in = pos[warp];
+        if (p_in >= 0) {
+            const int id = ids[warp], dest = id / per_rank;
+            const int64_t row = static_cast<int64_t>(send_base[id]) + p_in;
+            if (row < static_cast<int64_t>(pe.world) * pe.cap) {  // (the layout kernel reported the overflow)
+                uint4* dst = static_cast<uint4*>(pe.recv_x[dest]) + row * row_vec;
+                const uint4* src = x + static_cast<size_t>(warp / topk) * row_vec;
+                for (int v = lane; v < row_vec; v += 32) dst[v] = src[v];
+                if (lane == 0) *reinterpret_cast<int2*>(pe.recv_meta[dest] + 2 * row) = make_int2(pe.rank, warp);
+            }
         }
     }
-    eid[r] = e;
-    src_row[r] = static_cast<int32_t>(r);
-    row_ptr[r] = ptr;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(cta_done, 1) == static_cast<int>(gridDim.x) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence_system();
+    if (static_cast<int>(threadIdx.x) < pe.world) st_release_sys(pe.flags[threadIdx.x] + pe.world + pe.rank, epoch);
+    if (threadIdx.x == 0) *cta_done = 0;
+}
+
+// Each received row's destination: the pick's row of the source's `back`, as mapped on this rank.
+__global__ void ep_row_ptr_kernel(const eq_ep_peers pe, const int32_t* __restrict__ meta, const int32_t* __restrict__ total_rows, size_t row_bytes,
+                                  uint64_t* __restrict__ row_ptr) {
+    const int total = *total_rows;
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < total; r += gridDim.x * blockDim.x) {
+        const int2 m = *reinterpret_cast<const int2*>(meta + 2 * static_cast<size_t>(r));
+        row_ptr[r] = (m.x >= 0 && m.x < pe.world && m.y >= 0) ? reinterpret_cast<uint64_t>(static_cast<unsigned char*>(pe.back[m.x]) + static_cast<size_t>(m.y) * row_bytes)
+                                                              : 0ull;
+    }
 }
 
 // The call counter kept on the device (epoch argument 0): every call bumps it once, in lockstep on all ranks, so a
@@ -612,14 +683,16 @@ __global__ void ep_signal_done_kernel(const eq_ep_peers pe, uint32_t epoch, cons
     if (static_cast<int>(threadIdx.x) >= pe.world) return;
     if (epoch == 0) epoch = *epoch_dev;
     __threadfence_system();
-    st_release_sys(pe.flags[threadIdx.x] + pe.world + pe.rank, epoch);
+    st_release_sys(pe.flags[threadIdx.x] + 2 * pe.world + pe.rank, epoch);
 }
 
 struct EpWorkspace {
     MoeWorkspace moe;
-    int32_t *send_cursor, *cta_done, *eid, *src_row;
+    int32_t *cnt, *send_base, *pos, *cta_done;
     uint32_t* epoch;
     uint64_t* row_ptr;
+    RowBlock* blocks;
+    int block_rows, max_blocks;  // 8-row blocks through the streaming tier, or 256-row blocks through the tensor tier
     size_t bytes;
 };
 
@@ -634,12 +707,20 @@ static EpWorkspace carve_ep(void* base, int64_t world, int64_t cap, int64_t e_lo
         o += align_up(bytes, 256);
         return r;
     };
-    w.send_cursor = reinterpret_cast<int32_t*>(take(EQ_EP_MAX_RANKS * 4));
+    w.cnt = reinterpret_cast<int32_t*>(take(world * e_local * 4));        // zero between calls
+    w.send_base = reinterpret_cast<int32_t*>(take(world * e_local * 4));
+    w.pos = reinterpret_cast<int32_t*>(take(R * 4));                      // world * cap >= this rank's picks
     w.cta_done = reinterpret_cast<int32_t*>(take(4));
     w.epoch = reinterpret_cast<uint32_t*>(take(4));
-    w.eid = reinterpret_cast<int32_t*>(take(R * 4));
-    w.src_row = reinterpret_cast<int32_t*>(take(R * 4));
     w.row_ptr = reinterpret_cast<uint64_t*>(take(R * 8));
+    // The tier follows the rows a rank expects (about one source's worth: cap), not the buffer's capacity, which is
+    // `world` times that; the block list is sized for the capacity.
+    const int64_t stream_blocks = R / 8 + e_local + 1;
+    const bool stream_tier = stream_rows(cap, e_local) && stream_blocks < (1 << 30) && moe_stream_fits(static_cast<int>(stream_blocks), 2 * I) &&
+                             moe_stream_fits(static_cast<int>(stream_blocks), H);
+    w.block_rows = stream_tier ? 8 : 256;
+    w.max_blocks = static_cast<int>(R / w.block_rows + e_local + 1);
+    w.blocks = reinterpret_cast<RowBlock*>(take(sizeof(RowBlock) * w.max_blocks));
     w.bytes = o;
     return w;
 }
@@ -783,33 +864,71 @@ extern "C" int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int 
     EpWorkspace w = carve_ep(workspace, world, cap, E_local, H, I);
     const int me = peers->rank;
     const int64_t picks = T * topk, R = world * cap;
+    EQ_REQUIRE(picks <= R, EQ_ERR_UNSUPPORTED, "eq_ep_moe_w4a16: %lld picks exceed the %lld rows the buffers were made for", (long long)picks,
+               (long long)R);
     const int row_vec = static_cast<int>(H * 2 / 16);
+    const int per_rank = static_cast<int>(E_local);
     EQ_CUDA_OK(cudaMemsetAsync(w.moe.status, 0, 4, stream));
     if (epoch == 0) {
         ep_next_epoch_kernel<<<1, 1, 0, stream>>>(w.epoch);
         EQ_LAUNCH_OK("ep_next_epoch_kernel");
     }
-    // every rank launches the dispatch, with or without tokens of its own: its flag is what the others wait for
-    const unsigned dgrid = static_cast<unsigned>(picks > 0 ? ceil_div(picks * 32, 256) : 1);
-    ep_dispatch_kernel<<<dgrid, 256, 0, stream>>>(*peers, static_cast<const uint4*>(x), ids, static_cast<int>(picks), static_cast<int>(topk),
-                                                  static_cast<int>(E_local), row_vec, w.send_cursor, w.cta_done, epoch, w.epoch, w.moe.status);
-    EQ_LAUNCH_OK("ep_dispatch_kernel");
+    // 1. this rank's counts per (destination, expert), published to every rank (with or without tokens of its own)
+    if (picks > 0) {
+        ep_count_kernel<<<static_cast<unsigned>(ceil_div(picks, 256)), 256, 0, stream>>>(ids, static_cast<int>(picks), per_rank, static_cast<int>(world),
+                                                                                         w.cnt, w.pos, w.moe.status);
+        EQ_LAUNCH_OK("ep_count_kernel");
+    }
+    ep_publish_counts_kernel<<<1, 256, 0, stream>>>(*peers, w.cnt, per_rank, epoch, w.epoch);
+    EQ_LAUNCH_OK("ep_publish_counts_kernel");
     ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 0, epoch, w.epoch, w.moe.status);
     EQ_LAUNCH_OK("ep_wait_kernel");
-    ep_build_rows_kernel<<<static_cast<unsigned>(ceil_div(R, 256)), 256, 0, stream>>>(*peers, peers->recv_meta[me], peers->recv_count[me],
-                                                                                      static_cast<int>(E_local), static_cast<size_t>(H) * 2, w.eid,
-                                                                                      w.src_row, w.row_ptr, w.moe.status);
-    EQ_LAUNCH_OK("ep_build_rows_kernel");
-    if (act_dtype == EQ_F16)
-        st = experts_forward<__half>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, 0, w.eid, R, w.moe.out,
-                                     w.row_ptr, stream);
-    else
-        st = experts_forward<__nv_bfloat16>(w.moe, wq_gate_up, wq_down, scale_dtype, E_local, H, I, peers->recv_x[me], w.src_row, 0, w.eid, R,
-                                            w.moe.out, w.row_ptr, stream);
+    // 2. every destination's layout; this rank's row blocks
+    const bool stream_tier = w.block_rows == 8;
+    const int br = w.block_rows;
+    ep_layout_kernel<<<1, 256, world * per_rank * sizeof(int32_t), stream>>>(*peers, per_rank, br, w.max_blocks, w.cnt, w.send_base, w.moe.offsets,
+                                                                           w.blocks, w.moe.n_blocks, w.moe.status);
+    EQ_LAUNCH_OK("ep_layout_kernel");
+    // 3. rows to their owners, in expert order
+    const unsigned dgrid = static_cast<unsigned>(picks > 0 ? ceil_div(picks * 32, 256) : 1);
+    ep_dispatch_kernel<<<dgrid, 256, 0, stream>>>(*peers, static_cast<const uint4*>(x), ids, w.pos, w.send_base, static_cast<int>(picks),
+                                                  static_cast<int>(topk), per_rank, row_vec, w.cta_done, epoch, w.epoch);
+    EQ_LAUNCH_OK("ep_dispatch_kernel");
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 1, epoch, w.epoch, w.moe.status);
+    EQ_LAUNCH_OK("ep_wait_kernel");
+    ep_row_ptr_kernel<<<static_cast<unsigned>(4 * sm_count()), 256, 0, stream>>>(*peers, peers->recv_meta[me], w.moe.offsets + E_local,
+                                                                                 static_cast<size_t>(H) * 2, w.row_ptr);
+    EQ_LAUNCH_OK("ep_row_ptr_kernel");
+    // 4. the grouped FFN over the buffer as it lies; results straight to the tokens' ranks
+    const size_t stride_gu = static_cast<size_t>(2 * I / 16) * (H / 128) * kItemBytes, stride_dn = static_cast<size_t>(H / 16) * (I / 128) * kItemBytes;
+    const unsigned char* gu = static_cast<const unsigned char*>(wq_gate_up);
+    const unsigned char* dn = static_cast<const unsigned char*>(wq_down);
+    if (stream_tier) {
+        st = moe_stream_launch(gu, stride_gu, scale_dtype, peers->recv_x[me], w.moe.h1, nullptr, nullptr, nullptr, w.blocks, w.moe.n_blocks,
+                               w.max_blocks, H, 2 * I, act_dtype, stream);
+        if (st != EQ_OK) return st;
+        const unsigned sgrid = static_cast<unsigned>(ceil_div(R * I, 256));
+        if (act_dtype == EQ_F16)
+            moe_swiglu_kernel<__half><<<sgrid, 256, 0, stream>>>(reinterpret_cast<const __half*>(w.moe.h1), w.moe.offsets + E_local, static_cast<int>(I),
+                                                                 reinterpret_cast<__half*>(w.moe.h));
+        else
+            moe_swiglu_kernel<__nv_bfloat16><<<sgrid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(w.moe.h1), w.moe.offsets + E_local,
+                                                                        static_cast<int>(I), reinterpret_cast<__nv_bfloat16*>(w.moe.h));
+        EQ_LAUNCH_OK("moe_swiglu_kernel");
+        st = moe_stream_launch(dn, stride_dn, scale_dtype, w.moe.h, nullptr, nullptr, nullptr, w.row_ptr, w.blocks, w.moe.n_blocks, w.max_blocks, I, H,
+                               act_dtype, stream);
+    } else {
+        EQ_REQUIRE(aligned(peers->recv_x[me], 16), EQ_ERR_BAD_ALIGN, "eq_ep_moe_w4a16: the receive buffer must be 16-byte aligned");
+        st = w4_gemm_tc_grouped_launch(gu, stride_gu, scale_dtype, peers->recv_x[me], w.moe.h, R, 2 * I, H, act_dtype, w.blocks, w.moe.n_blocks,
+                                       w.max_blocks, nullptr, nullptr, true, w.moe.status, stream);
+        if (st != EQ_OK) return st;
+        st = w4_gemm_tc_grouped_launch(dn, stride_dn, scale_dtype, w.moe.h, nullptr, R, H, I, act_dtype, w.blocks, w.moe.n_blocks, w.max_blocks,
+                                       nullptr, w.row_ptr, false, w.moe.status, stream);
+    }
     if (st != EQ_OK) return st;
     ep_signal_done_kernel<<<1, 32, 0, stream>>>(*peers, epoch, w.epoch);
     EQ_LAUNCH_OK("ep_signal_done_kernel");
-    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 1, epoch, w.epoch, w.moe.status);
+    ep_wait_kernel<<<1, 32, 0, stream>>>(peers->flags[me], static_cast<int>(world), 2, epoch, w.epoch, w.moe.status);
     EQ_LAUNCH_OK("ep_wait_kernel");
     if (T == 0) return EQ_OK;
     return eq_moe_combine(peers->back[me], scores, T, topk, H, act_dtype, y, stream_);
@@ -823,9 +942,9 @@ extern "C" int eq_ep_moe_status(const void* workspace, int64_t world, int64_t ca
     EQ_CUDA_OK(cudaMemcpyAsync(&host, w.moe.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     EQ_CUDA_OK(cudaStreamSynchronize(stream));
     EQ_REQUIRE(host != kBadExpertId, EQ_ERR_BAD_ARG, "eq_ep_moe_status: an expert id out of range was met");
-    EQ_REQUIRE(host != kEpOverflow, EQ_ERR_UNSUPPORTED, "eq_ep_moe_status: a rank had more rows for one destination than the receive capacity; rows were dropped");
-    EQ_REQUIRE(host != kEpWaitReady && host != kEpWaitDone, EQ_ERR_TIMEOUT, "eq_ep_moe_status: a peer's %s did not arrive within the wait bound",
-               host == kEpWaitReady ? "dispatch" : "results");
+    EQ_REQUIRE(host != kEpOverflow, EQ_ERR_UNSUPPORTED, "eq_ep_moe_status: a rank was sent more rows than its receive buffer holds; rows were dropped");
+    EQ_REQUIRE(host != kEpWaitReady && host != kEpWaitDone && host != kEpWaitCounts, EQ_ERR_TIMEOUT,
+               "eq_ep_moe_status: a peer's %s did not arrive within the wait bound", host == kEpWaitCounts ? "counts" : host == kEpWaitReady ? "rows" : "results");
     EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_ep_moe_status: a bounded pipeline wait of the tensor path ran out (code %d)", host);
     return EQ_OK;
 }

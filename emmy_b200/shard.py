@@ -173,15 +173,16 @@ def ep_moe_forward(
 class EpMoe:
     """Expert-parallel W4A16 MoE whose token exchange is done by the kernels over peer memory (eq_ep_moe_w4a16).
 
-    Owns one symmetric buffer per rank (receive rows, their metadata and counts, returned rows, epoch flags), mapped
-    into every rank of `group` through torch symmetric memory, and a local workspace.  `t_max` bounds the tokens of a
-    call on any rank.  `cap` is the number of rows one source may send to one destination in one call; the default,
-    all of a rank's picks, can never overflow.  A smaller cap saves receive memory (`default_cap` gives twice the
-    balanced share plus slack) but is a bet on the routing: rows beyond it are DROPPED, which only the status word
-    reports.  Results of a call are defined only if `status()` (or `forward(..., check=True)`) comes back clean: an
-    overflow or a peer that did not arrive within the kernels' bounded wait leaves y undefined.  The call counter lives
-    on the device, so `forward` has no host read and can be captured in a CUDA graph.  Construction is collective: it
-    ends with a host barrier, so that no rank's first exchange waits on a peer that is still setting up."""
+    Owns one symmetric buffer per rank (receive rows, their return addresses, the ranks' count tables, returned rows,
+    epoch flags), mapped into every rank of `group` through torch symmetric memory, and a local workspace.  `t_max`
+    bounds the tokens of a call on any rank.  A rank's receive buffer holds `world * cap` rows, shared by the sources and
+    filled in expert order; the default cap, all of a rank's picks, can never overflow (even if every token of every rank
+    picks this rank's experts).  A smaller cap saves receive memory (`default_cap` gives twice the balanced share plus
+    slack) but is a bet on the routing: rows beyond the buffer are DROPPED, which only the status word reports.
+    Results of a call are defined only if `status()` (or `forward(..., check=True)`) comes back clean: an overflow or a
+    peer that did not arrive within the kernels' bounded wait leaves y undefined.  The call counter lives on the device,
+    so `forward` has no host read and can be captured in a CUDA graph.  Construction is collective: it ends with a host
+    barrier, so that no rank's first exchange waits on a peer that is still setting up."""
 
     @staticmethod
     def default_cap(t_max: int, topk: int, world: int) -> int:
@@ -211,7 +212,8 @@ class EpMoe:
         self.dtype, self.device = dtype, device
         esz = 2
         al = lambda v: (v + 255) // 256 * 256
-        sizes = [al(self.world * cap * hidden * esz), al(self.world * cap * 8), al(self.world * 4), al(picks * hidden * esz), al(2 * self.world * 4)]
+        sizes = [al(self.world * cap * hidden * esz), al(self.world * cap * 8), al(self.world * self.world * experts_local * 4), al(picks * hidden * esz),
+                 al(3 * self.world * 4)]
         offs = [0]
         for sz in sizes[:-1]:
             offs.append(offs[-1] + sz)

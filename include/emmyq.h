@@ -163,7 +163,8 @@ int eq_quant_fp8_per_token(const void* x, int64_t M, int64_t K, int in_dtype, ui
 size_t eq_fp8_workspace_bytes(int64_t M, int64_t K);
 /* y[M, N] = (sum_k q_x[m,k] q_w[n,k]) * s_x[m] * s_w[n] in act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * weight: e4m3 bits [N, K] as the checkpoint stores them, weight_scale: f32 [N] multiplier.  The activation is
- * quantized per token inside the call.  M <= 16 runs a weight-streaming kernel, larger M the tcgen05 tensor path.
+ * quantized per token inside the call.  Every M runs on tcgen05: M <= 16 a weight-streaming tile with the operands' roles
+ * swapped (weight tiles as the MMA's A operand), larger M the 128- and 256-row tiles.
  * The operator the reference spells as FP8 decode + dynamic activation round trip in front of a LinearOp
  * (emmy/compiler/loader/quant.py:1581-1768) and runs natively with both scales hoisted
  * (tests/compiler/passes/test_fp8_mma.py:111-120).  Needs K % 128 == 0, N % 16 == 0; workspace 256-byte aligned. */
@@ -279,12 +280,12 @@ int eq_moe_status(const void* workspace, int64_t T, int64_t E, int64_t topk, int
 #define EQ_EP_MAX_RANKS 8
 typedef struct eq_ep_peers {
     int32_t world, rank;
-    int64_t cap;                          /* rows one source may send to one destination in one call */
-    void* recv_x[EQ_EP_MAX_RANKS];        /* [world][cap][H] activation rows, written by the sources */
-    int32_t* recv_meta[EQ_EP_MAX_RANKS];  /* [world][cap][2]: local expert id, return slot (pick index at the source) */
-    int32_t* recv_count[EQ_EP_MAX_RANKS]; /* [world]: rows each source sent */
+    int64_t cap;                          /* a rank's receive buffer holds world * cap rows (shared by the sources) */
+    void* recv_x[EQ_EP_MAX_RANKS];        /* [world * cap][H] activation rows in expert order, written by the sources */
+    int32_t* recv_meta[EQ_EP_MAX_RANKS];  /* [world * cap][2]: source rank, return slot (pick index at the source) */
+    int32_t* recv_count[EQ_EP_MAX_RANKS]; /* [world sources][world destinations][E_local]: every rank's pick counts */
     void* back[EQ_EP_MAX_RANKS];          /* [T_max * topk][H]: expert outputs in the owner's pick order */
-    uint32_t* flags[EQ_EP_MAX_RANKS];     /* [2][world] uint32, zero before the first call */
+    uint32_t* flags[EQ_EP_MAX_RANKS];     /* [3][world] uint32 (counts, rows, results), zero before the first call */
 } eq_ep_peers;
 
 size_t eq_ep_moe_workspace_bytes(int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I);
@@ -297,7 +298,7 @@ size_t eq_ep_moe_workspace_bytes(int64_t world, int64_t cap, int64_t E_local, in
 int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype, int64_t E_local, int64_t topk, int64_t H,
                     int64_t I, int64_t G, const void* x, const int32_t* ids, const float* scores, int64_t T, int act_dtype,
                     void* y, const eq_ep_peers* peers, uint32_t epoch, void* workspace, size_t workspace_bytes, void* stream);
-/* EQ_ERR_TIMEOUT when a peer did not arrive in time, EQ_ERR_UNSUPPORTED when rows overflowed `cap`. */
+/* EQ_ERR_TIMEOUT when a peer did not arrive in time, EQ_ERR_UNSUPPORTED when a rank was sent more than world * cap rows. */
 int eq_ep_moe_status(const void* workspace, int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I, void* stream);
 
 #ifdef __cplusplus

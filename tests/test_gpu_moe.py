@@ -155,9 +155,9 @@ def test_expert_parallel_wait_runs_out_and_reports():
     for r in range(world):
         recv_x = torch.zeros(world * cap * h, dtype=torch.bfloat16, device="cuda")
         meta = torch.zeros(world * cap * 2, dtype=torch.int32, device="cuda")
-        count = torch.zeros(world, dtype=torch.int32, device="cuda")
+        count = torch.zeros(world * world * e_local, dtype=torch.int32, device="cuda")
         back = torch.zeros(t * k * h, dtype=torch.bfloat16, device="cuda")
-        flags = torch.zeros(2 * world, dtype=torch.int32, device="cuda")
+        flags = torch.zeros(3 * world, dtype=torch.int32, device="cuda")
         bufs.append((recv_x, meta, count, back, flags))
         peers.recv_x[r], peers.recv_meta[r], peers.recv_count[r] = recv_x.data_ptr(), meta.data_ptr(), count.data_ptr()
         peers.back[r], peers.flags[r] = back.data_ptr(), flags.data_ptr()
