@@ -67,16 +67,24 @@ __global__ void __launch_bounds__(256) quant_fp8_rows_kernel(const InT* __restri
 // one TMA thread instead of 128 lanes' loads.  Six stages are 108 KB: the CTAs of two consecutive launches share an SM,
 // the later one requesting its weights before griddepcontrol.wait while the earlier one computes.  The accumulator is
 // [channel = TMEM lane][row = column]; the epilogue applies s_x[m] * s_w[n].
-constexpr int kDtStages = 6;
-constexpr int kDtTileW = 128 * 128, kDtTileX = 16 * 128;
-constexpr size_t kDtSmem = static_cast<size_t>(kDtStages) * (kDtTileW + kDtTileX) + 1024 + 256;
+constexpr int kDtTileW = 128 * 128;
 constexpr int kDtThreads = 6 * 32;
-constexpr uint32_t kDtTmemCols = 32;
+// BX: activation rows per tile (the MMA's N): 16, 32 or 64 (128 rows leave room for three stages only and measured
+// slower than the 128 x 128 tile below: 33-35 us against 29-30 us).  As many stages as leave room for a second CTA on the SM.
+template <int BX>
+struct DtCfg {
+    static constexpr int kTileX = BX * 128;
+    static constexpr int kStages = BX == 16 ? 6 : BX == 32 ? 5 : 4;
+    static constexpr size_t kSmem = static_cast<size_t>(kStages) * (kDtTileW + kTileX) + 1024 + 256;
+    static constexpr uint32_t kTmemCols = BX < 32 ? 32 : BX;
+};
 
-template <typename OutT>
+template <typename OutT, int BX>
 __global__ void __launch_bounds__(kDtThreads, 2)
     fp8_decode_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const float* __restrict__ sx,
                          const float* __restrict__ sw, OutT* __restrict__ y, int M, int N, int K, int* __restrict__ status) {
+    constexpr int kDtStages = DtCfg<BX>::kStages, kDtTileX = DtCfg<BX>::kTileX;
+    constexpr uint32_t kDtTmemCols = DtCfg<BX>::kTmemCols;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* tiles_w = smem;
@@ -133,7 +141,7 @@ __global__ void __launch_bounds__(kDtThreads, 2)
     } else if (warp == 1) {
         asm volatile("griddepcontrol.wait;" ::: "memory");  // bounded waits count from the moment the codes exist
         if (tc::elect_one()) {
-            constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, 16);
+            constexpr uint32_t idesc = tc::instr_desc(0, 0, 128, BX);
             for (int kb = 0; kb < k_blocks; ++kb) {
                 const int s = kb % kDtStages;
                 if (!tc::mbar_wait(tc::smem_u32(full + s), (kb / kDtStages) & 1)) {
@@ -157,14 +165,17 @@ __global__ void __launch_bounds__(kDtThreads, 2)
         if (!ok && lane == 0) atomicExch(status, 3);
         tc::fence_after_sync();
         if (ok) {
-            uint32_t r[16];
-            tc::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), r);
-            tc::tmem_ld_wait();
-            if (n < N) {
-                const float wsc = sw[n];
+            const float wsc = n < N ? sw[n] : 0.f;
 #pragma unroll
-                for (int m = 0; m < 16; ++m)
-                    if (m < M) y[static_cast<size_t>(m) * N + n] = from_float<OutT>(__uint_as_float(r[m]) * sx[m] * wsc);
+            for (int c = 0; c < BX; c += 16) {
+                uint32_t r[16];
+                tc::tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, r);
+                tc::tmem_ld_wait();
+                if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < 16; ++m)
+                        if (c + m < M) y[static_cast<size_t>(c + m) * N + n] = from_float<OutT>(__uint_as_float(r[m]) * sx[c + m] * wsc);
+                }
             }
         }
     }
@@ -477,29 +488,34 @@ static int fp8_tc_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K
 template <typename OutT>
 static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K, const uint8_t* qx, const float* sx, int64_t M,
                              OutT* y, int* status, cudaStream_t stream) {
-    if (M <= 16) {
+    if (M <= 64) {
         // (measured at K = 5120, N = 17408: 18.4 / 19.0 / 19.8 us at M = 1 / 8 / 16 against 21.0 / 24.4 / 32.7 us for the
         // mma.sync bandwidth kernel this replaced)
         CUtensorMap map_w, map_x;
+        const int bx = M <= 16 ? 16 : M <= 32 ? 32 : 64;
         int st = make_tensor_map_2d(&map_w, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EQ_OK) return st;
-        st = make_tensor_map_2d(&map_x, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, 16, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+        st = make_tensor_map_2d(&map_x, qx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, bx, 128, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EQ_OK) return st;
-        auto kernel = fp8_decode_tc_kernel<OutT>;
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDtSmem)));
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(N, 128)));
-        cfg.blockDim = dim3(kDtThreads);
-        cfg.dynamicSmemBytes = kDtSmem;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status));
-        return EQ_OK;
+        auto run = [&](auto kernel, size_t smem) -> int {
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+            EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(N, 128)));
+            cfg.blockDim = dim3(kDtThreads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status));
+            return EQ_OK;
+        };
+        if (bx == 16) return run(fp8_decode_tc_kernel<OutT, 16>, DtCfg<16>::kSmem);
+        if (bx == 32) return run(fp8_decode_tc_kernel<OutT, 32>, DtCfg<32>::kSmem);
+        return run(fp8_decode_tc_kernel<OutT, 64>, DtCfg<64>::kSmem);
     }
     if (M <= 128) return fp8_tc_launch<OutT, 1, 128>(w, sw, N, K, qx, sx, M, y, status, stream);
     return fp8_tc_launch<OutT, 2, 256>(w, sw, N, K, qx, sx, M, y, status, stream);
