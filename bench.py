@@ -764,11 +764,13 @@ def run_other(args, rank, world, local_rank):
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
     name = args.workload
-    m = args.rows or {"fp8_gemm": 8192, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
+    m = args.rows or {"fp8_gemm": 8192, "fp8_block_gemm": 2048, "nvfp4_gemm": 4096, "w4a16_prefill": 2048, "moe": 4096}[name]
     if name == "moe":
         wl, metric = wl_moe(device, rank, world, m, args.exchange), "moe_w4a16_tflops"
     elif name == "fp8_gemm":
         wl, metric = wl_fp8(device, rank, m), "fp8_w8a8_gemm_tflops"
+    elif name == "fp8_block_gemm":
+        wl, metric = wl_fp8_block(device, rank, m), "fp8_block_gemm_tflops"
     elif name == "nvfp4_gemm":
         wl, metric = wl_nvfp4(device, rank, m), "nvfp4_gemm_tflops"
     else:
@@ -920,7 +922,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gptq_llama8b_mlp_m1",
-                    choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "nvfp4_gemm", "moe"])
+                    choices=["gptq_llama8b_mlp_m1", "w4a16_prefill", "fp8_gemm", "fp8_block_gemm", "nvfp4_gemm", "moe"])
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="moe workload at N > 1: who moves the tokens")
     ap.add_argument("--rows", type=int, default=0, help="rows (tokens) of the secondary workloads; 0 = the workload's default")
     ap.add_argument("--no-extra", action="store_true", help="headline only: skip the extra records")

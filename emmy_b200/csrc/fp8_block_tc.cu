@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(BlkCfg<BN>::kThreads, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + kBufs);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    // row tiles run fastest: the CTAs that share a weight tile are co-resident and the weight comes from DRAM once
+    const int n0 = blockIdx.y * kBN, m0 = blockIdx.x * kBM;
     const int k_blocks = K / kBK;
 
     if (threadIdx.x == 0) {
@@ -347,7 +348,7 @@ int launch(const uint8_t* qx, const float* sx, const uint8_t* w, const float* sw
     if (st != EQ_OK) return st;
     auto kernel = fp8_block_tc_kernel<OutT, BN>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
-    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, kBM)));
+    dim3 grid(static_cast<unsigned>(ceil_div(M, kBM)), static_cast<unsigned>(ceil_div(N, BN)));
     kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status);
     EQ_LAUNCH_OK("fp8_block_tc_kernel");
     return EQ_OK;

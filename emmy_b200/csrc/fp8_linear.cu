@@ -227,7 +227,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     float* sw_tile = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256);  // the tile's BN weight scales
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    // row tiles run fastest: the CTAs that share a weight tile are co-resident and the weight comes from DRAM once
+    const int n0 = blockIdx.y * kBN, m0 = blockIdx.x * kBM;
     const int k_blocks = K / kBK;
     const bool two_halves = HALVES == 2 && M - m0 > 128;  // the second 128 rows hold real rows
 
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tc::mbar_fence_init();
     }
     if (warp == 1) tc::tmem_alloc(tc::smem_u32(tmem_slot), kTmemCols);
-    for (int i = threadIdx.x; i < kBN; i += kGemmThreads) sw_tile[i] = blockIdx.x * kBN + i < N ? sw[blockIdx.x * kBN + i] : 0.f;
+    for (int i = threadIdx.x; i < kBN; i += kGemmThreads) sw_tile[i] = n0 + i < N ? sw[n0 + i] : 0.f;
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
@@ -478,7 +479,7 @@ static int fp8_tc_launch(const uint8_t* w, const float* sw, int64_t N, int64_t K
     if (st != EQ_OK) return st;
     auto kernel = fp8_gemm_tc_kernel<OutT, HALVES, BN>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
-    dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), static_cast<unsigned>(ceil_div(M, Cfg::kBM)));
+    dim3 grid(static_cast<unsigned>(ceil_div(M, Cfg::kBM)), static_cast<unsigned>(ceil_div(N, BN)));
     kernel<<<grid, kGemmThreads, Cfg::kSmem, stream>>>(map_a, map_b, sx, sw, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
                                                        status);
     EQ_LAUNCH_OK("fp8_gemm_tc_kernel");

@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * kBM;
+    // row tiles run fastest: the CTAs that share a weight tile are co-resident and the weight comes from DRAM once
+    const int n0 = blockIdx.y * kBN, m0 = blockIdx.x * kBM;
     const int k_blocks = K / 256;   // stages of 256 elements
     const int k64_blocks = K / 64;  // scale atoms along K
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -501,7 +502,7 @@ __global__ void __launch_bounds__(kWThreads, 1)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kWStages + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kWideBN, m0 = blockIdx.y * 256;
+    const int n0 = blockIdx.y * kWideBN, m0 = blockIdx.x * 256;  // row tiles run fastest (see above)
     const int k_blocks = K / 256;
     const int k64_blocks = K / 64;
     const bool two_halves = M - m0 > 128;
@@ -541,7 +542,7 @@ __global__ void __launch_bounds__(kWThreads, 1)
                 bulk_g2s(tc::smem_u32(sfs_a + s * kWSf), sfa + (static_cast<size_t>(rb_a) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
                 if (two_halves)
                     bulk_g2s(tc::smem_u32(sfs_a + s * kWSf + kSfBlock), sfa + (static_cast<size_t>(rb_a + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
-                const size_t tile_blocks = static_cast<size_t>(blockIdx.x) * 2;
+                const size_t tile_blocks = static_cast<size_t>(blockIdx.y) * 2;
                 bulk_g2s(tc::smem_u32(sfs_b + s * kWSf), sfb + (tile_blocks * k64_blocks + kb * 4) * 512, kSfBlock, bar);
                 bulk_g2s(tc::smem_u32(sfs_b + s * kWSf + kSfBlock), sfb + ((tile_blocks + 1) * k64_blocks + kb * 4) * 512, kSfBlock, bar);
             }
@@ -800,7 +801,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
         const int bn = M <= 128 ? 128 : 256;
         st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, bn, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != EQ_OK) return st;
-        dim3 grid(static_cast<unsigned>(ceil_div(N, bn)), static_cast<unsigned>(ceil_div(M, kBM)));
+        dim3 grid(static_cast<unsigned>(ceil_div(M, kBM)), static_cast<unsigned>(ceil_div(N, bn)));
         auto run = [&](auto kernel, size_t smem, auto* yt) -> int {
             EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
             EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
@@ -831,7 +832,7 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     st = make_tensor_map_2d(&map_b, weight, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, kWideBN, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const uint8_t* sfb_wide = weight_scale_tiled + align_up(sf_tiled_bytes(N, K), 256);
-    dim3 grid(static_cast<unsigned>(ceil_div(N, kWideBN)), static_cast<unsigned>(ceil_div(M, 256)));
+    dim3 grid(static_cast<unsigned>(ceil_div(M, 256)), static_cast<unsigned>(ceil_div(N, kWideBN)));
     auto run = [&](auto kernel, auto* yt) -> int {
         EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kWSmem)));
         kernel<<<grid, kWThreads, kWSmem, stream>>>(map_a, map_b, sfa, sfb_wide, input_scale, weight_scale_2, yt, static_cast<int>(M),
