@@ -130,7 +130,7 @@ def test_fp8_linear_full_size_m1(n):
     _check(synth.activations(1, 5120, "bf16", seed=1), bits, sw)
 
 
-@pytest.mark.parametrize("m,n,k", [(17, 144, 128), (33, 400, 1024), (48, 144, 640), (65, 272, 384), (100, 400, 256), (129, 144, 128), (257, 528, 640),
+@pytest.mark.parametrize("m,n,k", [(3, 144, 128), (17, 144, 128), (33, 400, 1024), (48, 144, 640), (65, 272, 384), (100, 400, 256), (129, 144, 128), (257, 528, 640),
                                    (600, 784, 384)])
 def test_fp8_linear_tile_edges(m, n, k):
     """Row counts on either side of the 16 / 32 / 64 / 128 / 256 boundaries where the kernel or the tiling changes, and widths

@@ -67,6 +67,22 @@ def _worker(rank, world, port, ret):
         y4 = pipe.forward(x2[:t3], ids2[:t3], scores2[:t3], local, check=True).float()
         ret[60 + rank] = float((y4 - ref2[:t3]).abs().max() / ref2[:t3].abs().max())
 
+        # many experts, few tokens: the receive side runs eight-row blocks through the streaming tier
+        e2, t4 = 64, 12
+        ex2 = make_experts(e2, h, inter, seed=5)
+        full2 = om.moe_repack(tuple(dev(a) for a in ex2["gate_up"]), tuple(dev(a) for a in ex2["down"]))
+        per2 = e2 // world
+        mine2 = slice(rank * per2, (rank + 1) * per2)
+        local2 = om.moe_repack(tuple(dev(a[mine2]) for a in ex2["gate_up"]), tuple(dev(a[mine2]) for a in ex2["down"]))
+        x4 = torch.from_numpy(synth.activations(t4, h, "bf16", seed=90 + rank)).bfloat16().cuda()
+        logits4 = torch.randn(t4, e2, generator=torch.Generator().manual_seed(95 + rank)).cuda()
+        ref4 = om.moe_forward(x4, logits4, full2, k).float()
+        ids4, scores4 = om.moe_route(logits4, k)
+        ep2 = shard.EpMoe(None, 16, k, h, inter, per2, torch.bfloat16, torch.device("cuda", rank))
+        for _ in range(2):
+            y5 = ep2.forward(x4, ids4, scores4, local2, check=True).float()
+        ret[70 + rank] = float((y5 - ref4).abs().max() / ref4.abs().max())
+
         kk, n = 512, 256
         qw, qz, sc, gi = synth.gptq_linear(kk, n, seed=9)
         tq = [torch.from_numpy(a) for a in (qw, qz, sc, gi)]
@@ -97,5 +113,6 @@ def test_sharded_paths_on_two_gpus():
     assert all(out[r] < 1e-2 for r in range(world)), out            # EP == single device up to f32 summation order
     assert all(out[30 + r] < 1e-2 and out[40 + r] < 1e-2 for r in range(world)), out  # peer-memory exchange
     assert all(out[50 + r] < 1e-2 and out[60 + r] < 1e-2 for r in range(world)), out  # the same, sliced over streams
+    assert all(out[70 + r] < 1e-2 for r in range(world)), out                          # streaming tier on the receive side
     assert all(out[10 + r] == 0.0 for r in range(world)), out      # column shards are the same columns
     assert all(out[20 + r] < 1e-2 for r in range(world)), out      # row partials summed in f32
