@@ -108,7 +108,7 @@ def _check(m, n, k, seed=0, dtype="bf16"):
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 256, 1024), (64, 512, 512), (1, 256, 512), (200, 264, 768), (128, 128, 256), (129, 224, 256), (300, 504, 512), (700, 1000, 1024),
                                    (2048, 17408, 256), (1900, 17400, 512),  # these two are large enough for the 256 x 224 tiling
-                                   (5, 264, 2048), (16, 1000, 1280), (9, 136, 256)])  # the decode tile: ragged N, ring wrap at K > 1280
+                                   (5, 264, 2048), (16, 1000, 1280), (9, 136, 256), (2, 264, 1024), (1, 136, 256)])  # the decode tile: ragged N, ring wrap at K > 1280
 def test_nvfp4_linear_tensor_path(m, n, k):
     _check(m, n, k, seed=m + n)
 
