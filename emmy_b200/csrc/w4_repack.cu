@@ -47,6 +47,9 @@ __device__ __forceinline__ int64_t word_offset(int64_t K, int64_t t, int64_t c, 
 // One thread per output word.
 __global__ void w4_repack_kernel(int fmt, const uint32_t* __restrict__ qweight, const int32_t* __restrict__ perm,
                                  int64_t K, int64_t N, unsigned char* __restrict__ wq) {
+    // blockIdx.y: the expert of a stacked call (inputs and outputs of the experts lie back to back)
+    qweight += blockIdx.y * (K * N / 8);
+    wq += blockIdx.y * ((N / 16) * (K / 128) * kItemRecord);
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     if (idx >= K * N / 8) return;
     const int wi = static_cast<int>(idx & 3);
@@ -71,6 +74,9 @@ __global__ void w4_repack_kernel(int fmt, const uint32_t* __restrict__ qweight, 
 __global__ void w4_repack_meta_kernel(int fmt, const uint32_t* __restrict__ qzeros, const uint16_t* __restrict__ scales,
                                       const int32_t* __restrict__ g_idx, const int32_t* __restrict__ perm, int64_t K,
                                       int64_t N, int64_t G, unsigned char* __restrict__ wq) {
+    qzeros += blockIdx.y * ((K / G) * (N / 8));
+    scales += blockIdx.y * ((K / G) * N);
+    wq += blockIdx.y * ((N / 16) * (K / 128) * kItemRecord);
     const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     const int64_t items = K / 128;
     if (idx >= items * (N / 2)) return;
@@ -214,6 +220,28 @@ extern "C" int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzer
     w4_repack_meta_kernel<<<static_cast<unsigned>(ceil_div((K / 128) * (N / 2), threads)), threads, 0, stream>>>(
         fmt, reinterpret_cast<const uint32_t*>(qzeros), static_cast<const uint16_t*>(scales), g_idx, row_perm, K, N, G,
         static_cast<unsigned char*>(wq));
+    EQ_LAUNCH_OK("w4_repack_meta_kernel");
+    return EQ_OK;
+}
+
+// E stacked weights (the experts of an MoE layer: qweight [E, ...], qzeros [E, ...], scales [E, K/G, N], each expert in
+// its checkpoint layout) -> E repacked blobs back to back, in two launches for the whole stack.  No g_idx (expert
+// checkpoints with act-order go through eq_w4_repack one by one).
+extern "C" int eq_w4_repack_stack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, int64_t E, int64_t K, int64_t N,
+                                  int64_t G, void* wq, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    EQ_REQUIRE(fmt == EQ_W4_AWQ || fmt == EQ_W4_GPTQ || fmt == EQ_W4_CT, EQ_ERR_BAD_ARG, "eq_w4_repack_stack: unknown format %d", fmt);
+    EQ_REQUIRE(E > 0 && E <= 65535 && qweight && qzeros && scales && wq, EQ_ERR_BAD_ARG, "eq_w4_repack_stack: null pointer or bad expert count");
+    int st = check_geometry("eq_w4_repack_stack", K, N, G);
+    if (st != EQ_OK) return st;
+    EQ_REQUIRE(aligned(wq, 16), EQ_ERR_BAD_ALIGN, "eq_w4_repack_stack: wq must be 16-byte aligned");
+    const int threads = 256;
+    const dim3 g1(static_cast<unsigned>(ceil_div(K * N / 8, threads)), static_cast<unsigned>(E));
+    w4_repack_kernel<<<g1, threads, 0, stream>>>(fmt, reinterpret_cast<const uint32_t*>(qweight), nullptr, K, N, static_cast<unsigned char*>(wq));
+    EQ_LAUNCH_OK("w4_repack_kernel");
+    const dim3 g2(static_cast<unsigned>(ceil_div((K / 128) * (N / 2), threads)), static_cast<unsigned>(E));
+    w4_repack_meta_kernel<<<g2, threads, 0, stream>>>(fmt, reinterpret_cast<const uint32_t*>(qzeros), static_cast<const uint16_t*>(scales), nullptr,
+                                                       nullptr, K, N, G, static_cast<unsigned char*>(wq));
     EQ_LAUNCH_OK("w4_repack_meta_kernel");
     return EQ_OK;
 }

@@ -80,6 +80,7 @@ def load() -> C.CDLL:
         "eq_dequant_nvfp4": (i, [p, p, p, i64, i64, i, p, p]),
         "eq_w4_repack_sizes": (i, [i64, i64, i64, szp, szp]),
         "eq_w4_repack": (i, [i, p, p, p, p, i64, i64, i64, p, p, ip, p]),
+        "eq_w4_repack_stack": (i, [i, p, p, p, i64, i64, i64, i64, p, p]),
         "eq_w4_unpack_repacked": (i, [p, i64, i64, p, p]),
         "eq_w4a16_workspace_bytes": (sz, [i64, i64, i64]),
         "eq_w4a16_linear": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p, sz, p]),

@@ -30,11 +30,9 @@ def _repack_stack(qweight, qzeros, scales, group, fmt):
     a, c = C.c_size_t(), C.c_size_t()
     L.check(lib.eq_w4_repack_sizes(k, n, group, C.byref(a), C.byref(c)))
     blob = torch.empty(e * a.value, dtype=torch.uint8, device=qweight.device)
-    uses = C.c_int(0)
-    for i in range(e):
-        dst = C.c_void_p(blob.data_ptr() + i * a.value)
-        L.check(lib.eq_w4_repack(_FMT[fmt], _ptr(qweight[i]), _ptr(qzeros[i]), _ptr(scales[i]), None, k, n, group, dst, None,
-                                 C.byref(uses), _stream()))
+    # the whole stack in two launches
+    L.check(lib.eq_w4_repack_stack(_FMT[fmt], _ptr(qweight.contiguous()), _ptr(qzeros.contiguous()), _ptr(scales.contiguous()), e, k, n, group,
+                                   _ptr(blob), _stream()))
     return blob, k, n
 
 

@@ -104,6 +104,12 @@ int eq_w4_repack_sizes(int64_t K, int64_t N, int64_t G, size_t* wq_bytes, size_t
  * stream once to read that flag.  `perm` may be NULL when g_idx is NULL. */
 int eq_w4_repack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, const int32_t* g_idx,
                  int64_t K, int64_t N, int64_t G, void* wq, int32_t* perm, int* uses_perm, void* stream);
+/* The experts of an MoE layer in one call: E stacked weights (qweight [E, ...], qzeros [E, ...], scales [E, K/G, N], each
+ * expert in its checkpoint layout, no g_idx) -> E repacked blobs back to back (eq_w4_repack_sizes bytes each), the layout
+ * eq_moe_w4a16 takes.  Two launches for the whole stack, no host synchronization (the reference stacks expert weights at
+ * load the same way, emmy/compiler/trace/huggingface.py:2110-2141). */
+int eq_w4_repack_stack(int fmt, const int32_t* qweight, const int32_t* qzeros, const void* scales, int64_t E, int64_t K, int64_t N,
+                       int64_t G, void* wq, void* stream);
 /* Inverse view for round-trip checks: repacked blob -> uint8 nibbles [K, N] in repacked row order. */
 int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, void* stream);
 
