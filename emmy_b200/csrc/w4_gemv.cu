@@ -1,7 +1,8 @@
 // W4A16 linear: the entry points and their dispatch.
 //
 //   M == 1         w4a16_gemv1_kernel (w4_gemv1.cu): half-SM CTAs, equal item spans, launches overlap in pairs.
-//   2 <= M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles.
+//   2 <= M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles, x staged in shared
+//                  memory (whole, or a K slice per CTA with the slices meeting in the workspace).
 //   M > 16         w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
 //   w4a16_tile_kernel below: M > 16 with an output that is not 16-byte aligned (in 64-row blocks), and decode
 //   shapes whose activations do not fit shared memory (K beyond about 100 k at M == 1).

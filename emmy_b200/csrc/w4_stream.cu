@@ -6,13 +6,16 @@
 // spans of the CTA's items, whatever the tile boundaries.  A warp keeps kStreamDepth items in flight in a private
 // shared-memory ring filled by cp.async, runs each through w4_item, and when its span leaves a tile it adds its
 // sums into the CTA's shared accumulators.  One __syncthreads at the end, then the CTA converts and stores the tiles
-// it owns.  No global atomics, no fences, no workspace: measured on B200, the f32 workspace hand-over of an earlier
-// form of this kernel (atomic adds, fence, arrival counter) cost 4.6 us of a 10.4 us launch, the stream itself 5.8.
+// it owns.  In this form there are no global atomics, no fences, no workspace: measured on B200, the f32 workspace
+// hand-over of an earlier form of this kernel (atomic adds, fence, arrival counter) cost 4.6 us of a 10.4 us launch, the
+// stream itself 5.8.  (The K-sliced form below pays for one such hand-over per CTA where x would not fit otherwise.)
 //
 // Every item multiplies the same M rows of x, 4 KB per item at M = 16: read from global memory that is 117 MB per
 // launch through L1 / L2 against 29 MB of weights, and it bounded the launch.  Where M x K fits beside the ring
 // (STAGED) the CTA copies x once into shared memory in the order the MMA operands are read (conflict-free 16-byte
-// reads); otherwise the rows are read from global memory, one item ahead of the weights where registers allow.
+// reads).  Where it does not fit, K is cut into slices: a CTA is (group of column tiles, K slice), stages its slice of x,
+// and the slices' sums meet in the f32 workspace (SPLIT).  Without a workspace region, or with gathered rows, the rows are
+// read from global memory, one item ahead of the weights where registers allow.
 #include "w4_tile.cuh"
 
 namespace eq {
