@@ -105,6 +105,22 @@ __global__ void dequant_nvfp4_kernel(const uint8_t* __restrict__ packed, const u
     }
 }
 
+// MXFP4: one thread per 32-value group (16 bytes, one power-of-two scale).  out is [N][K] (the stored orientation).
+template <typename OutT>
+__global__ void dequant_mxfp4_kernel(const uint8_t* __restrict__ blocks, const uint8_t* __restrict__ scales, int64_t groups_total,
+                                     OutT* __restrict__ out) {
+    const int64_t grp = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (grp >= groups_total) return;
+    const int e = static_cast<int>(scales[grp]) - 127;
+    const uint4 bytes = *reinterpret_cast<const uint4*>(blocks + grp * 16);
+    const uint32_t w[4] = {bytes.x, bytes.y, bytes.z, bytes.w};
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const uint32_t code = (w[i / 8] >> (4 * (i % 8))) & 0xF;
+        out[grp * 32 + i] = from_float<OutT>(ldexpf(e2m1_to_float(code), e));  // exact, or infinity at the largest exponents
+    }
+}
+
 template <typename F>
 static int dispatch_out(int out_dtype, F&& f) {
     switch (out_dtype) {
@@ -189,6 +205,21 @@ extern "C" int eq_dequant_nvfp4(const uint8_t* packed, const uint8_t* scale_bits
                                      static_cast<cudaStream_t>(stream)>>>(packed, scale_bits, scale_2, N, K,
                                                                           static_cast<OutT*>(out));
         EQ_LAUNCH_OK("dequant_nvfp4_kernel");
+        return (int)EQ_OK;
+    });
+}
+
+extern "C" int eq_dequant_mxfp4(const uint8_t* blocks, const uint8_t* scales, int64_t N, int64_t K, int out_dtype, void* out, void* stream) {
+    EQ_REQUIRE(blocks && scales && out, EQ_ERR_BAD_ARG, "eq_dequant_mxfp4: null pointer");
+    EQ_REQUIRE(N > 0 && K > 0 && K % 32 == 0, EQ_ERR_BAD_ARG, "eq_dequant_mxfp4: K must be a positive multiple of 32");
+    EQ_REQUIRE(aligned(blocks, 16), EQ_ERR_BAD_ALIGN, "eq_dequant_mxfp4: blocks must be 16-byte aligned");
+    const int threads = 256;
+    const int64_t groups = N * (K / 32);
+    return dispatch_out(out_dtype, [&](auto* tag) {
+        using OutT = std::remove_pointer_t<decltype(tag)>;
+        dequant_mxfp4_kernel<OutT><<<static_cast<unsigned>(ceil_div(groups, threads)), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+            blocks, scales, groups, static_cast<OutT*>(out));
+        EQ_LAUNCH_OK("dequant_mxfp4_kernel");
         return (int)EQ_OK;
     });
 }

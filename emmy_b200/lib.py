@@ -78,6 +78,7 @@ def load() -> C.CDLL:
         "eq_dequant_w4": (i, [i, p, p, p, i, p, i64, i64, i64, i, i, p, p]),
         "eq_dequant_fp8": (i, [p, p, i64, i64, i64, i64, i, p, p]),
         "eq_dequant_nvfp4": (i, [p, p, p, i64, i64, i, p, p]),
+        "eq_dequant_mxfp4": (i, [p, p, i64, i64, i, p, p]),
         "eq_w4_repack_sizes": (i, [i64, i64, i64, szp, szp]),
         "eq_w4_repack": (i, [i, p, p, p, p, i64, i64, i64, p, p, ip, p]),
         "eq_w4_repack_stack": (i, [i, p, p, p, i64, i64, i64, i64, p, p]),

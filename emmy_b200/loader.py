@@ -88,6 +88,12 @@ def declares_nvfp4(qc: dict | None) -> bool:
     return method == "compressed-tensors" and _has_group(qc, 4, "float", 16)
 
 
+def declares_mxfp4(qc: dict | None) -> bool:
+    """The checkpoint's native MXFP4 declaration, `quant_method: mxfp4` (gpt-oss; emmy/compiler/loader/quant.py:330-342).
+    This library decodes such tensors (`ops.dequant_mxfp4`) but has no MXFP4 linear."""
+    return bool(qc) and qc.get("quant_method") == "mxfp4"
+
+
 def packed_int4_family(qc: dict | None) -> tuple[str, int] | None:
     """(family, group_size) of a packed-int4 declaration, None when there is none; unsupported variants raise instead
     of loading wrongly, as in the reference (an off-by-one zero convention would shift every weight by a scale unit)."""

@@ -78,6 +78,18 @@ def dequant_nvfp4(packed, scale_bits, scale_2, out_dtype=torch.float32):
     return out
 
 
+def dequant_mxfp4(blocks, scales, out_dtype=torch.float32):
+    """Native MXFP4 storage (blocks uint8 [N, K/32, 16], scales uint8 [N, K/32]) -> [N, K] values, the stored orientation
+    (the reference's decode_mxfp4 returns the transpose)."""
+    _need_cuda(blocks, scales)
+    if blocks.dim() != 3 or blocks.shape[-1] != 16 or tuple(scales.shape) != tuple(blocks.shape[:-1]):
+        raise ValueError(f"MXFP4 storage geometry mismatch: blocks {tuple(blocks.shape)}, scales {tuple(scales.shape)}")
+    n, k = blocks.shape[0], blocks.shape[1] * 32
+    out = torch.empty((n, k), dtype=out_dtype, device=blocks.device)
+    L.check(L.load().eq_dequant_mxfp4(_ptr(blocks.contiguous()), _ptr(scales.contiguous()), n, k, _DTYPE[out_dtype], _ptr(out), _stream()))
+    return out
+
+
 class W4Weight:
     """A repacked int4 weight resident on the device."""
 

@@ -85,6 +85,13 @@ int eq_dequant_fp8(const uint8_t* bits, const float* scale, int64_t N, int64_t K
 int eq_dequant_nvfp4(const uint8_t* packed, const uint8_t* scale_bits, const float* scale_2, int64_t N, int64_t K,
                      int out_dtype, void* out, void* stream);
 
+/* Native MXFP4 (gpt-oss experts): blocks uint8 [N, K/32, 16] (a byte = the even value in its low nibble, the odd one in its
+ * high nibble; the e2m1 value table of NVFP4), scales uint8 [N, K/32] (a power of two, exponent biased by 127).
+ * out[n, k] = F4[code] * 2^(scale - 127), exact (infinity at the largest exponents), [N, K] in out_dtype: the stored
+ * orientation; the reference's decode_mxfp4 returns its transpose (emmy/compiler/loader/quant.py:477-496).  Decoder
+ * only: an MXFP4 linear is not part of this library. */
+int eq_dequant_mxfp4(const uint8_t* blocks, const uint8_t* scales, int64_t N, int64_t K, int out_dtype, void* out, void* stream);
+
 /* ------------------------------------------------------------------ load-time repack (W4) */
 
 /* The reference binds checkpoint bytes verbatim and lets its compiler pick a folded or source layout per weight

@@ -296,6 +296,24 @@ def dequant_nvfp4(packed, scale_bits, scale_2) -> np.ndarray:
     return vals * np.repeat(fused, NVFP4_BLOCK, axis=-1)
 
 
+def dequant_mxfp4(blocks, scales) -> np.ndarray:
+    """Native MXFP4 storage -> its logical (..., in, out) f32 matrix (emmy/compiler/loader/quant.py:477-496).
+    blocks uint8 (..., out, groups, 16): a byte holds the even value in its low nibble and the odd one in its high
+    nibble, 32 values to a group; scales uint8 (..., out, groups): a power of two, exponent biased by 127.  The e2m1
+    value table is NVFP4's; the product with the power of two is exact, then one cast to f32 (the largest exponents
+    overflow to infinity, as in the reference)."""
+    b = np.asarray(blocks)
+    sc = np.asarray(scales)
+    if b.dtype != np.uint8 or sc.dtype != np.uint8:
+        raise ValueError("MXFP4 blocks and scales are uint8")
+    if b.ndim < 3 or b.shape[-1] != 16 or sc.shape != b.shape[:-1]:
+        raise ValueError(f"MXFP4 storage geometry mismatch: blocks {b.shape}, scales {sc.shape}")
+    vals = e2m1_decode_pairs(b).astype(np.float64)  # (..., out, groups, 32)
+    with np.errstate(over="ignore"):
+        dense = np.ldexp(vals, sc.astype(np.int32)[..., None] - 127).reshape(*b.shape[:-2], b.shape[-2] * 32).astype(np.float32)
+    return np.swapaxes(dense, -2, -1)
+
+
 def quant_nvfp4(values) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
     """f32 [.., K] -> (packed u8 [.., K/2], scale_bits u8 [.., K/16], scale_2
     f32 [1]), the weight quantizer of emmy/compiler/loader/quant.py:206-237:

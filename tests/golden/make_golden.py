@@ -157,6 +157,14 @@ def main(root: str) -> None:
     out["act8_in"], out["act8_scale"] = xa, sx
     out["act8_bits"] = d.encode_f8((xa / sx).astype(np.float32), "f8e4m3")
 
+    # --- MXFP4 (own generator: the arrays above keep their values) ------------
+    rng4 = np.random.default_rng(1234)
+    mx_blocks = rng4.integers(0, 256, (24, 6, 16)).astype(np.uint8)   # (out, groups, 16): 24 channels, 192 inputs
+    mx_scales = rng4.integers(112, 136, (24, 6)).astype(np.uint8)
+    mx_scales[0, 0], mx_scales[1, 1], mx_scales[2, 2] = 0, 254, 127   # the smallest and the largest exponent, and 2^0
+    out["mxfp4_blocks"], out["mxfp4_scales"] = mx_blocks, mx_scales
+    out["mxfp4_decoded"] = q.decode_mxfp4(mx_blocks, mx_scales)          # (in, out) f32
+
     dest = Path(__file__).with_name("quant_golden.npz")
     np.savez_compressed(dest, **out)
     print(f"wrote {dest} ({dest.stat().st_size} bytes, {len(out)} arrays)")

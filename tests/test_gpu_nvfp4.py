@@ -162,3 +162,20 @@ def test_weight_quantizer_bit_exact():
     pz, sz, s2z = fm.quant_nvfp4(np.zeros((8, 64), np.float32))
     np.testing.assert_array_equal(z[2].cpu().numpy(), s2z)
     assert int(z[0].count_nonzero()) == 0 and int(z[1].count_nonzero()) == 0 and not pz.any() and not sz.any()
+
+
+def test_mxfp4_decode_bit_exact(golden):
+    """The MXFP4 decoder against the reference's own output (incl. a denormal result and the overflow to infinity) and,
+    on a larger random tensor, against the oracle; f32 and bf16 outputs."""
+    from emmy_b200 import ops
+
+    blocks, scales = golden["mxfp4_blocks"], golden["mxfp4_scales"]
+    got = ops.dequant_mxfp4(dev(blocks), dev(scales)).cpu().numpy()
+    np.testing.assert_array_equal(got, golden["mxfp4_decoded"].T)
+    rng = np.random.default_rng(7)
+    blocks = rng.integers(0, 256, (300, 20, 16)).astype(np.uint8)
+    scales = rng.integers(100, 150, (300, 20)).astype(np.uint8)
+    ref = fm.dequant_mxfp4(blocks, scales).T
+    np.testing.assert_array_equal(ops.dequant_mxfp4(dev(blocks), dev(scales)).cpu().numpy(), ref)
+    got16 = ops.dequant_mxfp4(dev(blocks), dev(scales), torch.bfloat16).float().cpu().numpy()
+    np.testing.assert_array_equal(got16, fm.round_bf16(ref))

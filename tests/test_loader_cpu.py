@@ -140,6 +140,7 @@ def test_nvfp4_trio_is_taken_before_the_fp8_pair(tmp_path):
     assert specs["m.attn.q_proj"].family == "fp8"
     assert loader.declares_nvfp4(qc) and loader.declares_fp8(qc)
     assert not loader.declares_nvfp4({"quant_method": "compressed-tensors", "config_groups": {"g": {"weights": {"type": "float", "num_bits": 4, "group_size": 32}}}})
+    assert loader.declares_mxfp4({"quant_method": "mxfp4"}) and not loader.declares_mxfp4({"quant_method": "fp8"}) and not loader.declares_mxfp4(None)
     assert not loader.declares_fp8({"quant_method": "modelopt", "quant_algo": "NVFP4"})
 
 

@@ -201,3 +201,22 @@ def test_dynamic_fp8_activation_matches_eager_hook():
     scale = x.abs().amax(dim=-1, keepdim=True).clamp(min=1e-12) / 448.0
     ref = (x / scale).to(torch.float8_e4m3fn).float() * scale
     np.testing.assert_array_equal(act.fp8_dynamic_round_trip(x.numpy()), ref.numpy())
+
+
+def test_mxfp4_decode_matches_reference(golden):
+    """decode_mxfp4 of the reference on random blocks, incl. the smallest exponent (a denormal result), 2^0 and the
+    largest one (overflow to infinity, as the reference's cast does)."""
+    got = fm.dequant_mxfp4(golden["mxfp4_blocks"], golden["mxfp4_scales"])
+    assert got.shape == golden["mxfp4_decoded"].shape and got.dtype == np.float32
+    np.testing.assert_array_equal(got, golden["mxfp4_decoded"])
+
+
+def test_mxfp4_hand_example():
+    """0x21: low nibble 1 -> 0.5 (even position), high nibble 2 -> 1.0 (odd position); scale 128 -> x2."""
+    blocks = np.zeros((1, 1, 16), np.uint8)
+    blocks[0, 0, 0] = 0x21
+    blocks[0, 0, 15] = 0xF7  # 6.0 and -6.0
+    out = fm.dequant_mxfp4(blocks, np.array([[128]], np.uint8))
+    assert out.shape == (32, 1)
+    assert out[0, 0] == 1.0 and out[1, 0] == 2.0 and out[30, 0] == 12.0 and out[31, 0] == -12.0
+    assert not out[2:30].any()
