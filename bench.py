@@ -519,8 +519,10 @@ def wl_tp_mlp(device, rank, world, m):
     def mlp(weights, xx):
         return torch.nn.functional.silu(ops.w4a16_linear(xx, weights["gate"])) * ops.w4a16_linear(xx, weights["up"])
 
+    # this rank's gate and up columns as ONE linear ([gate | up], as the reference stores them): one launch for both
+    local_gu = ops.w4_concat([local["gate"], local["up"]])
     def step():
-        hidden = mlp(local, x)  # [M, inter / world]: this rank's columns
+        hidden = ops.w4a16_gate_up_swiglu(x, local_gu)  # [M, inter / world]: this rank's columns, SwiGLU in the GEMM's epilogue
         y.copy_(down(hidden) if world > 1 else ops.w4a16_linear(hidden, local["down"]))
 
     def parity():

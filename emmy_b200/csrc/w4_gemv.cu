@@ -182,6 +182,87 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     return EQ_OK;
 }
 
+// ---- gate / up + SwiGLU in one call ---------------------------------------------------------------------------
+// h[M, I] = act(silu(x W_gate)) * (x W_up) for a [gate | up] weight (the two projections concatenated along N, as the
+// reference stores them: emmy/compiler/trace/huggingface.py:1663-1669, 2110-2141), with the eager form's two roundings.
+// M > 16: the tensor path's SwiGLU tile (128 gate + 128 up columns per CTA, the activation in the epilogue) over row
+// blocks of the dense matrix; fewer rows: the [gate | up] linear into scratch, then an elementwise pass.
+namespace eq {
+namespace {
+
+__global__ void dense_row_blocks_kernel(RowBlock* __restrict__ blocks, int32_t* __restrict__ n_blocks, int M) {
+    const int nb = (M + 255) / 256;
+    for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+        blocks[b].expert = 0;
+        blocks[b].row0 = b * 256;
+        blocks[b].rows = min(256, M - b * 256);
+        blocks[b].pad = 0;
+    }
+    if (threadIdx.x == 0) *n_blocks = nb;
+}
+
+template <typename ActT>
+__global__ void swiglu_rows_kernel(const ActT* __restrict__ gu, int64_t M, int64_t I, ActT* __restrict__ h) {
+    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (idx >= M * I) return;
+    const int64_t r = idx / I, i = idx - r * I;
+    const float g = to_float(gu[r * 2 * I + i]), u = to_float(gu[r * 2 * I + I + i]);
+    const ActT s = from_float<ActT>(g / (1.f + expf(-g)));
+    h[idx] = from_float<ActT>(to_float(s) * u);
+}
+
+size_t gu_align(size_t v) { return (v + 255) / 256 * 256; }
+size_t gu_blocks_bytes(int64_t M) { return gu_align((static_cast<size_t>((M + 255) / 256) + 1) * sizeof(RowBlock)); }
+
+}  // namespace
+
+int w4_gemm_tc_grouped_launch(const unsigned char* wq, size_t expert_stride, int scale_dtype, const void* x, void* y, int64_t R, int64_t N,
+                              int64_t K, int act_dtype, const RowBlock* blocks, const int32_t* n_blocks, int max_blocks,
+                              const int32_t* y_rows, const uint64_t* y_ptrs, bool swiglu, int* status, cudaStream_t stream);  // w4_gemm.cu
+
+}  // namespace eq
+
+extern "C" size_t eq_w4a16_gate_up_workspace_bytes(int64_t M, int64_t I, int64_t K) {
+    if (M <= 0 || I <= 0 || K <= 0) return 0;
+    // the linear's own workspace, then the row-block list (M > 16) or the [M, 2 I] scratch (M <= 16)
+    return gu_align(eq_w4a16_workspace_bytes(M, 2 * I, K)) + (M > 16 ? gu_blocks_bytes(M) : gu_align(static_cast<size_t>(M) * 2 * I * 2));
+}
+
+extern "C" int eq_w4a16_gate_up_swiglu(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t I, int64_t G, const void* x,
+                                       int64_t M, int act_dtype, void* h, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int st = w4a16_check("eq_w4a16_gate_up_swiglu", wq, scale_dtype, K, 2 * I, &G, x, M, act_dtype, h);
+    if (st != EQ_OK) return st;
+    if (M == 0) return EQ_OK;
+    EQ_REQUIRE(I % 16 == 0, EQ_ERR_UNSUPPORTED, "eq_w4a16_gate_up_swiglu: the intermediate size must be a multiple of 16 (I=%lld)", (long long)I);
+    EQ_REQUIRE(workspace && aligned(workspace, 256) && workspace_bytes >= eq_w4a16_gate_up_workspace_bytes(M, I, K), EQ_ERR_WORKSPACE,
+               "eq_w4a16_gate_up_swiglu: workspace of %zu bytes (256-byte aligned) needed, %zu given", eq_w4a16_gate_up_workspace_bytes(M, I, K),
+               workspace_bytes);
+    const size_t inner = gu_align(eq_w4a16_workspace_bytes(M, 2 * I, K));
+    unsigned char* extra = static_cast<unsigned char*>(workspace) + inner;
+    if (M > 16 && !perm && aligned(h, 16)) {
+        int* status = static_cast<int*>(workspace);
+        EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+        RowBlock* blocks = reinterpret_cast<RowBlock*>(extra);
+        const int nb = static_cast<int>((M + 255) / 256);
+        int32_t* n_blocks = reinterpret_cast<int32_t*>(blocks + nb);
+        dense_row_blocks_kernel<<<1, 256, 0, stream>>>(blocks, n_blocks, static_cast<int>(M));
+        EQ_LAUNCH_OK("dense_row_blocks_kernel");
+        return w4_gemm_tc_grouped_launch(static_cast<const unsigned char*>(wq), 0, scale_dtype, x, h, M, 2 * I, K, act_dtype, blocks, n_blocks, nb, nullptr,
+                                         nullptr, true, status, stream);
+    }
+    // few rows, scattered act-order groups or an unaligned output: the [gate | up] linear, then the activation
+    EQ_REQUIRE(M <= 16, EQ_ERR_UNSUPPORTED, "eq_w4a16_gate_up_swiglu: M > 16 needs a 16-byte aligned output and a weight without a row permutation");
+    void* gu = extra;  // [M][2 I] scratch
+    st = eq_w4a16_linear(wq, scale_dtype, perm, K, 2 * I, G, x, M, act_dtype, gu, workspace, inner, stream_);
+    if (st != EQ_OK) return st;
+    const unsigned grid = static_cast<unsigned>(ceil_div(M * I, 256));
+    if (act_dtype == EQ_F16) swiglu_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(gu), M, I, static_cast<__half*>(h));
+    else swiglu_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gu), M, I, static_cast<__nv_bfloat16*>(h));
+    EQ_LAUNCH_OK("swiglu_rows_kernel");
+    return EQ_OK;
+}
+
 // The tensor-path kernel and the GEMV's hand-over wait are bounded; one that runs out sets the status word.
 extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);

@@ -86,6 +86,8 @@ def load() -> C.CDLL:
         "eq_w4a16_workspace_bytes": (sz, [i64, i64, i64]),
         "eq_w4a16_linear": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_w4a16_status": (i, [p, i64, i64, p]),
+        "eq_w4a16_gate_up_workspace_bytes": (sz, [i64, i64, i64]),
+        "eq_w4a16_gate_up_swiglu": (i, [p, i, p, i64, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_quant_fp8_per_token": (i, [p, i64, i64, i, p, p, p]),
         "eq_fp8_workspace_bytes": (sz, [i64, i64]),
         "eq_fp8_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),

@@ -177,6 +177,22 @@ def w4a16_linear(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = 
     return y
 
 
+def w4a16_gate_up_swiglu(x: torch.Tensor, w: W4Weight, workspace: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """h[M, I] = act(silu(gate)) * up for a [gate | up] weight (`w4_concat([gate, up])`, or a checkpoint that stores the two
+    projections as one tensor): one call, and above 16 rows one kernel (the activation sits in the GEMM's epilogue)."""
+    _need_cuda(x)
+    m, k = x.shape
+    if k != w.k or w.n % 32:
+        raise ValueError(f"x has {k} features, the weight {w.k}; the [gate | up] width {w.n} must be a multiple of 32")
+    inter = w.n // 2
+    h = out if out is not None else torch.empty((m, inter), dtype=x.dtype, device=x.device)
+    need = L.load().eq_w4a16_gate_up_workspace_bytes(m, inter, k)
+    ws = workspace if workspace is not None else torch.zeros(max(need, 256), dtype=torch.uint8, device=x.device)
+    L.check(L.load().eq_w4a16_gate_up_swiglu(_ptr(w.wq), _DTYPE[w.scale_dtype], _ptr(w.perm), w.k, inter, w.group, _ptr(x), m, _DTYPE[x.dtype],
+                                             _ptr(h), _ptr(ws), ws.numel(), _stream()))
+    return h
+
+
 def w4a16_status(workspace: torch.Tensor, m: int, n: int) -> None:
     """Raises EmmyqError(EQ_ERR_TIMEOUT) if a bounded device-side wait of an earlier call ran out."""
     L.check(L.load().eq_w4a16_status(_ptr(workspace), m, n, _stream()))

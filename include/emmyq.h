@@ -144,6 +144,18 @@ int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_
  * reference's counterpart is the host-side hung-launch deadline, crates/emmy-runtime/src/cuda.rs:1401-1451). */
 int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 
+/* gate / up + SwiGLU in one call: h[M, I] = act(silu(x W_gate)) * (x W_up), wq the repacked [gate | up] weight (the two
+ * projections concatenated along N: K x 2I), with the eager form's roundings (both projections, the silu and the product
+ * each rounded to the activation dtype; emmy/compiler/trace/huggingface.py:1663-1669).  M > 16 runs the tensor path with
+ * the activation in the GEMM's epilogue (the [M, 2I] intermediate never exists in memory; needs perm == NULL and a
+ * 16-byte aligned h); M <= 16 runs the linear into scratch and an elementwise pass.  One of the fused forms the
+ * reference's compiler realizes around its linears (tests/compiler/realization/cases/fused/gate-up-*.json).
+ * The workspace starts like eq_w4a16_linear's (zero on first use, left zero; eq_w4a16_status(workspace, M, 2 * I) reads
+ * its status word). */
+size_t eq_w4a16_gate_up_workspace_bytes(int64_t M, int64_t I, int64_t K);
+int eq_w4a16_gate_up_swiglu(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t I, int64_t G, const void* x,
+                            int64_t M, int act_dtype, void* h, void* workspace, size_t workspace_bytes, void* stream);
+
 /* eq_w4a16_linear for hosts that cannot hand over scratch memory.  (No counterpart in the reference: its runtime
  * owns all device memory itself.)  Some callers of this library run where device allocation is off limits: a
  * serving engine that has already given every byte to its KV-cache pool and forbids cudaMalloc afterwards, code on

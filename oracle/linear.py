@@ -25,6 +25,18 @@ def w4a16_linear(x, qweight, qzeros, scales, group_size, fmt, dtype, g_idx=None)
     return _matmul_f32(x, w)
 
 
+def w4a16_gate_up_swiglu(x, qweight, qzeros, scales, group_size, fmt, dtype, g_idx=None) -> np.ndarray:
+    """act(silu(gate)) * up for a [gate | up] weight (gate columns, then up columns): both projections rounded to the
+    activation dtype, silu in f32 rounded to the dtype, the product rounded again -- the eager form's roundings
+    (emmy/compiler/trace/huggingface.py:1663-1669).  Returns f32 values representable in `dtype`."""
+    rnd = fm.round_f16 if dtype == "f16" else fm.round_bf16
+    gu = rnd(w4a16_linear(x, qweight, qzeros, scales, group_size, fmt, dtype, g_idx))
+    inter = gu.shape[1] // 2
+    gate, up = gu[:, :inter].astype(np.float32), gu[:, inter:].astype(np.float32)
+    act = rnd(gate / (np.float32(1) + np.exp(-gate, dtype=np.float32)))
+    return rnd(act * up)
+
+
 def fp8_linear(x, w_bits, w_scale, dtype="bf16") -> np.ndarray:
     """W8A8 value path: x_hat = dtype(dec(q_x) * s_x), w_hat = dtype(dec(w) *
     s_w), ordinary linear (emmy/compiler/loader/quant.py:1655-1768)."""

@@ -392,3 +392,33 @@ def test_workspace_is_left_zero_by_every_path():
             ops.w4a16_status(ws, m, n)
             assert int(ws[256:].count_nonzero()) == 0, f"M={m} N={n} left the workspace dirty"
             check_close(y, ol.w4a16_linear(x, qw, qz, sc, g, "gptq", "f16", gi))
+
+
+@pytest.mark.parametrize("m", [1, 9, 40, 300, 513])
+def test_gate_up_swiglu_in_one_call(m):
+    """[gate | up] + SwiGLU: the elementwise form below 17 rows, the GEMM-epilogue form above (ragged last row block),
+    against the oracle's eager roundings; twice on one workspace, which stays zero behind its header."""
+    from emmy_b200 import ops
+
+    k, inter = 1024, 1184  # 2 I = 2368: the last 128 + 128 column tile is partial
+    parts = []
+    raw = []
+    for i in range(2):
+        qw, qz, sc, gi = synth.gptq_linear(k, inter, seed=40 + i)
+        raw.append((qw, qz, sc, gi))
+        parts.append(ops.w4_repack(dev(qw), dev(qz), dev(sc), 128, "gptq", g_idx=dev(gi)))
+    w = ops.w4_concat(parts)
+    x = synth.activations(m, k, "bf16", seed=m)
+    # the oracle on the concatenated checkpoint tensors (block-constant g_idx: each half gathers its own scale rows)
+    gate = ol.w4a16_linear(x, *raw[0][:3], 128, "gptq", "bf16", raw[0][3])
+    up = ol.w4a16_linear(x, *raw[1][:3], 128, "gptq", "bf16", raw[1][3])
+    g, u = fm.round_bf16(gate), fm.round_bf16(up)
+    ref = fm.round_bf16(fm.round_bf16(g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u)
+    lib = ops.L.load()
+    ws = torch.zeros(lib.eq_w4a16_gate_up_workspace_bytes(m, inter, k) + 256, dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        h = ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws)
+        ops.w4a16_status(ws, m, 2 * inter)
+    check_close(h, ref)
+    front = lib.eq_w4a16_workspace_bytes(m, 2 * inter, k)
+    assert int(ws[256:front].count_nonzero()) == 0
