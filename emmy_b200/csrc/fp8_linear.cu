@@ -61,6 +61,57 @@ __global__ void __launch_bounds__(256) quant_fp8_rows_kernel(const InT* __restri
     }
 }
 
+// RMSNorm in front of the quantize, in one kernel (the fused prologue the reference's compiler realizes around its
+// linears, tests/compiler/realization/cases/fused/norm-linear-*.json): h = dtype(dtype(x * rsqrt(mean(x^2) + eps)) * gamma)
+// -- the model's RMSNorm, its normalised value rounded to the activation dtype before the weight multiplies it -- then the
+// per-token rule on h.  One CTA per row; the row is read three times (sum of squares, maximum, encode) and stays in L1 / L2
+// between them; the normalised row is never written.
+template <typename InT>
+__global__ void __launch_bounds__(256) rmsnorm_quant_fp8_rows_kernel(const InT* __restrict__ x, const InT* __restrict__ gamma, float eps, int64_t K,
+                                                                     uint8_t* __restrict__ q, float* __restrict__ scale, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float part[8];
+    __shared__ float bcast;
+    const int64_t row = blockIdx.x;
+    const InT* xr = x + row * K;
+    if (status && row == 0 && threadIdx.x == 0) *status = 0;
+    auto block_reduce = [&](float v, bool is_max) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float o = __shfl_xor_sync(0xFFFFFFFFu, v, off);
+            v = is_max ? fmaxf(v, o) : v + o;
+        }
+        __syncthreads();  // the previous use of part[] is over
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = part[0];
+            for (int w = 1; w < 8; ++w) m = is_max ? fmaxf(m, part[w]) : m + part[w];
+            bcast = m;
+        }
+        __syncthreads();
+        return bcast;
+    };
+    float ss = 0.f;
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+        const float v = load_as_float(xr + k);
+        ss = fmaf(v, v, ss);
+    }
+    const float rstd = rsqrtf(__fdiv_rn(block_reduce(ss, false), static_cast<float>(K)) + eps);
+    auto normed = [&](int64_t k) {
+        const InT n = from_float<InT>(load_as_float(xr + k) * rstd);
+        return to_float(from_float<InT>(to_float(n) * load_as_float(gamma + k)));
+    };
+    float amax = 0.f;
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(normed(k)));
+    const float s = __fdiv_rn(fmaxf(block_reduce(amax, true), 1e-12f), 448.0f);
+    if (threadIdx.x == 0) scale[row] = s;
+    uint8_t* qr = q + row * K;
+    for (int64_t k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x)
+        *reinterpret_cast<uint16_t*>(qr + k) = e4m3x2_satfinite(__fdiv_rn(normed(k), s), __fdiv_rn(normed(k + 1), s));
+}
+
 // ------------------------------------------------------------------------------------------------ decode-shaped
 // M <= 16 on tcgen05 with the operands' roles swapped: a 128-channel tile of the WEIGHT is the MMA's A operand (M = 128),
 // the activation rows are B (N = 16), so a K step stages 16 KB of weights and 2 KB of rows and the streaming is done by
@@ -523,7 +574,8 @@ static int fp8_linear_launch(const uint8_t* w, const float* sw, int64_t N, int64
 }
 
 static int fp8_linear_any(const char* who, const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x,
-                          const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                          const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                          const void* gamma = nullptr, float eps = 0.f) {
     EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "%s: bad extents M=%lld K=%lld N=%lld", who, (long long)M, (long long)K, (long long)N);
     if (M == 0) return EQ_OK;
     EQ_REQUIRE(weight && weight_scale && x && y, EQ_ERR_BAD_ARG, "%s: null pointer", who);
@@ -538,7 +590,24 @@ static int fp8_linear_any(const char* who, const uint8_t* weight, const float* w
     float* sx = reinterpret_cast<float*>(qx + align_up(static_cast<size_t>(M) * K, 256));
     int* status = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(sx) + align_up(static_cast<size_t>(M) * sizeof(float), 256));
     int st = EQ_OK;
-    if (input_scale) {
+    if (gamma) {
+        // RMSNorm and the per-token quantize in one kernel (a programmatic dependent, like the plain quantize)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(M));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = M <= 128 ? 1 : 0;
+        if (act_dtype == EQ_F16)
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, rmsnorm_quant_fp8_rows_kernel<__half>, static_cast<const __half*>(x), static_cast<const __half*>(gamma), eps, K,
+                                          qx, sx, status));
+        else
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, rmsnorm_quant_fp8_rows_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<const __nv_bfloat16*>(gamma), eps, K, qx, sx, status));
+    } else if (input_scale) {
         const int64_t total = M * K;
         const unsigned grid = static_cast<unsigned>(ceil_div(total / 2 > M ? total / 2 : M, 256));
         if (act_dtype == EQ_F16) quant_fp8_static_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), total, input_scale, M, qx, sx, status);
@@ -564,6 +633,13 @@ extern "C" int eq_fp8_linear_static(const uint8_t* weight, const float* weight_s
     EQ_REQUIRE(input_scale, EQ_ERR_BAD_ARG, "eq_fp8_linear_static: null input_scale");
     return fp8_linear_any("eq_fp8_linear_static", weight, weight_scale, N, K, x, input_scale, M, act_dtype, y, workspace, workspace_bytes,
                           static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int eq_fp8_linear_rmsnorm(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, const void* gamma,
+                                     float eps, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream_) {
+    EQ_REQUIRE(gamma, EQ_ERR_BAD_ARG, "eq_fp8_linear_rmsnorm: null norm weight");
+    return fp8_linear_any("eq_fp8_linear_rmsnorm", weight, weight_scale, N, K, x, nullptr, M, act_dtype, y, workspace, workspace_bytes,
+                          static_cast<cudaStream_t>(stream_), gamma, eps);
 }
 
 extern "C" int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream_) {

@@ -92,6 +92,7 @@ def load() -> C.CDLL:
         "eq_fp8_workspace_bytes": (sz, [i64, i64]),
         "eq_fp8_linear": (i, [p, p, i64, i64, p, i64, i, p, p, sz, p]),
         "eq_fp8_linear_static": (i, [p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
+        "eq_fp8_linear_rmsnorm": (i, [p, p, i64, i64, p, p, C.c_float, i64, i, p, p, sz, p]),
         "eq_fp8_status": (i, [p, i64, i64, p]),
         "eq_quant_fp8_per_group": (i, [p, i64, i64, i, p, p, p]),
         "eq_fp8_block_workspace_bytes": (sz, [i64, i64]),

@@ -232,16 +232,27 @@ def fp8_workspace(m: int, k: int, device) -> torch.Tensor:
     return torch.zeros(max(need, 256), dtype=torch.uint8, device=device)
 
 
-def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None, input_scale=None):
+def fp8_linear(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, workspace=None, out=None, input_scale=None,
+               norm_weight: torch.Tensor | None = None, eps: float = 1e-6):
     """y[M, N] = x @ (weight * scale).T with x quantized per token (or with the static `input_scale`, f32 [1]);
-    weight uint8 e4m3 bits [N, K], scale f32 [N]."""
-    _need_cuda(x, weight, weight_scale, input_scale)
+    weight uint8 e4m3 bits [N, K], scale f32 [N].  `norm_weight` ([K], x's dtype): the model's RMSNorm runs inside the
+    quantize kernel, y = linear(rmsnorm(x) * norm_weight)."""
+    _need_cuda(x, weight, weight_scale, input_scale, norm_weight)
     m, k = x.shape
     n = weight.shape[0]
     if weight.shape[1] != k:
         raise ValueError(f"x has {k} features, the weight takes {weight.shape[1]}")
     y = out if out is not None else torch.empty((m, n), dtype=x.dtype, device=x.device)
     ws = workspace if workspace is not None else fp8_workspace(m, k, x.device)
+    if norm_weight is not None:
+        if input_scale is not None or norm_weight.dtype != x.dtype or norm_weight.numel() != k:
+            raise ValueError("fp8_linear: norm_weight is [K] in x's dtype and excludes a static input_scale")
+        L.check(
+            L.load().eq_fp8_linear_rmsnorm(
+                _ptr(weight), _ptr(weight_scale), n, k, _ptr(x), _ptr(norm_weight), float(eps), m, _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream()
+            )
+        )
+        return y
     if input_scale is not None:
         L.check(
             L.load().eq_fp8_linear_static(

@@ -200,6 +200,13 @@ int eq_fp8_linear(const uint8_t* weight, const float* weight_scale, int64_t N, i
  * the reference spells for `activation_scheme: static` checkpoints (emmy/compiler/loader/quant.py:1818-1905). */
 int eq_fp8_linear_static(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, const float* input_scale,
                          int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
+/* RMSNorm -> quantize -> linear with the norm inside the quantize kernel (one of the fused forms the reference's compiler
+ * realizes around its linears, tests/compiler/realization/cases/fused/norm-linear-*.json): y = fp8_linear(h) with
+ * h = dtype(dtype(x * rsqrt(mean(x^2) + eps)) * gamma), the model's RMSNorm (the normalised value is rounded to the
+ * activation dtype before gamma multiplies it); gamma: [K] in act_dtype.  The normalised row is never written to memory.
+ * Same workspace and status as eq_fp8_linear. */
+int eq_fp8_linear_rmsnorm(const uint8_t* weight, const float* weight_scale, int64_t N, int64_t K, const void* x, const void* gamma,
+                          float eps, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes, void* stream);
 /* Synchronizes the stream and returns EQ_ERR_TIMEOUT if a bounded pipeline wait of the last eq_fp8_linear call on
  * this workspace ran out (same role as eq_w4a16_status). */
 int eq_fp8_status(const void* workspace, int64_t M, int64_t K, void* stream);

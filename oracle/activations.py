@@ -67,3 +67,16 @@ def nvfp4_static_round_trip(x, s2) -> np.ndarray:
     """Quantize then reconstruct with the f16 fused scale, in f32."""
     packed, scale_bits = nvfp4_static_act(x, s2)
     return dequant_nvfp4(packed, scale_bits, np.float32(s2).reshape(1))
+
+
+def rmsnorm(x, gamma, eps: float, dtype: str = "bf16") -> np.ndarray:
+    """The model's RMSNorm as its eager module computes it (the HF Llama / Qwen3 form the reference traces): the mean of
+    squares and the reciprocal root in f32, the normalised value rounded to the activation dtype, then the weight's
+    product rounded again.  x and gamma hold values representable in `dtype`; returns such values as f32."""
+    from . import formats as fm
+
+    rnd = fm.round_bf16 if dtype == "bf16" else fm.round_f16
+    xf = np.asarray(x, dtype=np.float32)
+    var = np.mean(xf * xf, axis=-1, keepdims=True, dtype=np.float32)
+    normed = rnd(xf * (np.float32(1) / np.sqrt(var + np.float32(eps))))
+    return rnd(normed * np.asarray(gamma, dtype=np.float32))

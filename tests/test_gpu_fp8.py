@@ -145,3 +145,23 @@ def test_fp8_linear_empty_batch():
     bits, sw = synth.fp8_weight(64, 128, seed=0)
     y = ops.fp8_linear(torch.empty(0, 128, dtype=torch.bfloat16, device="cuda"), dev(bits), dev(sw.reshape(-1)))
     assert y.shape == (0, 64)
+
+
+@pytest.mark.parametrize("m", [1, 20, 300])
+def test_rmsnorm_inside_the_quantize(m):
+    """y = fp8_linear(rmsnorm(x) * gamma) with the norm fused into the quantize kernel, against the oracle's eager RMSNorm
+    followed by the oracle linear.  (The mean of squares is summed in another order than numpy's, so a normalised value
+    may land one rounding step away; the linear's tolerance covers it.)"""
+    from emmy_b200 import ops
+    from oracle import activations as oact
+
+    n, k = 384, 1280
+    bits, sw = synth.fp8_weight(n, k, seed=m)
+    x = synth.activations(m, k, "bf16", seed=200 + m) * 3.0
+    x = fm.round_bf16(x)
+    gamma = fm.round_bf16(1.0 + 0.1 * np.random.default_rng(m).standard_normal(k).astype(np.float32))
+    ref = ol.fp8_linear(oact.rmsnorm(x, gamma, 1e-6, "bf16"), bits, sw)
+    y = ops.fp8_linear(dev(x).bfloat16(), dev(bits), dev(sw.reshape(-1)), norm_weight=dev(gamma).bfloat16(), eps=1e-6)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
