@@ -57,6 +57,28 @@ def _(x, weight, weight_scale, input_scale):
     return x.new_empty((x.shape[0], weight.shape[0]))
 
 
+@torch.library.custom_op("emmyq::fp8_linear_rmsnorm", mutates_args=(), device_types="cuda")
+def _fp8_rmsnorm_op(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, weight: torch.Tensor, weight_scale: torch.Tensor) -> torch.Tensor:
+    return ops.fp8_linear(x.contiguous(), weight, weight_scale, norm_weight=norm_weight, eps=eps)
+
+
+@_fp8_rmsnorm_op.register_fake
+def _(x, norm_weight, eps, weight, weight_scale):
+    return x.new_empty((x.shape[0], weight.shape[0]))
+
+
+@torch.library.custom_op("emmyq::w4a16_gate_up_swiglu", mutates_args=(), device_types="cuda")
+def _w4_gate_up_op(x: torch.Tensor, wq: torch.Tensor, k: int, n: int, group: int, scale_bf16: bool) -> torch.Tensor:
+    w = ops.W4Weight()
+    w.wq, w.perm, w.k, w.n, w.group, w.scale_dtype, w.fmt = wq, None, k, n, group, torch.bfloat16 if scale_bf16 else torch.float16, "gptq"
+    return ops.w4a16_gate_up_swiglu(x.contiguous(), w)
+
+
+@_w4_gate_up_op.register_fake
+def _(x, wq, k, n, group, scale_bf16):
+    return x.new_empty((x.shape[0], n // 2))
+
+
 @torch.library.custom_op("emmyq::fp8_block_linear", mutates_args=(), device_types="cuda")
 def _fp8_block_op(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor) -> torch.Tensor:
     return ops.fp8_block_linear(x.contiguous(), weight, weight_scale)

@@ -59,6 +59,41 @@ def test_modules_trace_under_torch_compile():
     torch.testing.assert_close(compiled, eager, atol=2e-3, rtol=2e-2)
 
 
+def test_fused_forms_as_custom_ops_under_torch_compile():
+    """emmyq::w4a16_gate_up_swiglu and emmyq::fp8_linear_rmsnorm trace under torch.compile (fake kernels give the shapes)
+    and equal their unfused compositions."""
+    import emmy_b200.linear  # noqa: F401  (registers the ops)
+    from emmy_b200 import ops
+
+    k, inter, n = 256, 384, 256
+    parts = []
+    for i in range(2):
+        qw, qz, sc = synth.awq_linear(k, inter, seed=6 + i)
+        parts.append(ops.w4_repack(torch.from_numpy(qw).cuda(), torch.from_numpy(qz).cuda(), torch.from_numpy(sc).cuda(), 128, "awq"))
+    gu = ops.w4_concat(parts)
+    bits, sw = synth.fp8_weight(n, inter, seed=8)
+    wb, ws = torch.from_numpy(bits).cuda(), torch.from_numpy(sw.reshape(-1)).cuda()
+    gamma = (1.0 + 0.1 * torch.randn(inter, generator=torch.Generator().manual_seed(1))).bfloat16().cuda()
+
+    def fused(x):
+        h = torch.ops.emmyq.w4a16_gate_up_swiglu(x, gu.wq, k, 2 * inter, 128, False)
+        return torch.ops.emmyq.fp8_linear_rmsnorm(h.bfloat16(), gamma, 1e-6, wb, ws).float()
+
+    def unfused(x):
+        g, u = ops.w4a16_linear(x, parts[0]), ops.w4a16_linear(x, parts[1])
+        h = (torch.nn.functional.silu(g) * u).bfloat16()
+        hf = h.float()
+        normed = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6)).bfloat16()
+        return ops.fp8_linear(gamma * normed, wb, ws).float()
+
+    for m in (3, 40):
+        x = torch.from_numpy(synth.activations(m, k, "f16", seed=9 + m)).half().cuda()
+        ref = unfused(x)
+        got = torch.compile(fused, fullgraph=True, backend="eager")(x)
+        assert got.shape == ref.shape
+        assert float((got - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
 def test_nvfp4_module():
     from emmy_b200.linear import NVFP4Linear
 
