@@ -125,6 +125,56 @@ __global__ void quant_nvfp4_act_kernel(const InT* __restrict__ x, int64_t M, int
     if (sf_tiled) sf_tiled[sf_tiled_offset(row, b, K / 64)] = sbits;
 }
 
+// RMSNorm in front of the static quantize, in one kernel: h = dtype(dtype(x * rsqrt(mean(x^2) + eps)) * gamma), the model's
+// RMSNorm (its normalised value rounded to the activation dtype before the weight multiplies it), then the block rule on h.
+// One CTA per row: the sum of squares first, then one thread per 16-element block; the normalised row is never written.
+template <typename InT>
+__global__ void __launch_bounds__(256) rmsnorm_quant_nvfp4_rows_kernel(const InT* __restrict__ x, const InT* __restrict__ gamma, float eps, int64_t K,
+                                                                       const float* __restrict__ scale2, uint8_t* __restrict__ codes,
+                                                                       uint8_t* __restrict__ sf_tiled, int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float part[8];
+    const int64_t row = blockIdx.x;
+    const InT* xr = x + row * K;
+    if (status && row == 0 && threadIdx.x == 0) *status = 0;
+    float ss = 0.f;
+    for (int64_t k = threadIdx.x; k < K; k += blockDim.x) {
+        const float v = to_float(xr[k]);
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += part[w];
+    const float rstd = rsqrtf(__fdiv_rn(total, static_cast<float>(K)) + eps);
+    const float s2 = scale2[0];
+    for (int64_t b = threadIdx.x; b < K / 16; b += blockDim.x) {
+        float v[16];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const InT n = from_float<InT>(to_float(xr[b * 16 + i]) * rstd);
+            v[i] = to_float(from_float<InT>(to_float(n) * to_float(gamma[b * 16 + i])));
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+        const float ratio = __fmul_rn(__fmul_rn(amax, __fdiv_rn(1.0f, 6.0f)), __fdiv_rn(1.0f, s2));
+        const uint8_t sbits = e4m3_satfinite(ratio);
+        const float div = fmaxf(__fmul_rn(e4m3_to_float(sbits), s2), 1e-12f);
+        uint32_t w[2] = {0, 0};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint8_t byte = e2m1x2_satfinite(__fdiv_rn(v[2 * i], div), __fdiv_rn(v[2 * i + 1], div));
+            w[i >> 2] |= static_cast<uint32_t>(byte) << (8 * (i & 3));
+        }
+        *reinterpret_cast<uint2*>(codes + row * (K / 2) + b * 8) = make_uint2(w[0], w[1]);
+        sf_tiled[sf_tiled_offset(row, b, K / 64)] = sbits;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ weight quantize
 // The two-level weight quantizer (emmy/compiler/loader/quant.py:206-237), one thread per 16-element block:
 // block scale = amax_blk / 6 stored as e4m3 relative to scale_2; the divisor is the FUSED scale f16(dec(bits) * scale_2);
@@ -744,9 +794,28 @@ extern "C" size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K) {
     return align_up(static_cast<size_t>(M) * K / 2, 256) + align_up(sf_tiled_bytes(M, K), 256) + 256;
 }
 
+static int nvfp4_linear_any(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N, int64_t K,
+                            const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                            void* stream_, const void* gamma, float eps);
+
 extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N,
                                int64_t K, const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace,
                                size_t workspace_bytes, void* stream_) {
+    return nvfp4_linear_any(weight, weight_scale_tiled, weight_scale_2, N, K, x, input_scale, M, act_dtype, y, workspace, workspace_bytes, stream_,
+                            nullptr, 0.f);
+}
+
+extern "C" int eq_nvfp4_linear_rmsnorm(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N, int64_t K,
+                                       const void* x, const void* gamma, float eps, const float* input_scale, int64_t M, int act_dtype, void* y,
+                                       void* workspace, size_t workspace_bytes, void* stream_) {
+    EQ_REQUIRE(gamma, EQ_ERR_BAD_ARG, "eq_nvfp4_linear_rmsnorm: null norm weight");
+    return nvfp4_linear_any(weight, weight_scale_tiled, weight_scale_2, N, K, x, input_scale, M, act_dtype, y, workspace, workspace_bytes, stream_, gamma,
+                            eps);
+}
+
+static int nvfp4_linear_any(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N, int64_t K,
+                            const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
+                            void* stream_, const void* gamma, float eps) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     EQ_REQUIRE(N > 0 && K > 0 && M >= 0, EQ_ERR_BAD_ARG, "eq_nvfp4_linear: bad extents M=%lld K=%lld N=%lld", (long long)M, (long long)K, (long long)N);
     if (M == 0) return EQ_OK;
@@ -760,7 +829,27 @@ extern "C" int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scal
     uint8_t* codes = static_cast<uint8_t*>(workspace);
     uint8_t* sfa = codes + align_up(static_cast<size_t>(M) * K / 2, 256);
     int* status = reinterpret_cast<int*>(sfa + align_up(sf_tiled_bytes(M, K), 256));
-    int st = quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, false, status, stream);
+    int st = EQ_OK;
+    if (gamma) {
+        // the model's RMSNorm inside the quantize kernel (a programmatic dependent, like the plain quantize)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(M));
+        cfg.blockDim = dim3(256);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (act_dtype == EQ_F16)
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, rmsnorm_quant_nvfp4_rows_kernel<__half>, static_cast<const __half*>(x), static_cast<const __half*>(gamma), eps,
+                                          K, input_scale, codes, sfa, status));
+        else
+            EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, rmsnorm_quant_nvfp4_rows_kernel<__nv_bfloat16>, static_cast<const __nv_bfloat16*>(x),
+                                          static_cast<const __nv_bfloat16*>(gamma), eps, K, input_scale, codes, sfa, status));
+    } else {
+        st = quant_nvfp4_act(x, M, K, act_dtype, input_scale, codes, nullptr, sfa, false, status, stream);
+    }
     if (st != EQ_OK) return st;
     CUtensorMap map_a, map_b;
     if (M <= 16) {

@@ -107,6 +107,7 @@ def load() -> C.CDLL:
         "eq_nvfp4_tile_weight_scales": (i, [p, i64, i64, p, p]),
         "eq_nvfp4_workspace_bytes": (sz, [i64, i64]),
         "eq_nvfp4_linear": (i, [p, p, p, i64, i64, p, p, i64, i, p, p, sz, p]),
+        "eq_nvfp4_linear_rmsnorm": (i, [p, p, p, i64, i64, p, p, C.c_float, p, i64, i, p, p, sz, p]),
         "eq_nvfp4_status": (i, [p, i64, i64, p]),
         "eq_moe_route": (i, [p, i64, i64, i64, i, p, p, p]),
         "eq_moe_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),

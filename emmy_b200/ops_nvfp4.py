@@ -68,15 +68,27 @@ def nvfp4_workspace(m: int, k: int, device) -> torch.Tensor:
     return torch.zeros(max(L.load().eq_nvfp4_workspace_bytes(m, k), 256), dtype=torch.uint8, device=device)
 
 
-def nvfp4_linear(x, weight, weight_scale_tiled, weight_scale_2, input_scale, workspace=None, out=None):
-    """y[M, N] for packed e2m1 weight [N, K/2], tiled block scales, f32 weight_scale_2 [1] and input_scale [1]."""
-    _need_cuda(x, weight, weight_scale_tiled, weight_scale_2, input_scale)
+def nvfp4_linear(x, weight, weight_scale_tiled, weight_scale_2, input_scale, workspace=None, out=None, norm_weight=None, eps: float = 1e-6):
+    """y[M, N] for packed e2m1 weight [N, K/2], tiled block scales, f32 weight_scale_2 [1] and input_scale [1].
+    `norm_weight` ([K], x's dtype): the model's RMSNorm runs inside the quantize kernel, y = linear(rmsnorm(x) * norm_weight),
+    and input_scale is the global scale of those normalised activations."""
+    _need_cuda(x, weight, weight_scale_tiled, weight_scale_2, input_scale, norm_weight)
     m, k = x.shape
     n = weight.shape[0]
     if weight.shape[1] * 2 != k:
         raise ValueError(f"x has {k} features, the weight takes {weight.shape[1] * 2}")
     y = out if out is not None else torch.empty((m, n), dtype=x.dtype, device=x.device)
     ws = workspace if workspace is not None else nvfp4_workspace(m, k, x.device)
+    if norm_weight is not None:
+        if norm_weight.dtype != x.dtype or norm_weight.numel() != k:
+            raise ValueError("nvfp4_linear: norm_weight is [K] in x's dtype")
+        L.check(
+            L.load().eq_nvfp4_linear_rmsnorm(
+                _ptr(weight), _ptr(weight_scale_tiled), _ptr(weight_scale_2), n, k, _ptr(x), _ptr(norm_weight), float(eps), _ptr(input_scale), m,
+                _DTYPE[x.dtype], _ptr(y), _ptr(ws), ws.numel(), _stream(),
+            )
+        )
+        return y
     L.check(
         L.load().eq_nvfp4_linear(
             _ptr(weight), _ptr(weight_scale_tiled), _ptr(weight_scale_2), n, k, _ptr(x), _ptr(input_scale), m, _DTYPE[x.dtype],

@@ -264,6 +264,11 @@ size_t eq_nvfp4_workspace_bytes(int64_t M, int64_t K);
 int eq_nvfp4_linear(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N,
                     int64_t K, const void* x, const float* input_scale, int64_t M, int act_dtype, void* y, void* workspace,
                     size_t workspace_bytes, void* stream);
+/* RMSNorm -> static quantize -> linear with the norm inside the quantize kernel (as eq_fp8_linear_rmsnorm): gamma [K] in
+ * act_dtype; input_scale is the calibrated global scale of the NORMALISED activations. */
+int eq_nvfp4_linear_rmsnorm(const uint8_t* weight, const uint8_t* weight_scale_tiled, const float* weight_scale_2, int64_t N, int64_t K,
+                            const void* x, const void* gamma, float eps, const float* input_scale, int64_t M, int act_dtype, void* y,
+                            void* workspace, size_t workspace_bytes, void* stream);
 int eq_nvfp4_status(const void* workspace, int64_t M, int64_t K, void* stream);
 
 /* ------------------------------------------------------------------ MoE on W4A16 experts */

@@ -179,3 +179,23 @@ def test_mxfp4_decode_bit_exact(golden):
     np.testing.assert_array_equal(ops.dequant_mxfp4(dev(blocks), dev(scales)).cpu().numpy(), ref)
     got16 = ops.dequant_mxfp4(dev(blocks), dev(scales), torch.bfloat16).float().cpu().numpy()
     np.testing.assert_array_equal(got16, fm.round_bf16(ref))
+
+
+@pytest.mark.parametrize("m", [1, 12, 200])
+def test_rmsnorm_inside_the_quantize(m):
+    """y = nvfp4_linear(rmsnorm(x) * gamma) with the norm fused into the static quantize kernel, against the oracle's eager
+    RMSNorm followed by the oracle linear (decode tile, 128-row tile)."""
+    from emmy_b200 import ops_nvfp4 as o4
+
+    n, k = 264, 1024
+    packed, sbits, s2 = synth.nvfp4_weight(n, k, seed=m)
+    x = fm.round_bf16(synth.activations(m, k, "bf16", seed=300 + m) * 2.0)
+    gamma = fm.round_bf16(1.0 + 0.1 * np.random.default_rng(m).standard_normal(k).astype(np.float32))
+    h = oact.rmsnorm(x, gamma, 1e-6, "bf16")
+    s2x = oact.nvfp4_global_scale(h)
+    ref = ol.nvfp4_linear(h, packed, sbits, s2, s2x)
+    tiled = o4.nvfp4_tile_weight_scales(dev(sbits), k)
+    y = o4.nvfp4_linear(dev(x).bfloat16(), dev(packed), tiled, dev(s2), torch.tensor([s2x], device="cuda"), norm_weight=dev(gamma).bfloat16(), eps=1e-6)
+    got = y.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
