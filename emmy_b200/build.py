@@ -63,7 +63,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
             list(pool.map(compile_one, jobs))
     objs = [OBJ / (s.stem + ".o") for s in sources]
-    if jobs or not LIB.exists():
+    # relink also when an earlier build compiled objects and was interrupted before this step
+    if jobs or not LIB.exists() or LIB.stat().st_mtime < max(o.stat().st_mtime for o in objs):
         cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:

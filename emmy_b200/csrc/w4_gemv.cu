@@ -1,8 +1,9 @@
 // W4A16 linear: the entry points and their dispatch.
 //
 //   M == 1         w4a16_gemv1_kernel (w4_gemv1.cu): half-SM CTAs, equal item spans, launches overlap in pairs.
-//   2 <= M <= 16   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles, x staged in shared
-//                  memory (whole, or a K slice per CTA with the slices meeting in the workspace).
+//   2 <= M <= 32   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles, x staged in shared
+//                  memory (whole, or a K slice per CTA with the slices meeting in the workspace).  From 17 rows on only
+//                  where a slice of x fits; otherwise the next line.
 //   M > 16         w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
 //   w4a16_tile_kernel below: M > 16 with an output that is not 16-byte aligned (in 64-row blocks), and decode
 //   shapes whose activations do not fit shared memory (K beyond about 100 k at M == 1).
@@ -117,6 +118,27 @@ static int w4a16_check(const char* who, const void* wq, int scale_dtype, int64_t
     return EQ_OK;
 }
 
+static W4Params w4_params(const void* wq, const int32_t* perm, const void* x, void* y, float* partial, int* counters, int64_t K, int64_t N, int M,
+                          int scale_dtype) {
+    W4Params p;
+    p.wq = static_cast<const unsigned char*>(wq);
+    p.perm = perm;
+    p.x = x;
+    p.y = y;
+    p.wsp = partial;
+    p.counters = counters;
+    p.K = static_cast<int>(K);
+    p.N = static_cast<int>(N);
+    p.M = M;
+    p.items = static_cast<int>(K / 128);
+    p.splits = plan_splits(K, N);
+    p.scale_dtype = scale_dtype;
+    p.x_rows = nullptr;
+    p.y_rows = nullptr;
+    p.y_ptrs = nullptr;
+    return p;
+}
+
 extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                                const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
                                void* stream_) {
@@ -131,6 +153,15 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     float* partial = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kW4Header);
     int* counters = reinterpret_cast<int*>(partial + w4_front_rows(M) * N);
 
+    const bool streamable = static_cast<long long>(N / 16) * (K / 128) < (1LL << 30);
+    if (M > 16 && M <= 32 && streamable) {
+        // up to 32 rows still stream the weight once through the mma.sync tile (x staged in shared memory, K sliced where
+        // it does not fit); a shape that does not fit falls through to the tensor path
+        W4Params p = w4_params(wq, perm, x, y, partial, counters, K, N, static_cast<int>(M), scale_dtype);
+        bool fits = false;
+        const int st = w4_stream_launch(p, act_dtype, stream, &fits);
+        if (st != EQ_OK || fits) return st;
+    }
     if (M > 16 && aligned(y, 16)) {
         // prefill-shaped: the tcgen05 kernel; its bounded waits report through the status word, cleared per call
         EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
@@ -153,25 +184,11 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     const size_t esz = 2;
     for (int64_t m0 = 0; m0 < M; m0 += 64) {
         const int mb = static_cast<int>(M - m0 < 64 ? M - m0 : 64);
-        W4Params p;
-        p.wq = static_cast<const unsigned char*>(wq);
-        p.perm = perm;
-        p.x = static_cast<const char*>(x) + static_cast<size_t>(m0) * K * esz;
-        p.y = static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz;
-        p.wsp = partial;
-        p.counters = counters;
-        p.K = static_cast<int>(K);
-        p.N = static_cast<int>(N);
-        p.M = mb;
-        p.items = static_cast<int>(K / 128);
-        p.splits = plan_splits(K, N);
-        p.scale_dtype = scale_dtype;
-        p.x_rows = nullptr;
-        p.y_rows = nullptr;
-        p.y_ptrs = nullptr;
+        W4Params p = w4_params(wq, perm, static_cast<const char*>(x) + static_cast<size_t>(m0) * K * esz,
+                               static_cast<char*>(y) + static_cast<size_t>(m0) * N * esz, partial, counters, K, N, mb, scale_dtype);
         int st = EQ_OK;
         bool fits = false;
-        if (mb > 1 && mb <= 16 && static_cast<long long>(N / 16) * (K / 128) < (1LL << 30))
+        if (mb > 1 && mb <= 16 && streamable)
             st = w4_stream_launch(p, act_dtype, stream, &fits);  // decode-shaped: one wave of equal spans
         if (st != EQ_OK) return st;
         if (!fits)  // shapes whose staging does not fit shared memory, and row blocks of an unaligned output: K splits

@@ -1,4 +1,4 @@
-// W4A16 linear, 2 <= M <= 16: the streaming form of the tile kernel (w4_tile.cuh).  (One row has its own kernel,
+// W4A16 linear, 2 <= M <= 32: the streaming form of the tile kernel (w4_tile.cuh).  (One row has its own kernel,
 // w4_gemv1.cu.)
 //
 // The weight is one flat run of item records, [n-tile][item].  The grid is one CTA of 16 warps per SM; a CTA owns a
@@ -138,8 +138,11 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     // Unstaged with one row block: the rows of x run one item ahead of the weights in registers (they come from L1 /
     // L2, and with four warps per scheduler nothing else would cover that latency); two row blocks would spill.
     constexpr bool kAhead = !STAGED && MT == 1;
-    uint4 xv[MT][4];
-    if (kAhead && n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
+    static_assert(STAGED || MT <= 2, "three and four row blocks read their operands from shared memory, block by block");
+    uint4 xv[MT > 2 ? 1 : MT][4];
+    if constexpr (kAhead) {
+        if (n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
+    }
 
     for (int i = 0; i < n; ++i) {
         const int d = i % kStreamDepth;
@@ -151,14 +154,16 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
         const uint2 mt_ = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
         __syncwarp();  // every lane has read the slot before any lane refills it
         issue(d, i + kStreamDepth);  // the slot's bytes are in registers: refill it
-        if (STAGED) {
+        if constexpr (STAGED && MT > 2) {
+            w4_item_math_smem<ActT, MT>(p, xs + static_cast<size_t>(it) * MT * 2048 + lane * 16, wl, wh, mt_, yacc);
+        } else if constexpr (STAGED) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
                     xv[mt][c] = *reinterpret_cast<const uint4*>(xs + (static_cast<size_t>(it * MT + mt) * 4 + c) * 512 + lane * 16);
             w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
-        } else if (kAhead) {
+        } else if constexpr (kAhead) {
             uint4 xn[MT][4];
             const int it_next = it + 1 == p.items ? 0 : it + 1;
             if (i + 1 < n) w4_item_x<ActT, MT, false>(p, x, it_next, g, j, xn);
@@ -242,6 +247,33 @@ static int launch_stream_depth(W4Params p, size_t smem, long long ctas, cudaStre
     return EQ_OK;
 }
 
+// K slices for a staged x that does not fit whole: 2, 4 or 8 slices so that a slice does, groups of tiles x slices
+// filling the SMs as evenly as whole tiles allow.  Returns the slice count (0: none fits) for a ring of `depth` items.
+struct SplitPlan {
+    int slices = 0;
+    long long ctas = 0, group_tiles = 0;
+    size_t smem = 0;
+};
+static SplitPlan plan_split(const W4Params& p, long long tiles, int rows, int depth) {
+    SplitPlan best;
+    for (int sp = 2; sp <= 8; sp *= 2) {
+        if (p.items < sp) break;
+        const size_t slice = staged_x_bytes(static_cast<int64_t>(ceil_div(static_cast<long long>(p.items), sp)) * 128, rows);
+        const long long groups_want = sm_count() / sp > 0 ? sm_count() / sp : 1;
+        const long long tpg = ceil_div(tiles, groups_want);
+        const long long groups = ceil_div(tiles, tpg);
+        const size_t smem = stream_smem(tpg, 1, rows, depth, slice);
+        if (!smem) continue;
+        if (groups * sp > best.ctas) {
+            best.ctas = groups * sp;
+            best.slices = sp;
+            best.group_tiles = tpg;
+            best.smem = smem;
+        }
+    }
+    return best;
+}
+
 template <typename ActT, int MT>
 static int launch_stream(W4Params p, cudaStream_t stream, bool* fits) {
     const long long tiles = p.N / 16;
@@ -260,47 +292,38 @@ static int launch_stream(W4Params p, cudaStream_t stream, bool* fits) {
         if (const size_t smem = stream_smem(tiles, ctas, rows, 6, staged)) return launch_stream_depth<ActT, MT, 6, true>(p, smem, ctas, stream);
         if (const size_t smem = stream_smem(tiles, ctas, rows, 4, staged)) return launch_stream_depth<ActT, MT, 4, true>(p, smem, ctas, stream);
         if (const size_t smem = stream_smem(tiles, ctas, rows, 3, staged)) return launch_stream_depth<ActT, MT, 3, true>(p, smem, ctas, stream);
-        // x does not fit: cut K into 2, 4 or 8 slices so that a slice does, groups of tiles x slices filling the SMs as
-        // evenly as whole tiles allow (needs the f32 workspace)
+        // x does not fit: cut K into slices (needs the f32 workspace)
         if (p.wsp && p.counters) {
-            int best_s = 0;
-            long long best_ctas = 0, best_tpg = 0;
-            for (int sp = 2; sp <= 8; sp *= 2) {
-                if (p.items < sp) break;
-                const size_t slice = staged_x_bytes(static_cast<int64_t>(ceil_div(static_cast<long long>(p.items), sp)) * 128, rows);
-                const long long groups_want = sm_count() / sp > 0 ? sm_count() / sp : 1;
-                const long long tpg = ceil_div(tiles, groups_want);
-                const long long groups = ceil_div(tiles, tpg);
-                if (!stream_smem(tpg, 1, rows, 4, slice)) continue;
-                if (groups * sp > best_ctas) {
-                    best_ctas = groups * sp;
-                    best_s = sp;
-                    best_tpg = tpg;
-                }
-            }
-            if (best_s) {
-                p.splits = best_s;
-                p.group_tiles = static_cast<int>(best_tpg);
-                p.acc_tiles = static_cast<int>(best_tpg);
-                const size_t slice = staged_x_bytes(static_cast<int64_t>(ceil_div(static_cast<long long>(p.items), best_s)) * 128, rows);
-                return launch_stream_depth<ActT, MT, 4, true, true>(p, stream_smem(best_tpg, 1, rows, 4, slice), best_ctas, stream);
+            SplitPlan plan = plan_split(p, tiles, rows, 4);
+            const bool deep = plan.slices != 0;
+            if (!deep) plan = plan_split(p, tiles, rows, 3);
+            if (plan.slices) {
+                p.splits = plan.slices;
+                p.group_tiles = static_cast<int>(plan.group_tiles);
+                p.acc_tiles = static_cast<int>(plan.group_tiles);
+                return deep ? launch_stream_depth<ActT, MT, 4, true, true>(p, plan.smem, plan.ctas, stream)
+                            : launch_stream_depth<ActT, MT, 3, true, true>(p, plan.smem, plan.ctas, stream);
             }
         }
     }
-    // the deepest ring that fits
-    if (const size_t smem = stream_smem(tiles, ctas, rows, 6, 0)) return launch_stream_depth<ActT, MT, 6, false>(p, smem, ctas, stream);
-    if (const size_t smem = stream_smem(tiles, ctas, rows, 4, 0)) return launch_stream_depth<ActT, MT, 4, false>(p, smem, ctas, stream);
-    *fits = false;  // the accumulators of the CTA's tiles do not fit shared memory
+    if constexpr (MT <= 2) {
+        // the deepest ring that fits, x read from global memory
+        if (const size_t smem = stream_smem(tiles, ctas, rows, 6, 0)) return launch_stream_depth<ActT, MT, 6, false>(p, smem, ctas, stream);
+        if (const size_t smem = stream_smem(tiles, ctas, rows, 4, 0)) return launch_stream_depth<ActT, MT, 4, false>(p, smem, ctas, stream);
+    }
+    *fits = false;  // the accumulators of the CTA's tiles (or, with more than 16 rows, a slice of x) do not fit shared memory
     return EQ_OK;
 }
 
 template <typename ActT>
 static int stream_dispatch(const W4Params& p, cudaStream_t stream, bool* fits) {
     if (p.M <= 8) return launch_stream<ActT, 1>(p, stream, fits);
-    return launch_stream<ActT, 2>(p, stream, fits);
+    if (p.M <= 16) return launch_stream<ActT, 2>(p, stream, fits);
+    if (p.M <= 24) return launch_stream<ActT, 3>(p, stream, fits);
+    return launch_stream<ActT, 4>(p, stream, fits);
 }
 
-// 2 <= M <= 16, total items < 2^31.  *fits is cleared, and nothing launched, when the shape does not fit.
+// 2 <= M <= 32, total items < 2^31.  *fits is cleared, and nothing launched, when the shape does not fit.
 int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream, bool* fits) {
     return act_dtype == EQ_F16 ? stream_dispatch<__half>(p, stream, fits) : stream_dispatch<__nv_bfloat16>(p, stream, fits);
 }

@@ -195,6 +195,50 @@ __device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv
     }
 }
 
+// The same product for three or four row blocks whose operands lie in shared memory in the order the lanes read them
+// (xs_lane: this lane's first 16 bytes of the item; row block mt, chunk c at (mt * 4 + c) * 512).  The eight weight
+// fragments are expanded once and kept; each row block then loads its own operands, so the registers hold one block's
+// operands at a time instead of all of them.
+template <typename ActT, int MT>
+__device__ __forceinline__ void w4_item_math_smem(const W4Params& p, const unsigned char* xs_lane, const uint4& wl, const uint4& wh,
+                                                  const uint2& mt_, float (&yacc)[MT][4]) {
+    float s_lo, s_hi;
+    if (p.scale_dtype == EQ_F16) {
+        const __half2 s = *reinterpret_cast<const __half2*>(&mt_.x);
+        s_lo = __low2float(s);
+        s_hi = __high2float(s);
+    } else {
+        s_lo = __uint_as_float(mt_.x << 16);
+        s_hi = __uint_as_float(mt_.x & 0xFFFF0000u);
+    }
+    const typename Frag<ActT>::Zero z_lo = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x1010));
+    const typename Frag<ActT>::Zero z_hi = Frag<ActT>::zero(__byte_perm(mt_.y, 0, 0x3232));
+    const uint32_t words[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
+    uint32_t a[8][4];
+#pragma unroll
+    for (int s = 0; s < 8; ++s) Frag<ActT>::expand(words[s], z_lo, z_hi, a[s]);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        uint4 xv[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) xv[c] = *reinterpret_cast<const uint4*>(xs_lane + (mt * 4 + c) * 512);
+        const uint32_t* lo = reinterpret_cast<const uint32_t*>(&xv[0]);
+        const uint32_t* hi = reinterpret_cast<const uint32_t*>(&xv[2]);
+        float acc[2][4];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            if (s < 2)
+                Frag<ActT>::mma0(acc[s & 1], a[s], lo[s], hi[s]);
+            else
+                Frag<ActT>::mma(acc[s & 1], a[s], lo[s], hi[s]);
+        }
+        yacc[mt][0] = fmaf(s_lo, acc[0][0] + acc[1][0], yacc[mt][0]);
+        yacc[mt][1] = fmaf(s_lo, acc[0][1] + acc[1][1], yacc[mt][1]);
+        yacc[mt][2] = fmaf(s_hi, acc[0][2] + acc[1][2], yacc[mt][2]);
+        yacc[mt][3] = fmaf(s_hi, acc[0][3] + acc[1][3], yacc[mt][3]);
+    }
+}
+
 template <typename ActT, int MT, bool ONE>
 __device__ __forceinline__ void w4_item(const W4Params& p, const ActT* x, int it, const uint4& wl, const uint4& wh, const uint2& mt_,
                                         int g, int j, float (&yacc)[MT][4]) {
