@@ -159,6 +159,10 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     uint64_t* acc_ready = bars + 3 * kStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
 
+    // Plain launches are programmatic dependents (launch_cfg): the next grid may start its prologue and its first weight
+    // loads while this one runs, and this one does the same behind its predecessor.  Weights never depend on the
+    // previous grid; x, y and the split-K scratch may, so the warps that touch them wait below.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN;
     int m0 = blockIdx.y * (128 * HALVES), m_end = M;
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
         // ---- TMA producer of the activation tiles
         if (tc::elect_one()) {
             tc::tma_prefetch_desc(&map_x);
+            asm volatile("griddepcontrol.wait;" ::: "memory");  // x may be the previous grid's output
             int stage = 0;
             uint32_t phase = 0;
             bool first = true;
@@ -299,6 +304,7 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
                 }
             }
         }
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // these warps store y / add into the split-K scratch later
         bool broken = false, first = true;
         int stage = 0;
         uint32_t phase = 0;
@@ -573,6 +579,24 @@ __global__ void __launch_bounds__(GemmCfg<HALVES, BN, DW, AHEAD>::kThreads)
     }
 }
 
+// Launch, as a programmatic dependent of the stream's previous kernel when asked (plain linears; the grouped modes read a
+// block list the previous kernel wrote before anything else and stay ordinary launches).
+template <typename Kernel, typename... Args>
+int launch_pdl(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, kernel, args...));
+    return EQ_OK;
+}
+
 template <typename ActT, int HALVES, int BN, int DW, int AHEAD, int MODE>
 int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y, int64_t M, int64_t N, int64_t K, int* status,
                const GroupArgs& grp, unsigned grid_y, cudaStream_t stream) {
@@ -586,10 +610,8 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
     auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, true, MODE> : w4a16_gemm_tc_kernel<ActT, HALVES, BN, DW, AHEAD, false, MODE>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
     dim3 grid(static_cast<unsigned>(ceil_div(N, BN)), grid_y);
-    kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, grp,
-                                                        SplitArgs{nullptr, nullptr});
-    EQ_LAUNCH_OK("w4a16_gemm_tc_kernel");
-    return EQ_OK;
+    return launch_pdl(kernel, grid, Cfg::kThreads, Cfg::kSmem, stream, MODE == kPlain, map_x, wq, y, static_cast<int>(M), static_cast<int>(N),
+                      static_cast<int>(K), status, grp, SplitArgs{nullptr, nullptr});
 }
 
 // M <= 128: 128 x 256 tiles with K split over gridDim.z so that about one CTA per SM runs.
@@ -613,14 +635,13 @@ int launch_split(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* 
     if (splits == 1) {
         auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, false> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, false>;
         EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
-        kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, none, sp);
-    } else {
-        auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, true> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, true>;
-        EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
-        kernel<<<grid, Cfg::kThreads, Cfg::kSmem, stream>>>(map_x, wq, y, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), status, none, sp);
+        return launch_pdl(kernel, grid, Cfg::kThreads, Cfg::kSmem, stream, true, map_x, wq, y, static_cast<int>(M), static_cast<int>(N),
+                          static_cast<int>(K), status, none, sp);
     }
-    EQ_LAUNCH_OK("w4a16_gemm_tc_kernel (split K)");
-    return EQ_OK;
+    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, true> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, true>;
+    EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
+    return launch_pdl(kernel, grid, Cfg::kThreads, Cfg::kSmem, stream, true, map_x, wq, y, static_cast<int>(M), static_cast<int>(N),
+                      static_cast<int>(K), status, none, sp);
 }
 
 template <typename ActT>

@@ -163,8 +163,9 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
         if (st != EQ_OK || fits) return st;
     }
     if (M > 16 && aligned(y, 16)) {
-        // prefill-shaped: the tcgen05 kernel; its bounded waits report through the status word, cleared per call
-        EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+        // prefill-shaped: the tcgen05 kernel; its bounded waits report through the status word.  No call clears the
+        // word (a clear would be one more node between this kernel and the one before it, which it overlaps as a
+        // programmatic dependent): it stays set until eq_w4a16_status has reported it.
         void* gathered = static_cast<unsigned char*>(workspace) + w4_gather_offset(M, N);
         const int st = w4_gemm_tc_launch(static_cast<const unsigned char*>(wq), scale_dtype, perm, x, y, M, N, K, act_dtype, gathered, status,
                                          partial, counters, stream);
@@ -258,8 +259,7 @@ extern "C" int eq_w4a16_gate_up_swiglu(const void* wq, int scale_dtype, const in
     const size_t inner = gu_align(eq_w4a16_workspace_bytes(M, 2 * I, K));
     unsigned char* extra = static_cast<unsigned char*>(workspace) + inner;
     if (M > 16 && !perm && aligned(h, 16)) {
-        int* status = static_cast<int*>(workspace);
-        EQ_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), stream));
+        int* status = static_cast<int*>(workspace);  // sticky until eq_w4a16_status reports it, as in eq_w4a16_linear
         RowBlock* blocks = reinterpret_cast<RowBlock*>(extra);
         const int nb = static_cast<int>((M + 255) / 256);
         int32_t* n_blocks = reinterpret_cast<int32_t*>(blocks + nb);
@@ -287,6 +287,10 @@ extern "C" int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void
     int host = 0;
     EQ_CUDA_OK(cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream));
     EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    if (host != 0) {  // reported once: the next calls start from a clean word
+        EQ_CUDA_OK(cudaMemsetAsync(const_cast<void*>(workspace), 0, sizeof(int), stream));
+        EQ_CUDA_OK(cudaStreamSynchronize(stream));
+    }
     EQ_REQUIRE(host == 0, EQ_ERR_TIMEOUT, "eq_w4a16_status: the workspace status word is set (%d)", host);
     return EQ_OK;
 }

@@ -140,7 +140,8 @@ int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_
                     void* stream);
 /* The device-side waits (the tensor-path kernel's pipeline barriers, the GEMV's wait for a neighbour's sixteen words)
  * are bounded; one that runs out sets the status word at the start of the workspace and the affected outputs are
- * undefined.  This call synchronizes the stream, reads the word and returns EQ_ERR_TIMEOUT if it is set (the
+ * undefined.  The linear itself never clears the word: it stays set over later calls until this call, which
+ * synchronizes the stream, reads the word, clears it if it was set and returns EQ_ERR_TIMEOUT in that case (the
  * reference's counterpart is the host-side hung-launch deadline, crates/emmy-runtime/src/cuda.rs:1401-1451). */
 int eq_w4a16_status(const void* workspace, int64_t M, int64_t N, void* stream);
 
