@@ -295,7 +295,7 @@ def wl_w4(device, rank, fmt, k, n, m):
         for w in ws:
             ops.w4a16_linear(x, w, workspace=wsp, out=y)
 
-    kernel = GEMV_KERNEL if m == 1 else ("w4a16_stream_kernel" if m <= 32 else "w4a16_gemm_tc_kernel<__half>")
+    kernel = GEMV_KERNEL if m == 1 else ("w4a16_stream_kernel" if m <= 24 else "w4a16_gemm_tc_kernel<__half>")
     return dict(step=step, calls=copies, kernels_per_call=1, alg_bytes=algorithmic_bytes(k, n, m, fmt == "gptq"), flops=2.0 * m * k * n, peak_mult=1.0,
                 h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: ops.w4a16_status(wsp, m, n), kernel=kernel,
                 dtype="int4 weights, f16 activations, f32 accumulate")
@@ -588,10 +588,10 @@ def extra_records(device, rank, world, clocks, quick_steps=3):
             add(lambda: wl_w4(device, rank, "awq", 4096, 4096, m), quick_steps, clocks, f"awq_4096_m{m}", "w4a16_gemv_hbm_gbs", "GB/s",
                 f"AWQ W4A16, K=N=4096, group 128, M={m}")
         for proj, (k, n) in (("gate_up", SHAPES["gate"]), ("down", SHAPES["down"])):
-            for m in (4, 16, 32, 64, 256, 8192):
-                unit = "GB/s" if m <= 32 else "TFLOP/s"
+            for m in (4, 16, 24, 64, 256, 8192):
+                unit = "GB/s" if m <= 24 else "TFLOP/s"
                 add(lambda: wl_w4(device, rank, "gptq", k, n, m), quick_steps, clocks, f"gptq_{proj}_m{m}",
-                    "w4a16_gemv_hbm_gbs" if m <= 32 else "w4a16_gemm_tflops", unit, f"GPTQ act-order W4A16, Llama-3.1-8B {proj} K={k} N={n}, M={m}")
+                    "w4a16_gemv_hbm_gbs" if m <= 24 else "w4a16_gemm_tflops", unit, f"GPTQ act-order W4A16, Llama-3.1-8B {proj} K={k} N={n}, M={m}")
         add(lambda: wl_gate_up_fused(device, rank), quick_steps, clocks, "gptq_gate_up_fused_m1", "w4a16_gemv_hbm_gbs", "GB/s",
             "GPTQ act-order W4A16, Llama-3.1-8B gate and up as one [gate | up] linear K=4096 N=28672, M=1: one launch for both projections")
         for m in (1, 16, 2048):

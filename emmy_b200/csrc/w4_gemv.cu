@@ -1,7 +1,7 @@
 // W4A16 linear: the entry points and their dispatch.
 //
 //   M == 1         w4a16_gemv1_kernel (w4_gemv1.cu): half-SM CTAs, equal item spans, launches overlap in pairs.
-//   2 <= M <= 32   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles, x staged in shared
+//   2 <= M <= 24   w4a16_stream_kernel (w4_stream.cu): one fat CTA per SM streams whole column tiles, x staged in shared
 //                  memory (whole, or a K slice per CTA with the slices meeting in the workspace).  From 17 rows on only
 //                  where a slice of x fits; otherwise the next line.
 //   M > 16         w4a16_gemm_tc_kernel (w4_gemm.cu): tcgen05, weights dequantised into shared memory.
@@ -154,8 +154,8 @@ extern "C" int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* p
     int* counters = reinterpret_cast<int*>(partial + w4_front_rows(M) * N);
 
     const bool streamable = static_cast<long long>(N / 16) * (K / 128) < (1LL << 30);
-    if (M > 16 && M <= 32 && streamable) {
-        // up to 32 rows still stream the weight once through the mma.sync tile (x staged in shared memory, K sliced where
+    if (M > 16 && M <= 24 && streamable) {
+        // up to 24 rows still stream the weight once through the mma.sync tile (x staged in shared memory, K sliced where
         // it does not fit); a shape that does not fit falls through to the tensor path
         W4Params p = w4_params(wq, perm, x, y, partial, counters, K, N, static_cast<int>(M), scale_dtype);
         bool fits = false;

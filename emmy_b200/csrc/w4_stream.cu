@@ -1,4 +1,4 @@
-// W4A16 linear, 2 <= M <= 32: the streaming form of the tile kernel (w4_tile.cuh).  (One row has its own kernel,
+// W4A16 linear, 2 <= M <= 24: the streaming form of the tile kernel (w4_tile.cuh).  (One row has its own kernel,
 // w4_gemv1.cu.)
 //
 // The weight is one flat run of item records, [n-tile][item].  The grid is one CTA of 16 warps per SM; a CTA owns a
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
     // Unstaged with one row block: the rows of x run one item ahead of the weights in registers (they come from L1 /
     // L2, and with four warps per scheduler nothing else would cover that latency); two row blocks would spill.
     constexpr bool kAhead = !STAGED && MT == 1;
-    static_assert(STAGED || MT <= 2, "three and four row blocks read their operands from shared memory, block by block");
+    static_assert(STAGED || MT <= 2, "three row blocks read their operands from shared memory, block by block");
     uint4 xv[MT > 2 ? 1 : MT][4];
     if constexpr (kAhead) {
         if (n > 0) w4_item_x<ActT, MT, false>(p, x, it, g, j, xv);
@@ -319,11 +319,10 @@ template <typename ActT>
 static int stream_dispatch(const W4Params& p, cudaStream_t stream, bool* fits) {
     if (p.M <= 8) return launch_stream<ActT, 1>(p, stream, fits);
     if (p.M <= 16) return launch_stream<ActT, 2>(p, stream, fits);
-    if (p.M <= 24) return launch_stream<ActT, 3>(p, stream, fits);
-    return launch_stream<ActT, 4>(p, stream, fits);
+    return launch_stream<ActT, 3>(p, stream, fits);
 }
 
-// 2 <= M <= 32, total items < 2^31.  *fits is cleared, and nothing launched, when the shape does not fit.
+// 2 <= M <= 24, total items < 2^31.  *fits is cleared, and nothing launched, when the shape does not fit.
 int w4_stream_launch(const W4Params& p, int act_dtype, cudaStream_t stream, bool* fits) {
     return act_dtype == EQ_F16 ? stream_dispatch<__half>(p, stream, fits) : stream_dispatch<__nv_bfloat16>(p, stream, fits);
 }

@@ -195,7 +195,7 @@ __device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv
     }
 }
 
-// The same product for three or four row blocks whose operands lie in shared memory in the order the lanes read them
+// The same product for three (or more) row blocks whose operands lie in shared memory in the order the lanes read them
 // (xs_lane: this lane's first 16 bytes of the item; row block mt, chunk c at (mt * 4 + c) * 512).  The eight weight
 // fragments are expanded once and kept; each row block then loads its own operands, so the registers hold one block's
 // operands at a time instead of all of them.

@@ -163,7 +163,7 @@ def test_awq_linear_config1(m):
 @pytest.mark.parametrize("shape", [(4096, 14336), (14336, 4096)])
 @pytest.mark.parametrize("m", [1, 4, 16, 20, 32])
 def test_gptq_act_order_llama_mlp(shape, m):
-    """GPTQ act-order, Llama-3.1-8B MLP shapes, decode-shaped M (from 17 rows on x is staged in K slices)."""
+    """GPTQ act-order, Llama-3.1-8B MLP shapes, decode-shaped M (17 to 24 rows: x staged in K slices; 32: the tensor path)."""
     from emmy_b200 import ops
 
     k, n = shape
