@@ -514,7 +514,10 @@ def wl_tp_mlp(device, rank, world, m):
     y_host = torch.empty(m, h, dtype=torch.float16).pin_memory()
     x = x_host.to(device)
     y = torch.empty(m, h, dtype=torch.float16, device=device)
-    down = shard.RowParallelLinear(lambda v: ops.w4a16_linear(v, local["down"]), slice(0, inter // world))
+    # decode-sized results are summed by one kernel over NVLink peer memory, larger ones by NCCL
+    reducer = shard.PeerAllReduce(None, 64 * h, device) if world > 1 else None
+    down = shard.RowParallelLinear(lambda v: ops.w4a16_linear(v, local["down"]), slice(0, inter // world), reducer=reducer)
+    peer_sum = reducer is not None and m * h <= reducer.cap
 
     def mlp(weights, xx):
         return torch.nn.functional.silu(ops.w4a16_linear(xx, weights["gate"])) * ops.w4a16_linear(xx, weights["up"])
@@ -523,7 +526,10 @@ def wl_tp_mlp(device, rank, world, m):
     local_gu = ops.w4_concat([local["gate"], local["up"]])
     def step():
         hidden = ops.w4a16_gate_up_swiglu(x, local_gu)  # [M, inter / world]: this rank's columns, SwiGLU in the GEMM's epilogue
-        y.copy_(down(hidden) if world > 1 else ops.w4a16_linear(hidden, local["down"]))
+        if world > 1:
+            down(hidden, sliced=True, out=y)
+        else:
+            ops.w4a16_linear(hidden, local["down"], out=y)
 
     def parity():
         rows = torch.arange(0, m, max(1, m // 32), device=device)
@@ -531,8 +537,10 @@ def wl_tp_mlp(device, rank, world, m):
         return float((y[rows].float() - ref).abs().max() / ref.abs().max())
 
     return dict(step=step, calls=1, kernels_per_call=5, alg_bytes=sum(algorithmic_bytes(k, n, m) for k, n in SHAPES.values()) // world,
-                flops=2.0 * m * 3 * h * inter / world, peak_mult=1.0, h2d=[(x, x_host)], d2h=[(y_host, y)], status=lambda: None, capture=True,
-                parity=parity, kernel="w4a16 linears + NCCL all-reduce", dtype="int4 weights, f16 activations, f32 accumulate and all-reduce")
+                flops=2.0 * m * 3 * h * inter / world, peak_mult=1.0, h2d=[(x, x_host)], d2h=[(y_host, y)],
+                status=(reducer.status if peer_sum else (lambda: None)), capture=True, parity=parity,
+                kernel="w4a16 linears + " + ("peer_allreduce_kernel (peer memory)" if peer_sum else "NCCL all-reduce"),
+                dtype="int4 weights, f16 activations, f32 accumulate and all-reduce")
 
 
 # --------------------------------------------------------------------------------------------- records
@@ -615,7 +623,8 @@ def extra_records(device, rank, world, clocks, quick_steps=3):
             "stored back from the second GEMM's epilogue over NVLink peer memory")
         for m in (16, 2048):
             add(lambda: wl_tp_mlp(device, rank, world, m), quick_steps, clocks, f"tp_mlp_m{m}", "w4a16_mlp_tflops", "TFLOP/s",
-                f"tensor-parallel Llama-3.1-8B MLP over {world} ranks: gate/up column-parallel, down row-parallel + f32 all-reduce (NCCL), M={m}")
+                f"tensor-parallel Llama-3.1-8B MLP over {world} ranks: gate/up column-parallel, down row-parallel + f32 sum of the partials "
+                f"({'one kernel over NVLink peer memory' if m * 4096 <= 64 * 4096 else 'NCCL all-reduce'}), M={m}")
     return recs
 
 

@@ -40,6 +40,19 @@ class EpPeers(C.Structure):
     ]
 
 
+class ArPeers(C.Structure):
+    """struct eq_ar_peers of include/emmyq.h."""
+
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("cap", C.c_int64),
+        ("max_blocks", C.c_int64),
+        ("recv", C.c_void_p * EQ_EP_MAX_RANKS),
+        ("flags", C.c_void_p * EQ_EP_MAX_RANKS),
+    ]
+
+
 class EmmyqError(RuntimeError):
     """A C-ABI call returned a negative status."""
 
@@ -120,6 +133,11 @@ def load() -> C.CDLL:
         "eq_ep_moe_workspace_bytes": (sz, [i64, i64, i64, i64, i64]),
         "eq_ep_moe_w4a16": (i, [p, p, i, i64, i64, i64, i64, i64, p, p, p, i64, i, p, C.POINTER(EpPeers), C.c_uint32, p, sz, p]),
         "eq_ep_moe_status": (i, [p, i64, i64, i64, i64, i64, p]),
+        "eq_peer_allreduce_recv_bytes": (sz, [i64, i64]),
+        "eq_peer_allreduce_flag_bytes": (sz, [i64, i64]),
+        "eq_peer_allreduce_state_bytes": (sz, []),
+        "eq_peer_allreduce": (i, [C.POINTER(ArPeers), p, i64, i, p, p, p]),
+        "eq_peer_allreduce_status": (i, [p, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

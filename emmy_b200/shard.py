@@ -6,7 +6,8 @@ Three partitions, as the path shards naturally:
   activation quantization is the same on every rank, there is no collective (outputs stay column-sharded, or are
   all-gathered on request);
 * row-parallel linear: rank r keeps input rows [r K/W, (r+1) K/W) on group boundaries, computes a full [M, N]
-  partial from its slice of x, and the partials are summed by one all-reduce over NVLink;
+  partial from its slice of x, and the partials are summed in f32 over NVLink: decode-sized results by one kernel
+  over peer memory (`PeerAllReduce`, eq_peer_allreduce), large ones by the process group's all-reduce;
 * expert-parallel MoE: expert e lives on rank e // (E / W); picks are dispatched to their experts' ranks, run
   through the local grouped expert FFN, returned and combined at the source in ascending expert order in f32.
   Two exchanges exist: `ep_moe_forward` uses NCCL all-to-alls (and runs on gloo for the CPU tests); `EpMoe` lets the
@@ -106,16 +107,24 @@ class ColumnParallelLinear:
 
 
 class RowParallelLinear:
-    """y[M, N] = all_reduce_sum( linear_fn(x[:, rows]) ).  `rows` is this rank's input-feature slice."""
+    """y[M, N] = all_reduce_sum( linear_fn(x[:, rows]) ).  `rows` is this rank's input-feature slice.  The partials are
+    summed in f32 and rounded once: by `reducer` (a `PeerAllReduce`: one kernel over NVLink peer memory) when one is given
+    and the result fits it, else by the process group's all-reduce."""
 
-    def __init__(self, linear_fn: Callable[[torch.Tensor], torch.Tensor], rows: slice, group=None, reduce_dtype=torch.float32):
-        self.linear_fn, self.rows, self.group, self.reduce_dtype = linear_fn, rows, group, reduce_dtype
+    def __init__(self, linear_fn: Callable[[torch.Tensor], torch.Tensor], rows: slice, group=None, reduce_dtype=torch.float32, reducer=None):
+        self.linear_fn, self.rows, self.group, self.reduce_dtype, self.reducer = linear_fn, rows, group, reduce_dtype, reducer
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        partial = self.linear_fn(x[:, self.rows].contiguous())
+    def __call__(self, x: torch.Tensor, sliced: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+        """`sliced=True`: x already holds only this rank's input features (the output of a column-parallel linear)."""
+        partial = self.linear_fn(x if sliced else x[:, self.rows].contiguous())
+        if self.reducer is not None and self.reducer.fits(partial):
+            return self.reducer(partial, out=out)
         acc = partial.to(self.reduce_dtype)
         dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.group)
-        return acc.to(partial.dtype)
+        if out is None:
+            return acc.to(partial.dtype)
+        out.copy_(acc)
+        return out
 
 
 # ---------------------------------------------------------------------------------------------- expert parallel
@@ -264,6 +273,71 @@ class EpMoe:
         from .ops import _ptr, _stream
 
         self.lib.check(self.lib.load().eq_ep_moe_status(_ptr(self.workspace), self.world, self.cap, self.experts_local, self.hidden, self.inter, _stream()))
+
+
+class PeerAllReduce:
+    """Sum of the ranks' f16 / bf16 partial results by one kernel over NVLink peer memory (eq_peer_allreduce): every
+    rank pushes its partial into every peer's receive buffer, flags it, waits for the peers' pieces and adds the world's
+    partials in rank order in f32 with one rounding, so all ranks hold bit-identical results.  One NVLink round and one
+    launch instead of a library all-reduce's protocol latency; the traffic is (world - 1) x the result per rank, so it
+    is meant for decode-sized results: `max_values` bounds what the symmetric buffers (two slots x world sources) can
+    carry and `fits` tells a caller when to take the process group's all-reduce instead.  Collective: every rank calls
+    it the same number of times with the same shape.  The call counter lives on the device, so calls replay from a
+    captured CUDA graph.  Results are defined only if `status()` comes back clean (a peer that did not arrive within
+    about a second sets the status word)."""
+
+    def __init__(self, group, max_values: int, device):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only, no NVLS binding
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import lib as L
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > L.EQ_EP_MAX_RANKS:
+            raise ValueError(f"at most {L.EQ_EP_MAX_RANKS} ranks")
+        self.cap = (max_values + 7) // 8 * 8
+        lib = L.load()
+        recv = (lib.eq_peer_allreduce_recv_bytes(self.world, self.cap) + 255) // 256 * 256
+        flags = lib.eq_peer_allreduce_flag_bytes(self.world, self.cap)
+        self.buf = symm_mem.empty(recv + flags, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        torch.cuda.synchronize(device)
+        self.handle.barrier()
+        peers = L.ArPeers()
+        peers.world, peers.rank, peers.cap, peers.max_blocks = self.world, self.rank, self.cap, (self.cap + 2047) // 2048
+        for r in range(self.world):
+            base = int(self.handle.buffer_ptrs[r])
+            peers.recv[r], peers.flags[r] = base, base + recv
+        self.peers, self.lib = peers, L
+        self.state = torch.zeros(lib.eq_peer_allreduce_state_bytes(), dtype=torch.uint8, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's buffers and flags exist before anybody's first push
+
+    def fits(self, partial: torch.Tensor) -> bool:
+        return partial.is_cuda and partial.dtype in (torch.float16, torch.bfloat16) and partial.numel() % 8 == 0 and partial.numel() <= self.cap
+
+    def __call__(self, partial: torch.Tensor, out: torch.Tensor | None = None, check: bool = False) -> torch.Tensor:
+        import ctypes as C
+
+        from .ops import _DTYPE, _ptr, _stream
+
+        partial = partial.contiguous()
+        y = out if out is not None else torch.empty_like(partial)
+        self.lib.check(self.lib.load().eq_peer_allreduce(C.byref(self.peers), _ptr(partial), partial.numel(), _DTYPE[partial.dtype], _ptr(y),
+                                                         _ptr(self.state), _stream()))
+        if check:
+            self.status()
+        return y
+
+    def status(self) -> None:
+        """Synchronizes the stream; raises if a peer's piece did not arrive in time."""
+        from .ops import _ptr, _stream
+
+        self.lib.check(self.lib.load().eq_peer_allreduce_status(_ptr(self.state), _stream()))
 
 
 class EpMoePipelined:

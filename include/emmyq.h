@@ -339,6 +339,31 @@ int eq_ep_moe_w4a16(const void* wq_gate_up, const void* wq_down, int scale_dtype
 /* EQ_ERR_TIMEOUT when a peer did not arrive in time, EQ_ERR_UNSUPPORTED when a rank was sent more than world * cap rows. */
 int eq_ep_moe_status(const void* workspace, int64_t world, int64_t cap, int64_t E_local, int64_t H, int64_t I, void* stream);
 
+/* ---- sum of a row-parallel linear's partial results over peer memory ------------------------------------------
+ * The reference completes a rank's partial sums by a reduction over the tensor-parallel group
+ * (emmy/serving/vllm_model_gen.py:986-991, vLLM's tensor_model_parallel_all_reduce).  This is that reduction for small
+ * results (decode steps), done by one kernel over NVLink peer mappings in one round: every rank pushes its partial into
+ * every peer's receive buffer, flags it, waits (bounded, about a second) for the peers' pieces and adds the world's
+ * partials in rank order in f32, rounded once -- all ranks end with bit-identical y.  Pointers as in eq_ep_peers: device
+ * addresses valid on the calling rank, entry r describing rank r's buffers. */
+typedef struct eq_ar_peers {
+    int32_t world, rank;
+    int64_t cap;                       /* values (2 bytes each) a call may carry at most; a multiple of 8 */
+    int64_t max_blocks;                /* ceil(cap / 2048) */
+    void* recv[EQ_EP_MAX_RANKS];       /* [2 slots][world sources][cap] values, written by the sources */
+    uint32_t* flags[EQ_EP_MAX_RANKS];  /* [2 slots][world sources][max_blocks] uint32, zero before the first call */
+} eq_ar_peers;
+size_t eq_peer_allreduce_recv_bytes(int64_t world, int64_t cap);
+size_t eq_peer_allreduce_flag_bytes(int64_t world, int64_t cap);
+size_t eq_peer_allreduce_state_bytes(void);
+/* y[count] = sum over ranks of partial[count] (f16 or bf16, f32 sum, one rounding).  Collective: every rank of the group
+ * calls it the same number of times with the same count.  `state` is local device memory of
+ * eq_peer_allreduce_state_bytes(), zero on first use (status word, the call counter -- kept on the device, so the call
+ * replays from a captured CUDA graph -- and a block counter).  partial and y must not be the receive buffers. */
+int eq_peer_allreduce(const eq_ar_peers* peers, const void* partial, int64_t count, int dtype, void* y, void* state, void* stream);
+/* Synchronizes the stream; EQ_ERR_TIMEOUT if a peer's piece did not arrive in time (y is undefined then). */
+int eq_peer_allreduce_status(const void* state, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -173,3 +173,62 @@ def test_expert_parallel_wait_runs_out_and_reports():
     assert err.value.status_name == "EQ_ERR_TIMEOUT"
     # the context is still usable
     assert torch.isfinite(om.moe_forward(x, torch.randn(t, e_local, device="cuda"), w, k).float()).all()
+
+
+def _local_ar_peers(world, rank, cap):
+    """eq_ar_peers whose ranks' buffers are all local allocations (single-GPU tests of the peer-memory sum)."""
+    from emmy_b200 import lib as L
+
+    lib = L.load()
+    peers = L.ArPeers()
+    peers.world, peers.rank, peers.cap, peers.max_blocks = world, rank, cap, (cap + 2047) // 2048
+    keep = []
+    for r in range(world):
+        recv = torch.zeros(lib.eq_peer_allreduce_recv_bytes(world, cap), dtype=torch.uint8, device="cuda")
+        flags = torch.zeros(lib.eq_peer_allreduce_flag_bytes(world, cap), dtype=torch.uint8, device="cuda")
+        keep.append((recv, flags))
+        peers.recv[r], peers.flags[r] = recv.data_ptr(), flags.data_ptr()
+    state = torch.zeros(lib.eq_peer_allreduce_state_bytes(), dtype=torch.uint8, device="cuda")
+    return peers, state, keep
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_peer_allreduce_of_one_rank_is_the_identity(dtype):
+    import ctypes as C
+
+    from emmy_b200 import lib as L
+    from emmy_b200.ops import _DTYPE, _ptr, _stream
+
+    lib = L.load()
+    peers, state, _keep = _local_ar_peers(1, 0, 4096 * 3)
+    x = torch.randn(3, 4096, device="cuda").to(dtype)
+    y = torch.empty_like(x)
+    for _ in range(3):
+        L.check(lib.eq_peer_allreduce(C.byref(peers), _ptr(x), x.numel(), _DTYPE[dtype], _ptr(y), _ptr(state), _stream()))
+    L.check(lib.eq_peer_allreduce_status(_ptr(state), _stream()))
+    assert torch.equal(x, y)
+    assert state.view(torch.int32)[1].item() == 3  # the call counter on the device
+    with pytest.raises(L.EmmyqError):  # more values than the buffers carry
+        L.check(lib.eq_peer_allreduce(C.byref(peers), _ptr(x), 4096 * 3 + 8, _DTYPE[dtype], _ptr(y), _ptr(state), _stream()))
+
+
+def test_peer_allreduce_wait_runs_out_and_reports():
+    """One rank of two calls alone: the peer's flags are never raised, the bounded wait runs out (about a second), the
+    call returns and the status word says so.  Both ranks' buffers are local allocations here."""
+    import ctypes as C
+
+    from emmy_b200 import lib as L
+    from emmy_b200.ops import _DTYPE, _ptr, _stream
+
+    lib = L.load()
+    peers, state, _keep = _local_ar_peers(2, 0, 4096)
+    x = torch.randn(1, 4096, device="cuda").half()
+    y = torch.empty_like(x)
+    L.check(lib.eq_peer_allreduce(C.byref(peers), _ptr(x), x.numel(), _DTYPE[x.dtype], _ptr(y), _ptr(state), _stream()))
+    with pytest.raises(L.EmmyqError) as err:
+        L.check(lib.eq_peer_allreduce_status(_ptr(state), _stream()))
+    assert err.value.status_name == "EQ_ERR_TIMEOUT"
+    # its own piece did reach the peer's buffer (slot 1 of the first call, source 0), and the context is still usable
+    recv1 = _keep[1][0].view(torch.float16).view(2, 2, 4096)
+    assert torch.equal(recv1[1, 0], x[0])
+    assert torch.isfinite(x.float().sum())

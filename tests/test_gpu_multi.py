@@ -96,6 +96,38 @@ def _worker(rank, world, port, ret):
         wrow = ops.w4_repack(a.cuda(), b.cuda(), c.cuda(), 128, "gptq", g_idx=g.cuda())
         yrow = shard.RowParallelLinear(lambda v: ops.w4a16_linear(v, wrow), rows)(xx).float()
         ret[20 + rank] = float((yrow - whole).abs().max() / whole.abs().max())
+
+        # the same sum by the peer-memory kernel: five calls (both buffer slots, reuse of each), then a larger bf16
+        # result against the process group's f32 all-reduce, bit-identical on every rank, and replayed from a CUDA graph
+        ar = shard.PeerAllReduce(None, 48 * 4096, torch.device("cuda", rank))
+        rp = shard.RowParallelLinear(lambda v: ops.w4a16_linear(v, wrow), rows, reducer=ar)
+        for _ in range(5):
+            ypeer = rp(xx)
+        ar.status()
+        ret[80 + rank] = float((ypeer.float() - yrow).abs().max() / whole.abs().max())
+        part = torch.randn(48, 4096, generator=torch.Generator().manual_seed(40 + rank)).bfloat16().cuda()
+        assert ar.fits(part) and not ar.fits(torch.empty(49, 4096, dtype=torch.bfloat16, device="cuda"))
+        want = part.float()
+        dist.all_reduce(want)
+        got = ar(part, check=True)
+        ret[90 + rank] = float((got.float() - want).abs().max() / want.abs().max())
+        theirs = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(theirs, got)
+        ret[100 + rank] = float(sum((t != got).sum().item() for t in theirs))
+        out = torch.empty_like(part)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ar(part, out=out)  # warm-up on the capture stream
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                ar(part, out=out)
+            for _ in range(3):
+                out.zero_()
+                graph.replay()
+            ar.status()
+        torch.cuda.current_stream().wait_stream(side)
+        ret[110 + rank] = float((out != got).sum().item())
         torch.cuda.synchronize()
     finally:
         dist.destroy_process_group()
@@ -116,3 +148,6 @@ def test_sharded_paths_on_two_gpus():
     assert all(out[70 + r] < 1e-2 for r in range(world)), out                          # streaming tier on the receive side
     assert all(out[10 + r] == 0.0 for r in range(world)), out      # column shards are the same columns
     assert all(out[20 + r] < 1e-2 for r in range(world)), out      # row partials summed in f32
+    assert all(out[80 + r] < 2e-3 for r in range(world)), out      # the peer-memory sum: the same up to the order of the f32 adds
+    assert all(out[90 + r] < 1e-2 for r in range(world)), out      # bf16, 48 x 4096, against the f32 all-reduce
+    assert all(out[100 + r] == 0.0 and out[110 + r] == 0.0 for r in range(world)), out  # identical on all ranks, and from a graph
