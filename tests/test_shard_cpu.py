@@ -159,6 +159,34 @@ def _ep_worker(rank, world, port, e, h, inter, k, t, ret):
         rows = slice(rank * h // world, (rank + 1) * h // world)
         rp = shard.RowParallelLinear(lambda xs: xs @ w[rows], rows, reduce_dtype=torch.float64)
         ret[10 + rank] = float((rp(xx) - xx @ w).abs().max())
+
+        # a reducer takes the sum when the result fits it (here a stand-in built on the group's all-reduce that counts
+        # its calls), the group's all-reduce otherwise; `sliced` inputs and `out=` on both routes
+        class CountingReducer:
+            calls = 0
+
+            def __init__(self, limit):
+                self.limit = limit
+
+            def fits(self, partial):
+                return partial.numel() <= self.limit
+
+            def __call__(self, partial, out=None):
+                CountingReducer.calls += 1
+                acc = partial.clone()
+                dist.all_reduce(acc)
+                if out is None:
+                    return acc
+                out.copy_(acc)
+                return out
+
+        small = shard.RowParallelLinear(lambda xs: xs @ w[rows], rows, reduce_dtype=torch.float64, reducer=CountingReducer(3 * 24))
+        big = shard.RowParallelLinear(lambda xs: xs @ w[rows], rows, reduce_dtype=torch.float64, reducer=CountingReducer(3 * 24 - 1))
+        out = torch.empty(3, 24, dtype=torch.float64)
+        err = float((small(xx[:, rows].contiguous(), sliced=True, out=out) - xx @ w).abs().max())
+        took = CountingReducer.calls
+        err = max(err, float((big(xx, out=out) - xx @ w).abs().max()), float((out - xx @ w).abs().max()))
+        ret[30 + rank] = err if (took == 1 and CountingReducer.calls == 1) else 1.0
         cp = shard.ColumnParallelLinear(lambda xs: xs @ w[:, rank * 12 : (rank + 1) * 12])
         ret[20 + rank] = float((cp(xx, gather=True) - xx @ w).abs().max())
     finally:
@@ -173,3 +201,4 @@ def test_expert_parallel_and_row_parallel_over_two_gloo_ranks():
         mp.spawn(_ep_worker, args=(world, port, 8, 16, 8, 2, 11, ret), nprocs=world, join=True)
         assert all(ret[r] < 1e-5 for r in range(world)), dict(ret)
         assert all(ret[10 + r] < 1e-12 and ret[20 + r] < 1e-12 for r in range(world)), dict(ret)
+        assert all(ret[30 + r] < 1e-12 for r in range(world)), dict(ret)  # reducer route and fallback agree
