@@ -91,25 +91,32 @@ __global__ void __launch_bounds__(kMsWarps * 32, 1) moe_stream_kernel(const MoeS
     for (int d = 0; d < DEPTH; ++d) issue(d);
     __syncthreads();  // accumulators are zero
 
-    // ---- the problem (row block) of the tile the warp is in
+    // ---- the row block of the tile the warp is in: its row count, and the lane's own row of x (MMA operand row g, the
+    //      32 input positions from 32 j on of every item), found once per block instead of once per item
     W4Params p;
-    p.perm = nullptr;
-    p.K = gp.K;
-    p.N = gp.N;
-    p.items = items;
     p.scale_dtype = gp.scale_dtype;
-    p.y_rows = nullptr;
-    p.y_ptrs = nullptr;
-    const ActT* x = nullptr;
+    int rows = 0, cur_block = -1;
+    const uint4* xlane = nullptr;  // null: the block has no row g
     auto enter_tile = [&](int rel) {
-        const RowBlock rb = gp.blocks[(tile0 + rel) / tpe];
-        p.M = rb.rows;
-        if (gp.x_rows) {
-            x = static_cast<const ActT*>(gp.x);
-            p.x_rows = gp.x_rows + rb.row0;
+        const int b = (tile0 + rel) / tpe;
+        if (b == cur_block) return;
+        cur_block = b;
+        const RowBlock rb = gp.blocks[b];
+        rows = rb.rows;
+        xlane = nullptr;
+        if (g < rb.rows) {
+            const size_t xr = gp.x_rows ? static_cast<size_t>(gp.x_rows[rb.row0 + g]) : static_cast<size_t>(rb.row0 + g);
+            xlane = reinterpret_cast<const uint4*>(static_cast<const ActT*>(gp.x) + xr * gp.K + 32 * j);
+        }
+    };
+    auto item_x = [&](int item, uint4 (&v)[1][4]) {
+        if (xlane) {
+            const uint4* src = xlane + item * 16;  // 128 activations per item
+#pragma unroll
+            for (int c = 0; c < 4; ++c) v[0][c] = __ldg(src + c);
         } else {
-            x = static_cast<const ActT*>(gp.x) + static_cast<size_t>(rb.row0) * gp.K;
-            p.x_rows = nullptr;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) v[0][c] = make_uint4(0, 0, 0, 0);
         }
     };
 
@@ -117,10 +124,11 @@ __global__ void __launch_bounds__(kMsWarps * 32, 1) moe_stream_kernel(const MoeS
     uint4 xv[1][4];
     if (n > 0) {
         enter_tile(slot_t);
-        w4_item_x<ActT, 1, false>(p, x, it, g, j, xv);
+        item_x(it, xv);
     }
+    int d = 0;  // ring slot of item i
+#pragma unroll 2
     for (int i = 0; i < n; ++i) {
-        const int d = i % DEPTH;
         asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");
         __syncwarp();  // the scale / zero entry was copied by another lane of the column pair
         const unsigned char* slot = ring + d * kMsSlot;
@@ -129,9 +137,10 @@ __global__ void __launch_bounds__(kMsWarps * 32, 1) moe_stream_kernel(const MoeS
         const uint2 meta = *reinterpret_cast<const uint2*>(slot + 1024 + g * 8);
         __syncwarp();  // every lane has read the slot before any lane refills it
         issue(d);
+        d = d + 1 == DEPTH ? 0 : d + 1;
         const bool leaves = it + 1 == items;
         uint4 xn[1][4];
-        if (!leaves && i + 1 < n) w4_item_x<ActT, 1, false>(p, x, it + 1, g, j, xn);  // the rows run one item ahead
+        if (!leaves && i + 1 < n) item_x(it + 1, xn);  // the rows run one item ahead
         w4_item_math<ActT, 1>(p, xv, wl, wh, meta, yacc);
         if (leaves) {
             // the span leaves this tile: add the sums into the CTA's accumulators, move to the next tile's problem
@@ -139,14 +148,14 @@ __global__ void __launch_bounds__(kMsWarps * 32, 1) moe_stream_kernel(const MoeS
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int m = 2 * j + (e & 1), nn = g + ((e & 2) ? 8 : 0);
-                if (m < p.M) atomicAdd(acc + m * 16 + nn, yacc[0][e]);
+                if (m < rows) atomicAdd(acc + m * 16 + nn, yacc[0][e]);
                 yacc[0][e] = 0.f;
             }
             it = 0;
             ++slot_t;
             if (i + 1 < n) {
                 enter_tile(slot_t);
-                w4_item_x<ActT, 1, false>(p, x, 0, g, j, xv);
+                item_x(0, xv);
             }
         } else {
             ++it;
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(kMsWarps * 32, 1) moe_stream_kernel(const MoeS
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int m = 2 * j + (e & 1), nn = g + ((e & 2) ? 8 : 0);
-            if (m < p.M) atomicAdd(acc + m * 16 + nn, yacc[0][e]);
+            if (m < rows) atomicAdd(acc + m * 16 + nn, yacc[0][e]);
         }
     }
     __syncthreads();
