@@ -219,14 +219,48 @@ __global__ void dense_row_blocks_kernel(RowBlock* __restrict__ blocks, int32_t* 
     if (threadIdx.x == 0) *n_blocks = nb;
 }
 
+// h[r][i] = act(silu(gu[r][i])) * gu[r][I + i], eight columns per thread (I is a multiple of 16).  A programmatic
+// dependent of the linear that wrote gu, and a primary of the kernel after it: that one is resident, with its weights on
+// the way, while this one runs.
 template <typename ActT>
 __global__ void swiglu_rows_kernel(const ActT* __restrict__ gu, int64_t M, int64_t I, ActT* __restrict__ h) {
-    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int64_t idx = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) * 8;
     if (idx >= M * I) return;
     const int64_t r = idx / I, i = idx - r * I;
-    const float g = to_float(gu[r * 2 * I + i]), u = to_float(gu[r * 2 * I + I + i]);
-    const ActT s = from_float<ActT>(g / (1.f + expf(-g)));
-    h[idx] = from_float<ActT>(to_float(s) * u);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + i), uv = *reinterpret_cast<const uint4*>(gu + r * 2 * I + I + i);
+    const ActT* ge = reinterpret_cast<const ActT*>(&gv);
+    const ActT* ue = reinterpret_cast<const ActT*>(&uv);
+    uint4 out;
+    ActT* oe = reinterpret_cast<ActT*>(&out);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float g = to_float(ge[e]);
+        const ActT s = from_float<ActT>(g / (1.f + expf(-g)));
+        oe[e] = from_float<ActT>(to_float(s) * to_float(ue[e]));
+    }
+    if ((reinterpret_cast<uintptr_t>(h) & 15) == 0) {
+        *reinterpret_cast<uint4*>(h + idx) = out;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[idx + e] = oe[e];
+    }
+}
+
+template <typename ActT>
+int launch_swiglu_rows(const void* gu, int64_t M, int64_t I, void* h, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ceil_div(M * I / 8, 256)));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    EQ_CUDA_OK(cudaLaunchKernelEx(&cfg, swiglu_rows_kernel<ActT>, static_cast<const ActT*>(gu), M, I, static_cast<ActT*>(h)));
+    return EQ_OK;
 }
 
 size_t gu_align(size_t v) { return (v + 255) / 256 * 256; }
@@ -273,11 +307,7 @@ extern "C" int eq_w4a16_gate_up_swiglu(const void* wq, int scale_dtype, const in
     void* gu = extra;  // [M][2 I] scratch
     st = eq_w4a16_linear(wq, scale_dtype, perm, K, 2 * I, G, x, M, act_dtype, gu, workspace, inner, stream_);
     if (st != EQ_OK) return st;
-    const unsigned grid = static_cast<unsigned>(ceil_div(M * I, 256));
-    if (act_dtype == EQ_F16) swiglu_rows_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(gu), M, I, static_cast<__half*>(h));
-    else swiglu_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(gu), M, I, static_cast<__nv_bfloat16*>(h));
-    EQ_LAUNCH_OK("swiglu_rows_kernel");
-    return EQ_OK;
+    return act_dtype == EQ_F16 ? launch_swiglu_rows<__half>(gu, M, I, h, stream) : launch_swiglu_rows<__nv_bfloat16>(gu, M, I, h, stream);
 }
 
 // The tensor-path kernel and the GEMV's hand-over wait are bounded; one that runs out sets the status word.

@@ -422,3 +422,12 @@ def test_gate_up_swiglu_in_one_call(m):
     check_close(h, ref)
     front = lib.eq_w4a16_workspace_bytes(m, 2 * inter, k)
     assert int(ws[256:front].count_nonzero()) == 0
+    # an output that starts two bytes off a 16-byte boundary takes the elementwise form with scalar stores
+    # (up to 16 rows; above, the epilogue form needs the alignment and the call says so)
+    odd = torch.empty(m * inter + 1, dtype=torch.bfloat16, device="cuda")[1:].view(m, inter)
+    assert odd.data_ptr() % 16 == 2
+    if m <= 16:
+        assert torch.equal(ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws, out=odd), h)
+    else:
+        with pytest.raises(ops.L.EmmyqError):
+            ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws, out=odd)
