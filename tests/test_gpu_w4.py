@@ -426,8 +426,8 @@ def test_gate_up_swiglu_in_one_call(m):
     # (up to 16 rows; above, the epilogue form needs the alignment and the call says so)
     odd = torch.empty(m * inter + 1, dtype=torch.bfloat16, device="cuda")[1:].view(m, inter)
     assert odd.data_ptr() % 16 == 2
-    if m <= 16:
-        assert torch.equal(ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws, out=odd), h)
+    if m <= 16:  # (not bit-equal to h: the warps of a CTA add their sums in arrival order)
+        check_close(ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws, out=odd), ref)
     else:
         with pytest.raises(ops.L.EmmyqError):
             ops.w4a16_gate_up_swiglu(act(x, "bf16"), w, workspace=ws, out=odd)
