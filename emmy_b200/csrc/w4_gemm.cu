@@ -614,14 +614,15 @@ int launch_cfg(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y,
                       static_cast<int>(K), status, grp, SplitArgs{nullptr, nullptr});
 }
 
-// M <= 128: 128 x 256 tiles with K split over gridDim.z so that about one CTA per SM runs.
-template <typename ActT>
+// Up to 128 * HALVES rows: one row tile of 128 * HALVES x 256 with K split over gridDim.z so that about one CTA per SM runs.
+template <typename ActT, int HALVES>
 int launch_split(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* y, int64_t M, int64_t N, int64_t K, int* status,
                  float* partial, int* counters, cudaStream_t stream) {
-    using Cfg = GemmCfg<1, 256, 16, 2>;
+    using Cfg = GemmCfg<HALVES, 256, 16, 2>;
     CUtensorMap map_x;
     const CUtensorMapDataType elem = ScaleMul<ActT>::kFmt == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, a_box_rows(static_cast<int>(M)), kGK, CU_TENSOR_MAP_SWIZZLE_128B);
+    const int box_rows = HALVES == 1 ? a_box_rows(static_cast<int>(M)) : 128 * Cfg::kBoxHalves;
+    int st = make_tensor_map_2d(&map_x, x, elem, 2, M, K, K * 2, box_rows, kGK, CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != EQ_OK) return st;
     const int64_t tiles = ceil_div(N, 256), items = K / 128;
     int64_t splits = sm_count() / tiles;
@@ -633,12 +634,12 @@ int launch_split(const unsigned char* wq, int scale_dtype, const ActT* x, ActT* 
     const SplitArgs sp = {partial, counters};
     dim3 grid(static_cast<unsigned>(tiles), 1, static_cast<unsigned>(splits));
     if (splits == 1) {
-        auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, false> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, false>;
+        auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, 256, 16, 2, true, kPlain, false> : w4a16_gemm_tc_kernel<ActT, HALVES, 256, 16, 2, false, kPlain, false>;
         EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
         return launch_pdl(kernel, grid, Cfg::kThreads, Cfg::kSmem, stream, true, map_x, wq, y, static_cast<int>(M), static_cast<int>(N),
                           static_cast<int>(K), status, none, sp);
     }
-    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, true, kPlain, true> : w4a16_gemm_tc_kernel<ActT, 1, 256, 16, 2, false, kPlain, true>;
+    auto kernel = cvt ? w4a16_gemm_tc_kernel<ActT, HALVES, 256, 16, 2, true, kPlain, true> : w4a16_gemm_tc_kernel<ActT, HALVES, 256, 16, 2, false, kPlain, true>;
     EQ_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Cfg::kSmem)));
     return launch_pdl(kernel, grid, Cfg::kThreads, Cfg::kSmem, stream, true, map_x, wq, y, static_cast<int>(M), static_cast<int>(N),
                       static_cast<int>(K), status, none, sp);
@@ -658,14 +659,16 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
         // wide matrices fill the SMs with 64-column tiles; narrow ones split K over 256-column tiles instead
         if (ceil_div(N, 64) >= sm_count())
             return launch_cfg<ActT, 1, 64, 8, 4, kPlain>(wq, scale_dtype, x, y, M, N, K, status, none, 1, stream);
-        return launch_split<ActT>(wq, scale_dtype, x, y, M, N, K, status, partial, counters, stream);
+        return launch_split<ActT, 1>(wq, scale_dtype, x, y, M, N, K, status, partial, counters, stream);
     }
     if (M <= 512 && ceil_div(N, 128) * ceil_div(M, 256) * 2 <= sm_count()) {
-        // a few hundred rows of a narrow matrix would leave most SMs idle on 256-row tiles: run 128-row blocks through the
-        // split-K form instead (each block streams the weight once more, which is still far cheaper)
-        for (int64_t m0 = 0; m0 < M; m0 += 128) {
-            const int64_t mb = M - m0 < 128 ? M - m0 : 128;
-            const int st = launch_split<ActT>(wq, scale_dtype, x + m0 * K, y + m0 * N, mb, N, K, status, partial, counters, stream);
+        // a few hundred rows of a narrow matrix would leave most SMs idle on whole-K tiles: run 256-row blocks through the
+        // split-K form instead (each block streams the weight once more, which is still far cheaper; the dequantisation,
+        // not the MMA, bounds these calls, so a 256-row block costs what a 128-row block costs)
+        for (int64_t m0 = 0; m0 < M; m0 += 256) {
+            const int64_t mb = M - m0 < 256 ? M - m0 : 256;
+            const int st = mb > 128 ? launch_split<ActT, 2>(wq, scale_dtype, x + m0 * K, y + m0 * N, mb, N, K, status, partial, counters, stream)
+                                    : launch_split<ActT, 1>(wq, scale_dtype, x + m0 * K, y + m0 * N, mb, N, K, status, partial, counters, stream);
             if (st != EQ_OK) return st;
         }
         return EQ_OK;
@@ -678,7 +681,7 @@ int launch_typed(const unsigned char* wq, int scale_dtype, const int32_t* perm, 
 }  // namespace
 
 // gathered: M * K elements of scratch when perm is given.  status: one word, set by a bounded wait that ran out.
-// partial / counters: f32 [min(M, 128)][N] and one int per 256 columns, zero between calls (used when M <= 128).
+// partial / counters: f32 [min(M, 256)][N] and one int per 256 columns, zero between calls (used by the split-K forms).
 int w4_gemm_tc_launch(const unsigned char* wq, int scale_dtype, const int32_t* perm, const void* x, void* y, int64_t M, int64_t N,
                       int64_t K, int act_dtype, void* gathered, int* status, float* partial, int* counters, cudaStream_t stream) {
     if (act_dtype == EQ_F16)

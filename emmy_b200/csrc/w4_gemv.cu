@@ -84,10 +84,10 @@ static int launch_w4(const W4Params& p, cudaStream_t stream) {
 using namespace eq;
 
 // Workspace layout: a 256-byte header whose first word is the status word (fixed place, whatever M and N are), then
-// f32 partial sums of up to 128 rows and one arrival counter per 16-column tile.  Calls with M > 16 add room for the
+// f32 partial sums of up to 256 rows and one arrival counter per 16-column tile.  Calls with M > 16 add room for the
 // column-gathered copy of x that act-order weights need on the tensor path.
 static constexpr size_t kW4Header = 256;
-static int64_t w4_front_rows(int64_t M) { return M < 128 ? M : 128; }
+static int64_t w4_front_rows(int64_t M) { return M < 256 ? M : 256; }
 static size_t w4_front_bytes(int64_t M, int64_t N) {
     const int64_t rows = w4_front_rows(M);
     return kW4Header + static_cast<size_t>(rows) * N * sizeof(float) + static_cast<size_t>(N / 16) * sizeof(int);
