@@ -13,7 +13,7 @@
 // Every item multiplies the same M rows of x, 4 KB per item at M = 16: read from global memory that is 117 MB per
 // launch through L1 / L2 against 29 MB of weights, and it bounded the launch.  Where M x K fits beside the ring
 // (STAGED) the CTA copies x once into shared memory in the order the MMA operands are read (conflict-free 16-byte
-// reads).  Where it does not fit, K is cut into slices: a CTA is (group of column tiles, K slice), stages its slice of x,
+// reads, the two B registers of every MMA next to each other).  Where it does not fit, K is cut into slices: a CTA is (group of column tiles, K slice), stages its slice of x,
 // and the slices' sums meet in the f32 workspace (SPLIT).  Without a workspace region, or with gathered rows, the rows are
 // read from global memory, one item ahead of the weights where registers allow.
 #include "w4_tile.cuh"
@@ -130,8 +130,12 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = make_uint4(0, 0, 0, 0);
             }
+            // pair order: chunk c holds {low, high} of steps 2c and 2c + 1 (the low slots are words 0..7 of the lane's
+            // 32 activations, the high slots words 8..15)
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&v[0]);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(xw + (static_cast<size_t>(b) * 4 + c) * 512 + lane * 16) = v[c];
+            for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(xw + (static_cast<size_t>(b) * 4 + c) * 512 + lane * 16) = make_uint4(w[2 * c], w[8 + 2 * c], w[2 * c + 1], w[9 + 2 * c]);
         }
         __syncthreads();
     }
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) w4a16_stream_kernel(cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
                     xv[mt][c] = *reinterpret_cast<const uint4*>(xs + (static_cast<size_t>(it * MT + mt) * 4 + c) * 512 + lane * 16);
-            w4_item_math<ActT, MT>(p, xv, wl, wh, mt_, yacc);
+            w4_item_math<ActT, MT, true>(p, xv, wl, wh, mt_, yacc);
         } else if constexpr (kAhead) {
             uint4 xn[MT][4];
             const int it_next = it + 1 == p.items ? 0 : it + 1;

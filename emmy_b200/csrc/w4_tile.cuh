@@ -155,7 +155,10 @@ __device__ __forceinline__ void w4_item_x(const W4Params& p, const ActT* x, int 
 // One item (128 input rows x 16 columns) of a tile against the rows of x: yacc += s * sum_k x_k (q_k - z).
 // wl / wh: the lane's 16 bytes of the item's two nibble tiles; meta: its scale / zero entry (columns g, g+8);
 // xv: the lane's operands from w4_item_x.
-template <typename ActT, int MT>
+// PAIRED: the sixteen operand words of a row block come in pair order {low slot, high slot} per k16 step (the staged
+// copies are stored that way), so an MMA's two B registers are neighbours of one vector and need no moves; otherwise
+// they are the natural order of 32 consecutive activations: words 0..7 the low slots, 8..15 the high ones.
+template <typename ActT, int MT, bool PAIRED = false>
 __device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv)[MT][4], const uint4& wl, const uint4& wh, const uint2& mt_,
                                              float (&yacc)[MT][4]) {
     float s_lo, s_hi;
@@ -178,12 +181,12 @@ __device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv
         Frag<ActT>::expand(words[s], z_lo, z_hi, a);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
-            const uint32_t* lo = reinterpret_cast<const uint32_t*>(&xv[mt][0]);  // 8 words: steps 0..7, low slots
-            const uint32_t* hi = reinterpret_cast<const uint32_t*>(&xv[mt][2]);  // high slots
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(&xv[mt][0]);
+            const uint32_t b0 = PAIRED ? w[2 * s] : w[s], b1 = PAIRED ? w[2 * s + 1] : w[8 + s];
             if (s < 2)
-                Frag<ActT>::mma0(acc[s & 1][mt], a, lo[s], hi[s]);
+                Frag<ActT>::mma0(acc[s & 1][mt], a, b0, b1);
             else
-                Frag<ActT>::mma(acc[s & 1][mt], a, lo[s], hi[s]);
+                Frag<ActT>::mma(acc[s & 1][mt], a, b0, b1);
         }
     }
 #pragma unroll
@@ -196,7 +199,7 @@ __device__ __forceinline__ void w4_item_math(const W4Params& p, const uint4 (&xv
 }
 
 // The same product for three (or more) row blocks whose operands lie in shared memory in the order the lanes read them
-// (xs_lane: this lane's first 16 bytes of the item; row block mt, chunk c at (mt * 4 + c) * 512).  The eight weight
+// (xs_lane: this lane's first 16 bytes of the item; row block mt, chunk c at (mt * 4 + c) * 512; words in pair order).  The eight weight
 // fragments are expanded once and kept; each row block then loads its own operands, so the registers hold one block's
 // operands at a time instead of all of them.
 template <typename ActT, int MT>
@@ -222,15 +225,14 @@ __device__ __forceinline__ void w4_item_math_smem(const W4Params& p, const unsig
         uint4 xv[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) xv[c] = *reinterpret_cast<const uint4*>(xs_lane + (mt * 4 + c) * 512);
-        const uint32_t* lo = reinterpret_cast<const uint32_t*>(&xv[0]);
-        const uint32_t* hi = reinterpret_cast<const uint32_t*>(&xv[2]);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&xv[0]);  // pair order: {low slot, high slot} per step
         float acc[2][4];
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
             if (s < 2)
-                Frag<ActT>::mma0(acc[s & 1], a[s], lo[s], hi[s]);
+                Frag<ActT>::mma0(acc[s & 1], a[s], w[2 * s], w[2 * s + 1]);
             else
-                Frag<ActT>::mma(acc[s & 1], a[s], lo[s], hi[s]);
+                Frag<ActT>::mma(acc[s & 1], a[s], w[2 * s], w[2 * s + 1]);
         }
         yacc[mt][0] = fmaf(s_lo, acc[0][0] + acc[1][0], yacc[mt][0]);
         yacc[mt][1] = fmaf(s_lo, acc[0][1] + acc[1][1], yacc[mt][1]);
