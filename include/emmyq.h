@@ -124,7 +124,7 @@ int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, vo
 
 /* Scratch for eq_w4a16_linear: a 256-byte header whose first word is the status word, then f32 words (the partial
  * sums of the split-K kernels; at M = 1 the sixteen-word hand-overs between neighbouring CTAs of the GEMV) and one
- * arrival counter per 16-column tile, plus, for M > 16, room for a column-gathered copy of x (used when the weight
+ * arrival counter per 16-column tile (up to 256 rows of sums), plus, for M > 16, room for a column-gathered copy of x (used when the weight
  * carries a row permutation).  The buffer must be zero the first time it is used; every call leaves the words it used
  * zero again, so it can be reused by calls on one stream (calls on different streams need different buffers). */
 size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
@@ -133,8 +133,9 @@ size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
  * (emmy/compiler/loader/quant.py:1235-1435) and evaluates eagerly as dequantize + F.linear
  * (emmy/compiler/trace/huggingface.py:2877-2920).  perm is NULL unless eq_w4_repack asked for it.
  * Needs K % 128 == 0, N % 16 == 0, G % 128 == 0 (or G = -1); x and wq 16-byte aligned.
- * M <= 16 runs the bandwidth kernels (any K: shapes whose activations do not fit shared memory run a split-K form
- * through the workspace); M > 16 runs the tcgen05 kernel, which dequantises into shared memory. */
+ * M <= 24 runs the bandwidth kernels (any K: shapes whose activations do not fit shared memory run a split-K form
+ * through the workspace, and from 17 rows on such shapes take the next path); above that the tcgen05 kernel, which
+ * dequantises into shared memory. */
 int eq_w4a16_linear(const void* wq, int scale_dtype, const int32_t* perm, int64_t K, int64_t N, int64_t G,
                     const void* x, int64_t M, int act_dtype, void* y, void* workspace, size_t workspace_bytes,
                     void* stream);
