@@ -124,9 +124,10 @@ int eq_w4_unpack_repacked(const void* wq, int64_t K, int64_t N, uint8_t* out, vo
 
 /* Scratch for eq_w4a16_linear: a 256-byte header whose first word is the status word, then f32 words (the partial
  * sums of the split-K kernels; at M = 1 the sixteen-word hand-overs between neighbouring CTAs of the GEMV) and one
- * arrival counter per 16-column tile (up to 256 rows of sums), plus, for M > 16, room for a column-gathered copy of x (used when the weight
- * carries a row permutation).  The buffer must be zero the first time it is used; every call leaves the words it used
- * zero again, so it can be reused by calls on one stream (calls on different streams need different buffers). */
+ * arrival counter per 16-column tile (up to 256 rows of sums), plus, for M > 16, room for a column-gathered copy of x
+ * (used when the weight carries a row permutation).  The buffer must be zero the first time it is used; every call
+ * leaves the words it used zero again, so it can be reused by calls on one stream (calls on different streams need
+ * different buffers). */
 size_t eq_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 /* y[M, N] = x[M, K] @ W on repacked weights; x and y are act_dtype (EQ_F16 or EQ_BF16), f32 accumulation.
  * The operator the reference spells as int4 decode algebra in front of a LinearOp
