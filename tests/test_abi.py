@@ -60,6 +60,28 @@ def test_bad_arguments_return_codes_not_crashes(eq):
     assert eq.eq_w4a16_workspace_bytes(100, 4096, 256) == (front + 255) // 256 * 256 + 100 * 256 * 2
 
 
+def test_peer_allreduce_validates_before_it_launches(eq):
+    null = C.c_void_p(0)
+    one = C.c_void_p(16)  # never dereferenced: validation fails first
+    peers = L.ArPeers()
+    peers.world, peers.rank, peers.cap, peers.max_blocks = 2, 0, 4096, 2
+    for r in range(2):
+        peers.recv[r], peers.flags[r] = 16, 16
+    ok = lambda count, dtype=L.EQ_F16, y=one: eq.eq_peer_allreduce(C.byref(peers), one, count, dtype, y, one, null)
+    assert ok(0) == 0                                   # an empty call does nothing
+    assert ok(12) == L.EQ_ERR_UNSUPPORTED               # whole 16-byte vectors only
+    assert ok(4104) == L.EQ_ERR_UNSUPPORTED             # more than the buffers carry
+    assert ok(8, dtype=L.EQ_F32) == L.EQ_ERR_BAD_ARG    # f16 / bf16 partials
+    assert ok(8, y=C.c_void_p(8)) == L.EQ_ERR_BAD_ALIGN
+    peers.max_blocks = 3
+    assert ok(8) == L.EQ_ERR_BAD_ARG                    # the flag layout must match the capacity
+    peers.max_blocks, peers.rank = 2, 2
+    assert ok(8) == L.EQ_ERR_BAD_ARG
+    assert eq.eq_peer_allreduce_recv_bytes(8, 64 * 4096) == 2 * 8 * 64 * 4096 * 2
+    assert eq.eq_peer_allreduce_flag_bytes(8, 64 * 4096) == 2 * 8 * 128 * 4
+    assert eq.eq_peer_allreduce_state_bytes() >= 12
+
+
 def test_ops_refuse_cpu_tensors():
     torch = pytest.importorskip("torch")
     from emmy_b200 import ops
